@@ -1,0 +1,173 @@
+/*
+ * niti_b200 -- C ABI of the B200 (sm_100a) kernels behind NITI's int8 training path.
+ *
+ * One shared library replaces the reference's four PyTorch extensions
+ * (pytorch/cutlass-extension, pytorch/int8mm-extension, pytorch/int8pool-extension,
+ * pytorch/int8conv-extension) and the element-wise torch code of ti_torch.py / ti_loss.py
+ * that sits between their calls.  File:line citations name the reference interface each
+ * entry point stands in for.
+ *
+ * Conventions
+ *   - every pointer is a DEVICE pointer unless its name ends in _host;
+ *   - activations / errors are int8 NHWC, conv weights int8 [K][R][S][C], FC weights [out][in];
+ *   - `stream` is a cudaStream_t passed as void*; work is enqueued on it on the CURRENT device,
+ *     nothing synchronises the host, nothing is allocated, nothing calls exit();
+ *   - every function returns 0 on success or a negative NITI_ERR_* code
+ *     (niti_strerror gives the text); CUDA launch errors come back as NITI_ERR_CUDA;
+ *   - `status` is a device int32[4] the tensor-core kernels write when a bounded wait inside
+ *     them expires (word 0: error code, 1: block, 2: role, 3: detail); zero it once, read it
+ *     whenever the host synchronises anyway.  It may be NULL.
+ *   - `maxabs` words are REDUCED INTO with an unsigned atomic max: the contraction entry points
+ *     clear them on the stream before launching their kernel.
+ *   - exponents and shifts live on the device as int32 scalars so that a training step never
+ *     has to synchronise (the reference reads them back twice per layer, ti_torch.py:366-377).
+ *   - `seed` arguments are device pointers to one uint64 that the kernel reads when it runs, so a
+ *     step captured in a CUDA graph draws fresh random bits after the host (or a kernel in the
+ *     graph) advances the word.
+ */
+#ifndef NITI_B200_H
+#define NITI_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#define NITI_API __attribute__((visibility("default")))
+#else
+#define NITI_API
+#endif
+
+#define NITI_OK 0
+#define NITI_ERR_BAD_ARG (-1)      /* null pointer, non-positive size, misaligned pointer */
+#define NITI_ERR_UNSUPPORTED (-2)  /* shape outside what the kernels implement (message says which) */
+#define NITI_ERR_CUDA (-3)         /* a CUDA runtime / driver call failed; see niti_last_cuda_error */
+#define NITI_ERR_SCRATCH (-4)      /* scratch buffer too small */
+
+/* rounding of the int32 -> int8 shift: RoundShift / StoShift / PstoShift (ti_torch.py:23-69) */
+#define NITI_ROUND_NEAREST 0
+#define NITI_ROUND_STOCHASTIC 1
+#define NITI_ROUND_PSEUDO_STOCHASTIC 2
+
+/* which of act_calc / err_calc / grad_calc (ti_torch.py:103-147) picks the shift */
+#define NITI_CALC_ACT 0
+#define NITI_CALC_ERR 1
+#define NITI_CALC_GRAD 2
+
+NITI_API int niti_version(void);
+NITI_API const char* niti_strerror(int code);
+/* text of the last CUDA error seen by this thread inside the library ("" if none) */
+NITI_API const char* niti_last_cuda_error(void);
+
+/* ---------------------------------------------------------------- contractions (int8 x int8 -> int32)
+ *
+ * niti_conv_fprop_i8: cutlassconv_cuda.sp_conv_optimized / sp_conv (cutlassconv.cpp:57-73,
+ * cutlassconv_kernel.cu:38-319) as called from conv2d_int8 (ti_torch.py:178-192).
+ * x [N][H][W][C], w [K][R][S][C] -> y32 [N][P][Q][K], cross-correlation, stride 1, P = H+2*pad-R+1.
+ * Unlike the reference no channel padding to 16 is needed (C = 3 is accepted).
+ * Tensor-core path when C % 64 == 0; otherwise a CUDA-core path.  *maxabs = max |y32|.
+ */
+NITI_API int niti_conv_fprop_i8(const int8_t* x, const int8_t* w, int32_t* y32, uint32_t* maxabs,
+                       int N, int H, int W, int C, int K, int R, int S, int pad, int stride,
+                       int32_t* status, void* stream);
+
+/* Error back-propagation of a convolution: TiConv2d.backward's
+ * conv2d_int8(err, flip(w,[1,2]).transpose(0,3)) (ti_torch.py:403-405).  `wt` is that flipped,
+ * transposed filter bank [C][R][S][K]; niti_weight_flip_transpose_i8 (or niti_update_i8) keeps
+ * it current so no per-step transpose of the weights is needed.
+ * err [N][H][W][K] -> e32 [N][H][W][C].
+ */
+NITI_API int niti_conv_dgrad_i8(const int8_t* err, const int8_t* wt, int32_t* e32, uint32_t* maxabs,
+                       int N, int H, int W, int C, int K, int R, int S, int pad,
+                       int32_t* status, void* stream);
+
+/* w [K][R][S][C] -> wt [C][R][S][K] with both filter axes reversed (ti_torch.py:404). */
+NITI_API int niti_weight_flip_transpose_i8(const int8_t* w, int8_t* wt, int K, int R, int S, int C, void* stream);
+
+/* Weight gradient of a convolution: the transposed-operand conv of ti_torch.py:429-432 and the
+ * first-layer group-conv form conv2d_weight_int8 (ti_torch.py:194-233, int8conv_kernel.cu:248-334):
+ * g32[k][r][s][c] = sum_{n,p,q} err[n][p][q][k] * x[n][p+r-pad][q+s-pad][c], exact int32.
+ * The reduction over pixels is split across thread blocks; partial sums go through `scratch`
+ * (niti_conv_wgrad_scratch_bytes) and a second kernel folds them and reduces *maxabs = max |g32|.
+ */
+NITI_API size_t niti_conv_wgrad_scratch_bytes(int N, int H, int W, int C, int K, int R, int S);
+NITI_API int niti_conv_wgrad_i8(const int8_t* x, const int8_t* err, int32_t* g32, uint32_t* maxabs,
+                       void* scratch, size_t scratch_bytes,
+                       int N, int H, int W, int C, int K, int R, int S, int pad,
+                       int32_t* status, void* stream);
+
+/* int8mm_cuda.int8_mm (int8mm.cpp:9-18, int8mm_kernel.cu:8-34) as used by TiLinear
+ * (ti_torch.py:241-266), without the padding / .contiguous() copies around it:
+ * C32[M][N] = op(A) * op(B); trans_a == 0: A is [M][K], else [K][M];
+ * trans_b == 0: B is [K][N], else [N][K].  Forward a*W^T: (0,1); error e*W: (0,0);
+ * gradient e^T*a: (1,0).  Tensor-core path when every row pitch is a multiple of 16 bytes
+ * and M,N,K >= 64; otherwise a CUDA-core path (the 10-class FC layer).
+ */
+NITI_API int niti_gemm_i8(const int8_t* A, const int8_t* B, int32_t* C32, uint32_t* maxabs,
+                 int M, int N, int K, int trans_a, int trans_b, int32_t* status, void* stream);
+
+/* ---------------------------------------------------------------- requantisation
+ *
+ * act_calc / err_calc / grad_calc + RoundShift / StoShift / PstoShift + int8_clip
+ * (ti_torch.py:23-72,103-147), with RangeEstimate (ti_torch.py:366-377) already reduced into
+ * *maxabs by the producing kernel.  bits = 0 if max==0 else bit_length(max-1);
+ * shift = max(bits - target_bits, 0); shift == 0 wraps (tensor.type(int8)), otherwise round
+ * and clamp to +-127; kind GRAD with bits == 0 writes zeros.
+ * Random word of element i (stochastic mode): Philox4x32-10 keyed by *seed, stream `rng_stream`,
+ * element index rng_offset + i.  If relu != 0, max(.,0) is applied after narrowing
+ * (TiReLU.forward, ti_torch.py:272-279).
+ * *exp_out = shift + (exp_a ? *exp_a : 0) + (exp_b ? *exp_b : 0); *shift_out = shift (each optional).
+ */
+NITI_API int niti_requant_i8(const int32_t* acc, int8_t* out, const uint32_t* maxabs, int64_t n,
+                    int kind, int target_bits, int round_mode,
+                    const uint64_t* seed, uint32_t rng_stream, uint64_t rng_offset, int relu,
+                    const int32_t* exp_a, const int32_t* exp_b, int32_t* exp_out, int32_t* shift_out,
+                    void* stream);
+
+/* max |acc| over n int32 values, reduced into *maxabs (cleared first).  RangeEstimate for
+ * tensors that did not come out of a contraction kernel (e.g. all-reduced gradients). */
+NITI_API int niti_absmax_i32(const int32_t* acc, int64_t n, uint32_t* maxabs, void* stream);
+
+/* ---------------------------------------------------------------- memory-bound layers
+ * int8pool_cuda.int8_pool / int8_pool_backward (int8pool.cpp, int8pool_kernel.cu:28-138) as
+ * used by TiMaxpool2d (ti_torch.py:292-316); int8 throughout (no fp16 copies), pad 0.
+ * Backward recomputes the window maximum from x and routes dy to the first position, scanning
+ * rows then columns, that holds it.
+ */
+NITI_API int niti_maxpool_fwd_i8(const int8_t* x, int8_t* y, int N, int H, int W, int C, int k, int stride, void* stream);
+NITI_API int niti_maxpool_bwd_i8(const int8_t* x, const int8_t* dy, int8_t* dx, int N, int H, int W, int C, int k, int stride, void* stream);
+/* TiReLU.forward / backward (ti_torch.py:268-290) */
+NITI_API int niti_relu_fwd_i8(const int8_t* x, int8_t* y, int64_t n, void* stream);
+NITI_API int niti_relu_bwd_i8(const int8_t* act, const int8_t* err, int8_t* out, int64_t n, void* stream);
+/* TiDropout (ti_torch.py:439-455): y[b][f] = x[b][f] * bit(f), bit = low bit of the Philox word of
+ * element f in stream rng_stream; the same call serves forward and backward. */
+NITI_API int niti_dropout_i8(const int8_t* x, int8_t* y, int64_t rows, int64_t features,
+                    const uint64_t* seed, uint32_t rng_stream, void* stream);
+
+/* TiLoss.forward (ti_loss.py:6-36): integer cross-entropy error.  out8 [B][classes] int8, *out_exp its
+ * exponent, target int64 [B]; err8 [B][classes].  classes <= 32.  The closing StoShift(.,4) draws the
+ * Philox word of element (sample_offset + b) * classes + c from stream rng_stream. */
+NITI_API int niti_loss_i8(const int8_t* out8, const int32_t* out_exp, const int64_t* target, int8_t* err8,
+                 int B, int classes, const uint64_t* seed, uint32_t rng_stream, uint64_t sample_offset, void* stream);
+
+/* UpdateWeight.weight_update (ti_torch.py:16-21): g8 = grad_calc(g32, mu); w = clamp(w - g8, +-127).
+ * *maxabs = max |g32| (from niti_conv_wgrad_i8 / niti_gemm_i8 / niti_absmax_i32).
+ * If wt != NULL the refreshed weights are also written as the flipped, transposed bank
+ * [C][R][S][K] that niti_conv_dgrad_i8 reads (w is [K][R][S][C]; pass R = S = 1, C = n / K otherwise). */
+NITI_API int niti_update_i8(int8_t* w, const int32_t* g32, const uint32_t* maxabs, int64_t n,
+                   int mu, int round_mode, const uint64_t* seed, uint32_t rng_stream,
+                   int8_t* wt, int K, int R, int S, int C, void* stream);
+
+/* TiFloatToInt8 + the NCHW -> NHWC permute of TiNet.forward (ti_torch.py:341-356, ti_net.py:18-19):
+ * x f32 [N][C][H][W] -> x8 int8 [N][H][W][C], *exp_out = ceil(log2(max|x|)) - 7.
+ * `scratch` is one uint32 word (cleared by the call). */
+NITI_API int niti_quantize_input_f32(const float* x, int8_t* x8, int32_t* exp_out, uint32_t* scratch,
+                            int N, int C, int H, int W, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* NITI_B200_H */

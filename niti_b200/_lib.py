@@ -1,0 +1,59 @@
+"""ctypes binding of libniti_b200.so (the C ABI declared in include/niti_b200.h).
+
+There is no other implementation behind these calls: if the library has not been built
+(``python -m niti_b200.build``) importing this module raises, and every non-zero status
+code becomes a ``RuntimeError`` carrying the library's own message.
+"""
+import ctypes as C
+import os
+
+_PKG = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_PKG, "libniti_b200.so")
+
+if not os.path.exists(LIB_PATH):
+    raise ImportError(
+        f"{LIB_PATH} is missing: the CUDA kernels of niti_b200 have not been built. "
+        "Run `python -m niti_b200.build` (needs nvcc); there is no CPU or PyTorch fallback.")
+
+lib = C.CDLL(LIB_PATH)
+
+_p, _i, _i64, _u64, _u32, _sz = C.c_void_p, C.c_int, C.c_int64, C.c_uint64, C.c_uint32, C.c_size_t
+
+SIGNATURES = {
+    "niti_version": (_i, []),
+    "niti_strerror": (C.c_char_p, [_i]),
+    "niti_last_cuda_error": (C.c_char_p, []),
+    "niti_conv_fprop_i8": (_i, [_p, _p, _p, _p] + [_i] * 9 + [_p, _p]),
+    "niti_conv_dgrad_i8": (_i, [_p, _p, _p, _p] + [_i] * 8 + [_p, _p]),
+    "niti_weight_flip_transpose_i8": (_i, [_p, _p, _i, _i, _i, _i, _p]),
+    "niti_conv_wgrad_scratch_bytes": (_sz, [_i] * 7),
+    "niti_conv_wgrad_i8": (_i, [_p, _p, _p, _p, _p, _sz] + [_i] * 8 + [_p, _p]),
+    "niti_gemm_i8": (_i, [_p, _p, _p, _p] + [_i] * 5 + [_p, _p]),
+    "niti_requant_i8": (_i, [_p, _p, _p, _i64, _i, _i, _i, _p, _u32, _u64, _i, _p, _p, _p, _p, _p]),
+    "niti_absmax_i32": (_i, [_p, _i64, _p, _p]),
+    "niti_maxpool_fwd_i8": (_i, [_p, _p] + [_i] * 6 + [_p]),
+    "niti_maxpool_bwd_i8": (_i, [_p, _p, _p] + [_i] * 6 + [_p]),
+    "niti_relu_fwd_i8": (_i, [_p, _p, _i64, _p]),
+    "niti_relu_bwd_i8": (_i, [_p, _p, _p, _i64, _p]),
+    "niti_dropout_i8": (_i, [_p, _p, _i64, _i64, _p, _u32, _p]),
+    "niti_loss_i8": (_i, [_p, _p, _p, _p, _i, _i, _p, _u32, _u64, _p]),
+    "niti_update_i8": (_i, [_p, _p, _p, _i64, _i, _i, _p, _u32, _p, _i, _i, _i, _i, _p]),
+    "niti_quantize_input_f32": (_i, [_p, _p, _p, _p, _i, _i, _i, _i, _p]),
+}
+
+for _name, (_res, _args) in SIGNATURES.items():
+    _fn = getattr(lib, _name)
+    _fn.restype = _res
+    _fn.argtypes = _args
+
+
+class NitiError(RuntimeError):
+    pass
+
+
+def check(code, what):
+    if code != 0:
+        msg = lib.niti_strerror(code).decode()
+        if code == -3:
+            msg += ": " + lib.niti_last_cuda_error().decode()
+        raise NitiError(f"{what} failed with status {code}: {msg}")

@@ -1,0 +1,842 @@
+// CUDA-core kernels: the memory-bound layers of the int8 training path (requantisation, max-pool,
+// ReLU, dropout, loss, weight update, input quantisation) and the contractions whose shapes cannot
+// fill a tensor-core tile (3-channel first convolution, 10-class FC layer).
+// All of them are bandwidth- or latency-bound: 16-byte accesses along the channel axis, packed
+// byte SIMD (__vmaxs4, __vcmpeq4, __dp4a), warp shuffles for reductions, one atomic per warp.
+#include <cuda_runtime.h>
+#include <cstdint>
+
+#include "../../include/niti_b200.h"
+#include "internal.h"
+#include "requant.cuh"
+
+namespace niti {
+
+static inline int blocks_for(long long work_items, int threads, int cap) {
+    long long b = (work_items + threads - 1) / threads;
+    if (b < 1) b = 1;
+    if (b > cap) b = cap;
+    return static_cast<int>(b);
+}
+static int sm_count_simt() {
+    static int n = 0;
+    if (n == 0) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+        if (n <= 0) n = 148;
+    }
+    return n;
+}
+
+__device__ __forceinline__ unsigned iabs_u(int x) { return static_cast<unsigned>(x < 0 ? -x : x); }
+
+__device__ __forceinline__ void warp_atomic_max(unsigned* dst, unsigned v) {
+    v = __reduce_max_sync(0xFFFFFFFFu, v);
+    if ((threadIdx.x & 31) == 0 && v != 0) atomicMax(dst, v);
+}
+
+// ------------------------------------------------------------------------------------------------
+// requantisation: int32 -> int8 by the tensor-wide shift
+// ------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+requant_kernel(const int32_t* __restrict__ acc, int8_t* __restrict__ out, const unsigned* __restrict__ maxabs,
+               long long n, int kind, int target_bits, int mode, const unsigned long long* seed_p, unsigned rng_stream,
+               unsigned long long rng_offset, int relu, const int32_t* exp_a, const int32_t* exp_b,
+               int32_t* exp_out, int32_t* shift_out) {
+    bool zero_out;
+    const int shift = shift_for(*maxabs, kind, target_bits, &zero_out);
+    if (blockIdx.x == 0 && threadIdx.x == 0) {
+        int e = shift + (exp_a ? *exp_a : 0) + (exp_b ? *exp_b : 0);
+        if (exp_out) *exp_out = e;
+        if (shift_out) *shift_out = shift;
+    }
+    const long long groups = n >> 4;  // 16 elements per thread-iteration
+    const bool stochastic = (mode == ROUND_STOCHASTIC) && shift > 0;
+    const unsigned long long seed = stochastic ? *seed_p : 0ull;
+    const bool aligned_rng = (rng_offset & 3ull) == 0;
+    for (long long g = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; g < groups;
+         g += static_cast<long long>(gridDim.x) * blockDim.x) {
+        const int4* src = reinterpret_cast<const int4*>(acc) + g * 4;
+        int4 v[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) v[i] = __ldcs(src + i);
+        uint32_t packed[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            uint32_t rnd[4] = {0, 0, 0, 0};
+            const unsigned long long e0 = static_cast<unsigned long long>(g) * 16 + i * 4;
+            if (stochastic) {
+                if (aligned_rng) random_block(seed, rng_stream, (rng_offset + e0) >> 2, rnd);
+                else {
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) rnd[j] = random_word(seed, rng_stream, rng_offset + e0 + j);
+                }
+            }
+            int x[4] = {v[i].x, v[i].y, v[i].z, v[i].w};
+            uint32_t w = 0;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                int8_t r = zero_out ? int8_t(0) : narrow(x[j], shift, mode, rnd[j]);
+                if (relu && r < 0) r = 0;
+                w |= static_cast<uint32_t>(static_cast<uint8_t>(r)) << (8 * j);
+            }
+            packed[i] = w;
+        }
+        reinterpret_cast<uint4*>(out)[g] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+    }
+    // tail (n not a multiple of 16)
+    const long long tail0 = groups << 4;
+    for (long long i = tail0 + blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n;
+         i += static_cast<long long>(gridDim.x) * blockDim.x) {
+        uint32_t rnd = stochastic ? random_word(seed, rng_stream, rng_offset + i) : 0u;
+        int8_t r = zero_out ? int8_t(0) : narrow(acc[i], shift, mode, rnd);
+        if (relu && r < 0) r = 0;
+        out[i] = r;
+    }
+}
+
+__global__ void __launch_bounds__(256)
+absmax_kernel(const int32_t* __restrict__ acc, long long n, unsigned* maxabs) {
+    unsigned m = 0;
+    const long long groups = n >> 2;
+    for (long long g = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; g < groups;
+         g += static_cast<long long>(gridDim.x) * blockDim.x) {
+        int4 v = reinterpret_cast<const int4*>(acc)[g];
+        m = max(max(m, iabs_u(v.x)), max(iabs_u(v.y), max(iabs_u(v.z), iabs_u(v.w))));
+    }
+    for (long long i = (groups << 2) + blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n;
+         i += static_cast<long long>(gridDim.x) * blockDim.x)
+        m = max(m, iabs_u(acc[i]));
+    warp_atomic_max(maxabs, m);
+}
+
+// out[i] = sum over splits of partial[s][i]; max|out| reduced into *maxabs
+__global__ void __launch_bounds__(256)
+reduce_partials_kernel(const int32_t* __restrict__ partial, int splits, long long n, int32_t* __restrict__ out,
+                       unsigned* maxabs) {
+    unsigned m = 0;
+    const long long groups = n >> 2;
+    for (long long g = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; g < groups;
+         g += static_cast<long long>(gridDim.x) * blockDim.x) {
+        int4 s = make_int4(0, 0, 0, 0);
+        for (int k = 0; k < splits; ++k) {
+            int4 v = __ldcs(reinterpret_cast<const int4*>(partial + static_cast<long long>(k) * n) + g);
+            s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
+        }
+        reinterpret_cast<int4*>(out)[g] = s;
+        m = max(max(m, iabs_u(s.x)), max(iabs_u(s.y), max(iabs_u(s.z), iabs_u(s.w))));
+    }
+    for (long long i = (groups << 2) + blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n;
+         i += static_cast<long long>(gridDim.x) * blockDim.x) {
+        int s = 0;
+        for (int k = 0; k < splits; ++k) s += partial[static_cast<long long>(k) * n + i];
+        out[i] = s;
+        m = max(m, iabs_u(s));
+    }
+    if (maxabs) warp_atomic_max(maxabs, m);
+}
+
+int reduce_partials(const int32_t* partial, int splits, long long n, int32_t* out, unsigned* maxabs, cudaStream_t st) {
+    reduce_partials_kernel<<<blocks_for(n / 4 + 1, 256, sm_count_simt() * 8), 256, 0, st>>>(partial, splits, n, out, maxabs);
+    return set_cuda_error(cudaGetLastError());
+}
+
+// ------------------------------------------------------------------------------------------------
+// max-pool, ReLU, dropout
+// ------------------------------------------------------------------------------------------------
+// 2x2 stride 2, C % 16 == 0: one thread per 16 channels of one output pixel
+__global__ void __launch_bounds__(256)
+maxpool2_fwd_kernel(const uint4* __restrict__ x, uint4* __restrict__ y, int Nimg, int H, int W, int C16, int P, int Q) {
+    const long long total = static_cast<long long>(Nimg) * P * Q * C16;
+    for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+         i += static_cast<long long>(gridDim.x) * blockDim.x) {
+        const int c = static_cast<int>(i % C16);
+        long long t = i / C16;
+        const int q = static_cast<int>(t % Q); t /= Q;
+        const int p = static_cast<int>(t % P);
+        const int n = static_cast<int>(t / P);
+        const long long base = ((static_cast<long long>(n) * H + 2 * p) * W + 2 * q) * C16 + c;
+        uint4 a = __ldg(x + base), b = __ldg(x + base + C16);
+        uint4 d = __ldg(x + base + static_cast<long long>(W) * C16), e = __ldg(x + base + static_cast<long long>(W) * C16 + C16);
+        uint4 r;
+        r.x = __vmaxs4(__vmaxs4(a.x, b.x), __vmaxs4(d.x, e.x));
+        r.y = __vmaxs4(__vmaxs4(a.y, b.y), __vmaxs4(d.y, e.y));
+        r.z = __vmaxs4(__vmaxs4(a.z, b.z), __vmaxs4(d.z, e.z));
+        r.w = __vmaxs4(__vmaxs4(a.w, b.w), __vmaxs4(d.w, e.w));
+        y[i] = r;
+    }
+}
+
+__device__ __forceinline__ void route4(unsigned a, unsigned b, unsigned d, unsigned e, unsigned dy,
+                                       unsigned& oa, unsigned& ob, unsigned& od, unsigned& oe) {
+    const unsigned m = __vmaxs4(__vmaxs4(a, b), __vmaxs4(d, e));
+    const unsigned ha = __vcmpeq4(a, m);
+    const unsigned hb = __vcmpeq4(b, m) & ~ha;
+    const unsigned hd = __vcmpeq4(d, m) & ~(ha | hb);
+    const unsigned he = ~(ha | hb | hd);  // the maximum is one of the four: what is left is the last
+    oa = dy & ha; ob = dy & hb; od = dy & hd; oe = dy & he;
+}
+
+__global__ void __launch_bounds__(256)
+maxpool2_bwd_kernel(const uint4* __restrict__ x, const uint4* __restrict__ dy, uint4* __restrict__ dx, int Nimg, int H,
+                    int W, int C16, int P, int Q) {
+    const long long total = static_cast<long long>(Nimg) * P * Q * C16;
+    for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+         i += static_cast<long long>(gridDim.x) * blockDim.x) {
+        const int c = static_cast<int>(i % C16);
+        long long t = i / C16;
+        const int q = static_cast<int>(t % Q); t /= Q;
+        const int p = static_cast<int>(t % P);
+        const int n = static_cast<int>(t / P);
+        const long long base = ((static_cast<long long>(n) * H + 2 * p) * W + 2 * q) * C16 + c;
+        const long long row = static_cast<long long>(W) * C16;
+        uint4 a = __ldg(x + base), b = __ldg(x + base + C16), d = __ldg(x + base + row), e = __ldg(x + base + row + C16);
+        uint4 g = __ldg(dy + i);
+        uint4 oa, ob, od, oe;
+        route4(a.x, b.x, d.x, e.x, g.x, oa.x, ob.x, od.x, oe.x);
+        route4(a.y, b.y, d.y, e.y, g.y, oa.y, ob.y, od.y, oe.y);
+        route4(a.z, b.z, d.z, e.z, g.z, oa.z, ob.z, od.z, oe.z);
+        route4(a.w, b.w, d.w, e.w, g.w, oa.w, ob.w, od.w, oe.w);
+        dx[base] = oa; dx[base + C16] = ob; dx[base + row] = od; dx[base + row + C16] = oe;
+    }
+}
+
+// any k / stride / C (pad 0): one thread per output (forward) or per input element (backward)
+__global__ void maxpool_fwd_generic(const int8_t* __restrict__ x, int8_t* __restrict__ y, int Nimg, int H, int W, int C,
+                                    int k, int stride, int P, int Q) {
+    const long long total = static_cast<long long>(Nimg) * P * Q * C;
+    for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+         i += static_cast<long long>(gridDim.x) * blockDim.x) {
+        const int c = static_cast<int>(i % C);
+        long long t = i / C;
+        const int q = static_cast<int>(t % Q); t /= Q;
+        const int p = static_cast<int>(t % P);
+        const int n = static_cast<int>(t / P);
+        int m = -128;
+        for (int a = 0; a < k; ++a)
+            for (int b = 0; b < k; ++b)
+                m = max(m, static_cast<int>(x[((static_cast<long long>(n) * H + p * stride + a) * W + q * stride + b) * C + c]));
+        y[i] = static_cast<int8_t>(m);
+    }
+}
+__global__ void maxpool_bwd_generic(const int8_t* __restrict__ x, const int8_t* __restrict__ dy, int8_t* __restrict__ dx,
+                                    int Nimg, int H, int W, int C, int k, int stride, int P, int Q) {
+    const long long total = static_cast<long long>(Nimg) * H * W * C;
+    for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+         i += static_cast<long long>(gridDim.x) * blockDim.x) {
+        const int c = static_cast<int>(i % C);
+        long long t = i / C;
+        const int w = static_cast<int>(t % W); t /= W;
+        const int h = static_cast<int>(t % H);
+        const int n = static_cast<int>(t / H);
+        int sum = 0;
+        // windows (p,q) that contain (h,w)
+        const int p_lo = max(0, (h - k + stride) / stride), p_hi = min(P - 1, h / stride);
+        const int q_lo = max(0, (w - k + stride) / stride), q_hi = min(Q - 1, w / stride);
+        for (int p = p_lo; p <= p_hi; ++p)
+            for (int q = q_lo; q <= q_hi; ++q) {
+                int m = -129, am = 0, bm = 0;
+                for (int a = 0; a < k; ++a)
+                    for (int b = 0; b < k; ++b) {
+                        int v = x[((static_cast<long long>(n) * H + p * stride + a) * W + q * stride + b) * C + c];
+                        if (v > m) { m = v; am = a; bm = b; }
+                    }
+                if (p * stride + am == h && q * stride + bm == w)
+                    sum += dy[((static_cast<long long>(n) * P + p) * Q + q) * C + c];
+            }
+        dx[i] = static_cast<int8_t>(sum);
+    }
+}
+
+__global__ void __launch_bounds__(256)
+relu_fwd_kernel(const int8_t* __restrict__ x, int8_t* __restrict__ y, long long n) {
+    const long long groups = n >> 4;
+    for (long long g = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; g < groups;
+         g += static_cast<long long>(gridDim.x) * blockDim.x) {
+        uint4 v = __ldg(reinterpret_cast<const uint4*>(x) + g);
+        v.x = __vmaxs4(v.x, 0); v.y = __vmaxs4(v.y, 0); v.z = __vmaxs4(v.z, 0); v.w = __vmaxs4(v.w, 0);
+        reinterpret_cast<uint4*>(y)[g] = v;
+    }
+    for (long long i = (groups << 4) + blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n;
+         i += static_cast<long long>(gridDim.x) * blockDim.x)
+        y[i] = x[i] > 0 ? x[i] : int8_t(0);
+}
+__global__ void __launch_bounds__(256)
+relu_bwd_kernel(const int8_t* __restrict__ act, const int8_t* __restrict__ err, int8_t* __restrict__ out, long long n) {
+    const long long groups = n >> 4;
+    for (long long g = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; g < groups;
+         g += static_cast<long long>(gridDim.x) * blockDim.x) {
+        uint4 a = __ldg(reinterpret_cast<const uint4*>(act) + g);
+        uint4 e = __ldg(reinterpret_cast<const uint4*>(err) + g);
+        uint4 o;
+        o.x = e.x & __vcmpgts4(a.x, 0); o.y = e.y & __vcmpgts4(a.y, 0);
+        o.z = e.z & __vcmpgts4(a.z, 0); o.w = e.w & __vcmpgts4(a.w, 0);
+        reinterpret_cast<uint4*>(out)[g] = o;
+    }
+    for (long long i = (groups << 4) + blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n;
+         i += static_cast<long long>(gridDim.x) * blockDim.x)
+        out[i] = act[i] > 0 ? err[i] : int8_t(0);
+}
+__global__ void __launch_bounds__(256)
+dropout_kernel(const int8_t* __restrict__ x, int8_t* __restrict__ y, long long rows, long long features,
+               const unsigned long long* seed_p, unsigned rng_stream) {
+    const unsigned long long seed = *seed_p;
+    const long long total = rows * features;
+    for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+         i += static_cast<long long>(gridDim.x) * blockDim.x) {
+        const unsigned long long f = static_cast<unsigned long long>(i % features);
+        y[i] = (random_word(seed, rng_stream, f) & 1u) ? x[i] : int8_t(0);
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
+// loss (ti_loss.py:6-36), one thread per sample.  float32 steps in the reference's order; 2**s by a
+// fixed sequence of IEEE double operations so that the result does not depend on a math library.
+// ------------------------------------------------------------------------------------------------
+__device__ __forceinline__ double exp2_det(double s) {
+    const double i = floor(s);
+    const double t = __dmul_rn(s - i, 0.6931471805599453);
+    // 1/j! for j = 17 .. 0
+    const double c[18] = {1.0 / 355687428096000.0, 1.0 / 20922789888000.0, 1.0 / 1307674368000.0, 1.0 / 87178291200.0,
+                          1.0 / 6227020800.0, 1.0 / 479001600.0, 1.0 / 39916800.0, 1.0 / 3628800.0, 1.0 / 362880.0,
+                          1.0 / 40320.0, 1.0 / 5040.0, 1.0 / 720.0, 1.0 / 120.0, 1.0 / 24.0, 1.0 / 6.0, 1.0 / 2.0, 1.0, 1.0};
+    double acc = c[0];
+#pragma unroll
+    for (int j = 1; j < 18; ++j) acc = __dadd_rn(__dmul_rn(acc, t), c[j]);
+    return scalbn(acc, static_cast<int>(i));
+}
+__device__ __forceinline__ float pow2f_int(int e) {  // 2**e as float, e in [-126, 127]
+    return __int_as_float((e + 127) << 23);
+}
+
+constexpr int LOSS_MAX_CLASSES = 32;
+
+__global__ void loss_kernel(const int8_t* __restrict__ out8, const int32_t* __restrict__ out_exp_p,
+                            const long long* __restrict__ target, int8_t* __restrict__ err8, int B, int classes,
+                            const unsigned long long* seed_p, unsigned rng_stream, unsigned long long sample_offset) {
+    const int b = blockIdx.x * blockDim.x + threadIdx.x;
+    if (b >= B) return;
+    const unsigned long long seed = *seed_p;
+    const int out_exp = *out_exp_p;
+    float g[LOSS_MAX_CLASSES];
+    long long out_sum = 0;
+    if (out_exp > -7) {
+        float mx = -3.0e38f;
+        for (int c = 0; c < classes; ++c) {
+            float s = __fdiv_rn(static_cast<float>(static_cast<int>(out8[b * classes + c]) * 47274), 32768.0f);
+            s = out_exp >= 0 ? __fmul_rn(s, pow2f_int(out_exp)) : __fdiv_rn(s, pow2f_int(-out_exp));
+            g[c] = s;
+            mx = fmaxf(mx, s);
+        }
+        const float offset = __fsub_rn(mx, 10.0f);
+        for (int c = 0; c < classes; ++c) {
+            float s = fmaxf(__fsub_rn(g[c], offset), 0.0f);
+            float v = __fsub_rn(static_cast<float>(exp2_det(static_cast<double>(s))), 1.0f);
+            g[c] = v;
+            out_sum += static_cast<long long>(v);
+        }
+    } else {
+        const long long a = 1ll << (1 - 2 * out_exp), bq = 1ll << (1 - out_exp);
+        for (int c = 0; c < classes; ++c) {
+            const long long s = out8[b * classes + c];
+            const long long gi = a + s * bq + s * s;
+            out_sum += gi;
+            g[c] = __ll2float_rn(gi);
+        }
+    }
+    const float denom = __ll2float_rn(out_sum);
+    long long row_sum = 0;
+    for (int c = 0; c < classes; ++c) {
+        g[c] = __fdiv_rn(__fmul_rn(g[c], 2048.0f), denom);
+        row_sum += static_cast<long long>(g[c]);
+    }
+    const int tgt = static_cast<int>(target[b]);
+    for (int c = 0; c < classes; ++c) {
+        float v = g[c];
+        if (c == tgt) v = __fsub_rn(v, __ll2float_rn(row_sum));
+        const int g32 = static_cast<int>(v);  // truncation, like tensor.type(torch.int32)
+        const unsigned long long idx = (sample_offset + b) * static_cast<unsigned long long>(classes) + c;
+        err8[b * classes + c] = narrow(g32, 4, ROUND_STOCHASTIC, random_word(seed, rng_stream, idx));
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
+// weight update and the flipped / transposed filter bank the error-backward convolution reads
+// ------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+update_kernel(int8_t* __restrict__ w, const int32_t* __restrict__ g32, const unsigned* __restrict__ maxabs, long long n,
+              int mu, int mode, const unsigned long long* seed_p, unsigned rng_stream, int8_t* __restrict__ wt, int K, int R,
+              int S, int C) {
+    bool zero_out;
+    const int shift = shift_for(*maxabs, CALC_GRAD, mu, &zero_out);
+    const bool stochastic = (mode == ROUND_STOCHASTIC) && shift > 0;
+    const unsigned long long seed = stochastic ? *seed_p : 0ull;
+    for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n;
+         i += static_cast<long long>(gridDim.x) * blockDim.x) {
+        const uint32_t rnd = stochastic ? random_word(seed, rng_stream, static_cast<unsigned long long>(i)) : 0u;
+        const int g8 = zero_out ? 0 : narrow(g32[i], shift, mode, rnd);
+        const int8_t nw = static_cast<int8_t>(clamp127(static_cast<int>(w[i]) - g8));
+        w[i] = nw;
+        if (wt != nullptr) {
+            const int c = static_cast<int>(i % C);
+            long long t = i / C;
+            const int s = static_cast<int>(t % S); t /= S;
+            const int r = static_cast<int>(t % R);
+            const int k = static_cast<int>(t / R);
+            wt[((static_cast<long long>(c) * R + (R - 1 - r)) * S + (S - 1 - s)) * K + k] = nw;
+        }
+    }
+}
+__global__ void __launch_bounds__(256)
+flip_transpose_kernel(const int8_t* __restrict__ w, int8_t* __restrict__ wt, int K, int R, int S, int C) {
+    const long long n = static_cast<long long>(K) * R * S * C;
+    // iterate in OUTPUT order so the writes coalesce
+    for (long long o = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; o < n;
+         o += static_cast<long long>(gridDim.x) * blockDim.x) {
+        const int k = static_cast<int>(o % K);
+        long long t = o / K;
+        const int s = static_cast<int>(t % S); t /= S;
+        const int r = static_cast<int>(t % R);
+        const int c = static_cast<int>(t / R);
+        wt[o] = w[((static_cast<long long>(k) * R + (R - 1 - r)) * S + (S - 1 - s)) * C + c];
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
+// input quantisation (ti_torch.py:341-356 + the permute of ti_net.py:19)
+// ------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) absmax_f32_kernel(const float* __restrict__ x, long long n, unsigned* bits) {
+    unsigned m = 0;  // |x| as IEEE bits orders like the value for non-negative floats
+    for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n;
+         i += static_cast<long long>(gridDim.x) * blockDim.x)
+        m = max(m, __float_as_uint(fabsf(x[i])));
+    warp_atomic_max(bits, m);
+}
+__global__ void __launch_bounds__(256)
+quantize_input_kernel(const float* __restrict__ x, int8_t* __restrict__ x8, int32_t* exp_out, const unsigned* bits,
+                      int Nimg, int C, int H, int W) {
+    const unsigned mb = *bits;
+    // ceil(log2(r)) from the exponent and mantissa fields of r
+    const int e = static_cast<int>((mb >> 23) & 0xFF) - 127;
+    const int bw = (mb & 0x7FFFFF) ? e + 1 : e;
+    if (blockIdx.x == 0 && threadIdx.x == 0) *exp_out = bw - 7;
+    const float scale = pow2f_int(7 - bw);
+    const long long total = static_cast<long long>(Nimg) * H * W * C;
+    for (long long o = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; o < total;
+         o += static_cast<long long>(gridDim.x) * blockDim.x) {
+        const int c = static_cast<int>(o % C);
+        long long t = o / C;
+        const int w = static_cast<int>(t % W); t /= W;
+        const int h = static_cast<int>(t % H);
+        const int n = static_cast<int>(t / H);
+        const float v = rintf(__fmul_rn(x[((static_cast<long long>(n) * C + c) * H + h) * W + w], scale));
+        x8[o] = static_cast<int8_t>(fminf(fmaxf(v, -128.0f), 127.0f));
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
+// CUDA-core contractions
+// ------------------------------------------------------------------------------------------------
+// Convolution forward for thin inputs (R*S*C <= 32, i.e. the 3-channel first layer): the patch of
+// a pixel is packed into T <= 8 words, each thread keeps the packed filter of its output channel
+// in registers and produces one output per pixel with T dp4a.
+template <int T>
+__global__ void __launch_bounds__(128)
+conv_fprop_thin_kernel(const int8_t* __restrict__ x, const int8_t* __restrict__ w, int32_t* __restrict__ y32,
+                       unsigned* maxabs, int Nimg, int H, int W, int C, int K, int R, int S, int pad) {
+    constexpr int TILE = 32;
+    __shared__ uint32_t patch[TILE][T];
+    const int rsc = R * S * C;
+    const long long pixels = static_cast<long long>(Nimg) * H * W;
+    unsigned m = 0;
+    for (int k0 = 0; k0 < K; k0 += 128) {
+        const int k = k0 + threadIdx.x;
+        uint32_t wreg[T];
+#pragma unroll
+        for (int t = 0; t < T; ++t) {
+            uint32_t v = 0;
+            for (int j = 0; j < 4; ++j) {
+                const int e = t * 4 + j;
+                if (k < K && e < rsc) v |= static_cast<uint32_t>(static_cast<uint8_t>(w[static_cast<long long>(k) * rsc + e])) << (8 * j);
+            }
+            wreg[t] = v;
+        }
+        for (long long p0 = static_cast<long long>(blockIdx.x) * TILE; p0 < pixels; p0 += static_cast<long long>(gridDim.x) * TILE) {
+            __syncthreads();
+            for (int i = threadIdx.x; i < TILE * T; i += blockDim.x) {
+                const int pl = i / T, t = i % T;
+                const long long pix = p0 + pl;
+                uint32_t v = 0;
+                if (pix < pixels) {
+                    const int wq = static_cast<int>(pix % W);
+                    const int hq = static_cast<int>((pix / W) % H);
+                    const long long n = pix / (static_cast<long long>(W) * H);
+                    for (int j = 0; j < 4; ++j) {
+                        const int e = t * 4 + j;
+                        if (e < rsc) {
+                            const int c = e % C, s = (e / C) % S, r = e / (C * S);
+                            const int hh = hq + r - pad, ww = wq + s - pad;
+                            if (hh >= 0 && hh < H && ww >= 0 && ww < W)
+                                v |= static_cast<uint32_t>(static_cast<uint8_t>(x[((n * H + hh) * W + ww) * C + c])) << (8 * j);
+                        }
+                    }
+                }
+                patch[pl][t] = v;
+            }
+            __syncthreads();
+            if (k < K) {
+                const int lim = static_cast<int>(min(static_cast<long long>(TILE), pixels - p0));
+                for (int pl = 0; pl < lim; ++pl) {
+                    int acc = 0;
+#pragma unroll
+                    for (int t = 0; t < T; ++t) acc = __dp4a(static_cast<int>(patch[pl][t]), static_cast<int>(wreg[t]), acc);
+                    y32[(p0 + pl) * K + k] = acc;
+                    m = max(m, iabs_u(acc));
+                }
+            }
+        }
+    }
+    warp_atomic_max(maxabs, m);
+}
+
+// Any shape: one thread per output element (slow; keeps odd shapes working).
+__global__ void conv_fprop_direct_kernel(const int8_t* __restrict__ x, const int8_t* __restrict__ w,
+                                         int32_t* __restrict__ y32, unsigned* maxabs, int Nimg, int H, int W, int C, int K,
+                                         int R, int S, int pad, int P, int Q) {
+    const long long total = static_cast<long long>(Nimg) * P * Q * K;
+    unsigned m = 0;
+    for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+         i += static_cast<long long>(gridDim.x) * blockDim.x) {
+        const int k = static_cast<int>(i % K);
+        long long t = i / K;
+        const int q = static_cast<int>(t % Q); t /= Q;
+        const int p = static_cast<int>(t % P);
+        const long long n = t / P;
+        int acc = 0;
+        for (int r = 0; r < R; ++r) {
+            const int hh = p + r - pad;
+            if (hh < 0 || hh >= H) continue;
+            for (int s = 0; s < S; ++s) {
+                const int ww = q + s - pad;
+                if (ww < 0 || ww >= W) continue;
+                const int8_t* xp = x + ((n * H + hh) * W + ww) * C;
+                const int8_t* wp = w + ((static_cast<long long>(k) * R + r) * S + s) * C;
+                for (int c = 0; c < C; ++c) acc += static_cast<int>(xp[c]) * static_cast<int>(wp[c]);
+            }
+        }
+        y32[i] = acc;
+        m = max(m, iabs_u(acc));
+    }
+    warp_atomic_max(maxabs, m);
+}
+
+int simt_conv_fprop(const int8_t* x, const int8_t* w, int32_t* y32, unsigned* maxabs, int Nimg, int H, int W, int C,
+                    int K, int R, int S, int pad, cudaStream_t st) {
+    const int P = H + 2 * pad - R + 1, Q = W + 2 * pad - S + 1;
+    const int rsc = R * S * C;
+    if (rsc <= 32 && P == H && Q == W) {
+        const long long pixels = static_cast<long long>(Nimg) * H * W;
+        const int grid = blocks_for(pixels, 32, sm_count_simt() * 16);
+        if (rsc <= 28) conv_fprop_thin_kernel<7><<<grid, 128, 0, st>>>(x, w, y32, maxabs, Nimg, H, W, C, K, R, S, pad);
+        else           conv_fprop_thin_kernel<8><<<grid, 128, 0, st>>>(x, w, y32, maxabs, Nimg, H, W, C, K, R, S, pad);
+    } else {
+        const long long total = static_cast<long long>(Nimg) * P * Q * K;
+        conv_fprop_direct_kernel<<<blocks_for(total, 256, sm_count_simt() * 16), 256, 0, st>>>(x, w, y32, maxabs, Nimg, H, W,
+                                                                                             C, K, R, S, pad, P, Q);
+    }
+    return set_cuda_error(cudaGetLastError());
+}
+
+// Weight gradient for thin inputs (R*S*C <= 28): thread = output channel k, registers hold the
+// R*S*C partial sums, four pixels are folded per dp4a.  Block b sums pixels [b*span, (b+1)*span)
+// into partial[b]; reduce_partials folds the blocks.
+constexpr int WG_THIN_TAPS = 28;
+constexpr int WG_THIN_TILE = 32;  // pixels staged per iteration
+
+__global__ void __launch_bounds__(128)
+conv_wgrad_thin_kernel(const int8_t* __restrict__ x, const int8_t* __restrict__ err, int32_t* __restrict__ partial,
+                       int Nimg, int H, int W, int C, int K, int R, int S, int pad, long long span) {
+    __shared__ uint32_t pq[WG_THIN_TAPS][WG_THIN_TILE / 4];  // tap t, pixel quad j: 4 packed bytes
+    const int rsc = R * S * C;
+    const long long pixels = static_cast<long long>(Nimg) * H * W;
+    const long long lo = blockIdx.x * span, hi = min(pixels, lo + span);
+    for (int k0 = 0; k0 < K; k0 += 128) {
+        const int k = k0 + threadIdx.x;
+        int acc[WG_THIN_TAPS];
+#pragma unroll
+        for (int t = 0; t < WG_THIN_TAPS; ++t) acc[t] = 0;
+        for (long long p0 = lo; p0 < hi; p0 += WG_THIN_TILE) {
+            __syncthreads();
+            for (int i = threadIdx.x; i < WG_THIN_TAPS * (WG_THIN_TILE / 4); i += blockDim.x) {
+                const int t = i / (WG_THIN_TILE / 4), j = i % (WG_THIN_TILE / 4);
+                uint32_t v = 0;
+                if (t < rsc) {
+                    const int c = t % C, s = (t / C) % S, r = t / (C * S);
+                    for (int b = 0; b < 4; ++b) {
+                        const long long pix = p0 + j * 4 + b;
+                        if (pix < hi) {
+                            const int wq = static_cast<int>(pix % W);
+                            const int hq = static_cast<int>((pix / W) % H);
+                            const long long n = pix / (static_cast<long long>(W) * H);
+                            const int hh = hq + r - pad, ww = wq + s - pad;
+                            if (hh >= 0 && hh < H && ww >= 0 && ww < W)
+                                v |= static_cast<uint32_t>(static_cast<uint8_t>(x[((n * H + hh) * W + ww) * C + c])) << (8 * b);
+                        }
+                    }
+                }
+                pq[t][j] = v;
+            }
+            __syncthreads();
+            if (k < K) {
+#pragma unroll
+                for (int j = 0; j < WG_THIN_TILE / 4; ++j) {
+                    uint32_t e4 = 0;
+#pragma unroll
+                    for (int b = 0; b < 4; ++b) {
+                        const long long pix = p0 + j * 4 + b;
+                        if (pix < hi) e4 |= static_cast<uint32_t>(static_cast<uint8_t>(err[pix * K + k])) << (8 * b);
+                    }
+#pragma unroll
+                    for (int t = 0; t < WG_THIN_TAPS; ++t) acc[t] = __dp4a(static_cast<int>(e4), static_cast<int>(pq[t][j]), acc[t]);
+                }
+            }
+        }
+        if (k < K) {
+            int32_t* out = partial + static_cast<long long>(blockIdx.x) * K * rsc + static_cast<long long>(k) * rsc;
+#pragma unroll
+            for (int t = 0; t < WG_THIN_TAPS; ++t)
+                if (t < rsc) out[t] = acc[t];
+        }
+    }
+}
+
+// Any shape: one thread per gradient element, summing over all pixels (slow fallback).
+__global__ void conv_wgrad_direct_kernel(const int8_t* __restrict__ x, const int8_t* __restrict__ err,
+                                         int32_t* __restrict__ g32, int Nimg, int H, int W, int C, int K, int R, int S,
+                                         int pad, int P, int Q) {
+    const long long total = static_cast<long long>(K) * R * S * C;
+    for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+         i += static_cast<long long>(gridDim.x) * blockDim.x) {
+        const int c = static_cast<int>(i % C);
+        long long t = i / C;
+        const int s = static_cast<int>(t % S); t /= S;
+        const int r = static_cast<int>(t % R);
+        const int k = static_cast<int>(t / R);
+        int acc = 0;
+        for (long long n = 0; n < Nimg; ++n)
+            for (int p = 0; p < P; ++p) {
+                const int hh = p + r - pad;
+                if (hh < 0 || hh >= H) continue;
+                for (int q = 0; q < Q; ++q) {
+                    const int ww = q + s - pad;
+                    if (ww < 0 || ww >= W) continue;
+                    acc += static_cast<int>(err[((n * P + p) * Q + q) * K + k]) * static_cast<int>(x[((n * H + hh) * W + ww) * C + c]);
+                }
+            }
+        g32[i] = acc;
+    }
+}
+
+static int thin_wgrad_splits(long long pixels) {
+    long long tiles = (pixels + WG_THIN_TILE - 1) / WG_THIN_TILE;
+    long long s = sm_count_simt() * 4;
+    return static_cast<int>(tiles < s ? tiles : s);
+}
+size_t simt_wgrad_scratch_bytes(int Nimg, int H, int W, int C, int K, int R, int S) {
+    if (R * S * C > WG_THIN_TAPS) return static_cast<size_t>(K) * R * S * C * 4;
+    return static_cast<size_t>(thin_wgrad_splits(static_cast<long long>(Nimg) * H * W)) * K * R * S * C * 4;
+}
+int simt_conv_wgrad_partials(const int8_t* x, const int8_t* err, int32_t* partial, int* splits_out, int Nimg, int H,
+                             int W, int C, int K, int R, int S, int pad, cudaStream_t st) {
+    const int P = H + 2 * pad - R + 1, Q = W + 2 * pad - S + 1;
+    if (R * S * C <= WG_THIN_TAPS && P == H && Q == W) {
+        const long long pixels = static_cast<long long>(Nimg) * H * W;
+        const int splits = thin_wgrad_splits(pixels);
+        long long span = (pixels + splits - 1) / splits;
+        span = (span + WG_THIN_TILE - 1) / WG_THIN_TILE * WG_THIN_TILE;
+        conv_wgrad_thin_kernel<<<splits, 128, 0, st>>>(x, err, partial, Nimg, H, W, C, K, R, S, pad, span);
+        *splits_out = splits;
+    } else {
+        const long long total = static_cast<long long>(K) * R * S * C;
+        conv_wgrad_direct_kernel<<<blocks_for(total, 128, 1 << 20), 128, 0, st>>>(x, err, partial, Nimg, H, W, C, K, R, S,
+                                                                                  pad, P, Q);
+        *splits_out = 1;
+    }
+    return set_cuda_error(cudaGetLastError());
+}
+
+// GEMM, both operands contiguous along the reduction (trans_a = 0, trans_b = 1): one warp per
+// output element, 16-byte loads, dp4a, shuffle reduction.  The 10-class FC forward.
+__global__ void __launch_bounds__(256)
+gemm_kk_kernel(const int8_t* __restrict__ A, const int8_t* __restrict__ B, int32_t* __restrict__ C32, unsigned* maxabs,
+               int M, int N, int K) {
+    const int lane = threadIdx.x & 31;
+    const long long warp = (blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x) >> 5;
+    const long long nwarps = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
+    unsigned mx = 0;
+    const bool vec = (K % 16 == 0) && ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B)) % 16 == 0);
+    for (long long o = warp; o < static_cast<long long>(M) * N; o += nwarps) {
+        const int m = static_cast<int>(o / N), n = static_cast<int>(o % N);
+        const int8_t* a = A + static_cast<long long>(m) * K;
+        const int8_t* b = B + static_cast<long long>(n) * K;
+        int acc = 0;
+        if (vec) {
+            for (int k = lane * 16; k < K; k += 32 * 16) {
+                const int4 av = __ldg(reinterpret_cast<const int4*>(a + k));
+                const int4 bv = __ldg(reinterpret_cast<const int4*>(b + k));
+                acc = __dp4a(av.x, bv.x, acc); acc = __dp4a(av.y, bv.y, acc);
+                acc = __dp4a(av.z, bv.z, acc); acc = __dp4a(av.w, bv.w, acc);
+            }
+        } else {
+            for (int k = lane; k < K; k += 32) acc += static_cast<int>(a[k]) * static_cast<int>(b[k]);
+        }
+        acc = __reduce_add_sync(0xFFFFFFFFu, acc);
+        if (lane == 0) { C32[o] = acc; mx = max(mx, iabs_u(acc)); }
+    }
+    if (lane == 0 && mx != 0) atomicMax(maxabs, mx);
+}
+// GEMM, any majors: one thread per output element, consecutive threads along N.
+__global__ void __launch_bounds__(256)
+gemm_generic_kernel(const int8_t* __restrict__ A, const int8_t* __restrict__ B, int32_t* __restrict__ C32,
+                    unsigned* maxabs, int M, int N, int K, int trans_a, int trans_b) {
+    unsigned mx = 0;
+    const long long sa_m = trans_a ? 1 : K, sa_k = trans_a ? M : 1;
+    const long long sb_k = trans_b ? 1 : N, sb_n = trans_b ? K : 1;
+    for (long long o = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; o < static_cast<long long>(M) * N;
+         o += static_cast<long long>(gridDim.x) * blockDim.x) {
+        const long long m = o / N, n = o % N;
+        int acc = 0;
+        for (int k = 0; k < K; ++k) acc += static_cast<int>(A[m * sa_m + k * sa_k]) * static_cast<int>(B[k * sb_k + n * sb_n]);
+        C32[o] = acc;
+        mx = max(mx, iabs_u(acc));
+    }
+    warp_atomic_max(maxabs, mx);
+}
+int simt_gemm(const int8_t* A, const int8_t* B, int32_t* C32, unsigned* maxabs, int M, int N, int K, int trans_a,
+              int trans_b, cudaStream_t st) {
+    const long long outs = static_cast<long long>(M) * N;
+    if (!trans_a && trans_b && K >= 256)
+        gemm_kk_kernel<<<blocks_for(outs * 32, 256, sm_count_simt() * 16), 256, 0, st>>>(A, B, C32, maxabs, M, N, K);
+    else
+        gemm_generic_kernel<<<blocks_for(outs, 256, sm_count_simt() * 32), 256, 0, st>>>(A, B, C32, maxabs, M, N, K, trans_a, trans_b);
+    return set_cuda_error(cudaGetLastError());
+}
+
+}  // namespace niti
+
+// ================================================================================================
+// C ABI for the CUDA-core kernels
+// ================================================================================================
+using namespace niti;
+
+#define NITI_REQUIRE(cond) do { if (!(cond)) return NITI_ERR_BAD_ARG; } while (0)
+
+extern "C" int niti_requant_i8(const int32_t* acc, int8_t* out, const uint32_t* maxabs, int64_t n, int kind,
+                               int target_bits, int round_mode, const uint64_t* seed, uint32_t rng_stream, uint64_t rng_offset,
+                               int relu, const int32_t* exp_a, const int32_t* exp_b, int32_t* exp_out, int32_t* shift_out,
+                               void* stream) {
+    NITI_REQUIRE(acc && out && maxabs && n >= 0 && kind >= 0 && kind <= 2 && round_mode >= 0 && round_mode <= 2);
+    NITI_REQUIRE(seed || round_mode != NITI_ROUND_STOCHASTIC);
+    NITI_REQUIRE(reinterpret_cast<uintptr_t>(acc) % 16 == 0 && reinterpret_cast<uintptr_t>(out) % 16 == 0);
+    requant_kernel<<<blocks_for(n / 16 + 1, 256, sm_count_simt() * 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        acc, out, maxabs, n, kind, target_bits, round_mode, reinterpret_cast<const unsigned long long*>(seed), rng_stream, rng_offset, relu, exp_a, exp_b, exp_out, shift_out);
+    return set_cuda_error(cudaGetLastError());
+}
+
+extern "C" int niti_absmax_i32(const int32_t* acc, int64_t n, uint32_t* maxabs, void* stream) {
+    NITI_REQUIRE(acc && maxabs && n >= 0 && reinterpret_cast<uintptr_t>(acc) % 16 == 0);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (int e = set_cuda_error(cudaMemsetAsync(maxabs, 0, 4, st))) return e;
+    absmax_kernel<<<blocks_for(n / 4 + 1, 256, sm_count_simt() * 8), 256, 0, st>>>(acc, n, maxabs);
+    return set_cuda_error(cudaGetLastError());
+}
+
+extern "C" int niti_maxpool_fwd_i8(const int8_t* x, int8_t* y, int N, int H, int W, int C, int k, int stride, void* stream) {
+    NITI_REQUIRE(x && y && N > 0 && H >= k && W >= k && C > 0 && k > 0 && stride > 0);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const int P = (H - k) / stride + 1, Q = (W - k) / stride + 1;
+    if (k == 2 && stride == 2 && C % 16 == 0 && reinterpret_cast<uintptr_t>(x) % 16 == 0 && reinterpret_cast<uintptr_t>(y) % 16 == 0) {
+        const long long total = static_cast<long long>(N) * P * Q * (C / 16);
+        maxpool2_fwd_kernel<<<blocks_for(total, 256, sm_count_simt() * 16), 256, 0, st>>>(
+            reinterpret_cast<const uint4*>(x), reinterpret_cast<uint4*>(y), N, H, W, C / 16, P, Q);
+    } else {
+        const long long total = static_cast<long long>(N) * P * Q * C;
+        maxpool_fwd_generic<<<blocks_for(total, 256, sm_count_simt() * 16), 256, 0, st>>>(x, y, N, H, W, C, k, stride, P, Q);
+    }
+    return set_cuda_error(cudaGetLastError());
+}
+
+extern "C" int niti_maxpool_bwd_i8(const int8_t* x, const int8_t* dy, int8_t* dx, int N, int H, int W, int C, int k,
+                                   int stride, void* stream) {
+    NITI_REQUIRE(x && dy && dx && N > 0 && H >= k && W >= k && C > 0 && k > 0 && stride > 0);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const int P = (H - k) / stride + 1, Q = (W - k) / stride + 1;
+    const bool al = (reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(dy) | reinterpret_cast<uintptr_t>(dx)) % 16 == 0;
+    if (k == 2 && stride == 2 && C % 16 == 0 && H % 2 == 0 && W % 2 == 0 && al) {
+        const long long total = static_cast<long long>(N) * P * Q * (C / 16);
+        maxpool2_bwd_kernel<<<blocks_for(total, 256, sm_count_simt() * 16), 256, 0, st>>>(
+            reinterpret_cast<const uint4*>(x), reinterpret_cast<const uint4*>(dy), reinterpret_cast<uint4*>(dx), N, H, W, C / 16, P, Q);
+    } else {
+        const long long total = static_cast<long long>(N) * H * W * C;
+        maxpool_bwd_generic<<<blocks_for(total, 256, sm_count_simt() * 16), 256, 0, st>>>(x, dy, dx, N, H, W, C, k, stride, P, Q);
+    }
+    return set_cuda_error(cudaGetLastError());
+}
+
+extern "C" int niti_relu_fwd_i8(const int8_t* x, int8_t* y, int64_t n, void* stream) {
+    NITI_REQUIRE(x && y && n >= 0 && (reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y)) % 16 == 0);
+    relu_fwd_kernel<<<blocks_for(n / 16 + 1, 256, sm_count_simt() * 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(x, y, n);
+    return set_cuda_error(cudaGetLastError());
+}
+extern "C" int niti_relu_bwd_i8(const int8_t* act, const int8_t* err, int8_t* out, int64_t n, void* stream) {
+    NITI_REQUIRE(act && err && out && n >= 0);
+    NITI_REQUIRE((reinterpret_cast<uintptr_t>(act) | reinterpret_cast<uintptr_t>(err) | reinterpret_cast<uintptr_t>(out)) % 16 == 0);
+    relu_bwd_kernel<<<blocks_for(n / 16 + 1, 256, sm_count_simt() * 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(act, err, out, n);
+    return set_cuda_error(cudaGetLastError());
+}
+extern "C" int niti_dropout_i8(const int8_t* x, int8_t* y, int64_t rows, int64_t features, const uint64_t* seed,
+                               uint32_t rng_stream, void* stream) {
+    NITI_REQUIRE(x && y && seed && rows >= 0 && features > 0);
+    dropout_kernel<<<blocks_for(rows * features, 256, sm_count_simt() * 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        x, y, rows, features, reinterpret_cast<const unsigned long long*>(seed), rng_stream);
+    return set_cuda_error(cudaGetLastError());
+}
+
+extern "C" int niti_loss_i8(const int8_t* out8, const int32_t* out_exp, const int64_t* target, int8_t* err8, int B,
+                            int classes, const uint64_t* seed, uint32_t rng_stream, uint64_t sample_offset, void* stream) {
+    NITI_REQUIRE(out8 && out_exp && target && err8 && seed && B > 0 && classes > 0);
+    if (classes > LOSS_MAX_CLASSES) return NITI_ERR_UNSUPPORTED;
+    loss_kernel<<<(B + 63) / 64, 64, 0, static_cast<cudaStream_t>(stream)>>>(
+        out8, out_exp, reinterpret_cast<const long long*>(target), err8, B, classes,
+        reinterpret_cast<const unsigned long long*>(seed), rng_stream, sample_offset);
+    return set_cuda_error(cudaGetLastError());
+}
+
+extern "C" int niti_update_i8(int8_t* w, const int32_t* g32, const uint32_t* maxabs, int64_t n, int mu, int round_mode,
+                              const uint64_t* seed, uint32_t rng_stream, int8_t* wt, int K, int R, int S, int C, void* stream) {
+    NITI_REQUIRE(w && g32 && maxabs && n > 0 && round_mode >= 0 && round_mode <= 2);
+    NITI_REQUIRE(seed || round_mode != NITI_ROUND_STOCHASTIC);
+    if (wt) NITI_REQUIRE(K > 0 && R > 0 && S > 0 && C > 0 && static_cast<int64_t>(K) * R * S * C == n);
+    update_kernel<<<blocks_for(n, 256, sm_count_simt() * 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        w, g32, maxabs, n, mu, round_mode, reinterpret_cast<const unsigned long long*>(seed), rng_stream, wt, K, R, S, C);
+    return set_cuda_error(cudaGetLastError());
+}
+
+extern "C" int niti_weight_flip_transpose_i8(const int8_t* w, int8_t* wt, int K, int R, int S, int C, void* stream) {
+    NITI_REQUIRE(w && wt && K > 0 && R > 0 && S > 0 && C > 0);
+    const long long n = static_cast<long long>(K) * R * S * C;
+    flip_transpose_kernel<<<blocks_for(n, 256, sm_count_simt() * 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(w, wt, K, R, S, C);
+    return set_cuda_error(cudaGetLastError());
+}
+
+extern "C" int niti_quantize_input_f32(const float* x, int8_t* x8, int32_t* exp_out, uint32_t* scratch, int N, int C,
+                                       int H, int W, void* stream) {
+    NITI_REQUIRE(x && x8 && exp_out && scratch && N > 0 && C > 0 && H > 0 && W > 0);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const long long n = static_cast<long long>(N) * C * H * W;
+    if (int e = set_cuda_error(cudaMemsetAsync(scratch, 0, 4, st))) return e;
+    absmax_f32_kernel<<<blocks_for(n, 256, sm_count_simt() * 4), 256, 0, st>>>(x, n, scratch);
+    quantize_input_kernel<<<blocks_for(n, 256, sm_count_simt() * 8), 256, 0, st>>>(x, x8, exp_out, scratch, N, C, H, W);
+    return set_cuda_error(cudaGetLastError());
+}

@@ -1,0 +1,561 @@
+// int8 x int8 -> int32 contractions on the 5th-generation tensor cores (sm_100a):
+// GEMM, implicit-GEMM convolution forward / error-backward, and convolution weight gradient.
+//
+// Common structure (one CTA per SM, 192 threads):
+//   warp 0      TMA producer: cp.async.bulk.tensor into 128-byte-swizzled shared-memory stages
+//   warp 1      allocates tensor memory, issues tcgen05.mma.kind::i8 (one lane), frees TMEM
+//   warps 2..5  epilogue: tcgen05.ld the int32 accumulators, reduce max|acc|, store
+// Stages hand over through mbarriers (TMA complete_tx -> MMA, tcgen05.commit -> producer);
+// accumulators are double-buffered in TMEM so the epilogue of one tile overlaps the main loop
+// of the next.  All waits are bounded (ptx.cuh).
+//
+// Operand layouts in shared memory.  Every operand tile is rows of 128 bytes, 8-row groups of
+// 1024 bytes, 128-byte swizzle -- exactly what a TMA box with a 128-byte inner extent writes.
+//   K-major  (reduction index contiguous in memory): row = M/N index, 128 bytes = 128 reduction
+//            elements; one MMA (K = 32) advances the descriptor by 32 bytes.
+//   MN-major (M/N index contiguous, e.g. [pixels][channels] read as channels x pixels): row =
+//            reduction index, 128 bytes = 128 M/N elements; one MMA advances by 32 rows = 4096 B;
+//            a second 128-wide panel sits `rows * 128` bytes further (leading byte offset).
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <cstdint>
+#include <cstdio>
+
+#include "internal.h"
+#include "ptx.cuh"
+
+namespace niti {
+
+constexpr int BLOCK_M = 128;
+constexpr int ROW_BYTES = 128;               // bytes per shared-memory row of an operand tile
+constexpr int PANEL_BYTES = 128 * ROW_BYTES; // one 128-row operand panel
+constexpr int UMMA_THREADS = 192;
+constexpr uint32_t SWIZZLE_128B_CODE = 2;
+
+// ------------------------------------------------------------------------------------------------
+// GEMM / convolution forward (and error-backward, which is a forward conv over flipped weights)
+// ------------------------------------------------------------------------------------------------
+struct GemmParams {
+    int conv;              // 0: plain GEMM, 1: implicit-GEMM convolution (A tile = 4-D box of pixels)
+    int M, N;              // output rows (GEMM rows or pixels) and columns
+    int num_kb;            // reduction blocks per output tile
+    int m_tiles, n_tiles;
+    int a_mn, b_mn;        // operand majors (0 = K-major, 1 = MN-major); conv uses 0/0
+    int a_bytes;           // bytes one A stage receives from TMA
+    // convolution geometry
+    int H, W, C, R, S, pad, Nimg;
+    int BW, BH, BI;        // pixels of one tile along w, h and images; BW*BH*BI <= 128
+    int tiles_w, tiles_h;
+    int cblocks;           // C / 128
+    int32_t* out;
+    long long ldc;         // output row pitch in elements
+    unsigned* maxabs;
+    int32_t* status;
+};
+
+template <int BN>
+struct GemmCfg {
+    static constexpr int B_STAGE_BYTES = BN * ROW_BYTES;
+    static constexpr int STAGE_BYTES = PANEL_BYTES + B_STAGE_BYTES;
+    static constexpr int STAGES = (192 * 1024) / STAGE_BYTES;
+    static constexpr int TMEM_COLS = 2 * BN;  // two accumulators; 256 or 512 columns
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+};
+
+__device__ __forceinline__ void report_abort(int32_t* status, int code, int role) {
+    if (status != nullptr && atomicCAS(status, 0, code) == 0) {
+        status[1] = static_cast<int32_t>(blockIdx.x + blockIdx.y * gridDim.x);
+        status[2] = role;
+    }
+}
+
+template <int BN>
+__global__ void __launch_bounds__(UMMA_THREADS, 1)
+umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const GemmParams p) {
+    using Cfg = GemmCfg<BN>;
+    constexpr int STAGES = Cfg::STAGES;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * Cfg::STAGE_BYTES);
+    uint64_t* full_bar = bars;
+    uint64_t* empty_bar = bars + STAGES;
+    uint64_t* tfull_bar = bars + 2 * STAGES;
+    uint64_t* tempty_bar = bars + 2 * STAGES + 2;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < STAGES; ++i) { mbar_init(smem_u32(&full_bar[i]), 1); mbar_init(smem_u32(&empty_bar[i]), 1); }
+        for (int i = 0; i < 2; ++i) { mbar_init(smem_u32(&tfull_bar[i]), 1); mbar_init(smem_u32(&tempty_bar[i]), 4); }
+        *abort_flag = 0;
+        fence_barrier_init();
+        tma_prefetch_desc(&tmA);
+        tma_prefetch_desc(&tmB);
+    }
+    if (warp == 1) { tmem_alloc(smem_u32(tmem_slot), Cfg::TMEM_COLS); tmem_relinquish(); }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    const int total_tiles = p.m_tiles * p.n_tiles;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            int s = 0; uint32_t ph = 0; bool ok = true;
+            for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+                const int m_t = tile / p.n_tiles, n_t = tile % p.n_tiles;
+                int tw = 0, th = 0, tn = 0;
+                if (p.conv) { tw = m_t % p.tiles_w; th = (m_t / p.tiles_w) % p.tiles_h; tn = m_t / (p.tiles_w * p.tiles_h); }
+                for (int kb = 0; kb < p.num_kb; ++kb) {
+                    if (!mbar_wait(smem_u32(&empty_bar[s]), ph ^ 1u, abort_flag)) { ok = false; report_abort(p.status, 1, 0); break; }
+                    const uint32_t fb = smem_u32(&full_bar[s]);
+                    const uint32_t sa = smem_u32(smem + s * Cfg::STAGE_BYTES);
+                    const uint32_t sb = sa + PANEL_BYTES;
+                    mbar_arrive_expect_tx(fb, static_cast<uint32_t>(p.a_bytes + Cfg::B_STAGE_BYTES));
+                    if (p.conv) {
+                        const int tap = kb / p.cblocks, cb = kb % p.cblocks;
+                        const int r = tap / p.S, sx = tap % p.S;
+                        tma_load_4d(sa, &tmA, fb, cb * ROW_BYTES, tw * p.BW + sx - p.pad, th * p.BH + r - p.pad, tn * p.BI);
+                        tma_load_2d(sb, &tmB, fb, tap * p.C + cb * ROW_BYTES, n_t * BN);
+                    } else {
+                        if (p.a_mn) tma_load_2d(sa, &tmA, fb, m_t * BLOCK_M, kb * 128);
+                        else        tma_load_2d(sa, &tmA, fb, kb * ROW_BYTES, m_t * BLOCK_M);
+                        if (p.b_mn) {
+#pragma unroll
+                            for (int pn = 0; pn < BN / 128; ++pn)
+                                tma_load_2d(sb + pn * PANEL_BYTES, &tmB, fb, n_t * BN + pn * 128, kb * 128);
+                        } else {
+                            tma_load_2d(sb, &tmB, fb, kb * ROW_BYTES, n_t * BN);
+                        }
+                    }
+                    if (++s == STAGES) { s = 0; ph ^= 1u; }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            const uint32_t idesc = make_idesc_i8(BLOCK_M, BN, p.a_mn, p.b_mn);
+            int s = 0; uint32_t ph = 0; bool ok = true; int it = 0;
+            for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x, ++it) {
+                const int acc = it & 1; const uint32_t aph = (it >> 1) & 1u;
+                if (!mbar_wait(smem_u32(&tempty_bar[acc]), aph ^ 1u, abort_flag)) { report_abort(p.status, 2, 1); break; }
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BN);
+                for (int kb = 0; kb < p.num_kb; ++kb) {
+                    if (!mbar_wait(smem_u32(&full_bar[s]), ph, abort_flag)) { ok = false; report_abort(p.status, 3, 1); break; }
+                    tc_fence_after();
+                    const uint32_t sa = smem_u32(smem + s * Cfg::STAGE_BYTES);
+                    const uint32_t sb = sa + PANEL_BYTES;
+                    const uint64_t a0 = p.a_mn ? make_smem_desc(sa, PANEL_BYTES, 1024, SWIZZLE_128B_CODE)
+                                               : make_smem_desc(sa, 16, 1024, SWIZZLE_128B_CODE);
+                    const uint64_t b0 = p.b_mn ? make_smem_desc(sb, PANEL_BYTES, 1024, SWIZZLE_128B_CODE)
+                                               : make_smem_desc(sb, 16, 1024, SWIZZLE_128B_CODE);
+                    const uint32_t a_step = p.a_mn ? 32u * ROW_BYTES : 32u;
+                    const uint32_t b_step = p.b_mn ? 32u * ROW_BYTES : 32u;
+#pragma unroll
+                    for (int k = 0; k < 4; ++k)
+                        umma_i8(d_tmem, desc_advance(a0, k * a_step), desc_advance(b0, k * b_step), idesc,
+                                static_cast<uint32_t>((kb | k) != 0));
+                    umma_commit(smem_u32(&empty_bar[s]));
+                    if (++s == STAGES) { s = 0; ph ^= 1u; }
+                }
+                if (ok) umma_commit(smem_u32(&tfull_bar[acc]));
+            }
+        }
+    } else {
+        // ------------------------------------------------------------------ epilogue (4 warps)
+        const int q = warp & 3;  // TMEM lanes [32q, 32q+32) are the ones this warp may read
+        const int row_in_tile = q * 32 + lane;
+        unsigned local_max = 0;
+        int it = 0;
+        for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++it) {
+            const int acc = it & 1; const uint32_t aph = (it >> 1) & 1u;
+            if (!mbar_wait(smem_u32(&tfull_bar[acc]), aph, abort_flag)) { report_abort(p.status, 4, 2); break; }
+            tc_fence_after();
+            const int m_t = tile / p.n_tiles, n_t = tile % p.n_tiles;
+            bool valid; long long row;
+            if (p.conv) {
+                const int tw = m_t % p.tiles_w, th = (m_t / p.tiles_w) % p.tiles_h, tn = m_t / (p.tiles_w * p.tiles_h);
+                const int w = tw * p.BW + row_in_tile % p.BW;
+                const int h = th * p.BH + (row_in_tile / p.BW) % p.BH;
+                const int n = tn * p.BI + row_in_tile / (p.BW * p.BH);
+                valid = row_in_tile < p.BW * p.BH * p.BI && w < p.W && h < p.H && n < p.Nimg;
+                row = (static_cast<long long>(n) * p.H + h) * p.W + w;
+            } else {
+                row = static_cast<long long>(m_t) * BLOCK_M + row_in_tile;
+                valid = row < p.M;
+            }
+            int32_t* out_row = p.out + row * p.ldc;
+            const int col0 = n_t * BN;
+            const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(acc * BN);
+#pragma unroll 1
+            for (int c = 0; c < BN; c += 32) {
+                uint32_t v[32];
+                __syncwarp();
+                tmem_ld_32x32(taddr + c, v);
+                tmem_ld_wait();
+                if (valid) {
+                    const int col = col0 + c;
+                    if (col + 32 <= p.N && (p.ldc & 3) == 0) {
+#pragma unroll
+                        for (int j = 0; j < 32; j += 4) {
+                            int4 o = make_int4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+                            *reinterpret_cast<int4*>(out_row + col + j) = o;
+                        }
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) {
+                            int x = static_cast<int>(v[j]);
+                            local_max = max(local_max, static_cast<unsigned>(x < 0 ? -x : x));
+                        }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) {
+                            if (col + j < p.N) {
+                                int x = static_cast<int>(v[j]);
+                                out_row[col + j] = x;
+                                local_max = max(local_max, static_cast<unsigned>(x < 0 ? -x : x));
+                            }
+                        }
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&tempty_bar[acc]));
+        }
+        local_max = __reduce_max_sync(0xFFFFFFFFu, local_max);
+        if (lane == 0 && local_max != 0 && p.maxabs != nullptr) atomicMax(p.maxabs, local_max);
+    }
+
+    // ---------------------------------------------------------------------- teardown
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        if (*abort_flag) __nanosleep(200000);  // let copies and MMAs already in flight land
+        tc_fence_after();
+        __syncwarp();
+        tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
+// Convolution weight gradient: g[k][r][s][c] = sum_pixels err[pixel][k] * x[pixel + (r,s) - pad][c]
+// A = err tile (MN-major: 128 k-channels x <=128 pixels), B = shifted x tile (MN-major:
+// 128 c-channels x the same pixels).  One CTA owns (128 k) x (128 c) x (one filter row r, all S
+// taps) and a contiguous range of pixel chunks; its S accumulators live in TMEM side by side.
+// Partial sums are written to scratch[split] and folded by wgrad_reduce_kernel.
+// ------------------------------------------------------------------------------------------------
+struct WgradParams {
+    int H, W, C, K, R, S, pad, Nimg;
+    int BW, BH, BI;
+    int tiles_w, tiles_h, tiles_n;
+    int chunks, splits;
+    int k_tiles, c_tiles;
+    int box_bytes;         // bytes of one TMA box (BW*BH*BI rows of 128 bytes)
+    int mma_per_chunk;     // ceil(rows / 32)
+    int32_t* partial;      // [splits][K*R*S*C]
+    int32_t* status;
+};
+
+constexpr int WG_MAX_S = 3;
+constexpr int WG_STAGE_BYTES = (1 + WG_MAX_S) * PANEL_BYTES;  // 64 KB
+constexpr int WG_STAGES = 3;
+constexpr int WG_SMEM_BYTES = WG_STAGES * WG_STAGE_BYTES + 1024 + 256;
+constexpr int WG_TMEM_COLS = 512;
+
+__global__ void __launch_bounds__(UMMA_THREADS, 1)
+umma_wgrad_kernel(const __grid_constant__ CUtensorMap tmErr, const __grid_constant__ CUtensorMap tmX, const WgradParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + WG_STAGES * WG_STAGE_BYTES);
+    uint64_t* full_bar = bars;
+    uint64_t* empty_bar = bars + WG_STAGES;
+    uint64_t* tfull_bar = bars + 2 * WG_STAGES;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * WG_STAGES + 1);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+
+    // Rows past the box (when a tile holds fewer than 128 pixels) are read by the MMA as part of
+    // the reduction: they must be zero.  TMA only ever writes the first box_bytes of a panel.
+    {
+        int4* z = reinterpret_cast<int4*>(smem);
+        for (int i = threadIdx.x; i < WG_STAGES * WG_STAGE_BYTES / 16; i += UMMA_THREADS) z[i] = make_int4(0, 0, 0, 0);
+    }
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < WG_STAGES; ++i) { mbar_init(smem_u32(&full_bar[i]), 1); mbar_init(smem_u32(&empty_bar[i]), 1); }
+        mbar_init(smem_u32(&tfull_bar[0]), 1);
+        *abort_flag = 0;
+        fence_barrier_init();
+        tma_prefetch_desc(&tmErr);
+        tma_prefetch_desc(&tmX);
+    }
+    if (warp == 1) { tmem_alloc(smem_u32(tmem_slot), WG_TMEM_COLS); tmem_relinquish(); }
+    fence_proxy_async();  // zero fill (generic proxy) before TMA writes (async proxy)
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    const int split = blockIdx.x;
+    const int item = blockIdx.y;
+    const int r = item % p.R;
+    const int kt = (item / p.R) % p.k_tiles;
+    const int ct = item / (p.R * p.k_tiles);
+    const int chunk_lo = static_cast<int>(static_cast<long long>(split) * p.chunks / p.splits);
+    const int chunk_hi = static_cast<int>(static_cast<long long>(split + 1) * p.chunks / p.splits);
+
+    if (warp == 0) {
+        if (lane == 0) {
+            int s = 0; uint32_t ph = 0;
+            for (int ch = chunk_lo; ch < chunk_hi; ++ch) {
+                const int tw = ch % p.tiles_w, th = (ch / p.tiles_w) % p.tiles_h, tn = ch / (p.tiles_w * p.tiles_h);
+                if (!mbar_wait(smem_u32(&empty_bar[s]), ph ^ 1u, abort_flag)) { report_abort(p.status, 11, 0); break; }
+                const uint32_t fb = smem_u32(&full_bar[s]);
+                const uint32_t sa = smem_u32(smem + s * WG_STAGE_BYTES);
+                mbar_arrive_expect_tx(fb, static_cast<uint32_t>((1 + p.S) * p.box_bytes));
+                tma_load_4d(sa, &tmErr, fb, kt * 128, tw * p.BW, th * p.BH, tn * p.BI);
+                for (int sx = 0; sx < p.S; ++sx)
+                    tma_load_4d(sa + (1 + sx) * PANEL_BYTES, &tmX, fb, ct * 128, tw * p.BW + sx - p.pad, th * p.BH + r - p.pad, tn * p.BI);
+                if (++s == WG_STAGES) { s = 0; ph ^= 1u; }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            const uint32_t idesc = make_idesc_i8(BLOCK_M, 128, 1, 1);
+            int s = 0; uint32_t ph = 0; bool ok = true;
+            for (int ch = chunk_lo; ch < chunk_hi; ++ch) {
+                if (!mbar_wait(smem_u32(&full_bar[s]), ph, abort_flag)) { ok = false; report_abort(p.status, 13, 1); break; }
+                tc_fence_after();
+                const uint32_t sa = smem_u32(smem + s * WG_STAGE_BYTES);
+                const uint64_t a0 = make_smem_desc(sa, PANEL_BYTES, 1024, SWIZZLE_128B_CODE);
+                for (int sx = 0; sx < p.S; ++sx) {
+                    const uint64_t b0 = make_smem_desc(sa + (1 + sx) * PANEL_BYTES, PANEL_BYTES, 1024, SWIZZLE_128B_CODE);
+                    for (int k = 0; k < p.mma_per_chunk; ++k)
+                        umma_i8(tmem_base + sx * 128, desc_advance(a0, k * 32u * ROW_BYTES), desc_advance(b0, k * 32u * ROW_BYTES),
+                                idesc, static_cast<uint32_t>(ch != chunk_lo || k != 0));
+                }
+                umma_commit(smem_u32(&empty_bar[s]));
+                if (++s == WG_STAGES) { s = 0; ph ^= 1u; }
+            }
+            if (ok) umma_commit(smem_u32(&tfull_bar[0]));
+        }
+    } else {
+        const int q = warp & 3;
+        const int k = kt * 128 + q * 32 + lane;  // output channel = accumulator row
+        if (mbar_wait(smem_u32(&tfull_bar[0]), 0, abort_flag)) {
+            tc_fence_after();
+            const long long per_split = static_cast<long long>(p.K) * p.R * p.S * p.C;
+            int32_t* base = p.partial + static_cast<long long>(split) * per_split;
+            for (int sx = 0; sx < p.S; ++sx) {
+                int32_t* out_row = base + ((static_cast<long long>(k) * p.R + r) * p.S + sx) * p.C + ct * 128;
+#pragma unroll 1
+                for (int c = 0; c < 128; c += 32) {
+                    uint32_t v[32];
+                    __syncwarp();
+                    tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + sx * 128 + c, v);
+                    tmem_ld_wait();
+                    if (k < p.K) {
+#pragma unroll
+                        for (int j = 0; j < 32; j += 4)
+                            if (ct * 128 + c + j < p.C)
+                                *reinterpret_cast<int4*>(out_row + c + j) = make_int4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+                    }
+                }
+            }
+        } else {
+            report_abort(p.status, 14, 2);
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        if (*abort_flag) __nanosleep(200000);
+        tc_fence_after();
+        __syncwarp();
+        tmem_dealloc(tmem_base, WG_TMEM_COLS);
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
+// host side
+// ------------------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode() {
+    static EncodeTiledFn fn = nullptr;
+    static bool tried = false;
+    if (!tried) {
+        tried = true;
+        void* sym = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(sym);
+    }
+    return fn;
+}
+
+// rank-2 or rank-4 uint8 tensor map with 128-byte swizzle; dims/box innermost first, strides in bytes.
+static int encode_map(CUtensorMap* map, const void* ptr, int rank, const uint64_t* dims, const uint64_t* strides,
+                      const uint32_t* box) {
+    EncodeTiledFn enc = get_encode();
+    if (!enc) return set_cuda_error_text("cuTensorMapEncodeTiled is not available from this driver");
+    cuuint64_t gdim[4]; cuuint64_t gstr[3]; cuuint32_t bx[4]; cuuint32_t es[4];
+    for (int i = 0; i < rank; ++i) { gdim[i] = dims[i]; bx[i] = box[i]; es[i] = 1; }
+    for (int i = 0; i + 1 < rank; ++i) gstr[i] = strides[i];
+    CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, rank, const_cast<void*>(ptr), gdim, gstr, bx, es,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        char buf[160];
+        snprintf(buf, sizeof buf, "cuTensorMapEncodeTiled failed with CUresult %d", static_cast<int>(r));
+        return set_cuda_error_text(buf);
+    }
+    return 0;
+}
+
+static int sm_count() {
+    static int n = 0;
+    if (n == 0) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+        if (n <= 0) n = 148;
+    }
+    return n;
+}
+
+template <int BN>
+static int launch_gemm_bn(const CUtensorMap& a, const CUtensorMap& b, const GemmParams& p, cudaStream_t st) {
+    using Cfg = GemmCfg<BN>;
+    static bool attr_set = false;
+    if (!attr_set) {
+        cudaError_t e = cudaFuncSetAttribute(umma_gemm_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
+        if (e != cudaSuccess) return set_cuda_error(e);
+        attr_set = true;
+    }
+    int grid = p.m_tiles * p.n_tiles;
+    if (grid > sm_count()) grid = sm_count();
+    umma_gemm_kernel<BN><<<grid, UMMA_THREADS, Cfg::SMEM_BYTES, st>>>(a, b, p);
+    return set_cuda_error(cudaGetLastError());
+}
+
+// Pixels of one 128-row tile: as much of a row as fits, then rows, then images.
+static void pick_pixel_box(int Nimg, int H, int W, int* BW, int* BH, int* BI) {
+    *BW = W < 128 ? W : 128;
+    int bh = 128 / *BW; if (bh > H) bh = H; if (bh < 1) bh = 1;
+    *BH = bh;
+    int bi = 128 / (*BW * *BH); if (bi > Nimg) bi = Nimg; if (bi < 1) bi = 1;
+    *BI = bi;
+}
+
+int umma_gemm(const int8_t* A, const int8_t* B, int32_t* C32, unsigned* maxabs, int M, int N, int K,
+              int trans_a, int trans_b, int32_t* status, cudaStream_t st) {
+    CUtensorMap ma, mb;
+    const int a_mn = trans_a ? 1 : 0, b_mn = trans_b ? 0 : 1;
+    const int bn = (N > 128) ? 256 : 128;
+    {
+        uint64_t dims[2], str[1]; uint32_t box[2] = {128, 128};
+        if (a_mn) { dims[0] = M; dims[1] = K; str[0] = M; } else { dims[0] = K; dims[1] = M; str[0] = K; }
+        if (int e = encode_map(&ma, A, 2, dims, str, box)) return e;
+        if (b_mn) { dims[0] = N; dims[1] = K; str[0] = N; box[1] = 128; } else { dims[0] = K; dims[1] = N; str[0] = K; box[1] = bn; }
+        if (int e = encode_map(&mb, B, 2, dims, str, box)) return e;
+    }
+    GemmParams p{};
+    p.conv = 0; p.M = M; p.N = N; p.num_kb = (K + 127) / 128;
+    p.m_tiles = (M + 127) / 128; p.n_tiles = (N + bn - 1) / bn;
+    p.a_mn = a_mn; p.b_mn = b_mn; p.a_bytes = PANEL_BYTES;
+    p.out = C32; p.ldc = N; p.maxabs = maxabs; p.status = status;
+    return bn == 256 ? launch_gemm_bn<256>(ma, mb, p, st) : launch_gemm_bn<128>(ma, mb, p, st);
+}
+
+int umma_conv_fprop(const int8_t* x, const int8_t* w, int32_t* y32, unsigned* maxabs, int Nimg, int H, int W, int C,
+                    int K, int R, int S, int pad, int32_t* status, cudaStream_t st) {
+    // stride 1 with P == H, Q == W ("same" padding) is what the tile decomposition covers
+    CUtensorMap ma, mb;
+    const int bn = (K > 128) ? 256 : 128;
+    GemmParams p{};
+    pick_pixel_box(Nimg, H, W, &p.BW, &p.BH, &p.BI);
+    {
+        uint64_t dims[4] = {(uint64_t)C, (uint64_t)W, (uint64_t)H, (uint64_t)Nimg};
+        uint64_t str[3] = {(uint64_t)C, (uint64_t)W * C, (uint64_t)H * W * C};
+        uint32_t box[4] = {128, (uint32_t)p.BW, (uint32_t)p.BH, (uint32_t)p.BI};
+        if (int e = encode_map(&ma, x, 4, dims, str, box)) return e;
+        uint64_t d2[2] = {(uint64_t)R * S * C, (uint64_t)K};
+        uint64_t s2[1] = {(uint64_t)R * S * C};
+        uint32_t b2[2] = {128, (uint32_t)bn};
+        if (int e = encode_map(&mb, w, 2, d2, s2, b2)) return e;
+    }
+    p.conv = 1;
+    p.H = H; p.W = W; p.C = C; p.R = R; p.S = S; p.pad = pad; p.Nimg = Nimg;
+    p.tiles_w = (W + p.BW - 1) / p.BW; p.tiles_h = (H + p.BH - 1) / p.BH;
+    const int tiles_n = (Nimg + p.BI - 1) / p.BI;
+    p.cblocks = C / 128;
+    p.M = Nimg * H * W; p.N = K; p.num_kb = R * S * p.cblocks;
+    p.m_tiles = p.tiles_w * p.tiles_h * tiles_n; p.n_tiles = (K + bn - 1) / bn;
+    p.a_mn = 0; p.b_mn = 0; p.a_bytes = p.BW * p.BH * p.BI * ROW_BYTES;
+    p.out = y32; p.ldc = K; p.maxabs = maxabs; p.status = status;
+    return bn == 256 ? launch_gemm_bn<256>(ma, mb, p, st) : launch_gemm_bn<128>(ma, mb, p, st);
+}
+
+static void wgrad_plan(int Nimg, int H, int W, int C, int K, int R, WgradParams* p) {
+    pick_pixel_box(Nimg, H, W, &p->BW, &p->BH, &p->BI);
+    p->tiles_w = (W + p->BW - 1) / p->BW; p->tiles_h = (H + p->BH - 1) / p->BH; p->tiles_n = (Nimg + p->BI - 1) / p->BI;
+    p->chunks = p->tiles_w * p->tiles_h * p->tiles_n;
+    p->k_tiles = (K + 127) / 128; p->c_tiles = (C + 127) / 128;
+    const int items = R * p->k_tiles * p->c_tiles;
+    int splits = (sm_count() + items / 2) / items;
+    if (splits < 1) splits = 1;
+    if (splits > p->chunks) splits = p->chunks;
+    p->splits = splits;
+}
+
+size_t umma_wgrad_scratch_bytes(int Nimg, int H, int W, int C, int K, int R, int S) {
+    WgradParams p{};
+    wgrad_plan(Nimg, H, W, C, K, R, &p);
+    return static_cast<size_t>(p.splits) * K * R * S * C * sizeof(int32_t);
+}
+
+int umma_conv_wgrad_partials(const int8_t* x, const int8_t* err, int32_t* partial, int* splits_out, int Nimg, int H,
+                             int W, int C, int K, int R, int S, int pad, int32_t* status, cudaStream_t st) {
+    WgradParams p{};
+    wgrad_plan(Nimg, H, W, C, K, R, &p);
+    CUtensorMap me, mx;
+    {
+        uint32_t box[4] = {128, (uint32_t)p.BW, (uint32_t)p.BH, (uint32_t)p.BI};
+        uint64_t de[4] = {(uint64_t)K, (uint64_t)W, (uint64_t)H, (uint64_t)Nimg};
+        uint64_t se[3] = {(uint64_t)K, (uint64_t)W * K, (uint64_t)H * W * K};
+        if (int e = encode_map(&me, err, 4, de, se, box)) return e;
+        uint64_t dx[4] = {(uint64_t)C, (uint64_t)W, (uint64_t)H, (uint64_t)Nimg};
+        uint64_t sx[3] = {(uint64_t)C, (uint64_t)W * C, (uint64_t)H * W * C};
+        if (int e = encode_map(&mx, x, 4, dx, sx, box)) return e;
+    }
+    p.H = H; p.W = W; p.C = C; p.K = K; p.R = R; p.S = S; p.pad = pad; p.Nimg = Nimg;
+    const int rows = p.BW * p.BH * p.BI;
+    p.box_bytes = rows * ROW_BYTES;
+    p.mma_per_chunk = (rows + 31) / 32;
+    p.partial = partial; p.status = status;
+    *splits_out = p.splits;
+    static bool attr_set = false;
+    if (!attr_set) {
+        cudaError_t e = cudaFuncSetAttribute(umma_wgrad_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, WG_SMEM_BYTES);
+        if (e != cudaSuccess) return set_cuda_error(e);
+        attr_set = true;
+    }
+    dim3 grid(p.splits, R * p.k_tiles * p.c_tiles);
+    umma_wgrad_kernel<<<grid, UMMA_THREADS, WG_SMEM_BYTES, st>>>(me, mx, p);
+    return set_cuda_error(cudaGetLastError());
+}
+
+}  // namespace niti

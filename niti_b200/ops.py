@@ -1,0 +1,213 @@
+"""torch-tensor front end of the C ABI: allocates outputs with torch, launches on torch's
+current stream of the tensors' device, never synchronises.
+
+Shapes and layouts are those of the reference's extension calls (NHWC int8 activations,
+[K,R,S,C] int8 filters); per-tensor exponents, shifts and max|acc| words are 0-dim / 1-element
+int32 CUDA tensors so that nothing here reads a value back to the host.
+"""
+import torch
+
+from ._lib import lib, check
+
+ROUND_NEAREST, ROUND_STOCHASTIC, ROUND_PSEUDO_STOCHASTIC = 0, 1, 2
+CALC_ACT, CALC_ERR, CALC_GRAD = 0, 1, 2
+
+_status = {}
+_scratch = {}
+
+
+def _st():
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _p(t):
+    return None if t is None else t.data_ptr()
+
+
+def _need_cuda(*ts):
+    for t in ts:
+        if t is not None and not (t.is_cuda and t.is_contiguous()):
+            raise RuntimeError("niti_b200 ops need contiguous CUDA tensors (there is no CPU path)")
+
+
+def status_word(device):
+    """int32[4] the tensor-core kernels write if one of their bounded waits expires."""
+    key = torch.device(device).index
+    if key not in _status:
+        _status[key] = torch.zeros(4, dtype=torch.int32, device=device)
+    return _status[key]
+
+
+def check_status(device):
+    """Synchronises and raises if a tensor-core kernel reported a timed-out wait."""
+    s = status_word(device).tolist()
+    if s[0] != 0:
+        raise RuntimeError(f"niti_b200 tensor-core kernel gave up waiting: code={s[0]} block={s[1]} role={s[2]}")
+
+
+def scratch(device, nbytes):
+    """Grow-only per-device scratch arena (stream-ordered reuse on the current stream)."""
+    key = torch.device(device).index
+    cur = _scratch.get(key)
+    if cur is None or cur.numel() < nbytes:
+        cur = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
+        _scratch[key] = cur
+    return cur
+
+
+def seed_tensor(value, device):
+    """uint64 seed word on the device (stored in an int64 tensor)."""
+    return torch.tensor([int(value)], dtype=torch.int64, device=device)
+
+
+# ------------------------------------------------------------------ contractions
+def conv_fprop_acc(x, w, pad=1, stride=1):
+    _need_cuda(x, w)
+    N, H, W, C = x.shape
+    K, R, S, C2 = w.shape
+    assert C == C2 and x.dtype == torch.int8 and w.dtype == torch.int8
+    P, Q = H + 2 * pad - R + 1, W + 2 * pad - S + 1
+    y32 = torch.empty((N, P, Q, K), dtype=torch.int32, device=x.device)
+    mx = torch.empty(1, dtype=torch.int32, device=x.device)
+    check(lib.niti_conv_fprop_i8(_p(x), _p(w), _p(y32), _p(mx), N, H, W, C, K, R, S, pad, stride,
+                                 _p(status_word(x.device)), _st()), "niti_conv_fprop_i8")
+    return y32, mx
+
+
+def flip_transpose(w):
+    _need_cuda(w)
+    K, R, S, C = w.shape
+    wt = torch.empty((C, R, S, K), dtype=torch.int8, device=w.device)
+    check(lib.niti_weight_flip_transpose_i8(_p(w), _p(wt), K, R, S, C, _st()), "niti_weight_flip_transpose_i8")
+    return wt
+
+
+def conv_dgrad_acc(err, wt, pad=1):
+    """err [N,H,W,K], wt [C,R,S,K] (flip_transpose of the filters) -> int32 [N,H,W,C]."""
+    _need_cuda(err, wt)
+    N, H, W, K = err.shape
+    C, R, S, K2 = wt.shape
+    assert K == K2
+    e32 = torch.empty((N, H, W, C), dtype=torch.int32, device=err.device)
+    mx = torch.empty(1, dtype=torch.int32, device=err.device)
+    check(lib.niti_conv_dgrad_i8(_p(err), _p(wt), _p(e32), _p(mx), N, H, W, C, K, R, S, pad,
+                                 _p(status_word(err.device)), _st()), "niti_conv_dgrad_i8")
+    return e32, mx
+
+
+def conv_wgrad_acc(x, err, R=3, S=3, pad=1, out=None):
+    _need_cuda(x, err, out)
+    N, H, W, C = x.shape
+    K = err.shape[3]
+    g32 = out if out is not None else torch.empty((K, R, S, C), dtype=torch.int32, device=x.device)
+    mx = torch.empty(1, dtype=torch.int32, device=x.device)
+    nbytes = lib.niti_conv_wgrad_scratch_bytes(N, H, W, C, K, R, S)
+    sc = scratch(x.device, nbytes)
+    check(lib.niti_conv_wgrad_i8(_p(x), _p(err), _p(g32), _p(mx), _p(sc), sc.numel(), N, H, W, C, K, R, S, pad,
+                                 _p(status_word(x.device)), _st()), "niti_conv_wgrad_i8")
+    return g32, mx
+
+
+def gemm_acc(a, b, trans_a=False, trans_b=False, out=None):
+    """C32[M,N] = op(a) @ op(b); a is [M,K] ([K,M] if trans_a), b is [K,N] ([N,K] if trans_b)."""
+    _need_cuda(a, b, out)
+    M, K = (a.shape[1], a.shape[0]) if trans_a else a.shape
+    N = b.shape[0] if trans_b else b.shape[1]
+    assert (b.shape[1] if trans_b else b.shape[0]) == K
+    c32 = out if out is not None else torch.empty((M, N), dtype=torch.int32, device=a.device)
+    mx = torch.empty(1, dtype=torch.int32, device=a.device)
+    check(lib.niti_gemm_i8(_p(a), _p(b), _p(c32), _p(mx), M, N, K, int(trans_a), int(trans_b),
+                           _p(status_word(a.device)), _st()), "niti_gemm_i8")
+    return c32, mx
+
+
+# ------------------------------------------------------------------ requantisation
+def requant(acc, maxabs, kind, target_bits, mode=ROUND_NEAREST, seed=None, rng_stream=0, rng_offset=0, relu=False,
+            exp_a=None, exp_b=None, want_shift=False):
+    """int32 -> int8 by the tensor-wide shift.  Returns (out8, exp_out, shift_out)."""
+    _need_cuda(acc, maxabs)
+    out = torch.empty(acc.shape, dtype=torch.int8, device=acc.device)
+    exp_out = torch.empty((), dtype=torch.int32, device=acc.device)
+    shift_out = torch.empty((), dtype=torch.int32, device=acc.device) if want_shift else None
+    check(lib.niti_requant_i8(_p(acc), _p(out), _p(maxabs), acc.numel(), kind, target_bits, mode, _p(seed), rng_stream,
+                              rng_offset, int(relu), _p(exp_a), _p(exp_b), _p(exp_out), _p(shift_out), _st()),
+          "niti_requant_i8")
+    return out, exp_out, shift_out
+
+
+def absmax(acc):
+    _need_cuda(acc)
+    mx = torch.empty(1, dtype=torch.int32, device=acc.device)
+    check(lib.niti_absmax_i32(_p(acc), acc.numel(), _p(mx), _st()), "niti_absmax_i32")
+    return mx
+
+
+# ------------------------------------------------------------------ memory-bound layers
+def maxpool_fwd(x, k=2, stride=2):
+    _need_cuda(x)
+    N, H, W, C = x.shape
+    y = torch.empty((N, (H - k) // stride + 1, (W - k) // stride + 1, C), dtype=torch.int8, device=x.device)
+    check(lib.niti_maxpool_fwd_i8(_p(x), _p(y), N, H, W, C, k, stride, _st()), "niti_maxpool_fwd_i8")
+    return y
+
+
+def maxpool_bwd(x, dy, k=2, stride=2):
+    _need_cuda(x, dy)
+    N, H, W, C = x.shape
+    dx = torch.empty_like(x)
+    check(lib.niti_maxpool_bwd_i8(_p(x), _p(dy), _p(dx), N, H, W, C, k, stride, _st()), "niti_maxpool_bwd_i8")
+    return dx
+
+
+def relu_fwd(x):
+    _need_cuda(x)
+    y = torch.empty_like(x)
+    check(lib.niti_relu_fwd_i8(_p(x), _p(y), x.numel(), _st()), "niti_relu_fwd_i8")
+    return y
+
+
+def relu_bwd(act, err):
+    _need_cuda(act, err)
+    out = torch.empty_like(err)
+    check(lib.niti_relu_bwd_i8(_p(act), _p(err), _p(out), err.numel(), _st()), "niti_relu_bwd_i8")
+    return out
+
+
+def dropout(x, seed, rng_stream):
+    _need_cuda(x, seed)
+    y = torch.empty_like(x)
+    check(lib.niti_dropout_i8(_p(x), _p(y), x.shape[0], x.numel() // x.shape[0], _p(seed), rng_stream, _st()),
+          "niti_dropout_i8")
+    return y
+
+
+def loss_err(out8, out_exp, target, seed, rng_stream=0xFFFF, sample_offset=0):
+    _need_cuda(out8, out_exp, target, seed)
+    assert target.dtype == torch.int64 and out_exp.dtype == torch.int32
+    err = torch.empty_like(out8)
+    check(lib.niti_loss_i8(_p(out8), _p(out_exp), _p(target), _p(err), out8.shape[0], out8.shape[1], _p(seed),
+                           rng_stream, sample_offset, _st()), "niti_loss_i8")
+    return err
+
+
+def update(w, g32, maxabs, mu, mode=ROUND_PSEUDO_STOCHASTIC, seed=None, rng_stream=0, wt=None):
+    """In-place weight update; refreshes the flipped/transposed bank `wt` when given."""
+    _need_cuda(w, g32, maxabs, wt)
+    if wt is not None:
+        K, R, S, C = w.shape
+    else:
+        K = R = S = C = 0
+    check(lib.niti_update_i8(_p(w), _p(g32), _p(maxabs), w.numel(), mu, mode, _p(seed), rng_stream, _p(wt), K, R, S, C,
+                             _st()), "niti_update_i8")
+
+
+def quantize_input(x):
+    """float32 NCHW -> (int8 NHWC, exponent)."""
+    _need_cuda(x)
+    assert x.dtype == torch.float32
+    N, C, H, W = x.shape
+    x8 = torch.empty((N, H, W, C), dtype=torch.int8, device=x.device)
+    e = torch.empty((), dtype=torch.int32, device=x.device)
+    tmp = torch.empty(1, dtype=torch.int32, device=x.device)
+    check(lib.niti_quantize_input_f32(_p(x), _p(x8), _p(e), _p(tmp), N, C, H, W, _st()), "niti_quantize_input_f32")
+    return x8, e

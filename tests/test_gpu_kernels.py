@@ -1,0 +1,213 @@
+"""Kernel-level parity: every C-ABI entry point against the CPU oracle, bit-exact."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import niti_oracle as O, philox
+
+pytestmark = pytest.mark.gpu
+
+if not torch.cuda.is_available():
+    pytest.skip("needs a CUDA device", allow_module_level=True)
+
+from niti_b200 import ops  # noqa: E402
+
+DEV = "cuda:0"
+
+
+def cu(a):
+    return torch.from_numpy(np.ascontiguousarray(a)).to(DEV)
+
+
+def rnd8(rng, shape, lo=-127, hi=128):
+    return rng.integers(lo, hi, size=shape).astype(np.int8)
+
+
+def describe_mismatch(got, want):
+    bad = np.argwhere(got != want)
+    return f"{len(bad)} of {got.size} differ; first {bad[:5].tolist()} got {got[tuple(bad[0])]} want {want[tuple(bad[0])]}" \
+        if len(bad) else "equal"
+
+
+def assert_same(got_t, want, what):
+    got = got_t.cpu().numpy()
+    assert got.shape == want.shape, (what, got.shape, want.shape)
+    assert np.array_equal(got, want), f"{what}: {describe_mismatch(got, want.astype(got.dtype))}"
+    ops.check_status(DEV)
+
+
+# ----------------------------------------------------------------------------- GEMM
+GEMM_CASES = [
+    # M, N, K, trans_a, trans_b
+    (128, 128, 128, 0, 1), (256, 128, 256, 0, 1), (384, 256, 512, 0, 1), (200, 144, 272, 0, 1),
+    (1024, 512, 1024, 0, 1), (128, 128, 128, 0, 0), (256, 256, 384, 0, 0), (200, 144, 272, 0, 0),
+    (128, 128, 128, 1, 0), (256, 384, 512, 1, 0), (208, 144, 272, 1, 0), (128, 128, 256, 1, 1),
+    # CUDA-core shapes of the 10-class FC layer: forward, error, gradient
+    (64, 10, 8192, 0, 1), (64, 8192, 10, 0, 0), (10, 8192, 64, 1, 0), (7, 5, 33, 0, 1), (7, 5, 33, 1, 1),
+]
+
+
+@pytest.mark.parametrize("M,N,K,ta,tb", GEMM_CASES)
+def test_gemm(M, N, K, ta, tb):
+    rng = np.random.default_rng(M * 7 + N * 3 + K + ta * 2 + tb)
+    a = rnd8(rng, (K, M) if ta else (M, K))
+    b = rnd8(rng, (N, K) if tb else (K, N))
+    want = O.int8_mm(a.T if ta else a, b.T if tb else b)
+    c32, mx = ops.gemm_acc(cu(a), cu(b), bool(ta), bool(tb))
+    assert_same(c32, want.astype(np.int32), "gemm accumulators")
+    assert int(mx.item()) == int(np.abs(want).max())
+
+
+# ----------------------------------------------------------------------------- convolution
+CONV_CASES = [
+    # N, H, W, C, K
+    (2, 8, 8, 128, 128), (4, 32, 32, 128, 128), (3, 16, 16, 128, 256), (5, 8, 8, 256, 512), (9, 4, 4, 256, 128),
+    (2, 12, 20, 128, 144), (1, 2, 2, 128, 128), (16, 2, 2, 128, 128),
+    (4, 32, 32, 3, 128), (3, 8, 8, 3, 32), (2, 8, 8, 16, 32), (2, 6, 10, 5, 7),
+]
+
+
+@pytest.mark.parametrize("N,H,W,C,K", CONV_CASES)
+def test_conv_fprop(N, H, W, C, K):
+    rng = np.random.default_rng(N + H * 3 + C * 5 + K)
+    x, w = rnd8(rng, (N, H, W, C)), rnd8(rng, (K, 3, 3, C))
+    want = O.conv_fprop(x, w)
+    y32, mx = ops.conv_fprop_acc(cu(x), cu(w))
+    assert_same(y32, want.astype(np.int32), "conv fprop accumulators")
+    assert int(mx.item()) == int(np.abs(want).max())
+
+
+@pytest.mark.parametrize("N,H,W,C,K", CONV_CASES)
+def test_conv_dgrad(N, H, W, C, K):
+    rng = np.random.default_rng(N + H * 3 + C * 5 + K + 1)
+    err, w = rnd8(rng, (N, H, W, K)), rnd8(rng, (K, 3, 3, C))
+    want = O.conv_dgrad(err, w)
+    wt = ops.flip_transpose(cu(w))
+    assert_same(wt, O.flip_transpose(w), "flipped/transposed filters")
+    e32, mx = ops.conv_dgrad_acc(cu(err), wt)
+    assert_same(e32, want.astype(np.int32), "conv dgrad accumulators")
+    assert int(mx.item()) == int(np.abs(want).max())
+
+
+@pytest.mark.parametrize("N,H,W,C,K", CONV_CASES)
+def test_conv_wgrad(N, H, W, C, K):
+    rng = np.random.default_rng(N + H * 3 + C * 5 + K + 2)
+    x, err = rnd8(rng, (N, H, W, C)), rnd8(rng, (N, H, W, K))
+    want = O.conv_wgrad(x, err)
+    g32, mx = ops.conv_wgrad_acc(cu(x), cu(err))
+    assert_same(g32, want.astype(np.int32), "conv wgrad accumulators")
+    assert int(mx.item()) == int(np.abs(want).max())
+
+
+def test_conv_rejects_stride():
+    x, w = cu(np.zeros((1, 8, 8, 128), np.int8)), cu(np.zeros((128, 3, 3, 128), np.int8))
+    with pytest.raises(RuntimeError):
+        ops.conv_fprop_acc(x, w, pad=1, stride=2)
+
+
+# ----------------------------------------------------------------------------- requantisation
+@pytest.mark.parametrize("mode", [0, 1, 2])
+@pytest.mark.parametrize("mx", [0, 1, 100, 127, 128, 129, 1000, 65536, 65537, 3000000, 2 ** 30])
+def test_requant_act(mode, mx):
+    rng = np.random.default_rng(mx % 1000 + mode)
+    n = 16 * 1000 + 7
+    acc = rng.integers(-mx, mx + 1, size=n).astype(np.int32)
+    acc[5] = mx
+    acc[n - 1] = -mx
+    words = philox.random_u32_tensor(99, 3, (n,), offset=8)
+    want, want_exp, _ = O.act_calc(acc, -4, mode, words)
+    a = cu(acc)
+    seed = ops.seed_tensor(99, DEV)
+    e_in = torch.tensor(-4, dtype=torch.int32, device=DEV)
+    out, e_out, sh = ops.requant(a, ops.absmax(a), ops.CALC_ACT, 7, mode, seed, 3, 8, exp_a=e_in, want_shift=True)
+    assert_same(out, want, f"requant mode {mode} max {mx}")
+    assert int(e_out.item()) == want_exp
+
+
+def test_requant_unaligned_rng_offset_and_relu():
+    rng = np.random.default_rng(5)
+    acc = rng.integers(-50000, 50000, size=4099).astype(np.int32)
+    words = philox.random_u32_tensor(7, 1, acc.shape, offset=13)
+    want, sh = O.err_calc(acc, O.STOCHASTIC, words)
+    a = cu(acc)
+    out, e_out, s = ops.requant(a, ops.absmax(a), ops.CALC_ERR, 7, 1, ops.seed_tensor(7, DEV), 1, 13, relu=True, want_shift=True)
+    assert_same(out, np.maximum(want, 0), "requant + relu")
+    assert int(s.item()) == sh and int(e_out.item()) == sh
+
+
+@pytest.mark.parametrize("mu", [5, 4, 3])
+@pytest.mark.parametrize("mode", [0, 1, 2])
+def test_update(mu, mode):
+    rng = np.random.default_rng(mu + mode)
+    K, R, S, C = 32, 3, 3, 16
+    w = rnd8(rng, (K, R, S, C))
+    for mx in (0, 3, 31, 40000):
+        g = rng.integers(-mx, mx + 1, size=w.shape).astype(np.int32)
+        words = philox.random_u32_tensor(21, 2, w.shape)
+        want_w, _, _ = O.weight_update(w, g, mu, mode, words)
+        wt_dev = torch.empty((C, R, S, K), dtype=torch.int8, device=DEV)
+        w_dev, g_dev = cu(w), cu(g)
+        ops.update(w_dev, g_dev, ops.absmax(g_dev), mu, mode, ops.seed_tensor(21, DEV), 2, wt=wt_dev)
+        assert_same(w_dev, want_w, f"updated weights mx={mx}")
+        assert_same(wt_dev, O.flip_transpose(want_w), "refreshed flipped/transposed filters")
+
+
+# ----------------------------------------------------------------------------- memory-bound layers
+@pytest.mark.parametrize("shape", [(4, 32, 32, 128), (3, 8, 8, 16), (2, 6, 10, 5), (1, 2, 2, 512)])
+def test_maxpool_relu(shape):
+    rng = np.random.default_rng(sum(shape))
+    x = np.maximum(rnd8(rng, shape, -128, 128), -20 if shape[3] == 5 else 0).astype(np.int8)  # many ties
+    y = ops.maxpool_fwd(cu(x))
+    assert_same(y, O.maxpool_fwd(x), "maxpool fwd")
+    dy = rnd8(rng, y.shape)
+    assert_same(ops.maxpool_bwd(cu(x), cu(dy)), O.maxpool_bwd(x, dy), "maxpool bwd")
+    x2 = rnd8(rng, shape, -128, 128)
+    assert_same(ops.relu_fwd(cu(x2)), O.relu_fwd(x2), "relu fwd")
+    e = rnd8(rng, shape)
+    assert_same(ops.relu_bwd(cu(x2), cu(e)), O.relu_bwd(x2, e), "relu bwd")
+
+
+def test_maxpool_generic_window():
+    rng = np.random.default_rng(3)
+    x = rnd8(rng, (2, 9, 9, 4), -5, 6)
+    assert_same(ops.maxpool_fwd(cu(x), 3, 2), O.maxpool_fwd(x, 3, 2), "maxpool 3/2 fwd")
+    dy = rnd8(rng, (2, 4, 4, 4), -30, 31)
+    assert_same(ops.maxpool_bwd(cu(x), cu(dy), 3, 2), O.maxpool_bwd(x, dy, 3, 2), "maxpool 3/2 bwd")
+
+
+def test_dropout():
+    rng = np.random.default_rng(8)
+    x = rnd8(rng, (16, 8192))
+    mask = O.dropout_mask(1234, 0xFFFE, 8192)
+    assert_same(ops.dropout(cu(x), ops.seed_tensor(1234, DEV), 0xFFFE), x * mask, "dropout")
+
+
+def test_loss_golden_and_oracle(golden_dir):
+    import os
+    g = np.load(os.path.join(golden_dir, "layers.npz"))
+    for k in range(6):
+        out, e, tgt = g[f"loss{k}_out"], int(g[f"loss{k}_exp"]), g[f"loss{k}_tgt"]
+        err = ops.loss_err(cu(out), torch.tensor(e, dtype=torch.int32, device=DEV), cu(tgt.astype(np.int64)),
+                           ops.seed_tensor(5, DEV))
+        assert_same(err, g[f"loss{k}_err"], f"loss vs reference golden {k}")
+    rng = np.random.default_rng(77)
+    for e in range(-12, 6):
+        B = 128
+        out = rnd8(rng, (B, 10), -127 // (1 + (e % 3) * 5), 128 // (1 + (e % 3) * 5))
+        tgt = rng.integers(0, 10, size=B)
+        words = philox.random_u32_tensor(40 + e, 0xFFFF, (B, 10), offset=30)
+        want, _ = O.ti_loss(out, e, tgt, words)
+        err = ops.loss_err(cu(out), torch.tensor(e, dtype=torch.int32, device=DEV), cu(tgt.astype(np.int64)),
+                           ops.seed_tensor(40 + e, DEV), sample_offset=3)
+        assert_same(err, want, f"loss exp={e}")
+
+
+def test_quantize_input():
+    from tests.golden.make_golden import synth_images
+    rng = np.random.default_rng(11)
+    for scale in (1.0, 0.3, 4.0, 2.0 / 2.6402):
+        x = (synth_images(rng, 8) * np.float32(scale)).astype(np.float32)
+        want8, want_e = O.float_to_int8(x)
+        x8, e = ops.quantize_input(cu(x))
+        assert_same(x8, np.ascontiguousarray(want8.transpose(0, 2, 3, 1)), "input quantisation")
+        assert int(e.item()) == want_e
