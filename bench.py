@@ -1,0 +1,359 @@
+"""Benchmark of the int8 training step (NITI VGG-small-7, synthetic 32x32 data).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W]            # this library on N B200s
+    python bench.py --impl reference [--gpus N] [--steps K] ...    # the reference's integer path on host cores
+
+One "step" = one integer training step (forward, integer loss, error back-propagation, weight
+gradients, integer SGD update) over one synthetic batch.  Weak scaling: every GPU trains its own
+shard of 128 images; the int32 weight gradients are summed with one NCCL all-reduce per step.
+Prints ONE JSON line (rank 0).  Fields:
+  value      images/s with the batch already resident in HBM (CUDA events, max over ranks)
+  e2e        images/s through Trainer.step with pinned host buffers in and the logits read back
+  roofline   the tensor-core contraction kernel (conv forward / error-backward), timed per launch
+             with CUDA events in an eager step: algorithmic int8 ops / time vs 2x the measured bf16 peak
+  cpu_baseline  the oracle's restatement of the reference's integer path on the host cores (rank 0, N=1)
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+VGG7 = [128, 128, "M", 256, 256, "M", 512, 512, "M"]
+PER_GPU_BATCH = 128
+METRIC = "int8 VGG-small-7 training throughput"
+UNIT = "images/s"
+
+
+def synth_batch(rng, B):
+    mean = np.array([0.49139968, 0.48215827, 0.44653124], dtype=np.float32)
+    std = np.array([0.24703233, 0.24348505, 0.26158768], dtype=np.float32)
+    u8 = rng.integers(0, 256, size=(B, 3, 32, 32), dtype=np.uint8)
+    x = (u8.astype(np.float32) / np.float32(255.0) - mean[None, :, None, None]) / std[None, :, None, None]
+    return x.astype(np.float32), rng.integers(0, 10, size=B).astype(np.int64)
+
+
+def vgg_shapes(cfg):
+    shapes, cin = [], 3
+    for c in cfg:
+        if c != "M":
+            shapes.append((c, 3, 3, cin))
+            cin = c
+    shapes.append((10, cin * (32 // 2 ** cfg.count("M")) ** 2))
+    return shapes
+
+
+def xavier_exp(shape):
+    if len(shape) == 4:
+        K, R, S, C = shape
+        fan_in, fan_out = C * R * S, K * R * S
+    else:
+        fan_out, fan_in = shape
+    return int(np.ceil(np.log2(np.sqrt(6.0 / (fan_in + fan_out))))) - 7
+
+
+def step_ops_per_image(cfg):
+    """Algorithmic int8 ops (2 per MAC) of one training step per image: forward + error-backward
+    (not for the first layer) + weight gradient of every convolution, and the three FC products."""
+    ops, cin, hw = 0, 3, 32
+    first = True
+    for c in cfg:
+        if c == "M":
+            hw //= 2
+            continue
+        mac = hw * hw * c * 9 * cin
+        ops += 2 * mac * (2 if first else 3)
+        first = False
+        cin = c
+    ops += 2 * (cin * hw * hw * 10) * 3
+    return ops
+
+
+# ------------------------------------------------------------------------------------------------
+# clocks
+# ------------------------------------------------------------------------------------------------
+class ClockSampler:
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.samples, self.proc, self.idx = [], None, gpu_index
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.idx), f"--query-gpu={self.FIELDS}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.samples.append(line.strip())
+
+    def stop(self):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+
+    def summary(self):
+        sm, mx, reasons = [], 0, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for s in self.samples:
+            f = [t.strip() for t in s.split(",")]
+            if len(f) < 7:
+                continue
+            try:
+                sm.append(float(f[0]))
+                mx = max(mx, float(f[1]))
+            except ValueError:
+                continue
+            for n, v in zip(names, f[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        busy = [v for v in sm if v >= 0.5 * max(sm)]
+        return {"sm_mhz": statistics.median(busy), "sm_max_mhz": mx, "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# ------------------------------------------------------------------------------------------------
+# CPU restatement of the reference (the oracle), timed on the host cores
+# ------------------------------------------------------------------------------------------------
+def cpu_oracle_images_per_s(batch, steps, warmup, seed=1234):
+    import torch
+    from oracle import niti_oracle as O
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    O.set_backend("int_mm")  # exact int8 x int8 -> int32 products on the CPU's VNNI/AMX units
+    rng = np.random.default_rng(seed)
+    shapes = vgg_shapes(VGG7)
+    weights = [rng.integers(-127, 128, size=s).astype(np.int8) for s in shapes]
+    net = O.Net(VGG7, weights, [xavier_exp(s) for s in shapes], dropout=True, mu=5, seed=seed)
+    times = []
+    for i in range(warmup + steps):
+        x, t = synth_batch(rng, batch)
+        t0 = time.perf_counter()
+        x8, xe = O.float_to_int8(x)
+        net.forward(np.ascontiguousarray(x8.transpose(0, 2, 3, 1)), xe, step=i)
+        net.backward(t, step=i)
+        dt = time.perf_counter() - t0
+        if i >= warmup:
+            times.append(dt)
+    O.set_backend("int64")
+    total = sum(times)
+    return batch * len(times) / total, cores, total / len(times)
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    batch = 16
+    v, cores, sec = cpu_oracle_images_per_s(batch, args.steps, args.warmup)
+    sample = (f"{args.steps} training steps of VGG-small-7 on batches of {batch} synthetic images (of the {PER_GPU_BATCH}-image "
+              f"workload), oracle port of ti_torch/ti_loss/ti_net with torch._int_mm contractions, {cores} threads")
+    line = {"impl": "reference", "metric": METRIC, "value": v, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": sec * 1e3, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "int8", "data": "synthetic",
+            "config": {"workload": "VGG-small-7 integer training step, 3x32x32 inputs, 10 classes", "batch_per_step": batch},
+            "cpu_baseline": {"value": v, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
+            "e2e": {"value": v, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line), flush=True)
+
+
+# ------------------------------------------------------------------------------------------------
+# this library
+# ------------------------------------------------------------------------------------------------
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return p.get("hbm_gbs", 6650.0), p.get("bf16_tflops_sustained", 1400.0), p.get("bf16_tflops", 1590.0), "measured"
+    return 6650.0, 1400.0, 1590.0, "fallback"
+
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+    from niti_b200 import ops, ti_torch, ti_vgg
+    from niti_b200.trainer import Trainer
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        if world == 1 and args.gpus > 1:
+            raise SystemExit("--gpus N>1 must be launched with torch.distributed.run --nproc-per-node N")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(dev)
+
+    def max_over_ranks(v):
+        if world == 1:
+            return v
+        t = torch.tensor([v], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    B = PER_GPU_BATCH
+    rng = np.random.default_rng(1235)
+    shapes = vgg_shapes(VGG7)
+    weights = [rng.integers(-127, 128, size=s).astype(np.int8) for s in shapes]
+    ti_torch.GRAD_BITWIDTH, ti_torch.TRAINING = 5, True
+    model = ti_vgg.TiVGG_cifar(7, dropout=True, fuse_relu=True)
+    for l, w, s in zip(model.weighted_layers(), weights, shapes):
+        l.weight = torch.from_numpy(w).to(dev)
+        l.weight_exp = ti_torch.exp_tensor(xavier_exp(s), dev)
+        if hasattr(l, "refresh_weight_t"):
+            l.refresh_weight_t()
+    trainer = Trainer(model, B, dev, rank=rank, world=world, use_graph=True, seed=1235)
+    data_rng = np.random.default_rng(5000 + rank)
+    batches = []
+    for _ in range(4):
+        x, t = synth_batch(data_rng, B)
+        batches.append((torch.from_numpy(x).pin_memory(), torch.from_numpy(t).pin_memory()))
+
+    # --- per-kernel timing of one eager step (before graph capture): roofline of the dominant kernel
+    trainer.step(*batches[0])
+    trainer.sync()
+    launches0 = ops.LAUNCHES
+    ops.PROFILE = []
+    trainer.step(*batches[1])
+    trainer.sync()
+    prof, ops.PROFILE = ops.PROFILE, None
+    launches_per_step = ops.LAUNCHES - launches0
+    per_kernel = {}
+    for name, aops, abytes, a, b in prof:
+        d = per_kernel.setdefault(name, [0, 0.0, 0, 0])
+        d[0] += 1
+        d[1] += a.elapsed_time(b) * 1e-3
+        d[2] += aops
+        d[3] += abytes
+
+    # --- warm-up (captures the CUDA graphs), then the two timed regions
+    for i in range(max(args.warmup, 3)):
+        trainer.step(*batches[i % 4])
+    trainer.sync()
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)  # > 126 MB L2
+
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    # (1) inputs resident in HBM, L2 flushed between steps, per-step CUDA events
+    trainer.x.copy_(batches[0][0])
+    trainer.t.copy_(batches[0][1])
+    barrier()
+    evs = []
+    for i in range(args.steps):
+        flush.zero_()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        trainer.run_device_step()
+        b.record()
+        evs.append((a, b))
+    barrier()
+    dev_s = max_over_ranks(sum(a.elapsed_time(b) for a, b in evs) * 1e-3)
+    # (2) end to end through Trainer.step: pinned host batch in, logits out, every step
+    barrier()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0 = time.perf_counter()
+    a.record()
+    for i in range(args.steps):
+        out_h, exp_h = trainer.step(*batches[i % 4])
+        torch.cuda.current_stream().synchronize()  # the caller reads the logits of every step
+        _ = int(out_h[0, 0])
+    b.record()
+    barrier()
+    e2e_s = max_over_ranks(max(a.elapsed_time(b) * 1e-3, time.perf_counter() - t0 if world == 1 else 0.0))
+    if rank == 0:
+        sampler.stop()
+    trainer.sync()
+    checksum = trainer.replica_checksum()
+    if world > 1:
+        cs = torch.tensor([checksum], dtype=torch.int64, device=dev)
+        lo, hi = cs.clone(), cs.clone()
+        dist.all_reduce(lo, op=dist.ReduceOp.MIN)
+        dist.all_reduce(hi, op=dist.ReduceOp.MAX)
+        replicas_equal = bool(lo.item() == hi.item())
+    else:
+        replicas_equal = True
+
+    if rank == 0:
+        hbm, bf16_sus, bf16_burst, src = measured_peaks()
+        images = B * world * args.steps
+        dom = per_kernel.get("niti_conv_fprop_i8", [0, 0, 0, 0]), per_kernel.get("niti_conv_dgrad_i8", [0, 0, 0, 0])
+        # the tensor-core launches: every conv forward except the 3-channel first layer, and every error-backward
+        first = next(p for p in prof if p[0] == "niti_conv_fprop_i8")
+        tc_time = dom[0][1] + dom[1][1] - first[3].elapsed_time(first[4]) * 1e-3
+        tc_ops = dom[0][2] + dom[1][2] - first[1]
+        tc_launches = dom[0][0] + dom[1][0] - 1
+        peak_tops = 2.0 * bf16_sus
+        achieved = tc_ops / tc_time / 1e12 if tc_time > 0 else 0.0
+        line = {
+            "metric": METRIC, "value": images / dev_s, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": dev_s / args.steps * 1e3, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "int8", "data": "synthetic",
+            "config": {"workload": "VGG-small-7 integer training step (conv 128-128-P-256-256-P-512-512-P, FC 8192->10), "
+                                   "3x32x32 synthetic images, 10 classes, dropout on, grad bit-width 5",
+                       "per_gpu_batch": B, "global_batch": B * world, "parallelism": f"dp{world}",
+                       "l2": "256 MB buffer written between timed steps (L2 flush); per-step CUDA events",
+                       "graph": "step replayed from CUDA graphs", "replicas_bit_identical": replicas_equal,
+                       "effective_int8_tops": step_ops_per_image(VGG7) * images / dev_s / 1e12},
+            "e2e": {"value": images / e2e_s, "unit": UNIT, "h2d_bytes_per_step": trainer.h2d_bytes,
+                    "d2h_bytes_per_step": trainer.d2h_bytes, "ms_per_step": e2e_s / args.steps * 1e3},
+            "gpu_launches": launches_per_step * args.steps,
+            "roofline": {"bound": "tensor", "kernel": "umma_gemm_kernel (conv forward + error-backward, tcgen05 kind::i8)",
+                         "achieved": achieved, "peak": peak_tops, "unit": "TOP/s", "frac": achieved / peak_tops,
+                         "traffic": None, "launches_timed": tc_launches, "avg_launch_us": tc_time / max(tc_launches, 1) * 1e6,
+                         "peak_source": f"2 x bf16_tflops_sustained ({src}); dense int8 rate is twice bf16 on this part"},
+            "kernels_eager_step": {k: {"launches": v[0], "ms": v[1] * 1e3,
+                                       "tops": (v[2] / v[1] / 1e12 if v[1] > 0 and v[2] else None),
+                                       "gbs": (v[3] / v[1] / 1e9 if v[1] > 0 else None)} for k, v in per_kernel.items()},
+            "clocks": sampler.summary(),
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            v, cores, sec = cpu_oracle_images_per_s(16, 3, 1)
+            line["cpu_baseline"] = {"value": v, "unit": UNIT, "cores": cores, "kind": "port",
+                                    "sample": f"3 training steps of VGG-small-7 on 16 of the {B} images per step "
+                                              f"({sec:.2f} s per step), oracle port with torch._int_mm, {cores} threads"}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

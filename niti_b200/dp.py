@@ -1,0 +1,54 @@
+"""Data-parallel plumbing for the integer training step: batch sharding and the flat int32
+gradient bucket that is summed across ranks.
+
+The only exchange of a data-parallel NITI step is the sum of the int32 weight-gradient
+accumulators (integer addition is associative, so the result does not depend on the reduction
+order); every rank then applies the identical integer update and replicas stay bit-identical.
+Nothing in this module touches CUDA: it works on whatever device its tensors live on, which is
+how the multi-rank logic is tested with the gloo backend on CPU.
+"""
+import torch
+import torch.distributed as dist
+
+
+def shard_range(global_batch, rank, world):
+    """Contiguous shard [lo, hi) of the batch owned by ``rank``; sizes differ by at most one."""
+    base, rem = divmod(global_batch, world)
+    lo = rank * base + min(rank, rem)
+    return lo, lo + base + (1 if rank < rem else 0)
+
+
+class GradBucket:
+    """One flat int32 buffer with a 16-byte-aligned view per weight tensor."""
+
+    def __init__(self, shapes, device):
+        self.shapes = [tuple(s) for s in shapes]
+        self.offsets = []
+        off = 0
+        for s in self.shapes:
+            self.offsets.append(off)
+            n = 1
+            for d in s:
+                n *= d
+            off += (n + 3) // 4 * 4
+        self.flat = torch.zeros(off, dtype=torch.int32, device=device)
+        self.views = []
+        for s, o in zip(self.shapes, self.offsets):
+            n = 1
+            for d in s:
+                n *= d
+            self.views.append(self.flat[o:o + n].view(s))
+
+    def nbytes(self):
+        return self.flat.numel() * 4
+
+    def allreduce_(self, group=None):
+        """Sum over ranks, in place (NCCL over NVLink on GPUs, gloo on CPU)."""
+        if dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1:
+            dist.all_reduce(self.flat, op=dist.ReduceOp.SUM, group=group)
+        return self.flat
+
+    def checksum(self):
+        """Order-independent digest used to assert that replicas hold identical values."""
+        f = self.flat.to(torch.int64)
+        return int(f.sum().item()), int((f * (torch.arange(f.numel(), device=f.device) % 8191 + 1)).sum().item())

@@ -15,6 +15,26 @@ CALC_ACT, CALC_ERR, CALC_GRAD = 0, 1, 2
 _status = {}
 _scratch = {}
 
+# Launch accounting.  LAUNCHES counts kernels of this library enqueued through this module.
+# PROFILE, when set to a list (eager execution only, never under graph capture), makes every
+# call record (name, algorithmic ops, algorithmic bytes, start event, end event) on the
+# launching stream.
+LAUNCHES = 0
+PROFILE = None
+
+
+def _call(name, kernels, algo_ops, algo_bytes, fn, *args):
+    global LAUNCHES
+    LAUNCHES += kernels
+    if PROFILE is None:
+        check(fn(*args), name)
+        return
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    check(fn(*args), name)
+    b.record()
+    PROFILE.append((name, algo_ops, algo_bytes, a, b))
+
 
 def _st():
     return torch.cuda.current_stream().cuda_stream
@@ -69,8 +89,9 @@ def conv_fprop_acc(x, w, pad=1, stride=1):
     P, Q = H + 2 * pad - R + 1, W + 2 * pad - S + 1
     y32 = torch.empty((N, P, Q, K), dtype=torch.int32, device=x.device)
     mx = torch.empty(1, dtype=torch.int32, device=x.device)
-    check(lib.niti_conv_fprop_i8(_p(x), _p(w), _p(y32), _p(mx), N, H, W, C, K, R, S, pad, stride,
-                                 _p(status_word(x.device)), _st()), "niti_conv_fprop_i8")
+    _call("niti_conv_fprop_i8", 1, 2 * N * P * Q * K * R * S * C, x.numel() + w.numel() + 4 * y32.numel(),
+          lib.niti_conv_fprop_i8, _p(x), _p(w), _p(y32), _p(mx), N, H, W, C, K, R, S, pad, stride,
+          _p(status_word(x.device)), _st())
     return y32, mx
 
 
@@ -78,7 +99,7 @@ def flip_transpose(w):
     _need_cuda(w)
     K, R, S, C = w.shape
     wt = torch.empty((C, R, S, K), dtype=torch.int8, device=w.device)
-    check(lib.niti_weight_flip_transpose_i8(_p(w), _p(wt), K, R, S, C, _st()), "niti_weight_flip_transpose_i8")
+    _call("niti_weight_flip_transpose_i8", 1, 0, 2 * w.numel(), lib.niti_weight_flip_transpose_i8, _p(w), _p(wt), K, R, S, C, _st())
     return wt
 
 
@@ -90,8 +111,9 @@ def conv_dgrad_acc(err, wt, pad=1):
     assert K == K2
     e32 = torch.empty((N, H, W, C), dtype=torch.int32, device=err.device)
     mx = torch.empty(1, dtype=torch.int32, device=err.device)
-    check(lib.niti_conv_dgrad_i8(_p(err), _p(wt), _p(e32), _p(mx), N, H, W, C, K, R, S, pad,
-                                 _p(status_word(err.device)), _st()), "niti_conv_dgrad_i8")
+    _call("niti_conv_dgrad_i8", 1, 2 * N * H * W * K * R * S * C, err.numel() + wt.numel() + 4 * e32.numel(),
+          lib.niti_conv_dgrad_i8, _p(err), _p(wt), _p(e32), _p(mx), N, H, W, C, K, R, S, pad,
+          _p(status_word(err.device)), _st())
     return e32, mx
 
 
@@ -103,8 +125,9 @@ def conv_wgrad_acc(x, err, R=3, S=3, pad=1, out=None):
     mx = torch.empty(1, dtype=torch.int32, device=x.device)
     nbytes = lib.niti_conv_wgrad_scratch_bytes(N, H, W, C, K, R, S)
     sc = scratch(x.device, nbytes)
-    check(lib.niti_conv_wgrad_i8(_p(x), _p(err), _p(g32), _p(mx), _p(sc), sc.numel(), N, H, W, C, K, R, S, pad,
-                                 _p(status_word(x.device)), _st()), "niti_conv_wgrad_i8")
+    _call("niti_conv_wgrad_i8", 2, 2 * N * H * W * K * R * S * C, x.numel() + err.numel() + 4 * g32.numel(),
+          lib.niti_conv_wgrad_i8, _p(x), _p(err), _p(g32), _p(mx), _p(sc), sc.numel(), N, H, W, C, K, R, S, pad,
+          _p(status_word(x.device)), _st())
     return g32, mx
 
 
@@ -116,8 +139,9 @@ def gemm_acc(a, b, trans_a=False, trans_b=False, out=None):
     assert (b.shape[1] if trans_b else b.shape[0]) == K
     c32 = out if out is not None else torch.empty((M, N), dtype=torch.int32, device=a.device)
     mx = torch.empty(1, dtype=torch.int32, device=a.device)
-    check(lib.niti_gemm_i8(_p(a), _p(b), _p(c32), _p(mx), M, N, K, int(trans_a), int(trans_b),
-                           _p(status_word(a.device)), _st()), "niti_gemm_i8")
+    _call("niti_gemm_i8", 1, 2 * M * N * K, a.numel() + b.numel() + 4 * c32.numel(),
+          lib.niti_gemm_i8, _p(a), _p(b), _p(c32), _p(mx), M, N, K, int(trans_a), int(trans_b),
+          _p(status_word(a.device)), _st())
     return c32, mx
 
 
@@ -129,16 +153,16 @@ def requant(acc, maxabs, kind, target_bits, mode=ROUND_NEAREST, seed=None, rng_s
     out = torch.empty(acc.shape, dtype=torch.int8, device=acc.device)
     exp_out = torch.empty((), dtype=torch.int32, device=acc.device)
     shift_out = torch.empty((), dtype=torch.int32, device=acc.device) if want_shift else None
-    check(lib.niti_requant_i8(_p(acc), _p(out), _p(maxabs), acc.numel(), kind, target_bits, mode, _p(seed), rng_stream,
-                              rng_offset, int(relu), _p(exp_a), _p(exp_b), _p(exp_out), _p(shift_out), _st()),
-          "niti_requant_i8")
+    _call("niti_requant_i8", 1, 0, 5 * acc.numel(),
+          lib.niti_requant_i8, _p(acc), _p(out), _p(maxabs), acc.numel(), kind, target_bits, mode, _p(seed), rng_stream,
+          rng_offset, int(relu), _p(exp_a), _p(exp_b), _p(exp_out), _p(shift_out), _st())
     return out, exp_out, shift_out
 
 
 def absmax(acc):
     _need_cuda(acc)
     mx = torch.empty(1, dtype=torch.int32, device=acc.device)
-    check(lib.niti_absmax_i32(_p(acc), acc.numel(), _p(mx), _st()), "niti_absmax_i32")
+    _call("niti_absmax_i32", 1, 0, 4 * acc.numel(), lib.niti_absmax_i32, _p(acc), acc.numel(), _p(mx), _st())
     return mx
 
 
@@ -147,7 +171,7 @@ def maxpool_fwd(x, k=2, stride=2):
     _need_cuda(x)
     N, H, W, C = x.shape
     y = torch.empty((N, (H - k) // stride + 1, (W - k) // stride + 1, C), dtype=torch.int8, device=x.device)
-    check(lib.niti_maxpool_fwd_i8(_p(x), _p(y), N, H, W, C, k, stride, _st()), "niti_maxpool_fwd_i8")
+    _call("niti_maxpool_fwd_i8", 1, 0, x.numel() + y.numel(), lib.niti_maxpool_fwd_i8, _p(x), _p(y), N, H, W, C, k, stride, _st())
     return y
 
 
@@ -155,29 +179,29 @@ def maxpool_bwd(x, dy, k=2, stride=2):
     _need_cuda(x, dy)
     N, H, W, C = x.shape
     dx = torch.empty_like(x)
-    check(lib.niti_maxpool_bwd_i8(_p(x), _p(dy), _p(dx), N, H, W, C, k, stride, _st()), "niti_maxpool_bwd_i8")
+    _call("niti_maxpool_bwd_i8", 1, 0, 2 * x.numel() + dy.numel(), lib.niti_maxpool_bwd_i8, _p(x), _p(dy), _p(dx), N, H, W, C, k, stride, _st())
     return dx
 
 
 def relu_fwd(x):
     _need_cuda(x)
     y = torch.empty_like(x)
-    check(lib.niti_relu_fwd_i8(_p(x), _p(y), x.numel(), _st()), "niti_relu_fwd_i8")
+    _call("niti_relu_fwd_i8", 1, 0, 2 * x.numel(), lib.niti_relu_fwd_i8, _p(x), _p(y), x.numel(), _st())
     return y
 
 
 def relu_bwd(act, err):
     _need_cuda(act, err)
     out = torch.empty_like(err)
-    check(lib.niti_relu_bwd_i8(_p(act), _p(err), _p(out), err.numel(), _st()), "niti_relu_bwd_i8")
+    _call("niti_relu_bwd_i8", 1, 0, 3 * err.numel(), lib.niti_relu_bwd_i8, _p(act), _p(err), _p(out), err.numel(), _st())
     return out
 
 
 def dropout(x, seed, rng_stream):
     _need_cuda(x, seed)
     y = torch.empty_like(x)
-    check(lib.niti_dropout_i8(_p(x), _p(y), x.shape[0], x.numel() // x.shape[0], _p(seed), rng_stream, _st()),
-          "niti_dropout_i8")
+    _call("niti_dropout_i8", 1, 0, 2 * x.numel(), lib.niti_dropout_i8, _p(x), _p(y), x.shape[0], x.numel() // x.shape[0],
+          _p(seed), rng_stream, _st())
     return y
 
 
@@ -185,8 +209,8 @@ def loss_err(out8, out_exp, target, seed, rng_stream=0xFFFF, sample_offset=0):
     _need_cuda(out8, out_exp, target, seed)
     assert target.dtype == torch.int64 and out_exp.dtype == torch.int32
     err = torch.empty_like(out8)
-    check(lib.niti_loss_i8(_p(out8), _p(out_exp), _p(target), _p(err), out8.shape[0], out8.shape[1], _p(seed),
-                           rng_stream, sample_offset, _st()), "niti_loss_i8")
+    _call("niti_loss_i8", 1, 0, 2 * out8.numel(), lib.niti_loss_i8, _p(out8), _p(out_exp), _p(target), _p(err),
+          out8.shape[0], out8.shape[1], _p(seed), rng_stream, sample_offset, _st())
     return err
 
 
@@ -197,8 +221,8 @@ def update(w, g32, maxabs, mu, mode=ROUND_PSEUDO_STOCHASTIC, seed=None, rng_stre
         K, R, S, C = w.shape
     else:
         K = R = S = C = 0
-    check(lib.niti_update_i8(_p(w), _p(g32), _p(maxabs), w.numel(), mu, mode, _p(seed), rng_stream, _p(wt), K, R, S, C,
-                             _st()), "niti_update_i8")
+    _call("niti_update_i8", 1, 0, (7 if wt is not None else 6) * w.numel(), lib.niti_update_i8, _p(w), _p(g32), _p(maxabs),
+          w.numel(), mu, mode, _p(seed), rng_stream, _p(wt), K, R, S, C, _st())
 
 
 def quantize_input(x):
@@ -209,5 +233,5 @@ def quantize_input(x):
     x8 = torch.empty((N, H, W, C), dtype=torch.int8, device=x.device)
     e = torch.empty((), dtype=torch.int32, device=x.device)
     tmp = torch.empty(1, dtype=torch.int32, device=x.device)
-    check(lib.niti_quantize_input_f32(_p(x), _p(x8), _p(e), _p(tmp), N, C, H, W, _st()), "niti_quantize_input_f32")
+    _call("niti_quantize_input_f32", 2, 0, 9 * x.numel(), lib.niti_quantize_input_f32, _p(x), _p(x8), _p(e), _p(tmp), N, C, H, W, _st())
     return x8, e

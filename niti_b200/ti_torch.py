@@ -1,0 +1,365 @@
+"""Drop-in for the reference's ``ti_torch`` module (integer layers of NITI) on the B200 kernels.
+
+Same public names, argument meaning and ``(int8 tensor, exponent)`` tuple convention as the
+reference's ti_torch.py; file:line citations below are to that file.  What differs, on purpose:
+
+* exponents and shift amounts are 0-dim ``int32`` CUDA tensors (the reference mixes Python ints
+  and float tensors and reads the bit-width back to the host twice per layer, :366-377); nothing
+  here synchronises, so a whole training step can be captured in a CUDA graph;
+* the four extension modules (``cutlassconv_cuda``, ``int8mm_cuda``, ``int8pool_cuda``,
+  ``int8conv_cuda``) are replaced by one C-ABI library (``niti_b200.ops``); there is no CPU or
+  PyTorch fallback: without the built library importing this module raises;
+* ``//`` follows the torch release the reference was written for (truncation toward zero);
+* accumulators are exact int32 (the reference's CUTLASS epilogue rounds through fp32);
+* random bits (StoShift, TiDropout) come from a counter-based generator keyed by ``RNG_SEED``
+  (a device word, advanced once per training step), a per-layer stream id and the GLOBAL element
+  index, so a batch shard draws the bits of its own samples.
+"""
+import torch
+from torch.nn.modules import Module
+
+from . import ops
+
+
+class UpdateWeight(Module):
+    """Parameter update shared by TiConv2d and TiLinear (:11-21)."""
+
+    layer_id = 0          # index among the weighted layers; selects the random-bit streams
+    grad_buffer = None    # optional preallocated int32 view the weight gradient is written into
+    defer_update = False  # data-parallel trainers sum gradients across ranks before updating
+
+    def weight_update(self):
+        """vanilla SGD on int8 weights: w <- clamp(w - grad_calc(grad_int32acc, GRAD_BITWIDTH))"""
+        ops.update(self.weight, self.grad_int32acc, self.grad_maxabs, GRAD_BITWIDTH, _mode(GRAD_ROUND_METHOD),
+                   RNG_SEED(self.weight.device), 16 * self.layer_id + 2, wt=getattr(self, "weight_t", None))
+
+
+def _fake_max(shift):
+    # a max|x| whose bit-width is exactly shift + BITWIDTH, so the kernel picks `shift`
+    return 1 << (shift + BITWIDTH)
+
+
+def _shift_with(mode, input, shift, stream=0):
+    if shift <= 0:
+        raise ValueError("shift must be positive")
+    mx = torch.full((1,), _fake_max(shift), dtype=torch.int32, device=input.device)
+    out, _, _ = ops.requant(input.contiguous(), mx, ops.CALC_ACT, BITWIDTH, mode, RNG_SEED(input.device), stream)
+    return out
+
+
+def RoundShift(input, shift):
+    """Shift right with round-half-away-from-zero, clamp to +-127 (:23-31)."""
+    return _shift_with(ops.ROUND_NEAREST, input, shift)
+
+
+def StoShift(input, shift):
+    """Shift right with stochastic rounding (:33-46); random bits from the keyed generator."""
+    return _shift_with(ops.ROUND_STOCHASTIC, input, shift)
+
+
+def PstoShift(input, shift):
+    """Shift right with pseudo-stochastic rounding: the dropped low bits are the random number (:48-69)."""
+    return _shift_with(ops.ROUND_PSEUDO_STOCHASTIC, input, shift)
+
+
+def _mode(method):
+    return {RoundShift: ops.ROUND_NEAREST, StoShift: ops.ROUND_STOCHASTIC, PstoShift: ops.ROUND_PSEUDO_STOCHASTIC}[method]
+
+
+def int8_clip(input, clip_val=127):
+    return torch.clamp(input, -clip_val, clip_val).type(torch.int8)
+
+
+def Int8Tensor(val):
+    return torch.tensor(val, dtype=torch.int8).to(GPU)
+
+
+def Int8zeros(size):
+    return torch.zeros(size=size, dtype=torch.int8, device=GPU)
+
+
+def exp_tensor(e, device=None):
+    """Exponent as a 0-dim int32 tensor on the device (accepts ints, floats, tensors)."""
+    device = device or GPU
+    if isinstance(e, torch.Tensor):
+        return e.to(device=device, dtype=torch.int32).reshape(())
+    return torch.full((), int(e), dtype=torch.int32, device=device)  # a fill kernel: legal under graph capture
+
+
+def UniformWeights(size):
+    """xavier-uniform float init on the host, then weight_quant (:77-85)."""
+    if len(size) == 4:
+        temp = torch.zeros(size).permute(0, 3, 1, 2).contiguous()
+        torch.nn.init.xavier_uniform_(temp)
+        return weight_quant(temp.permute(0, 2, 3, 1).contiguous())
+    temp = torch.zeros(size)
+    torch.nn.init.xavier_uniform_(temp)
+    return weight_quant(temp)
+
+
+def NormalWeight(size):
+    if len(size) == 4:
+        temp = torch.zeros(size).permute(0, 3, 1, 2).contiguous()
+        torch.nn.init.xavier_normal_(temp)
+        return weight_quant(temp.permute(0, 2, 3, 1).contiguous())
+    temp = torch.zeros(size)
+    torch.nn.init.xavier_normal_(temp)
+    return weight_quant(temp)
+
+
+def weight_quant(input):
+    """float weights -> (int8 on the device, exponent) (:334-339); setup only, runs on the host."""
+    input_range = torch.max(torch.abs(input))
+    input_bitwidth = torch.ceil(torch.log2(input_range))
+    act_exp = input_bitwidth - 7
+    round_val = torch.round(input / input_range * (2 ** 7 - 1)).type(torch.int8).to(GPU)
+    return round_val, exp_tensor(act_exp)
+
+
+def _calc(int32_acc, kind, target_bits, method, stream, exp_a=None, exp_b=None, maxabs=None, relu=False, offset=0):
+    acc = int32_acc.contiguous()
+    if maxabs is None:
+        maxabs = ops.absmax(acc)
+    return ops.requant(acc, maxabs, kind, target_bits, _mode(method), RNG_SEED(acc.device), stream, offset,
+                       relu=relu, exp_a=exp_a, exp_b=exp_b, want_shift=True)
+
+
+def act_calc(int32_acc, exp_in, maxabs=None, rng_stream=0, relu=False, rng_offset=0, exp_b=None):
+    """int32 accumulators -> (int8, exp_out) by the tensor's bit-width (:103-117)."""
+    out, exp_out, _ = _calc(int32_acc, ops.CALC_ACT, BITWIDTH, ACT_ROUND_METHOD, rng_stream,
+                            exp_tensor(exp_in, int32_acc.device), exp_b, maxabs, relu, rng_offset)
+    return out, exp_out
+
+
+def err_calc(int32_acc, maxabs=None, rng_stream=0, rng_offset=0):
+    """int32 accumulators -> (int8, shift) (:119-133)."""
+    out, _, shift = _calc(int32_acc, ops.CALC_ERR, BITWIDTH, ERROR_ROUND_METHOD, rng_stream, None, None, maxabs, False, rng_offset)
+    return out, shift
+
+
+def grad_calc(int32_acc, mu, maxabs=None, rng_stream=0):
+    """int32 gradient accumulators -> (int8, shift) with target bit-width mu (:135-147)."""
+    out, _, shift = _calc(int32_acc, ops.CALC_GRAD, mu, GRAD_ROUND_METHOD, rng_stream, None, None, maxabs)
+    return out, shift
+
+
+def roundoff4(size):
+    return (size + 3) // 4 * 4
+
+
+def int8mm(lhs, rhs):
+    """[m,k] int8 @ [k,n] int8 -> int32 [m,n] (:152-176); no padding to multiples of 4 is needed."""
+    return ops.gemm_acc(lhs.contiguous(), rhs.contiguous())[0]
+
+
+def conv2d_int8(input, weight, stride=1, padding=1):
+    """NHWC int8 conv -> int32 (:178-192); any channel count (the reference pads C to 16)."""
+    return ops.conv_fprop_acc(input.contiguous(), weight.contiguous(), padding, stride)[0]
+
+
+def conv2d_weight_int8(input, weight_size, grad_output, stride=1, padding=0, dilation=1):
+    """Weight gradient of a convolution -> int32 [K,R,S,C] (:194-233); exact integers, any batch size."""
+    if stride != 1 or dilation != 1:
+        raise RuntimeError("conv2d_weight_int8: only stride 1 / dilation 1 are implemented")
+    return ops.conv_wgrad_acc(input.contiguous(), grad_output.contiguous(), weight_size[1], weight_size[2], padding)[0]
+
+
+class TiLinear(UpdateWeight):
+    def __init__(self, in_features, out_features, last_layer=False):
+        super(TiLinear, self).__init__()
+        self.weight, self.weight_exp = WEIGHT_INIT_METHOD(torch.Size([out_features, in_features]))
+        self.last_layer = last_layer
+
+    def forward(self, input):
+        """(act int8 [B,in], exp) -> (act int8 [B,out], exp) (:241-253)"""
+        self.act_in = input
+        act_in, exp_in = input
+        acc, mx = ops.gemm_acc(act_in, self.weight, trans_b=True)
+        per = acc.shape[1]
+        return act_calc(acc, exp_in, mx, 16 * self.layer_id, rng_offset=SAMPLE_OFFSET * per, exp_b=self.weight_exp)
+
+    def backward(self, input):
+        """(err int8 [B,out], exp) -> (err int8 [B,in], exp); updates the weights (:255-266)"""
+        err_in, err_exp = input
+        act, self.act_in_exp = self.act_in
+        acc, mx = ops.gemm_acc(err_in, self.weight)
+        err_out, self.err_exp, _ = _calc(acc, ops.CALC_ERR, BITWIDTH, ERROR_ROUND_METHOD, 16 * self.layer_id + 1,
+                                         exp_tensor(err_exp, acc.device), self.weight_exp, mx, False,
+                                         SAMPLE_OFFSET * acc.shape[1])
+        self.grad_int32acc, self.grad_maxabs = ops.gemm_acc(err_in, act, trans_a=True, out=self.grad_buffer)
+        if not self.defer_update:
+            self.weight_update()
+        return err_out, self.err_exp
+
+
+class TiReLU(Module):
+    """Integer ReLU (:268-290).  ``fused=True`` marks a ReLU whose forward was already applied by
+    the preceding convolution's requantisation; backward is the same either way because
+    x > 0 exactly where max(x, 0) > 0."""
+
+    def __init__(self, fused=False):
+        super(TiReLU, self).__init__()
+        self.fused = fused
+
+    def forward(self, input):
+        act_in, exp_in = input
+        act_out = act_in if self.fused else ops.relu_fwd(act_in)
+        self.act_in = (act_out if self.fused else act_in, exp_in)
+        return act_out, exp_in
+
+    def backward(self, input):
+        err_in, err_exp = input
+        act, _ = self.act_in
+        return ops.relu_bwd(act, err_in.contiguous()), err_exp
+
+
+class TiMaxpool2d(Module):
+    """Integer max pooling (:292-316), int8 in both directions."""
+
+    def __init__(self, kernel_size, stride, padding=0):
+        super(TiMaxpool2d, self).__init__()
+        if padding != 0:
+            raise RuntimeError("TiMaxpool2d: padding is not implemented (the reference models use 0)")
+        self.kernel_size = kernel_size
+        self.stride = stride
+        self.padding = padding
+
+    def forward(self, input):
+        self.act_in, exp_in = input
+        self.act_out = ops.maxpool_fwd(self.act_in, self.kernel_size, self.stride)
+        return self.act_out, exp_in
+
+    def backward(self, input):
+        err_in, err_exp = input
+        return ops.maxpool_bwd(self.act_in, err_in.contiguous(), self.kernel_size, self.stride), err_exp
+
+
+class TiFlat(Module):
+    """Flatten everything but the batch dimension (:318-332)."""
+
+    def forward(self, input):
+        self.act_in = input
+        act_in, exp_in = input
+        return act_in.view(-1, act_in.nelement() // act_in.size(0)), exp_in
+
+    def backward(self, input):
+        err_in, err_exp = input
+        act, _ = self.act_in
+        return err_in.view_as(act), err_exp
+
+
+def TiFloatToInt8(input):
+    """float tensor -> (int8, exponent) with exponent = ceil(log2(max|x|)) - 7 (:341-356).
+    4-D inputs are taken as NCHW and returned NHWC (the permute of ti_net.py:19 is fused in)."""
+    x = input.to(GPU, dtype=torch.float32).contiguous()
+    if x.dim() == 4:
+        return ops.quantize_input(x)
+    q, e = ops.quantize_input(x.reshape(1, 1, 1, -1))
+    return q.reshape(x.shape), e
+
+
+def TiInt8ToFloat(input):
+    act_in, exp_in = input
+    return act_in.float() * (2 ** (exp_tensor(exp_in, act_in.device).float()))
+
+
+def TensorBitwidth(val):
+    m = int(val)
+    return 0 if m == 0 else (m - 1).bit_length()
+
+
+def RangeEstimate(input):
+    """Bit-width of max|x| (:366-377) as a Python int.  Synchronises: for inspection, not the hot path."""
+    return TensorBitwidth(ops.absmax(input.contiguous().to(torch.int32)).item())
+
+
+class TiConv2d(UpdateWeight):
+    """3x3 (or RxR) convolution, stride 1, NHWC (:379-437).  ``fuse_relu`` applies the following
+    TiReLU inside the requantisation kernel (pair it with ``TiReLU(fused=True)``)."""
+
+    def __init__(self, in_channels, out_channels, kernel_size=3, stride=1, padding=1, first_layer=False, fuse_relu=False):
+        super(TiConv2d, self).__init__()
+        self.weight, self.weight_exp = WEIGHT_INIT_METHOD(torch.Size([out_channels, kernel_size, kernel_size, in_channels]))
+        self.first_layer = first_layer
+        self.stride = stride
+        self.padding = padding
+        self.fuse_relu = fuse_relu
+        self.weight_t = None if first_layer else ops.flip_transpose(self.weight)
+
+    def refresh_weight_t(self):
+        """Rebuild the flipped/transposed filter bank after the weights were replaced from outside."""
+        if not self.first_layer:
+            self.weight_t = ops.flip_transpose(self.weight)
+
+    def forward(self, input):
+        self.act, self.act_in_exp = input
+        acc, mx = ops.conv_fprop_acc(self.act, self.weight, self.padding, self.stride)
+        per = acc[0].numel()
+        return act_calc(acc, self.act_in_exp, mx, 16 * self.layer_id, self.fuse_relu, SAMPLE_OFFSET * per, self.weight_exp)
+
+    def backward(self, input):
+        err_in, self.err_exp = input
+        err_in = err_in.contiguous()
+        err_out = None
+        if not self.first_layer:
+            acc, mx = ops.conv_dgrad_acc(err_in, self.weight_t, self.padding)
+            err_out, self.err_exp, _ = _calc(acc, ops.CALC_ERR, BITWIDTH, ERROR_ROUND_METHOD, 16 * self.layer_id + 1,
+                                             exp_tensor(self.err_exp, acc.device), self.weight_exp, mx, False,
+                                             SAMPLE_OFFSET * acc[0].numel())
+        K, R, S, C = self.weight.shape
+        self.grad_int32acc, self.grad_maxabs = ops.conv_wgrad_acc(self.act, err_in, R, S, self.padding, out=self.grad_buffer)
+        if not self.defer_update:
+            self.weight_update()
+        if not self.first_layer:
+            return err_out, self.err_exp
+
+
+class TiDropout(Module):
+    """Integer dropout (:439-455): one Bernoulli(1/2) bit per feature, shared by the whole batch."""
+
+    def forward(self, input):
+        if TRAINING:
+            act_in, exp_in = input
+            self.seed_used = RNG_SEED(act_in.device).clone()
+            return ops.dropout(act_in.contiguous(), self.seed_used, 0xFFFE), exp_tensor(exp_in, act_in.device) + 1
+        return input
+
+    def backward(self, input):
+        err_in, err_exp = input
+        return ops.dropout(err_in.contiguous(), self.seed_used, 0xFFFE), err_exp
+
+
+# ------------------------------------------------------------------------------------- globals
+GPU = 'cuda'
+BITWIDTH = 7
+
+ACT_ROUND_METHOD = RoundShift
+ERROR_ROUND_METHOD = RoundShift
+
+GRAD_ROUND_METHOD = PstoShift
+WEIGHT_INIT_METHOD = UniformWeights
+
+GRAD_BITWIDTH = 5      # the reference's training loop injects this per epoch (main.py:73-77)
+TRAINING = True        # likewise (main.py:147-149)
+SAMPLE_OFFSET = 0      # global index of this process's first sample (data-parallel shards)
+
+_seed_words = {}
+
+
+def RNG_SEED(device=None):
+    """The device word (int64[1]) that keys the random bits on ``device``."""
+    dev = torch.device(device or GPU)
+    if dev.index is None:
+        dev = torch.device("cuda", torch.cuda.current_device())
+    if dev.index not in _seed_words:
+        _seed_words[dev.index] = torch.zeros(1, dtype=torch.int64, device=dev)
+    return _seed_words[dev.index]
+
+
+def set_seed(value, device=None):
+    RNG_SEED(device).fill_(int(value))
+
+
+def advance_seed(device=None):
+    """Next training step: a device-side increment, safe inside CUDA-graph capture."""
+    RNG_SEED(device).add_(1)

@@ -1,0 +1,111 @@
+"""Training-step driver: host buffers in, one integer training step on the GPU, logits out.
+
+``Trainer.step`` is the public call a user makes per batch: it copies the float images and
+labels from pinned host memory, runs TiNet.forward + TiNet.backward (loss, error
+back-propagation, weight gradients, integer update) and copies the int8 logits and their
+exponent back.  After two eager steps the device work is captured in CUDA graphs and replayed,
+because a step is ~100 short kernels and would otherwise be bound by launch overhead.
+With a process group of more than one rank the batch is sharded (one process per GPU), the
+int32 gradient bucket is all-reduced between the backward graph and the update graph, and every
+rank applies the same update.
+"""
+import torch
+import torch.distributed as dist
+
+from . import ops, ti_torch
+from .dp import GradBucket
+
+
+class Trainer:
+    def __init__(self, model, local_batch, device, group=None, rank=0, world=1, use_graph=True, seed=0,
+                 in_shape=(3, 32, 32), warmup_steps=2):
+        self.model, self.device, self.group = model, torch.device(device), group
+        self.rank, self.world, self.use_graph = rank, world, use_graph
+        self.local_batch = local_batch
+        self.layers = model.weighted_layers()
+        self.bucket = GradBucket([l.weight.shape for l in self.layers], self.device)
+        for l, v in zip(self.layers, self.bucket.views):
+            l.grad_buffer = v
+            l.defer_update = world > 1
+        self.x = torch.zeros((local_batch,) + tuple(in_shape), dtype=torch.float32, device=self.device)
+        self.t = torch.zeros((local_batch,), dtype=torch.int64, device=self.device)
+        self.out_host = torch.zeros((local_batch, self.layers[-1].weight.shape[0]), dtype=torch.int8).pin_memory()
+        self.exp_host = torch.zeros((), dtype=torch.int32).pin_memory()
+        self.h2d_bytes = self.x.numel() * 4 + self.t.numel() * 8
+        self.d2h_bytes = self.out_host.numel() + 4
+        ti_torch.set_seed(seed, self.device)
+        ti_torch.SAMPLE_OFFSET = rank * local_batch
+        self._graphs = None
+        self._eager_steps = 0
+        self._warmup_steps = warmup_steps
+        self.kernels_per_step = None
+
+    # ------------------------------------------------------------------ pieces of one step
+    def _forward_backward(self):
+        self.model(self.x)
+        self.model.backward(self.t)
+
+    def _update(self):
+        if self.world > 1:
+            for l in self.layers:
+                l.grad_maxabs = ops.absmax(l.grad_int32acc)
+                l.weight_update()
+        ti_torch.advance_seed(self.device)
+
+    def _run_eager(self):
+        self._forward_backward()
+        if self.world > 1:
+            self.bucket.allreduce_(self.group)
+        self._update()
+
+    def _capture(self):
+        torch.cuda.synchronize(self.device)
+        g1 = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g1):
+            self._forward_backward()
+            if self.world == 1:
+                self._update()
+        g2 = None
+        if self.world > 1:
+            g2 = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g2, pool=g1.pool()):
+                self._update()
+        self._graphs = (g1, g2)
+
+    def run_device_step(self):
+        """The device part of a step on inputs already resident in self.x / self.t."""
+        if self.use_graph and self._graphs is None and self._eager_steps >= self._warmup_steps:
+            self._capture()
+        if self._graphs is not None:
+            g1, g2 = self._graphs
+            g1.replay()
+            if g2 is not None:
+                self.bucket.allreduce_(self.group)
+                g2.replay()
+        else:
+            self._run_eager()
+            self._eager_steps += 1
+
+    # ------------------------------------------------------------------ public call
+    def step(self, x_host, target_host):
+        """x_host float32 [B,3,32,32] and target_host int64 [B] in (pinned) host memory.
+        Returns (pinned int8 logits [B, classes], pinned int32 exponent); valid after the
+        stream is synchronised (``Trainer.sync``)."""
+        self.x.copy_(x_host, non_blocking=True)
+        self.t.copy_(target_host, non_blocking=True)
+        self.run_device_step()
+        self.out_host.copy_(self.model.out, non_blocking=True)
+        self.exp_host.copy_(self.model.out_exp, non_blocking=True)
+        return self.out_host, self.exp_host
+
+    def sync(self):
+        torch.cuda.synchronize(self.device)
+        ops.check_status(self.device)
+
+    def replica_checksum(self):
+        """Digest of all weights; equal on every rank of a healthy data-parallel run."""
+        tot = 0
+        for l in self.layers:
+            w = l.weight.to(torch.int64).flatten()
+            tot = (tot * 1000003 + int((w * (torch.arange(w.numel(), device=w.device) % 65521 + 1)).sum().item())) % (1 << 61)
+        return tot

@@ -1,0 +1,146 @@
+"""Whole training steps through the drop-in modules (TiVGG_cifar / TiNet / Trainer) against the
+oracle's layer-by-layer restatement and the reference-generated golden records."""
+import os
+import zlib
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import niti_oracle as O
+from tests.golden.make_golden import synth_images, xavier_exp
+
+pytestmark = pytest.mark.gpu
+
+if not torch.cuda.is_available():
+    pytest.skip("needs a CUDA device", allow_module_level=True)
+
+from niti_b200 import ti_torch, ti_vgg  # noqa: E402
+from niti_b200.trainer import Trainer  # noqa: E402
+
+DEV = "cuda:0"
+
+
+def crc(a):
+    return np.uint32(zlib.crc32(np.ascontiguousarray(a).tobytes()))
+
+
+def build(cfg, seed, dropout, fuse_relu, mu):
+    rng = np.random.default_rng(seed)
+    shapes, cin = [], 3
+    for c in cfg:
+        if c != "M":
+            shapes.append((c, 3, 3, cin))
+            cin = c
+    shapes.append((10, cin * (32 // 2 ** cfg.count("M")) ** 2))
+    weights = [rng.integers(-127, 128, size=s).astype(np.int8) for s in shapes]
+    wexps = [xavier_exp(s) for s in shapes]
+    ti_torch.GRAD_BITWIDTH = mu
+    ti_torch.TRAINING = True
+    model = ti_vgg.TiVGG_cifar(list(cfg), dropout=dropout, fuse_relu=fuse_relu)
+    for l, w, e in zip(model.weighted_layers(), weights, wexps):
+        l.weight = torch.from_numpy(w).to(DEV)
+        l.weight_exp = ti_torch.exp_tensor(e, DEV)
+        if hasattr(l, "refresh_weight_t"):
+            l.refresh_weight_t()
+    oracle = O.Net(cfg, weights, wexps, dropout=dropout, mu=mu, seed=seed)
+    return model, oracle, rng
+
+
+def run_steps(cfg, B, seed, dropout, steps, mu, fuse_relu, use_graph, rec=None):
+    model, oracle, rng = build(cfg, seed, dropout, fuse_relu, mu)
+    tr = Trainer(model, B, DEV, use_graph=use_graph, seed=seed, warmup_steps=1)
+    for step in range(steps):
+        x = synth_images(rng, B)
+        tgt = rng.integers(0, 10, size=B)
+        out_h, exp_h = tr.step(torch.from_numpy(x).pin_memory(), torch.from_numpy(tgt).pin_memory())
+        tr.sync()
+        x8, xe = O.float_to_int8(x)
+        want, want_e = oracle.forward(np.ascontiguousarray(x8.transpose(0, 2, 3, 1)), xe, step=step)
+        grads = oracle.backward(tgt, step=step)
+        assert np.array_equal(out_h.numpy(), want), f"logits differ at step {step}"
+        assert int(exp_h) == want_e
+        assert np.array_equal(model.loss.out_grad.cpu().numpy(), oracle.trace["loss_err"]), f"loss error differs at step {step}"
+        for i, l in enumerate(model.weighted_layers()):
+            assert np.array_equal(l.grad_int32acc.cpu().numpy(), grads[i].astype(np.int32)), f"grad {i} step {step}"
+            assert np.array_equal(l.weight.cpu().numpy(), oracle.w[i]), f"weights {i} step {step}"
+            if getattr(l, "weight_t", None) is not None:
+                assert np.array_equal(l.weight_t.cpu().numpy(), O.flip_transpose(oracle.w[i])), f"weight_t {i}"
+            if rec is not None:
+                assert crc(l.weight.cpu().numpy()) == rec[f"s{step}_w{i}_crc"]
+                assert crc(l.grad_int32acc.cpu().numpy()) == rec[f"s{step}_g{i}_crc"]
+        if rec is not None:
+            assert np.array_equal(out_h.numpy(), rec[f"s{step}_out"]) and int(exp_h) == rec[f"s{step}_out_exp"]
+            assert np.array_equal(model.loss.out_grad.cpu().numpy(), rec[f"s{step}_loss_err"])
+
+
+@pytest.mark.parametrize("name,fuse_relu,use_graph", [
+    ("net_small", False, False), ("net_small", True, True), ("net_small_nodrop", True, False),
+    ("net_vgg7_b4", True, False)])
+def test_against_reference_golden(golden_dir, name, fuse_relu, use_graph):
+    rec = np.load(os.path.join(golden_dir, name + ".npz"))
+    cfg = ["M" if c == 0 else int(c) for c in rec["cfg"]]
+    run_steps(cfg, int(rec["B"]), int(rec["seed"]), bool(rec["dropout"]), int(rec["steps"]), int(rec["mu"]),
+              fuse_relu, use_graph, rec)
+
+
+def test_vgg7_three_steps_graph_replay():
+    """Eager warm-up step, capture, then replays: the captured step must keep matching the oracle."""
+    run_steps([128, 128, "M", 256, 256, "M", 512, 512, "M"], 8, 4321, True, 3, 5, True, True)
+
+
+def test_stochastic_act_err_grad_rounding():
+    saved = ti_torch.ACT_ROUND_METHOD, ti_torch.ERROR_ROUND_METHOD, ti_torch.GRAD_ROUND_METHOD
+    try:
+        ti_torch.ACT_ROUND_METHOD = ti_torch.ERROR_ROUND_METHOD = ti_torch.GRAD_ROUND_METHOD = ti_torch.StoShift
+        cfg = [128, "M", 128, "M", 512, "M"]
+        model, oracle, rng = build(cfg, 77, True, True, 4)
+        oracle.act_mode = oracle.err_mode = oracle.grad_mode = O.STOCHASTIC
+        tr = Trainer(model, 4, DEV, use_graph=False, seed=77)
+        for step in range(2):
+            x = synth_images(rng, 4)
+            tgt = rng.integers(0, 10, size=4)
+            out_h, exp_h = tr.step(torch.from_numpy(x).pin_memory(), torch.from_numpy(tgt).pin_memory())
+            tr.sync()
+            x8, xe = O.float_to_int8(x)
+            want, want_e = oracle.forward(np.ascontiguousarray(x8.transpose(0, 2, 3, 1)), xe, step=step)
+            oracle.backward(tgt, step=step)
+            assert np.array_equal(out_h.numpy(), want) and int(exp_h) == want_e
+            for i, l in enumerate(model.weighted_layers()):
+                assert np.array_equal(l.weight.cpu().numpy(), oracle.w[i]), f"weights {i} step {step}"
+    finally:
+        ti_torch.ACT_ROUND_METHOD, ti_torch.ERROR_ROUND_METHOD, ti_torch.GRAD_ROUND_METHOD = saved
+
+
+def test_reference_function_names_and_shift_helpers():
+    """RoundShift / StoShift / PstoShift, act/err/grad_calc, int8mm, conv2d_int8 keep the reference's call shapes."""
+    rng = np.random.default_rng(1)
+    x = rng.integers(-100000, 100000, size=(5, 7, 3)).astype(np.int32)
+    xt = torch.from_numpy(x).to(DEV)
+    for s in (1, 4, 9):
+        assert np.array_equal(ti_torch.RoundShift(xt, s).cpu().numpy(), O.round_shift(x, s))
+        assert np.array_equal(ti_torch.PstoShift(xt, s).cpu().numpy(), O.psto_shift(x, s))
+    a, e = ti_torch.act_calc(xt, 3)
+    wa, we, _ = O.act_calc(x, 3)
+    assert np.array_equal(a.cpu().numpy(), wa) and int(e) == we
+    a, s = ti_torch.err_calc(xt)
+    wa, ws = O.err_calc(x)
+    assert np.array_equal(a.cpu().numpy(), wa) and int(s) == ws
+    a, s = ti_torch.grad_calc(xt, 5)
+    wa, ws = O.grad_calc(x, 5)
+    assert np.array_equal(a.cpu().numpy(), wa) and int(s) == ws
+    assert ti_torch.RangeEstimate(xt) == O.range_estimate(x)
+    l, r = rng.integers(-127, 128, size=(6, 10)).astype(np.int8), rng.integers(-127, 128, size=(10, 9)).astype(np.int8)
+    assert np.array_equal(ti_torch.int8mm(torch.from_numpy(l).to(DEV), torch.from_numpy(r).to(DEV)).cpu().numpy(), O.int8_mm(l, r))
+
+
+def test_state_dict_roundtrip_reference_format():
+    model, _, _ = build([16, "M", 32, "M", 512, "M"], 5, True, True, 5)
+    sd = model.state_dict()
+    assert list(sd.keys())[:2] == ["layers.0.weight", "layers.0.weight_exp"]
+    # a reference checkpoint stores weight_exp as a 0-dim float tensor on the host
+    ref_style = {k: (v.float().cpu() if k.endswith("weight_exp") else v.cpu()) for k, v in sd.items()}
+    model2, _, _ = build([16, "M", 32, "M", 512, "M"], 6, True, True, 5)
+    model2.load_state_dict(ref_style)
+    for a, b in zip(model.weighted_layers(), model2.weighted_layers()):
+        assert torch.equal(a.weight, b.weight) and int(a.weight_exp) == int(b.weight_exp)
