@@ -224,8 +224,6 @@ def run_ours(args):
     for l, w, s in zip(model.weighted_layers(), weights, shapes):
         l.weight = torch.from_numpy(w).to(dev)
         l.weight_exp = ti_torch.exp_tensor(xavier_exp(s), dev)
-        if hasattr(l, "refresh_weight_t"):
-            l.refresh_weight_t()
     trainer = Trainer(model, B, dev, rank=rank, world=world, use_graph=True, seed=1235)
     data_rng = np.random.default_rng(5000 + rank)
     batches = []

@@ -67,30 +67,33 @@ NITI_API const char* niti_last_cuda_error(void);
  * niti_conv_fprop_i8: cutlassconv_cuda.sp_conv_optimized / sp_conv (cutlassconv.cpp:57-73,
  * cutlassconv_kernel.cu:38-319) as called from conv2d_int8 (ti_torch.py:178-192).
  * x [N][H][W][C], w [K][R][S][C] -> y32 [N][P][Q][K], cross-correlation, stride 1, P = H+2*pad-R+1.
- * Unlike the reference no channel padding to 16 is needed (C = 3 is accepted).
- * Tensor-core path when C % 64 == 0; otherwise a CUDA-core path.  *maxabs = max |y32|.
+ * Unlike the reference no channel padding to 16 is needed (C = 3 is accepted).  *maxabs = max |y32|.
+ * Kernel choice: implicit GEMM on the tensor cores when C % 128 == 0 (and R = S = 2*pad+1, K % 4 == 0);
+ * R*S*C <= 32 (3-channel first layer) goes through a patch matrix in `scratch`
+ * (niti_conv_fprop_scratch_bytes, 0 for the other paths; scratch may then be NULL) and the
+ * tensor-core GEMM; anything else runs on CUDA cores.
  */
+NITI_API size_t niti_conv_fprop_scratch_bytes(int N, int H, int W, int C, int K, int R, int S);
 NITI_API int niti_conv_fprop_i8(const int8_t* x, const int8_t* w, int32_t* y32, uint32_t* maxabs,
+                       void* scratch, size_t scratch_bytes,
                        int N, int H, int W, int C, int K, int R, int S, int pad, int stride,
                        int32_t* status, void* stream);
 
 /* Error back-propagation of a convolution: TiConv2d.backward's
- * conv2d_int8(err, flip(w,[1,2]).transpose(0,3)) (ti_torch.py:403-405).  `wt` is that flipped,
- * transposed filter bank [C][R][S][K]; niti_weight_flip_transpose_i8 (or niti_update_i8) keeps
- * it current so no per-step transpose of the weights is needed.
- * err [N][H][W][K] -> e32 [N][H][W][C].
+ * conv2d_int8(err, flip(w,[1,2]).transpose(0,3)) (ti_torch.py:403-405) WITHOUT the flipped,
+ * transposed copy of the weights: the kernel reads w [K][R][S][C] in place (as the reduction
+ * operand, taps mirrored).  err [N][H][W][K] -> e32 [N][H][W][C]; R = S = 2*pad+1.
+ * Tensor cores when K % 128 == 0 and C % 16 == 0.
  */
-NITI_API int niti_conv_dgrad_i8(const int8_t* err, const int8_t* wt, int32_t* e32, uint32_t* maxabs,
+NITI_API int niti_conv_dgrad_i8(const int8_t* err, const int8_t* w, int32_t* e32, uint32_t* maxabs,
                        int N, int H, int W, int C, int K, int R, int S, int pad,
                        int32_t* status, void* stream);
 
-/* w [K][R][S][C] -> wt [C][R][S][K] with both filter axes reversed (ti_torch.py:404). */
-NITI_API int niti_weight_flip_transpose_i8(const int8_t* w, int8_t* wt, int K, int R, int S, int C, void* stream);
-
 /* Weight gradient of a convolution: the transposed-operand conv of ti_torch.py:429-432 and the
  * first-layer group-conv form conv2d_weight_int8 (ti_torch.py:194-233, int8conv_kernel.cu:248-334):
- * g32[k][r][s][c] = sum_{n,p,q} err[n][p][q][k] * x[n][p+r-pad][q+s-pad][c], exact int32.
- * The reduction over pixels is split across thread blocks; partial sums go through `scratch`
+ * g32[k][r][s][c] = sum_{n,p,q} err[n][p][q][k] * x[n][p+r-pad][q+s-pad][c], exact int32, read
+ * straight from the NHWC tensors (no transposes).  On the tensor-core paths the reduction over
+ * pixels is split across thread blocks; partial sums go through `scratch`
  * (niti_conv_wgrad_scratch_bytes) and a second kernel folds them and reduces *maxabs = max |g32|.
  */
 NITI_API size_t niti_conv_wgrad_scratch_bytes(int N, int H, int W, int C, int K, int R, int S);
@@ -103,8 +106,8 @@ NITI_API int niti_conv_wgrad_i8(const int8_t* x, const int8_t* err, int32_t* g32
  * (ti_torch.py:241-266), without the padding / .contiguous() copies around it:
  * C32[M][N] = op(A) * op(B); trans_a == 0: A is [M][K], else [K][M];
  * trans_b == 0: B is [K][N], else [N][K].  Forward a*W^T: (0,1); error e*W: (0,0);
- * gradient e^T*a: (1,0).  Tensor-core path when every row pitch is a multiple of 16 bytes
- * and M,N,K >= 64; otherwise a CUDA-core path (the 10-class FC layer).
+ * gradient e^T*a: (1,0).  Tensor-core path when every row pitch is a multiple of 16 bytes,
+ * M >= 64 and N, K >= 32; otherwise a CUDA-core path (the 10-class FC layer).
  */
 NITI_API int niti_gemm_i8(const int8_t* A, const int8_t* B, int32_t* C32, uint32_t* maxabs,
                  int M, int N, int K, int trans_a, int trans_b, int32_t* status, void* stream);
@@ -154,12 +157,9 @@ NITI_API int niti_loss_i8(const int8_t* out8, const int32_t* out_exp, const int6
                  int B, int classes, const uint64_t* seed, uint32_t rng_stream, uint64_t sample_offset, void* stream);
 
 /* UpdateWeight.weight_update (ti_torch.py:16-21): g8 = grad_calc(g32, mu); w = clamp(w - g8, +-127).
- * *maxabs = max |g32| (from niti_conv_wgrad_i8 / niti_gemm_i8 / niti_absmax_i32).
- * If wt != NULL the refreshed weights are also written as the flipped, transposed bank
- * [C][R][S][K] that niti_conv_dgrad_i8 reads (w is [K][R][S][C]; pass R = S = 1, C = n / K otherwise). */
+ * *maxabs = max |g32| (from niti_conv_wgrad_i8 / niti_gemm_i8 / niti_absmax_i32). */
 NITI_API int niti_update_i8(int8_t* w, const int32_t* g32, const uint32_t* maxabs, int64_t n,
-                   int mu, int round_mode, const uint64_t* seed, uint32_t rng_stream,
-                   int8_t* wt, int K, int R, int S, int C, void* stream);
+                   int mu, int round_mode, const uint64_t* seed, uint32_t rng_stream, void* stream);
 
 /* TiFloatToInt8 + the NCHW -> NHWC permute of TiNet.forward (ti_torch.py:341-356, ti_net.py:18-19):
  * x f32 [N][C][H][W] -> x8 int8 [N][H][W][C], *exp_out = ceil(log2(max|x|)) - 7.

@@ -23,9 +23,9 @@ SIGNATURES = {
     "niti_version": (_i, []),
     "niti_strerror": (C.c_char_p, [_i]),
     "niti_last_cuda_error": (C.c_char_p, []),
-    "niti_conv_fprop_i8": (_i, [_p, _p, _p, _p] + [_i] * 9 + [_p, _p]),
+    "niti_conv_fprop_scratch_bytes": (_sz, [_i] * 7),
+    "niti_conv_fprop_i8": (_i, [_p, _p, _p, _p, _p, _sz] + [_i] * 9 + [_p, _p]),
     "niti_conv_dgrad_i8": (_i, [_p, _p, _p, _p] + [_i] * 8 + [_p, _p]),
-    "niti_weight_flip_transpose_i8": (_i, [_p, _p, _i, _i, _i, _i, _p]),
     "niti_conv_wgrad_scratch_bytes": (_sz, [_i] * 7),
     "niti_conv_wgrad_i8": (_i, [_p, _p, _p, _p, _p, _sz] + [_i] * 8 + [_p, _p]),
     "niti_gemm_i8": (_i, [_p, _p, _p, _p] + [_i] * 5 + [_p, _p]),
@@ -37,7 +37,7 @@ SIGNATURES = {
     "niti_relu_bwd_i8": (_i, [_p, _p, _p, _i64, _p]),
     "niti_dropout_i8": (_i, [_p, _p, _i64, _i64, _p, _u32, _p]),
     "niti_loss_i8": (_i, [_p, _p, _p, _p, _i, _i, _p, _u32, _u64, _p]),
-    "niti_update_i8": (_i, [_p, _p, _p, _i64, _i, _i, _p, _u32, _p, _i, _i, _i, _i, _p]),
+    "niti_update_i8": (_i, [_p, _p, _p, _i64, _i, _i, _p, _u32, _p]),
     "niti_quantize_input_f32": (_i, [_p, _p, _p, _p, _i, _i, _i, _i, _p]),
 }
 

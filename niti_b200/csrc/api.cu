@@ -46,59 +46,105 @@ extern "C" const char* niti_last_cuda_error(void) { return g_cuda_error; }
 
 static int clear_word(uint32_t* p, cudaStream_t st) { return set_cuda_error(cudaMemsetAsync(p, 0, 4, st)); }
 
-static bool conv_on_tensor_cores(int H, int W, int C, int R, int S, int pad) {
-    // 128-byte reduction blocks over channels, "same" output size, at most 3 taps per filter row
-    return C % 128 == 0 && R == 2 * pad + 1 && S == 2 * pad + 1 && S <= 3 && R <= 8 && H >= 1 && W >= 1;
+static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+// Which kernel family takes a convolution.  TC: implicit GEMM on the tensor cores (reduction
+// channels in 128-byte blocks).  THIN: R*S*C <= 32 (the 3-channel first layer): explicit patch
+// matrix + tensor-core GEMM.  Otherwise the CUDA-core kernels.
+enum ConvPath { CONV_SIMT = 0, CONV_TC = 1, CONV_THIN = 2 };
+
+static bool same_padding(int R, int S, int pad) { return R == 2 * pad + 1 && S == 2 * pad + 1; }
+
+static ConvPath fprop_path(int C, int K, int R, int S, int pad) {
+    if (!same_padding(R, S, pad) || K % 4 != 0) return CONV_SIMT;
+    if (C % 128 == 0) return CONV_TC;
+    if (R * S * C <= 32) return CONV_THIN;
+    return CONV_SIMT;
+}
+static ConvPath wgrad_path(int C, int K, int R, int S, int pad) {
+    if (!same_padding(R, S, pad) || K % 16 != 0) return CONV_SIMT;
+    if (C % 128 == 0 && S <= 3) return CONV_TC;
+    if (R * S * C <= 32) return CONV_THIN;
+    return CONV_SIMT;
 }
 
-extern "C" int niti_conv_fprop_i8(const int8_t* x, const int8_t* w, int32_t* y32, uint32_t* maxabs, int N, int H, int W,
-                                  int C, int K, int R, int S, int pad, int stride, int32_t* status, void* stream) {
+extern "C" size_t niti_conv_fprop_scratch_bytes(int N, int H, int W, int C, int K, int R, int S) {
+    if (N <= 0 || H <= 0 || W <= 0 || C <= 0 || K <= 0 || R <= 0 || S <= 0) return 0;
+    if (fprop_path(C, K, R, S, (R - 1) / 2) != CONV_THIN) return 0;
+    return align_up(static_cast<size_t>(N) * H * W * 32, 1024) + static_cast<size_t>(K) * 32;
+}
+
+extern "C" int niti_conv_fprop_i8(const int8_t* x, const int8_t* w, int32_t* y32, uint32_t* maxabs, void* scratch,
+                                  size_t scratch_bytes, int N, int H, int W, int C, int K, int R, int S, int pad, int stride,
+                                  int32_t* status, void* stream) {
     NITI_REQUIRE(x && w && y32 && maxabs && N > 0 && H > 0 && W > 0 && C > 0 && K > 0 && R > 0 && S > 0 && pad >= 0);
     if (stride != 1) return NITI_ERR_UNSUPPORTED;
     if (H + 2 * pad - R + 1 <= 0 || W + 2 * pad - S + 1 <= 0) return NITI_ERR_BAD_ARG;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (int e = clear_word(maxabs, st)) return e;
-    if (conv_on_tensor_cores(H, W, C, R, S, pad) && K % 4 == 0 && aligned16(x) && aligned16(w) && aligned16(y32))
-        return umma_conv_fprop(x, w, y32, maxabs, N, H, W, C, K, R, S, pad, status, st);
+    ConvPath path = fprop_path(C, K, R, S, pad);
+    if (!(aligned16(x) && aligned16(w) && aligned16(y32))) path = CONV_SIMT;
+    if (path == CONV_TC) return umma_conv(x, w, y32, maxabs, N, H, W, C, K, R, S, pad, 0, status, st);
+    if (path == CONV_THIN) {
+        const size_t m = static_cast<size_t>(N) * H * W;
+        if (!scratch || !aligned16(scratch) || scratch_bytes < niti_conv_fprop_scratch_bytes(N, H, W, C, K, R, S)) return NITI_ERR_SCRATCH;
+        int8_t* xcol = static_cast<int8_t*>(scratch);
+        int8_t* wp = xcol + align_up(m * 32, 1024);
+        if (int e = im2col32(x, xcol, N, H, W, C, R, S, pad, st)) return e;
+        if (int e = pad_rows32(w, wp, K, R * S * C, st)) return e;
+        return umma_gemm(xcol, wp, y32, maxabs, static_cast<int>(m), K, 32, 0, 1, 1, status, st);
+    }
     return simt_conv_fprop(x, w, y32, maxabs, N, H, W, C, K, R, S, pad, st);
 }
 
-extern "C" int niti_conv_dgrad_i8(const int8_t* err, const int8_t* wt, int32_t* e32, uint32_t* maxabs, int N, int H,
+extern "C" int niti_conv_dgrad_i8(const int8_t* err, const int8_t* w, int32_t* e32, uint32_t* maxabs, int N, int H,
                                   int W, int C, int K, int R, int S, int pad, int32_t* status, void* stream) {
-    // dX = err (x) wt with wt[c][r][s][k] = w[k][R-1-r][S-1-s][c]: a forward convolution whose
-    // input channels are K and output channels are C, padded by R-1-pad
-    NITI_REQUIRE(pad >= 0 && R - 1 - pad >= 0);
-    return niti_conv_fprop_i8(err, wt, e32, maxabs, N, H, W, K, C, R, S, R - 1 - pad, 1, status, stream);
+    NITI_REQUIRE(err && w && e32 && maxabs && N > 0 && H > 0 && W > 0 && C > 0 && K > 0 && R > 0 && S > 0 && pad >= 0);
+    if (!same_padding(R, S, pad)) return NITI_ERR_UNSUPPORTED;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (int e = clear_word(maxabs, st)) return e;
+    if (K % 128 == 0 && C % 16 == 0 && aligned16(err) && aligned16(w) && aligned16(e32))
+        return umma_conv(err, w, e32, maxabs, N, H, W, C, K, R, S, pad, 1, status, st);
+    return simt_conv_dgrad(err, w, e32, maxabs, N, H, W, C, K, R, S, pad, st);
 }
 
 extern "C" size_t niti_conv_wgrad_scratch_bytes(int N, int H, int W, int C, int K, int R, int S) {
     if (N <= 0 || H <= 0 || W <= 0 || C <= 0 || K <= 0 || R <= 0 || S <= 0) return 0;
-    const int pad = (R - 1) / 2;
-    if (conv_on_tensor_cores(H, W, C, R, S, pad) && R == S) return umma_wgrad_scratch_bytes(N, H, W, C, K, R, S);
-    return simt_wgrad_scratch_bytes(N, H, W, C, K, R, S);
+    const ConvPath path = wgrad_path(C, K, R, S, (R - 1) / 2);
+    if (path == CONV_TC) return umma_wgrad_scratch_bytes(N, H, W, C, K, R, S);
+    if (path == CONV_THIN) {
+        const size_t m = static_cast<size_t>(N) * H * W;
+        return align_up(m * 32, 1024) + static_cast<size_t>(umma_gemm_splits(K, 32, static_cast<int>(m))) * K * 32 * 4;
+    }
+    return 16;
 }
 
 extern "C" int niti_conv_wgrad_i8(const int8_t* x, const int8_t* err, int32_t* g32, uint32_t* maxabs, void* scratch,
                                   size_t scratch_bytes, int N, int H, int W, int C, int K, int R, int S, int pad,
                                   int32_t* status, void* stream) {
-    NITI_REQUIRE(x && err && g32 && maxabs && scratch && N > 0 && H > 0 && W > 0 && C > 0 && K > 0 && R > 0 && S > 0 && pad >= 0);
-    NITI_REQUIRE(aligned16(scratch) && aligned16(g32));
-    if (H + 2 * pad - R + 1 != H || W + 2 * pad - S + 1 != W) {
-        // the CUDA-core fallback handles other paddings; the gradient then has P != H
-        if (H + 2 * pad - R + 1 <= 0 || W + 2 * pad - S + 1 <= 0) return NITI_ERR_BAD_ARG;
-    }
+    NITI_REQUIRE(x && err && g32 && maxabs && N > 0 && H > 0 && W > 0 && C > 0 && K > 0 && R > 0 && S > 0 && pad >= 0);
+    NITI_REQUIRE(aligned16(g32));
+    if (H + 2 * pad - R + 1 <= 0 || W + 2 * pad - S + 1 <= 0) return NITI_ERR_BAD_ARG;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (int e = clear_word(maxabs, st)) return e;
+    ConvPath path = wgrad_path(C, K, R, S, pad);
+    if (!(aligned16(x) && aligned16(err))) path = CONV_SIMT;
+    if (path == CONV_SIMT) return simt_conv_wgrad(x, err, g32, maxabs, N, H, W, C, K, R, S, pad, st);
+    if (!scratch || !aligned16(scratch) || scratch_bytes < niti_conv_wgrad_scratch_bytes(N, H, W, C, K, R, S)) return NITI_ERR_SCRATCH;
     const long long n = static_cast<long long>(K) * R * S * C;
-    int splits = 0;
-    int rc;
-    const bool tc = conv_on_tensor_cores(H, W, C, R, S, pad) && R == S && K % 16 == 0 && aligned16(x) && aligned16(err);
-    const size_t need = tc ? umma_wgrad_scratch_bytes(N, H, W, C, K, R, S) : simt_wgrad_scratch_bytes(N, H, W, C, K, R, S);
-    if (scratch_bytes < need) return NITI_ERR_SCRATCH;
-    if (tc) rc = umma_conv_wgrad_partials(x, err, static_cast<int32_t*>(scratch), &splits, N, H, W, C, K, R, S, pad, status, st);
-    else    rc = simt_conv_wgrad_partials(x, err, static_cast<int32_t*>(scratch), &splits, N, H, W, C, K, R, S, pad, st);
-    if (rc) return rc;
-    return reduce_partials(static_cast<const int32_t*>(scratch), splits, n, g32, maxabs, st);
+    if (path == CONV_TC) {
+        int splits = 0;
+        if (int rc = umma_conv_wgrad_partials(x, err, static_cast<int32_t*>(scratch), &splits, N, H, W, C, K, R, S, pad, status, st)) return rc;
+        return reduce_partials(static_cast<const int32_t*>(scratch), splits, n, g32, maxabs, st);
+    }
+    // thin: g[k][0..R*S*C) = sum_pixels err[pixel][k] * xcol[pixel][0..32)  (split-K GEMM, then fold and drop the padding)
+    const size_t m = static_cast<size_t>(N) * H * W;
+    int8_t* xcol = static_cast<int8_t*>(scratch);
+    int32_t* partial = reinterpret_cast<int32_t*>(xcol + align_up(m * 32, 1024));
+    const int splits = umma_gemm_splits(K, 32, static_cast<int>(m));
+    if (int e = im2col32(x, xcol, N, H, W, C, R, S, pad, st)) return e;
+    if (int e = umma_gemm(err, xcol, partial, nullptr, K, 32, static_cast<int>(m), 1, 0, splits, status, st)) return e;
+    return reduce_rows32(partial, splits, K, R * S * C, g32, maxabs, st);
 }
 
 extern "C" int niti_gemm_i8(const int8_t* A, const int8_t* B, int32_t* C32, uint32_t* maxabs, int M, int N, int K,
@@ -107,8 +153,8 @@ extern "C" int niti_gemm_i8(const int8_t* A, const int8_t* B, int32_t* C32, uint
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (int e = clear_word(maxabs, st)) return e;
     const int pitch_a = trans_a ? M : K, pitch_b = trans_b ? K : N;
-    const bool tc = pitch_a % 16 == 0 && pitch_b % 16 == 0 && M >= 64 && N >= 64 && K >= 64 && aligned16(A) && aligned16(B) &&
-                    aligned16(C32);
-    if (tc) return umma_gemm(A, B, C32, maxabs, M, N, K, trans_a, trans_b, status, st);
+    const bool tc = pitch_a % 16 == 0 && pitch_b % 16 == 0 && N % 4 == 0 && M >= 64 && N >= 32 && K >= 32 && aligned16(A) &&
+                    aligned16(B) && aligned16(C32);
+    if (tc) return umma_gemm(A, B, C32, maxabs, M, N, K, trans_a, trans_b, 1, status, st);
     return simt_gemm(A, B, C32, maxabs, M, N, K, trans_a, trans_b, st);
 }

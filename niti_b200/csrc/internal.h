@@ -11,10 +11,11 @@ int set_cuda_error(cudaError_t e);
 int set_cuda_error_text(const char* text);
 
 // tensor-core (tcgen05) paths, umma_kernels.cu
+int umma_gemm_splits(int M, int N, int K);
 int umma_gemm(const int8_t* A, const int8_t* B, int32_t* C32, unsigned* maxabs, int M, int N, int K,
-              int trans_a, int trans_b, int32_t* status, cudaStream_t st);
-int umma_conv_fprop(const int8_t* x, const int8_t* w, int32_t* y32, unsigned* maxabs, int Nimg, int H, int W, int C,
-                    int K, int R, int S, int pad, int32_t* status, cudaStream_t st);
+              int trans_a, int trans_b, int splits, int32_t* status, cudaStream_t st);
+int umma_conv(const int8_t* x, const int8_t* w, int32_t* y32, unsigned* maxabs, int Nimg, int H, int W, int C, int K,
+              int R, int S, int pad, int flip, int32_t* status, cudaStream_t st);
 size_t umma_wgrad_scratch_bytes(int Nimg, int H, int W, int C, int K, int R, int S);
 int umma_conv_wgrad_partials(const int8_t* x, const int8_t* err, int32_t* partial, int* splits_out, int Nimg, int H,
                              int W, int C, int K, int R, int S, int pad, int32_t* status, cudaStream_t st);
@@ -22,11 +23,15 @@ int umma_conv_wgrad_partials(const int8_t* x, const int8_t* err, int32_t* partia
 // CUDA-core paths, simt_kernels.cu
 int simt_conv_fprop(const int8_t* x, const int8_t* w, int32_t* y32, unsigned* maxabs, int Nimg, int H, int W, int C,
                     int K, int R, int S, int pad, cudaStream_t st);
-size_t simt_wgrad_scratch_bytes(int Nimg, int H, int W, int C, int K, int R, int S);
-int simt_conv_wgrad_partials(const int8_t* x, const int8_t* err, int32_t* partial, int* splits_out, int Nimg, int H,
-                             int W, int C, int K, int R, int S, int pad, cudaStream_t st);
+int simt_conv_dgrad(const int8_t* err, const int8_t* w, int32_t* e32, unsigned* maxabs, int Nimg, int H, int W, int C,
+                    int K, int R, int S, int pad, cudaStream_t st);
+int simt_conv_wgrad(const int8_t* x, const int8_t* err, int32_t* g32, unsigned* maxabs, int Nimg, int H, int W, int C,
+                    int K, int R, int S, int pad, cudaStream_t st);
 int simt_gemm(const int8_t* A, const int8_t* B, int32_t* C32, unsigned* maxabs, int M, int N, int K, int trans_a,
               int trans_b, cudaStream_t st);
 int reduce_partials(const int32_t* partial, int splits, long long n, int32_t* out, unsigned* maxabs, cudaStream_t st);
+int reduce_rows32(const int32_t* partial, int splits, int rows, int cols_out, int32_t* out, unsigned* maxabs, cudaStream_t st);
+int im2col32(const int8_t* x, int8_t* xcol, int Nimg, int H, int W, int C, int R, int S, int pad, cudaStream_t st);
+int pad_rows32(const int8_t* w, int8_t* wp, int K, int rsc, cudaStream_t st);
 
 }  // namespace niti

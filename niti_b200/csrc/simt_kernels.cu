@@ -111,34 +111,110 @@ absmax_kernel(const int32_t* __restrict__ acc, long long n, unsigned* maxabs) {
     warp_atomic_max(maxabs, m);
 }
 
-// out[i] = sum over splits of partial[s][i]; max|out| reduced into *maxabs
+// out[i] = sum over splits of partial[s][i]; max|out| reduced into *maxabs.
+// Block = 64 int4 columns x 4 split groups: each thread sums every fourth split (loads of different
+// splits are independent, so several are in flight), the groups meet in shared memory.
 __global__ void __launch_bounds__(256)
 reduce_partials_kernel(const int32_t* __restrict__ partial, int splits, long long n, int32_t* __restrict__ out,
                        unsigned* maxabs) {
+    __shared__ int4 sm[4][64];
+    const int tx = threadIdx.x & 63, ty = threadIdx.x >> 6;
     unsigned m = 0;
-    const long long groups = n >> 2;
-    for (long long g = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; g < groups;
-         g += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long groups = (n + 3) >> 2;  // n is a multiple of 4 for every caller (asserted on the host)
+    for (long long g0 = static_cast<long long>(blockIdx.x) * 64; g0 < groups; g0 += static_cast<long long>(gridDim.x) * 64) {
+        const long long g = g0 + tx;
         int4 s = make_int4(0, 0, 0, 0);
-        for (int k = 0; k < splits; ++k) {
-            int4 v = __ldcs(reinterpret_cast<const int4*>(partial + static_cast<long long>(k) * n) + g);
-            s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
+        if (g < groups) {
+#pragma unroll 4
+            for (int k = ty; k < splits; k += 4) {
+                const int4 v = __ldcs(reinterpret_cast<const int4*>(partial + static_cast<long long>(k) * n) + g);
+                s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
+            }
         }
-        reinterpret_cast<int4*>(out)[g] = s;
-        m = max(max(m, iabs_u(s.x)), max(iabs_u(s.y), max(iabs_u(s.z), iabs_u(s.w))));
-    }
-    for (long long i = (groups << 2) + blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n;
-         i += static_cast<long long>(gridDim.x) * blockDim.x) {
-        int s = 0;
-        for (int k = 0; k < splits; ++k) s += partial[static_cast<long long>(k) * n + i];
-        out[i] = s;
-        m = max(m, iabs_u(s));
+        sm[ty][tx] = s;
+        __syncthreads();
+        if (ty == 0 && g < groups) {
+#pragma unroll
+            for (int j = 1; j < 4; ++j) { const int4 v = sm[j][tx]; s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w; }
+            reinterpret_cast<int4*>(out)[g] = s;
+            m = max(max(m, iabs_u(s.x)), max(iabs_u(s.y), max(iabs_u(s.z), iabs_u(s.w))));
+        }
+        __syncthreads();
     }
     if (maxabs) warp_atomic_max(maxabs, m);
 }
 
 int reduce_partials(const int32_t* partial, int splits, long long n, int32_t* out, unsigned* maxabs, cudaStream_t st) {
-    reduce_partials_kernel<<<blocks_for(n / 4 + 1, 256, sm_count_simt() * 8), 256, 0, st>>>(partial, splits, n, out, maxabs);
+    if (n % 4 != 0) return NITI_ERR_UNSUPPORTED;
+    reduce_partials_kernel<<<blocks_for((n / 4 + 63) / 64, 1, sm_count_simt() * 8), 256, 0, st>>>(partial, splits, n, out, maxabs);
+    return set_cuda_error(cudaGetLastError());
+}
+
+// Same fold for row-padded partials: partial[s][row][cols_in] -> out[row][cols_out] (cols_out <= cols_in = 32).
+// One block per row; thread = (column, split group of 8).
+__global__ void __launch_bounds__(256)
+reduce_rows_kernel(const int32_t* __restrict__ partial, int splits, int rows, int cols_out, int32_t* __restrict__ out,
+                   unsigned* maxabs) {
+    __shared__ int sm[8][32];
+    const int col = threadIdx.x & 31, grp = threadIdx.x >> 5;
+    const int row = blockIdx.x;
+    int s = 0;
+    for (int k = grp; k < splits; k += 8) s += __ldcs(partial + (static_cast<long long>(k) * rows + row) * 32 + col);
+    sm[grp][col] = s;
+    __syncthreads();
+    unsigned m = 0;
+    if (grp == 0) {
+#pragma unroll
+        for (int j = 1; j < 8; ++j) s += sm[j][col];
+        if (col < cols_out) { out[static_cast<long long>(row) * cols_out + col] = s; m = iabs_u(s); }
+    }
+    if (maxabs) warp_atomic_max(maxabs, m);
+}
+
+int reduce_rows32(const int32_t* partial, int splits, int rows, int cols_out, int32_t* out, unsigned* maxabs, cudaStream_t st) {
+    reduce_rows_kernel<<<rows, 256, 0, st>>>(partial, splits, rows, cols_out, out, maxabs);
+    return set_cuda_error(cudaGetLastError());
+}
+
+// Thin convolutions (R*S*C <= 32, the 3-channel first layer) run as GEMMs over an explicit patch
+// matrix: xcol[pixel][32] holds the R*S*C bytes of the pixel's receptive field, zero padded.
+__global__ void __launch_bounds__(256)
+im2col32_kernel(const int8_t* __restrict__ x, uint32_t* __restrict__ xcol, int Nimg, int H, int W, int C, int R, int S, int pad) {
+    const int rsc = R * S * C;
+    const long long total = static_cast<long long>(Nimg) * H * W * 8;  // 8 words of 4 bytes per pixel
+    for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+         i += static_cast<long long>(gridDim.x) * blockDim.x) {
+        const int t = static_cast<int>(i & 7);
+        const long long pix = i >> 3;
+        const int wq = static_cast<int>(pix % W);
+        const int hq = static_cast<int>((pix / W) % H);
+        const long long n = pix / (static_cast<long long>(W) * H);
+        uint32_t v = 0;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int e = t * 4 + j;
+            if (e < rsc) {
+                const int c = e % C, sx = (e / C) % S, r = e / (C * S);
+                const int hh = hq + r - pad, ww = wq + sx - pad;
+                if (hh >= 0 && hh < H && ww >= 0 && ww < W)
+                    v |= static_cast<uint32_t>(static_cast<uint8_t>(x[((n * H + hh) * W + ww) * C + c])) << (8 * j);
+            }
+        }
+        xcol[i] = v;
+    }
+}
+// w[K][rsc] -> wp[K][32], zero padded
+__global__ void pad_rows32_kernel(const int8_t* __restrict__ w, int8_t* __restrict__ wp, int K, int rsc) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < K * 32) { const int k = i >> 5, e = i & 31; wp[i] = e < rsc ? w[k * rsc + e] : int8_t(0); }
+}
+int im2col32(const int8_t* x, int8_t* xcol, int Nimg, int H, int W, int C, int R, int S, int pad, cudaStream_t st) {
+    const long long total = static_cast<long long>(Nimg) * H * W * 8;
+    im2col32_kernel<<<blocks_for(total, 256, sm_count_simt() * 16), 256, 0, st>>>(x, reinterpret_cast<uint32_t*>(xcol), Nimg, H, W, C, R, S, pad);
+    return set_cuda_error(cudaGetLastError());
+}
+int pad_rows32(const int8_t* w, int8_t* wp, int K, int rsc, cudaStream_t st) {
+    pad_rows32_kernel<<<(K * 32 + 255) / 256, 256, 0, st>>>(w, wp, K, rsc);
     return set_cuda_error(cudaGetLastError());
 }
 
@@ -366,40 +442,33 @@ __global__ void loss_kernel(const int8_t* __restrict__ out8, const int32_t* __re
 // ------------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(256)
 update_kernel(int8_t* __restrict__ w, const int32_t* __restrict__ g32, const unsigned* __restrict__ maxabs, long long n,
-              int mu, int mode, const unsigned long long* seed_p, unsigned rng_stream, int8_t* __restrict__ wt, int K, int R,
-              int S, int C) {
+              int mu, int mode, const unsigned long long* seed_p, unsigned rng_stream) {
     bool zero_out;
     const int shift = shift_for(*maxabs, CALC_GRAD, mu, &zero_out);
     const bool stochastic = (mode == ROUND_STOCHASTIC) && shift > 0;
     const unsigned long long seed = stochastic ? *seed_p : 0ull;
-    for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n;
+    const long long groups = n >> 2;  // four weights per thread-iteration: one int4 of gradients, one word of weights
+    for (long long g = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; g < groups;
+         g += static_cast<long long>(gridDim.x) * blockDim.x) {
+        const int4 gv = __ldcs(reinterpret_cast<const int4*>(g32) + g);
+        const uint32_t wv = reinterpret_cast<const uint32_t*>(w)[g];
+        uint32_t rnd[4] = {0, 0, 0, 0};
+        if (stochastic) random_block(seed, rng_stream, static_cast<unsigned long long>(g), rnd);
+        const int gx[4] = {gv.x, gv.y, gv.z, gv.w};
+        uint32_t o = 0;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int g8 = zero_out ? 0 : narrow(gx[j], shift, mode, rnd[j]);
+            const int wj = static_cast<int8_t>(wv >> (8 * j));
+            o |= static_cast<uint32_t>(static_cast<uint8_t>(clamp127(wj - g8))) << (8 * j);
+        }
+        reinterpret_cast<uint32_t*>(w)[g] = o;
+    }
+    for (long long i = (groups << 2) + blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n;
          i += static_cast<long long>(gridDim.x) * blockDim.x) {
         const uint32_t rnd = stochastic ? random_word(seed, rng_stream, static_cast<unsigned long long>(i)) : 0u;
         const int g8 = zero_out ? 0 : narrow(g32[i], shift, mode, rnd);
-        const int8_t nw = static_cast<int8_t>(clamp127(static_cast<int>(w[i]) - g8));
-        w[i] = nw;
-        if (wt != nullptr) {
-            const int c = static_cast<int>(i % C);
-            long long t = i / C;
-            const int s = static_cast<int>(t % S); t /= S;
-            const int r = static_cast<int>(t % R);
-            const int k = static_cast<int>(t / R);
-            wt[((static_cast<long long>(c) * R + (R - 1 - r)) * S + (S - 1 - s)) * K + k] = nw;
-        }
-    }
-}
-__global__ void __launch_bounds__(256)
-flip_transpose_kernel(const int8_t* __restrict__ w, int8_t* __restrict__ wt, int K, int R, int S, int C) {
-    const long long n = static_cast<long long>(K) * R * S * C;
-    // iterate in OUTPUT order so the writes coalesce
-    for (long long o = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; o < n;
-         o += static_cast<long long>(gridDim.x) * blockDim.x) {
-        const int k = static_cast<int>(o % K);
-        long long t = o / K;
-        const int s = static_cast<int>(t % S); t /= S;
-        const int r = static_cast<int>(t % R);
-        const int c = static_cast<int>(t / R);
-        wt[o] = w[((static_cast<long long>(k) * R + (R - 1 - r)) * S + (S - 1 - s)) * C + c];
+        w[i] = static_cast<int8_t>(clamp127(static_cast<int>(w[i]) - g8));
     }
 }
 
@@ -436,71 +505,10 @@ quantize_input_kernel(const float* __restrict__ x, int8_t* __restrict__ x8, int3
 }
 
 // ------------------------------------------------------------------------------------------------
-// CUDA-core contractions
+// CUDA-core contractions: shapes the tensor-core kernels do not take (odd channel counts, other
+// paddings) and the 10-class FC layer.
 // ------------------------------------------------------------------------------------------------
-// Convolution forward for thin inputs (R*S*C <= 32, i.e. the 3-channel first layer): the patch of
-// a pixel is packed into T <= 8 words, each thread keeps the packed filter of its output channel
-// in registers and produces one output per pixel with T dp4a.
-template <int T>
-__global__ void __launch_bounds__(128)
-conv_fprop_thin_kernel(const int8_t* __restrict__ x, const int8_t* __restrict__ w, int32_t* __restrict__ y32,
-                       unsigned* maxabs, int Nimg, int H, int W, int C, int K, int R, int S, int pad) {
-    constexpr int TILE = 32;
-    __shared__ uint32_t patch[TILE][T];
-    const int rsc = R * S * C;
-    const long long pixels = static_cast<long long>(Nimg) * H * W;
-    unsigned m = 0;
-    for (int k0 = 0; k0 < K; k0 += 128) {
-        const int k = k0 + threadIdx.x;
-        uint32_t wreg[T];
-#pragma unroll
-        for (int t = 0; t < T; ++t) {
-            uint32_t v = 0;
-            for (int j = 0; j < 4; ++j) {
-                const int e = t * 4 + j;
-                if (k < K && e < rsc) v |= static_cast<uint32_t>(static_cast<uint8_t>(w[static_cast<long long>(k) * rsc + e])) << (8 * j);
-            }
-            wreg[t] = v;
-        }
-        for (long long p0 = static_cast<long long>(blockIdx.x) * TILE; p0 < pixels; p0 += static_cast<long long>(gridDim.x) * TILE) {
-            __syncthreads();
-            for (int i = threadIdx.x; i < TILE * T; i += blockDim.x) {
-                const int pl = i / T, t = i % T;
-                const long long pix = p0 + pl;
-                uint32_t v = 0;
-                if (pix < pixels) {
-                    const int wq = static_cast<int>(pix % W);
-                    const int hq = static_cast<int>((pix / W) % H);
-                    const long long n = pix / (static_cast<long long>(W) * H);
-                    for (int j = 0; j < 4; ++j) {
-                        const int e = t * 4 + j;
-                        if (e < rsc) {
-                            const int c = e % C, s = (e / C) % S, r = e / (C * S);
-                            const int hh = hq + r - pad, ww = wq + s - pad;
-                            if (hh >= 0 && hh < H && ww >= 0 && ww < W)
-                                v |= static_cast<uint32_t>(static_cast<uint8_t>(x[((n * H + hh) * W + ww) * C + c])) << (8 * j);
-                        }
-                    }
-                }
-                patch[pl][t] = v;
-            }
-            __syncthreads();
-            if (k < K) {
-                const int lim = static_cast<int>(min(static_cast<long long>(TILE), pixels - p0));
-                for (int pl = 0; pl < lim; ++pl) {
-                    int acc = 0;
-#pragma unroll
-                    for (int t = 0; t < T; ++t) acc = __dp4a(static_cast<int>(patch[pl][t]), static_cast<int>(wreg[t]), acc);
-                    y32[(p0 + pl) * K + k] = acc;
-                    m = max(m, iabs_u(acc));
-                }
-            }
-        }
-    }
-    warp_atomic_max(maxabs, m);
-}
-
-// Any shape: one thread per output element (slow; keeps odd shapes working).
+// Convolution forward, any shape: one thread per output element.
 __global__ void conv_fprop_direct_kernel(const int8_t* __restrict__ x, const int8_t* __restrict__ w,
                                          int32_t* __restrict__ y32, unsigned* maxabs, int Nimg, int H, int W, int C, int K,
                                          int R, int S, int pad, int P, int Q) {
@@ -530,92 +538,58 @@ __global__ void conv_fprop_direct_kernel(const int8_t* __restrict__ x, const int
     }
     warp_atomic_max(maxabs, m);
 }
-
+// Error-backward, any shape with "same" padding: dX[n,h,w,c] = sum_{r,s,k} err[n,h+pad-r,w+pad-s,k] * w[k,r,s,c].
+__global__ void conv_dgrad_direct_kernel(const int8_t* __restrict__ err, const int8_t* __restrict__ w,
+                                         int32_t* __restrict__ e32, unsigned* maxabs, int Nimg, int H, int W, int C, int K,
+                                         int R, int S, int pad) {
+    const long long total = static_cast<long long>(Nimg) * H * W * C;
+    unsigned m = 0;
+    for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+         i += static_cast<long long>(gridDim.x) * blockDim.x) {
+        const int c = static_cast<int>(i % C);
+        long long t = i / C;
+        const int wq = static_cast<int>(t % W); t /= W;
+        const int hq = static_cast<int>(t % H);
+        const long long n = t / H;
+        int acc = 0;
+        for (int r = 0; r < R; ++r) {
+            const int hh = hq + pad - r;
+            if (hh < 0 || hh >= H) continue;
+            for (int s = 0; s < S; ++s) {
+                const int ww = wq + pad - s;
+                if (ww < 0 || ww >= W) continue;
+                const int8_t* ep = err + ((n * H + hh) * W + ww) * K;
+                for (int k = 0; k < K; ++k)
+                    acc += static_cast<int>(ep[k]) * static_cast<int>(w[((static_cast<long long>(k) * R + r) * S + s) * C + c]);
+            }
+        }
+        e32[i] = acc;
+        m = max(m, iabs_u(acc));
+    }
+    warp_atomic_max(maxabs, m);
+}
 int simt_conv_fprop(const int8_t* x, const int8_t* w, int32_t* y32, unsigned* maxabs, int Nimg, int H, int W, int C,
                     int K, int R, int S, int pad, cudaStream_t st) {
     const int P = H + 2 * pad - R + 1, Q = W + 2 * pad - S + 1;
-    const int rsc = R * S * C;
-    if (rsc <= 32 && P == H && Q == W) {
-        const long long pixels = static_cast<long long>(Nimg) * H * W;
-        const int grid = blocks_for(pixels, 32, sm_count_simt() * 16);
-        if (rsc <= 28) conv_fprop_thin_kernel<7><<<grid, 128, 0, st>>>(x, w, y32, maxabs, Nimg, H, W, C, K, R, S, pad);
-        else           conv_fprop_thin_kernel<8><<<grid, 128, 0, st>>>(x, w, y32, maxabs, Nimg, H, W, C, K, R, S, pad);
-    } else {
-        const long long total = static_cast<long long>(Nimg) * P * Q * K;
-        conv_fprop_direct_kernel<<<blocks_for(total, 256, sm_count_simt() * 16), 256, 0, st>>>(x, w, y32, maxabs, Nimg, H, W,
-                                                                                             C, K, R, S, pad, P, Q);
-    }
+    const long long total = static_cast<long long>(Nimg) * P * Q * K;
+    conv_fprop_direct_kernel<<<blocks_for(total, 256, sm_count_simt() * 16), 256, 0, st>>>(x, w, y32, maxabs, Nimg, H, W, C, K,
+                                                                                         R, S, pad, P, Q);
+    return set_cuda_error(cudaGetLastError());
+}
+int simt_conv_dgrad(const int8_t* err, const int8_t* w, int32_t* e32, unsigned* maxabs, int Nimg, int H, int W, int C,
+                    int K, int R, int S, int pad, cudaStream_t st) {
+    const long long total = static_cast<long long>(Nimg) * H * W * C;
+    conv_dgrad_direct_kernel<<<blocks_for(total, 256, sm_count_simt() * 16), 256, 0, st>>>(err, w, e32, maxabs, Nimg, H, W, C,
+                                                                                         K, R, S, pad);
     return set_cuda_error(cudaGetLastError());
 }
 
-// Weight gradient for thin inputs (R*S*C <= 28): thread = output channel k, registers hold the
-// R*S*C partial sums, four pixels are folded per dp4a.  Block b sums pixels [b*span, (b+1)*span)
-// into partial[b]; reduce_partials folds the blocks.
-constexpr int WG_THIN_TAPS = 28;
-constexpr int WG_THIN_TILE = 32;  // pixels staged per iteration
-
-__global__ void __launch_bounds__(128)
-conv_wgrad_thin_kernel(const int8_t* __restrict__ x, const int8_t* __restrict__ err, int32_t* __restrict__ partial,
-                       int Nimg, int H, int W, int C, int K, int R, int S, int pad, long long span) {
-    __shared__ uint32_t pq[WG_THIN_TAPS][WG_THIN_TILE / 4];  // tap t, pixel quad j: 4 packed bytes
-    const int rsc = R * S * C;
-    const long long pixels = static_cast<long long>(Nimg) * H * W;
-    const long long lo = blockIdx.x * span, hi = min(pixels, lo + span);
-    for (int k0 = 0; k0 < K; k0 += 128) {
-        const int k = k0 + threadIdx.x;
-        int acc[WG_THIN_TAPS];
-#pragma unroll
-        for (int t = 0; t < WG_THIN_TAPS; ++t) acc[t] = 0;
-        for (long long p0 = lo; p0 < hi; p0 += WG_THIN_TILE) {
-            __syncthreads();
-            for (int i = threadIdx.x; i < WG_THIN_TAPS * (WG_THIN_TILE / 4); i += blockDim.x) {
-                const int t = i / (WG_THIN_TILE / 4), j = i % (WG_THIN_TILE / 4);
-                uint32_t v = 0;
-                if (t < rsc) {
-                    const int c = t % C, s = (t / C) % S, r = t / (C * S);
-                    for (int b = 0; b < 4; ++b) {
-                        const long long pix = p0 + j * 4 + b;
-                        if (pix < hi) {
-                            const int wq = static_cast<int>(pix % W);
-                            const int hq = static_cast<int>((pix / W) % H);
-                            const long long n = pix / (static_cast<long long>(W) * H);
-                            const int hh = hq + r - pad, ww = wq + s - pad;
-                            if (hh >= 0 && hh < H && ww >= 0 && ww < W)
-                                v |= static_cast<uint32_t>(static_cast<uint8_t>(x[((n * H + hh) * W + ww) * C + c])) << (8 * b);
-                        }
-                    }
-                }
-                pq[t][j] = v;
-            }
-            __syncthreads();
-            if (k < K) {
-#pragma unroll
-                for (int j = 0; j < WG_THIN_TILE / 4; ++j) {
-                    uint32_t e4 = 0;
-#pragma unroll
-                    for (int b = 0; b < 4; ++b) {
-                        const long long pix = p0 + j * 4 + b;
-                        if (pix < hi) e4 |= static_cast<uint32_t>(static_cast<uint8_t>(err[pix * K + k])) << (8 * b);
-                    }
-#pragma unroll
-                    for (int t = 0; t < WG_THIN_TAPS; ++t) acc[t] = __dp4a(static_cast<int>(e4), static_cast<int>(pq[t][j]), acc[t]);
-                }
-            }
-        }
-        if (k < K) {
-            int32_t* out = partial + static_cast<long long>(blockIdx.x) * K * rsc + static_cast<long long>(k) * rsc;
-#pragma unroll
-            for (int t = 0; t < WG_THIN_TAPS; ++t)
-                if (t < rsc) out[t] = acc[t];
-        }
-    }
-}
-
-// Any shape: one thread per gradient element, summing over all pixels (slow fallback).
+// Weight gradient, any shape: one thread per gradient element, summing over all pixels.
 __global__ void conv_wgrad_direct_kernel(const int8_t* __restrict__ x, const int8_t* __restrict__ err,
-                                         int32_t* __restrict__ g32, int Nimg, int H, int W, int C, int K, int R, int S,
-                                         int pad, int P, int Q) {
+                                         int32_t* __restrict__ g32, unsigned* maxabs, int Nimg, int H, int W, int C, int K,
+                                         int R, int S, int pad, int P, int Q) {
     const long long total = static_cast<long long>(K) * R * S * C;
+    unsigned m = 0;
     for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
          i += static_cast<long long>(gridDim.x) * blockDim.x) {
         const int c = static_cast<int>(i % C);
@@ -635,34 +609,15 @@ __global__ void conv_wgrad_direct_kernel(const int8_t* __restrict__ x, const int
                 }
             }
         g32[i] = acc;
+        m = max(m, iabs_u(acc));
     }
+    warp_atomic_max(maxabs, m);
 }
-
-static int thin_wgrad_splits(long long pixels) {
-    long long tiles = (pixels + WG_THIN_TILE - 1) / WG_THIN_TILE;
-    long long s = sm_count_simt() * 4;
-    return static_cast<int>(tiles < s ? tiles : s);
-}
-size_t simt_wgrad_scratch_bytes(int Nimg, int H, int W, int C, int K, int R, int S) {
-    if (R * S * C > WG_THIN_TAPS) return static_cast<size_t>(K) * R * S * C * 4;
-    return static_cast<size_t>(thin_wgrad_splits(static_cast<long long>(Nimg) * H * W)) * K * R * S * C * 4;
-}
-int simt_conv_wgrad_partials(const int8_t* x, const int8_t* err, int32_t* partial, int* splits_out, int Nimg, int H,
-                             int W, int C, int K, int R, int S, int pad, cudaStream_t st) {
+int simt_conv_wgrad(const int8_t* x, const int8_t* err, int32_t* g32, unsigned* maxabs, int Nimg, int H, int W, int C,
+                    int K, int R, int S, int pad, cudaStream_t st) {
     const int P = H + 2 * pad - R + 1, Q = W + 2 * pad - S + 1;
-    if (R * S * C <= WG_THIN_TAPS && P == H && Q == W) {
-        const long long pixels = static_cast<long long>(Nimg) * H * W;
-        const int splits = thin_wgrad_splits(pixels);
-        long long span = (pixels + splits - 1) / splits;
-        span = (span + WG_THIN_TILE - 1) / WG_THIN_TILE * WG_THIN_TILE;
-        conv_wgrad_thin_kernel<<<splits, 128, 0, st>>>(x, err, partial, Nimg, H, W, C, K, R, S, pad, span);
-        *splits_out = splits;
-    } else {
-        const long long total = static_cast<long long>(K) * R * S * C;
-        conv_wgrad_direct_kernel<<<blocks_for(total, 128, 1 << 20), 128, 0, st>>>(x, err, partial, Nimg, H, W, C, K, R, S,
-                                                                                  pad, P, Q);
-        *splits_out = 1;
-    }
+    const long long total = static_cast<long long>(K) * R * S * C;
+    conv_wgrad_direct_kernel<<<blocks_for(total, 128, 1 << 20), 128, 0, st>>>(x, err, g32, maxabs, Nimg, H, W, C, K, R, S, pad, P, Q);
     return set_cuda_error(cudaGetLastError());
 }
 
@@ -814,19 +769,12 @@ extern "C" int niti_loss_i8(const int8_t* out8, const int32_t* out_exp, const in
 }
 
 extern "C" int niti_update_i8(int8_t* w, const int32_t* g32, const uint32_t* maxabs, int64_t n, int mu, int round_mode,
-                              const uint64_t* seed, uint32_t rng_stream, int8_t* wt, int K, int R, int S, int C, void* stream) {
+                              const uint64_t* seed, uint32_t rng_stream, void* stream) {
     NITI_REQUIRE(w && g32 && maxabs && n > 0 && round_mode >= 0 && round_mode <= 2);
     NITI_REQUIRE(seed || round_mode != NITI_ROUND_STOCHASTIC);
-    if (wt) NITI_REQUIRE(K > 0 && R > 0 && S > 0 && C > 0 && static_cast<int64_t>(K) * R * S * C == n);
-    update_kernel<<<blocks_for(n, 256, sm_count_simt() * 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(
-        w, g32, maxabs, n, mu, round_mode, reinterpret_cast<const unsigned long long*>(seed), rng_stream, wt, K, R, S, C);
-    return set_cuda_error(cudaGetLastError());
-}
-
-extern "C" int niti_weight_flip_transpose_i8(const int8_t* w, int8_t* wt, int K, int R, int S, int C, void* stream) {
-    NITI_REQUIRE(w && wt && K > 0 && R > 0 && S > 0 && C > 0);
-    const long long n = static_cast<long long>(K) * R * S * C;
-    flip_transpose_kernel<<<blocks_for(n, 256, sm_count_simt() * 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(w, wt, K, R, S, C);
+    NITI_REQUIRE(reinterpret_cast<uintptr_t>(w) % 4 == 0 && reinterpret_cast<uintptr_t>(g32) % 16 == 0);
+    update_kernel<<<blocks_for(n / 4 + 1, 256, sm_count_simt() * 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        w, g32, maxabs, n, mu, round_mode, reinterpret_cast<const unsigned long long*>(seed), rng_stream);
     return set_cuda_error(cudaGetLastError());
 }
 

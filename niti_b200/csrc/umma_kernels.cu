@@ -31,6 +31,18 @@ constexpr int ROW_BYTES = 128;               // bytes per shared-memory row of a
 constexpr int PANEL_BYTES = 128 * ROW_BYTES; // one 128-row operand panel
 constexpr int UMMA_THREADS = 192;
 constexpr uint32_t SWIZZLE_128B_CODE = 2;
+constexpr int EPI_CHUNK_BYTES = 128 * 32 * 4;  // 128 rows x 32 int32 columns, one TMA store box
+constexpr int EPI_BARRIER = 1;                 // named barrier of the 128 epilogue threads
+
+// Epilogue staging: each thread owns one accumulator row of 32 int32 (128 bytes) and writes it as
+// eight 16-byte chunks at the 128-byte-swizzled position the TMA store expects (chunk ^ row%8);
+// that placement is also free of shared-memory bank conflicts.
+__device__ __forceinline__ void stage_row(uint32_t buf, int row, const uint32_t (&v)[32]) {
+    const uint32_t base = buf + static_cast<uint32_t>(row) * 128u;
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+        st_shared_v4(base + (static_cast<uint32_t>(j ^ (row & 7)) << 4), v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+}
 
 // ------------------------------------------------------------------------------------------------
 // GEMM / convolution forward (and error-backward, which is a forward conv over flipped weights)
@@ -38,18 +50,19 @@ constexpr uint32_t SWIZZLE_128B_CODE = 2;
 struct GemmParams {
     int conv;              // 0: plain GEMM, 1: implicit-GEMM convolution (A tile = 4-D box of pixels)
     int M, N;              // output rows (GEMM rows or pixels) and columns
-    int num_kb;            // reduction blocks per output tile
+    int num_kb;            // reduction blocks of the whole problem
+    int splits;            // split-K: each output tile is produced `splits` times over disjoint reduction ranges
     int m_tiles, n_tiles;
-    int a_mn, b_mn;        // operand majors (0 = K-major, 1 = MN-major); conv uses 0/0
+    int a_mn, b_mn;        // operand majors (0 = K-major, 1 = MN-major)
     int a_bytes;           // bytes one A stage receives from TMA
     // convolution geometry
-    int H, W, C, R, S, pad, Nimg;
+    int H, W, S, pad, Nimg;
+    int flip;              // 1: error-backward, taps are read mirrored (offset pad - r instead of r - pad)
+    int tapstride;         // elements between consecutive taps in a filter row
     int BW, BH, BI;        // pixels of one tile along w, h and images; BW*BH*BI <= 128
     int tiles_w, tiles_h;
-    int cblocks;           // C / 128
-    int32_t* out;
-    long long ldc;         // output row pitch in elements
-    unsigned* maxabs;
+    int cblocks;           // reduction channels / 128
+    unsigned* maxabs;      // may be null (split-K partials)
     int32_t* status;
 };
 
@@ -59,7 +72,8 @@ struct GemmCfg {
     static constexpr int STAGE_BYTES = PANEL_BYTES + B_STAGE_BYTES;
     static constexpr int STAGES = (192 * 1024) / STAGE_BYTES;
     static constexpr int TMEM_COLS = 2 * BN;  // two accumulators; 256 or 512 columns
-    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+    static constexpr int EPI_BYTES = 2 * EPI_CHUNK_BYTES;  // double-buffered 128 x 32 int32 staging tile
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + EPI_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
 };
 
 __device__ __forceinline__ void report_abort(int32_t* status, int code, int role) {
@@ -71,12 +85,14 @@ __device__ __forceinline__ void report_abort(int32_t* status, int code, int role
 
 template <int BN>
 __global__ void __launch_bounds__(UMMA_THREADS, 1)
-umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const GemmParams p) {
+umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                 const __grid_constant__ CUtensorMap tmC, const GemmParams p) {
     using Cfg = GemmCfg<BN>;
     constexpr int STAGES = Cfg::STAGES;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * Cfg::STAGE_BYTES);
+    uint8_t* epi_smem = smem + STAGES * Cfg::STAGE_BYTES;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(epi_smem + Cfg::EPI_BYTES);
     uint64_t* full_bar = bars;
     uint64_t* empty_bar = bars + STAGES;
     uint64_t* tfull_bar = bars + 2 * STAGES;
@@ -94,6 +110,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         fence_barrier_init();
         tma_prefetch_desc(&tmA);
         tma_prefetch_desc(&tmB);
+        tma_prefetch_desc(&tmC);
     }
     if (warp == 1) { tmem_alloc(smem_u32(tmem_slot), Cfg::TMEM_COLS); tmem_relinquish(); }
     tc_fence_before();
@@ -101,17 +118,21 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
-    const int total_tiles = p.m_tiles * p.n_tiles;
+    const int mn_tiles = p.m_tiles * p.n_tiles;
+    const int total_tiles = mn_tiles * p.splits;
 
     if (warp == 0) {
         // ------------------------------------------------------------------ TMA producer
         if (lane == 0) {
             int s = 0; uint32_t ph = 0; bool ok = true;
             for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
-                const int m_t = tile / p.n_tiles, n_t = tile % p.n_tiles;
+                const int split = tile / mn_tiles, mn = tile % mn_tiles;
+                const int m_t = mn / p.n_tiles, n_t = mn % p.n_tiles;
+                const int kb_lo = static_cast<int>(static_cast<long long>(split) * p.num_kb / p.splits);
+                const int kb_hi = static_cast<int>(static_cast<long long>(split + 1) * p.num_kb / p.splits);
                 int tw = 0, th = 0, tn = 0;
                 if (p.conv) { tw = m_t % p.tiles_w; th = (m_t / p.tiles_w) % p.tiles_h; tn = m_t / (p.tiles_w * p.tiles_h); }
-                for (int kb = 0; kb < p.num_kb; ++kb) {
+                for (int kb = kb_lo; kb < kb_hi; ++kb) {
                     if (!mbar_wait(smem_u32(&empty_bar[s]), ph ^ 1u, abort_flag)) { ok = false; report_abort(p.status, 1, 0); break; }
                     const uint32_t fb = smem_u32(&full_bar[s]);
                     const uint32_t sa = smem_u32(smem + s * Cfg::STAGE_BYTES);
@@ -120,8 +141,15 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                     if (p.conv) {
                         const int tap = kb / p.cblocks, cb = kb % p.cblocks;
                         const int r = tap / p.S, sx = tap % p.S;
-                        tma_load_4d(sa, &tmA, fb, cb * ROW_BYTES, tw * p.BW + sx - p.pad, th * p.BH + r - p.pad, tn * p.BI);
-                        tma_load_2d(sb, &tmB, fb, tap * p.C + cb * ROW_BYTES, n_t * BN);
+                        const int dx = p.flip ? p.pad - sx : sx - p.pad, dy = p.flip ? p.pad - r : r - p.pad;
+                        tma_load_4d(sa, &tmA, fb, cb * ROW_BYTES, tw * p.BW + dx, th * p.BH + dy, tn * p.BI);
+                        if (p.b_mn) {
+#pragma unroll
+                            for (int pn = 0; pn < BN / 128; ++pn)
+                                tma_load_2d(sb + pn * PANEL_BYTES, &tmB, fb, tap * p.tapstride + n_t * BN + pn * 128, cb * 128);
+                        } else {
+                            tma_load_2d(sb, &tmB, fb, tap * p.tapstride + cb * ROW_BYTES, n_t * BN);
+                        }
                     } else {
                         if (p.a_mn) tma_load_2d(sa, &tmA, fb, m_t * BLOCK_M, kb * 128);
                         else        tma_load_2d(sa, &tmA, fb, kb * ROW_BYTES, m_t * BLOCK_M);
@@ -147,7 +175,10 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                 if (!mbar_wait(smem_u32(&tempty_bar[acc]), aph ^ 1u, abort_flag)) { report_abort(p.status, 2, 1); break; }
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BN);
-                for (int kb = 0; kb < p.num_kb; ++kb) {
+                const int split = tile / mn_tiles;
+                const int kb_lo = static_cast<int>(static_cast<long long>(split) * p.num_kb / p.splits);
+                const int kb_hi = static_cast<int>(static_cast<long long>(split + 1) * p.num_kb / p.splits);
+                for (int kb = kb_lo; kb < kb_hi; ++kb) {
                     if (!mbar_wait(smem_u32(&full_bar[s]), ph, abort_flag)) { ok = false; report_abort(p.status, 3, 1); break; }
                     tc_fence_after();
                     const uint32_t sa = smem_u32(smem + s * Cfg::STAGE_BYTES);
@@ -161,7 +192,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 #pragma unroll
                     for (int k = 0; k < 4; ++k)
                         umma_i8(d_tmem, desc_advance(a0, k * a_step), desc_advance(b0, k * b_step), idesc,
-                                static_cast<uint32_t>((kb | k) != 0));
+                                static_cast<uint32_t>(kb != kb_lo || k != 0));
                     umma_commit(smem_u32(&empty_bar[s]));
                     if (++s == STAGES) { s = 0; ph ^= 1u; }
                 }
@@ -170,65 +201,66 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         }
     } else {
         // ------------------------------------------------------------------ epilogue (4 warps)
+        // Per 32-column chunk: TMEM -> registers (max|acc| on the way) -> swizzled shared-memory
+        // staging tile -> one TMA store.  Two staging tiles, so a store drains while the next
+        // chunk is read.  The store clips rows/columns outside the tensor.
         const int q = warp & 3;  // TMEM lanes [32q, 32q+32) are the ones this warp may read
         const int row_in_tile = q * 32 + lane;
+        const bool leader = threadIdx.x == 64;
         unsigned local_max = 0;
+        uint32_t chunk_ctr = 0;
         int it = 0;
         for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++it) {
             const int acc = it & 1; const uint32_t aph = (it >> 1) & 1u;
-            if (!mbar_wait(smem_u32(&tfull_bar[acc]), aph, abort_flag)) { report_abort(p.status, 4, 2); break; }
+            const uint32_t failed = mbar_wait(smem_u32(&tfull_bar[acc]), aph, abort_flag) ? 0u : 1u;
+            if (barrier_or(EPI_BARRIER, 128, failed)) {  // same verdict in all 128 threads
+                if (failed) report_abort(p.status, 4, 2);
+                break;
+            }
             tc_fence_after();
-            const int m_t = tile / p.n_tiles, n_t = tile % p.n_tiles;
-            bool valid; long long row;
+            const int split = tile / mn_tiles, mn = tile % mn_tiles;
+            const int m_t = mn / p.n_tiles, n_t = mn % p.n_tiles;
+            bool valid; int cy, cz, cw;
             if (p.conv) {
                 const int tw = m_t % p.tiles_w, th = (m_t / p.tiles_w) % p.tiles_h, tn = m_t / (p.tiles_w * p.tiles_h);
                 const int w = tw * p.BW + row_in_tile % p.BW;
                 const int h = th * p.BH + (row_in_tile / p.BW) % p.BH;
                 const int n = tn * p.BI + row_in_tile / (p.BW * p.BH);
                 valid = row_in_tile < p.BW * p.BH * p.BI && w < p.W && h < p.H && n < p.Nimg;
-                row = (static_cast<long long>(n) * p.H + h) * p.W + w;
+                cy = tw * p.BW; cz = th * p.BH; cw = tn * p.BI;
             } else {
-                row = static_cast<long long>(m_t) * BLOCK_M + row_in_tile;
-                valid = row < p.M;
+                valid = m_t * BLOCK_M + row_in_tile < p.M;
+                cy = m_t * BLOCK_M; cz = split; cw = 0;
             }
-            int32_t* out_row = p.out + row * p.ldc;
             const int col0 = n_t * BN;
             const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(acc * BN);
 #pragma unroll 1
-            for (int c = 0; c < BN; c += 32) {
+            for (int c = 0; c < BN && col0 + c < p.N; c += 32) {
+                const uint32_t buf = smem_u32(epi_smem) + (chunk_ctr & 1u) * EPI_CHUNK_BYTES;
+                if (leader) bulk_wait_read<1>();  // the store that last used this tile has read it
+                named_barrier(EPI_BARRIER, 128);
                 uint32_t v[32];
-                __syncwarp();
                 tmem_ld_32x32(taddr + c, v);
                 tmem_ld_wait();
                 if (valid) {
-                    const int col = col0 + c;
-                    if (col + 32 <= p.N && (p.ldc & 3) == 0) {
+                    const int lim = p.N - (col0 + c);
 #pragma unroll
-                        for (int j = 0; j < 32; j += 4) {
-                            int4 o = make_int4(v[j], v[j + 1], v[j + 2], v[j + 3]);
-                            *reinterpret_cast<int4*>(out_row + col + j) = o;
-                        }
-#pragma unroll
-                        for (int j = 0; j < 32; ++j) {
-                            int x = static_cast<int>(v[j]);
-                            local_max = max(local_max, static_cast<unsigned>(x < 0 ? -x : x));
-                        }
-                    } else {
-#pragma unroll
-                        for (int j = 0; j < 32; ++j) {
-                            if (col + j < p.N) {
-                                int x = static_cast<int>(v[j]);
-                                out_row[col + j] = x;
-                                local_max = max(local_max, static_cast<unsigned>(x < 0 ? -x : x));
-                            }
-                        }
+                    for (int j = 0; j < 32; ++j) {
+                        const int x = static_cast<int>(v[j]);
+                        if (j < lim) local_max = max(local_max, static_cast<unsigned>(x < 0 ? -x : x));
                     }
                 }
+                stage_row(buf, row_in_tile, v);
+                fence_proxy_async();
+                named_barrier(EPI_BARRIER, 128);
+                if (leader) { tma_store_4d(&tmC, buf, col0 + c, cy, cz, cw); bulk_commit(); }
+                ++chunk_ctr;
             }
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&tempty_bar[acc]));
         }
+        if (leader) bulk_wait<0>();
         local_max = __reduce_max_sync(0xFFFFFFFFu, local_max);
         if (lane == 0 && local_max != 0 && p.maxabs != nullptr) atomicMax(p.maxabs, local_max);
     }
@@ -266,14 +298,16 @@ struct WgradParams {
 constexpr int WG_MAX_S = 3;
 constexpr int WG_STAGE_BYTES = (1 + WG_MAX_S) * PANEL_BYTES;  // 64 KB
 constexpr int WG_STAGES = 3;
-constexpr int WG_SMEM_BYTES = WG_STAGES * WG_STAGE_BYTES + 1024 + 256;
+constexpr int WG_SMEM_BYTES = WG_STAGES * WG_STAGE_BYTES + 2 * EPI_CHUNK_BYTES + 1024 + 256;
 constexpr int WG_TMEM_COLS = 512;
 
 __global__ void __launch_bounds__(UMMA_THREADS, 1)
-umma_wgrad_kernel(const __grid_constant__ CUtensorMap tmErr, const __grid_constant__ CUtensorMap tmX, const WgradParams p) {
+umma_wgrad_kernel(const __grid_constant__ CUtensorMap tmErr, const __grid_constant__ CUtensorMap tmX,
+                  const __grid_constant__ CUtensorMap tmP, const WgradParams p) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + WG_STAGES * WG_STAGE_BYTES);
+    uint8_t* epi_smem = smem + WG_STAGES * WG_STAGE_BYTES;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(epi_smem + 2 * EPI_CHUNK_BYTES);
     uint64_t* full_bar = bars;
     uint64_t* empty_bar = bars + WG_STAGES;
     uint64_t* tfull_bar = bars + 2 * WG_STAGES;
@@ -296,6 +330,7 @@ umma_wgrad_kernel(const __grid_constant__ CUtensorMap tmErr, const __grid_consta
         fence_barrier_init();
         tma_prefetch_desc(&tmErr);
         tma_prefetch_desc(&tmX);
+        tma_prefetch_desc(&tmP);
     }
     if (warp == 1) { tmem_alloc(smem_u32(tmem_slot), WG_TMEM_COLS); tmem_relinquish(); }
     fence_proxy_async();  // zero fill (generic proxy) before TMA writes (async proxy)
@@ -348,30 +383,34 @@ umma_wgrad_kernel(const __grid_constant__ CUtensorMap tmErr, const __grid_consta
             if (ok) umma_commit(smem_u32(&tfull_bar[0]));
         }
     } else {
+        // partial[split][k][r][s][c] viewed as a rank-4 tensor (c, r*S+s, k, split): one TMA store
+        // per (tap, 32-channel chunk) writes 128 k-rows of 32 int32
         const int q = warp & 3;
-        const int k = kt * 128 + q * 32 + lane;  // output channel = accumulator row
-        if (mbar_wait(smem_u32(&tfull_bar[0]), 0, abort_flag)) {
+        const int row_in_tile = q * 32 + lane;
+        const bool leader = threadIdx.x == 64;
+        const uint32_t failed = mbar_wait(smem_u32(&tfull_bar[0]), 0, abort_flag) ? 0u : 1u;
+        if (barrier_or(EPI_BARRIER, 128, failed)) {
+            if (failed) report_abort(p.status, 14, 2);
+        } else {
             tc_fence_after();
-            const long long per_split = static_cast<long long>(p.K) * p.R * p.S * p.C;
-            int32_t* base = p.partial + static_cast<long long>(split) * per_split;
+            uint32_t chunk_ctr = 0;
             for (int sx = 0; sx < p.S; ++sx) {
-                int32_t* out_row = base + ((static_cast<long long>(k) * p.R + r) * p.S + sx) * p.C + ct * 128;
 #pragma unroll 1
-                for (int c = 0; c < 128; c += 32) {
+                for (int c = 0; c < 128 && ct * 128 + c < p.C; c += 32) {
+                    const uint32_t buf = smem_u32(epi_smem) + (chunk_ctr & 1u) * EPI_CHUNK_BYTES;
+                    if (leader) bulk_wait_read<1>();
+                    named_barrier(EPI_BARRIER, 128);
                     uint32_t v[32];
-                    __syncwarp();
                     tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + sx * 128 + c, v);
                     tmem_ld_wait();
-                    if (k < p.K) {
-#pragma unroll
-                        for (int j = 0; j < 32; j += 4)
-                            if (ct * 128 + c + j < p.C)
-                                *reinterpret_cast<int4*>(out_row + c + j) = make_int4(v[j], v[j + 1], v[j + 2], v[j + 3]);
-                    }
+                    stage_row(buf, row_in_tile, v);
+                    fence_proxy_async();
+                    named_barrier(EPI_BARRIER, 128);
+                    if (leader) { tma_store_4d(&tmP, buf, ct * 128 + c, r * p.S + sx, kt * 128, split); bulk_commit(); }
+                    ++chunk_ctr;
                 }
             }
-        } else {
-            report_abort(p.status, 14, 2);
+            if (leader) bulk_wait<0>();
         }
     }
 
@@ -406,20 +445,21 @@ static EncodeTiledFn get_encode() {
     return fn;
 }
 
-// rank-2 or rank-4 uint8 tensor map with 128-byte swizzle; dims/box innermost first, strides in bytes.
-static int encode_map(CUtensorMap* map, const void* ptr, int rank, const uint64_t* dims, const uint64_t* strides,
-                      const uint32_t* box) {
+// Tensor map with 128-byte swizzle over uint8 (operands) or int32 (outputs) elements; dims/box
+// innermost first, in elements; strides of dims 1.. in bytes.
+static int encode_map(CUtensorMap* map, const void* ptr, bool int32_elems, int rank, const uint64_t* dims,
+                      const uint64_t* strides, const uint32_t* box) {
     EncodeTiledFn enc = get_encode();
     if (!enc) return set_cuda_error_text("cuTensorMapEncodeTiled is not available from this driver");
     cuuint64_t gdim[4]; cuuint64_t gstr[3]; cuuint32_t bx[4]; cuuint32_t es[4];
     for (int i = 0; i < rank; ++i) { gdim[i] = dims[i]; bx[i] = box[i]; es[i] = 1; }
     for (int i = 0; i + 1 < rank; ++i) gstr[i] = strides[i];
-    CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, rank, const_cast<void*>(ptr), gdim, gstr, bx, es,
-                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    CUresult r = enc(map, int32_elems ? CU_TENSOR_MAP_DATA_TYPE_INT32 : CU_TENSOR_MAP_DATA_TYPE_UINT8, rank,
+                     const_cast<void*>(ptr), gdim, gstr, bx, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                     CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) {
         char buf[160];
-        snprintf(buf, sizeof buf, "cuTensorMapEncodeTiled failed with CUresult %d", static_cast<int>(r));
+        snprintf(buf, sizeof buf, "cuTensorMapEncodeTiled failed with CUresult %d (rank %d)", static_cast<int>(r), rank);
         return set_cuda_error_text(buf);
     }
     return 0;
@@ -437,17 +477,14 @@ static int sm_count() {
 }
 
 template <int BN>
-static int launch_gemm_bn(const CUtensorMap& a, const CUtensorMap& b, const GemmParams& p, cudaStream_t st) {
+static int launch_gemm_bn(const CUtensorMap& a, const CUtensorMap& b, const CUtensorMap& c, const GemmParams& p,
+                          cudaStream_t st) {
     using Cfg = GemmCfg<BN>;
-    static bool attr_set = false;
-    if (!attr_set) {
-        cudaError_t e = cudaFuncSetAttribute(umma_gemm_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
-        if (e != cudaSuccess) return set_cuda_error(e);
-        attr_set = true;
-    }
-    int grid = p.m_tiles * p.n_tiles;
+    cudaError_t e = cudaFuncSetAttribute(umma_gemm_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
+    if (e != cudaSuccess) return set_cuda_error(e);
+    int grid = p.m_tiles * p.n_tiles * p.splits;
     if (grid > sm_count()) grid = sm_count();
-    umma_gemm_kernel<BN><<<grid, UMMA_THREADS, Cfg::SMEM_BYTES, st>>>(a, b, p);
+    umma_gemm_kernel<BN><<<grid, UMMA_THREADS, Cfg::SMEM_BYTES, st>>>(a, b, c, p);
     return set_cuda_error(cudaGetLastError());
 }
 
@@ -460,53 +497,77 @@ static void pick_pixel_box(int Nimg, int H, int W, int* BW, int* BH, int* BI) {
     *BI = bi;
 }
 
+int umma_gemm_splits(int M, int N, int K) {
+    const int bn = (N > 128) ? 256 : 128;
+    const int tiles = ((M + 127) / 128) * ((N + bn - 1) / bn);
+    const int kb = (K + 127) / 128;
+    if (tiles * 2 > sm_count() || kb < 8) return 1;
+    int splits = sm_count() / tiles;
+    if (splits > kb / 2) splits = kb / 2;
+    return splits < 1 ? 1 : splits;
+}
+
+// C32[splits][M][N] (splits == 1: the result itself) = op(A) * op(B) over disjoint reduction ranges
 int umma_gemm(const int8_t* A, const int8_t* B, int32_t* C32, unsigned* maxabs, int M, int N, int K,
-              int trans_a, int trans_b, int32_t* status, cudaStream_t st) {
-    CUtensorMap ma, mb;
+              int trans_a, int trans_b, int splits, int32_t* status, cudaStream_t st) {
+    CUtensorMap ma, mb, mc;
     const int a_mn = trans_a ? 1 : 0, b_mn = trans_b ? 0 : 1;
     const int bn = (N > 128) ? 256 : 128;
     {
         uint64_t dims[2], str[1]; uint32_t box[2] = {128, 128};
         if (a_mn) { dims[0] = M; dims[1] = K; str[0] = M; } else { dims[0] = K; dims[1] = M; str[0] = K; }
-        if (int e = encode_map(&ma, A, 2, dims, str, box)) return e;
+        if (int e = encode_map(&ma, A, false, 2, dims, str, box)) return e;
         if (b_mn) { dims[0] = N; dims[1] = K; str[0] = N; box[1] = 128; } else { dims[0] = K; dims[1] = N; str[0] = K; box[1] = bn; }
-        if (int e = encode_map(&mb, B, 2, dims, str, box)) return e;
+        if (int e = encode_map(&mb, B, false, 2, dims, str, box)) return e;
+        uint64_t dc[4] = {(uint64_t)N, (uint64_t)M, (uint64_t)splits, 1};
+        uint64_t sc[3] = {(uint64_t)N * 4, (uint64_t)M * N * 4, (uint64_t)splits * M * N * 4};
+        uint32_t bc[4] = {32, 128, 1, 1};
+        if (int e = encode_map(&mc, C32, true, 4, dc, sc, bc)) return e;
     }
     GemmParams p{};
-    p.conv = 0; p.M = M; p.N = N; p.num_kb = (K + 127) / 128;
+    p.conv = 0; p.M = M; p.N = N; p.num_kb = (K + 127) / 128; p.splits = splits;
     p.m_tiles = (M + 127) / 128; p.n_tiles = (N + bn - 1) / bn;
     p.a_mn = a_mn; p.b_mn = b_mn; p.a_bytes = PANEL_BYTES;
-    p.out = C32; p.ldc = N; p.maxabs = maxabs; p.status = status;
-    return bn == 256 ? launch_gemm_bn<256>(ma, mb, p, st) : launch_gemm_bn<128>(ma, mb, p, st);
+    p.maxabs = splits > 1 ? nullptr : maxabs; p.status = status;
+    return bn == 256 ? launch_gemm_bn<256>(ma, mb, mc, p, st) : launch_gemm_bn<128>(ma, mb, mc, p, st);
 }
 
-int umma_conv_fprop(const int8_t* x, const int8_t* w, int32_t* y32, unsigned* maxabs, int Nimg, int H, int W, int C,
-                    int K, int R, int S, int pad, int32_t* status, cudaStream_t st) {
-    // stride 1 with P == H, Q == W ("same" padding) is what the tile decomposition covers
-    CUtensorMap ma, mb;
-    const int bn = (K > 128) ? 256 : 128;
+// Forward convolution (flip == 0: x [N,H,W,C] with w [K,R,S,C] -> [N,H,W,K]) or error-backward
+// (flip == 1: err [N,H,W,K] with the same w -> [N,H,W,C]); "same" padding, stride 1.
+// Forward reads w rows as the N operand (K-major); backward reads the very same tensor as the
+// reduction operand (MN-major: 128 k rows of 128 c bytes per tap), so no transposed copy exists.
+int umma_conv(const int8_t* x, const int8_t* w, int32_t* y32, unsigned* maxabs, int Nimg, int H, int W, int C, int K,
+              int R, int S, int pad, int flip, int32_t* status, cudaStream_t st) {
+    CUtensorMap ma, mb, mc;
+    const int red = flip ? K : C;   // reduction channels per tap
+    const int outc = flip ? C : K;  // output channels
+    const int bn = (outc > 128) ? 256 : 128;
     GemmParams p{};
     pick_pixel_box(Nimg, H, W, &p.BW, &p.BH, &p.BI);
     {
-        uint64_t dims[4] = {(uint64_t)C, (uint64_t)W, (uint64_t)H, (uint64_t)Nimg};
-        uint64_t str[3] = {(uint64_t)C, (uint64_t)W * C, (uint64_t)H * W * C};
+        uint64_t dims[4] = {(uint64_t)red, (uint64_t)W, (uint64_t)H, (uint64_t)Nimg};
+        uint64_t str[3] = {(uint64_t)red, (uint64_t)W * red, (uint64_t)H * W * red};
         uint32_t box[4] = {128, (uint32_t)p.BW, (uint32_t)p.BH, (uint32_t)p.BI};
-        if (int e = encode_map(&ma, x, 4, dims, str, box)) return e;
+        if (int e = encode_map(&ma, x, false, 4, dims, str, box)) return e;
         uint64_t d2[2] = {(uint64_t)R * S * C, (uint64_t)K};
         uint64_t s2[1] = {(uint64_t)R * S * C};
-        uint32_t b2[2] = {128, (uint32_t)bn};
-        if (int e = encode_map(&mb, w, 2, d2, s2, b2)) return e;
+        uint32_t b2[2] = {128, flip ? 128u : (uint32_t)bn};
+        if (int e = encode_map(&mb, w, false, 2, d2, s2, b2)) return e;
+        uint64_t dc[4] = {(uint64_t)outc, (uint64_t)W, (uint64_t)H, (uint64_t)Nimg};
+        uint64_t sc[3] = {(uint64_t)outc * 4, (uint64_t)W * outc * 4, (uint64_t)H * W * outc * 4};
+        uint32_t bc[4] = {32, (uint32_t)p.BW, (uint32_t)p.BH, (uint32_t)p.BI};
+        if (int e = encode_map(&mc, y32, true, 4, dc, sc, bc)) return e;
     }
-    p.conv = 1;
-    p.H = H; p.W = W; p.C = C; p.R = R; p.S = S; p.pad = pad; p.Nimg = Nimg;
+    p.conv = 1; p.flip = flip; p.splits = 1;
+    p.H = H; p.W = W; p.S = S; p.pad = pad; p.Nimg = Nimg; p.tapstride = C;
     p.tiles_w = (W + p.BW - 1) / p.BW; p.tiles_h = (H + p.BH - 1) / p.BH;
     const int tiles_n = (Nimg + p.BI - 1) / p.BI;
-    p.cblocks = C / 128;
-    p.M = Nimg * H * W; p.N = K; p.num_kb = R * S * p.cblocks;
-    p.m_tiles = p.tiles_w * p.tiles_h * tiles_n; p.n_tiles = (K + bn - 1) / bn;
-    p.a_mn = 0; p.b_mn = 0; p.a_bytes = p.BW * p.BH * p.BI * ROW_BYTES;
-    p.out = y32; p.ldc = K; p.maxabs = maxabs; p.status = status;
-    return bn == 256 ? launch_gemm_bn<256>(ma, mb, p, st) : launch_gemm_bn<128>(ma, mb, p, st);
+    p.cblocks = red / 128;
+    p.M = Nimg * H * W; p.N = outc; p.num_kb = R * S * p.cblocks;
+    p.m_tiles = p.tiles_w * p.tiles_h * tiles_n; p.n_tiles = (outc + bn - 1) / bn;
+    p.a_mn = 0; p.b_mn = flip ? 1 : 0; p.a_bytes = p.BW * p.BH * p.BI * ROW_BYTES;
+    p.maxabs = maxabs; p.status = status;
+    return bn == 256 ? launch_gemm_bn<256>(ma, mb, mc, p, st) : launch_gemm_bn<128>(ma, mb, mc, p, st);
 }
 
 static void wgrad_plan(int Nimg, int H, int W, int C, int K, int R, WgradParams* p) {
@@ -531,15 +592,19 @@ int umma_conv_wgrad_partials(const int8_t* x, const int8_t* err, int32_t* partia
                              int W, int C, int K, int R, int S, int pad, int32_t* status, cudaStream_t st) {
     WgradParams p{};
     wgrad_plan(Nimg, H, W, C, K, R, &p);
-    CUtensorMap me, mx;
+    CUtensorMap me, mx, mp;
     {
         uint32_t box[4] = {128, (uint32_t)p.BW, (uint32_t)p.BH, (uint32_t)p.BI};
         uint64_t de[4] = {(uint64_t)K, (uint64_t)W, (uint64_t)H, (uint64_t)Nimg};
         uint64_t se[3] = {(uint64_t)K, (uint64_t)W * K, (uint64_t)H * W * K};
-        if (int e = encode_map(&me, err, 4, de, se, box)) return e;
+        if (int e = encode_map(&me, err, false, 4, de, se, box)) return e;
         uint64_t dx[4] = {(uint64_t)C, (uint64_t)W, (uint64_t)H, (uint64_t)Nimg};
         uint64_t sx[3] = {(uint64_t)C, (uint64_t)W * C, (uint64_t)H * W * C};
-        if (int e = encode_map(&mx, x, 4, dx, sx, box)) return e;
+        if (int e = encode_map(&mx, x, false, 4, dx, sx, box)) return e;
+        uint64_t dp[4] = {(uint64_t)C, (uint64_t)R * S, (uint64_t)K, (uint64_t)p.splits};
+        uint64_t sp[3] = {(uint64_t)C * 4, (uint64_t)R * S * C * 4, (uint64_t)K * R * S * C * 4};
+        uint32_t bp[4] = {32, 1, 128, 1};
+        if (int e = encode_map(&mp, partial, true, 4, dp, sp, bp)) return e;
     }
     p.H = H; p.W = W; p.C = C; p.K = K; p.R = R; p.S = S; p.pad = pad; p.Nimg = Nimg;
     const int rows = p.BW * p.BH * p.BI;
@@ -547,14 +612,10 @@ int umma_conv_wgrad_partials(const int8_t* x, const int8_t* err, int32_t* partia
     p.mma_per_chunk = (rows + 31) / 32;
     p.partial = partial; p.status = status;
     *splits_out = p.splits;
-    static bool attr_set = false;
-    if (!attr_set) {
-        cudaError_t e = cudaFuncSetAttribute(umma_wgrad_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, WG_SMEM_BYTES);
-        if (e != cudaSuccess) return set_cuda_error(e);
-        attr_set = true;
-    }
+    cudaError_t e = cudaFuncSetAttribute(umma_wgrad_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, WG_SMEM_BYTES);
+    if (e != cudaSuccess) return set_cuda_error(e);
     dim3 grid(p.splits, R * p.k_tiles * p.c_tiles);
-    umma_wgrad_kernel<<<grid, UMMA_THREADS, WG_SMEM_BYTES, st>>>(me, mx, p);
+    umma_wgrad_kernel<<<grid, UMMA_THREADS, WG_SMEM_BYTES, st>>>(me, mx, mp, p);
     return set_cuda_error(cudaGetLastError());
 }
 

@@ -89,30 +89,24 @@ def conv_fprop_acc(x, w, pad=1, stride=1):
     P, Q = H + 2 * pad - R + 1, W + 2 * pad - S + 1
     y32 = torch.empty((N, P, Q, K), dtype=torch.int32, device=x.device)
     mx = torch.empty(1, dtype=torch.int32, device=x.device)
-    _call("niti_conv_fprop_i8", 1, 2 * N * P * Q * K * R * S * C, x.numel() + w.numel() + 4 * y32.numel(),
-          lib.niti_conv_fprop_i8, _p(x), _p(w), _p(y32), _p(mx), N, H, W, C, K, R, S, pad, stride,
-          _p(status_word(x.device)), _st())
+    nbytes = lib.niti_conv_fprop_scratch_bytes(N, H, W, C, K, R, S)
+    sc = scratch(x.device, nbytes) if nbytes else None
+    _call("niti_conv_fprop_i8", 3 if nbytes else 1, 2 * N * P * Q * K * R * S * C, x.numel() + w.numel() + 4 * y32.numel(),
+          lib.niti_conv_fprop_i8, _p(x), _p(w), _p(y32), _p(mx), _p(sc), sc.numel() if nbytes else 0,
+          N, H, W, C, K, R, S, pad, stride, _p(status_word(x.device)), _st())
     return y32, mx
 
 
-def flip_transpose(w):
-    _need_cuda(w)
-    K, R, S, C = w.shape
-    wt = torch.empty((C, R, S, K), dtype=torch.int8, device=w.device)
-    _call("niti_weight_flip_transpose_i8", 1, 0, 2 * w.numel(), lib.niti_weight_flip_transpose_i8, _p(w), _p(wt), K, R, S, C, _st())
-    return wt
-
-
-def conv_dgrad_acc(err, wt, pad=1):
-    """err [N,H,W,K], wt [C,R,S,K] (flip_transpose of the filters) -> int32 [N,H,W,C]."""
-    _need_cuda(err, wt)
+def conv_dgrad_acc(err, w, pad=1):
+    """err [N,H,W,K] with the layer's own filters w [K,R,S,C] -> int32 [N,H,W,C] (error w.r.t. the input)."""
+    _need_cuda(err, w)
     N, H, W, K = err.shape
-    C, R, S, K2 = wt.shape
+    K2, R, S, C = w.shape
     assert K == K2
     e32 = torch.empty((N, H, W, C), dtype=torch.int32, device=err.device)
     mx = torch.empty(1, dtype=torch.int32, device=err.device)
-    _call("niti_conv_dgrad_i8", 1, 2 * N * H * W * K * R * S * C, err.numel() + wt.numel() + 4 * e32.numel(),
-          lib.niti_conv_dgrad_i8, _p(err), _p(wt), _p(e32), _p(mx), N, H, W, C, K, R, S, pad,
+    _call("niti_conv_dgrad_i8", 1, 2 * N * H * W * K * R * S * C, err.numel() + w.numel() + 4 * e32.numel(),
+          lib.niti_conv_dgrad_i8, _p(err), _p(w), _p(e32), _p(mx), N, H, W, C, K, R, S, pad,
           _p(status_word(err.device)), _st())
     return e32, mx
 
@@ -125,7 +119,7 @@ def conv_wgrad_acc(x, err, R=3, S=3, pad=1, out=None):
     mx = torch.empty(1, dtype=torch.int32, device=x.device)
     nbytes = lib.niti_conv_wgrad_scratch_bytes(N, H, W, C, K, R, S)
     sc = scratch(x.device, nbytes)
-    _call("niti_conv_wgrad_i8", 2, 2 * N * H * W * K * R * S * C, x.numel() + err.numel() + 4 * g32.numel(),
+    _call("niti_conv_wgrad_i8", 2 if C % 128 == 0 else 3, 2 * N * H * W * K * R * S * C, x.numel() + err.numel() + 4 * g32.numel(),
           lib.niti_conv_wgrad_i8, _p(x), _p(err), _p(g32), _p(mx), _p(sc), sc.numel(), N, H, W, C, K, R, S, pad,
           _p(status_word(x.device)), _st())
     return g32, mx
@@ -214,15 +208,11 @@ def loss_err(out8, out_exp, target, seed, rng_stream=0xFFFF, sample_offset=0):
     return err
 
 
-def update(w, g32, maxabs, mu, mode=ROUND_PSEUDO_STOCHASTIC, seed=None, rng_stream=0, wt=None):
-    """In-place weight update; refreshes the flipped/transposed bank `wt` when given."""
-    _need_cuda(w, g32, maxabs, wt)
-    if wt is not None:
-        K, R, S, C = w.shape
-    else:
-        K = R = S = C = 0
-    _call("niti_update_i8", 1, 0, (7 if wt is not None else 6) * w.numel(), lib.niti_update_i8, _p(w), _p(g32), _p(maxabs),
-          w.numel(), mu, mode, _p(seed), rng_stream, _p(wt), K, R, S, C, _st())
+def update(w, g32, maxabs, mu, mode=ROUND_PSEUDO_STOCHASTIC, seed=None, rng_stream=0):
+    """In-place integer SGD update of the int8 weights from their int32 gradient accumulators."""
+    _need_cuda(w, g32, maxabs)
+    _call("niti_update_i8", 1, 0, 6 * w.numel(), lib.niti_update_i8, _p(w), _p(g32), _p(maxabs),
+          w.numel(), mu, mode, _p(seed), rng_stream, _st())
 
 
 def quantize_input(x):

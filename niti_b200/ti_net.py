@@ -65,5 +65,3 @@ class TiNet(Module):
                 dev = l.weight.device
                 l.weight = state_dict[layer_prefix + 'weight'].to(device=dev, dtype=torch.int8).contiguous()
                 l.weight_exp = exp_tensor(state_dict[layer_prefix + 'weight_exp'], dev)
-                if hasattr(l, 'refresh_weight_t'):
-                    l.refresh_weight_t()

@@ -31,7 +31,7 @@ class UpdateWeight(Module):
     def weight_update(self):
         """vanilla SGD on int8 weights: w <- clamp(w - grad_calc(grad_int32acc, GRAD_BITWIDTH))"""
         ops.update(self.weight, self.grad_int32acc, self.grad_maxabs, GRAD_BITWIDTH, _mode(GRAD_ROUND_METHOD),
-                   RNG_SEED(self.weight.device), 16 * self.layer_id + 2, wt=getattr(self, "weight_t", None))
+                   RNG_SEED(self.weight.device), 16 * self.layer_id + 2)
 
 
 def _fake_max(shift):
@@ -284,12 +284,6 @@ class TiConv2d(UpdateWeight):
         self.stride = stride
         self.padding = padding
         self.fuse_relu = fuse_relu
-        self.weight_t = None if first_layer else ops.flip_transpose(self.weight)
-
-    def refresh_weight_t(self):
-        """Rebuild the flipped/transposed filter bank after the weights were replaced from outside."""
-        if not self.first_layer:
-            self.weight_t = ops.flip_transpose(self.weight)
 
     def forward(self, input):
         self.act, self.act_in_exp = input
@@ -302,7 +296,8 @@ class TiConv2d(UpdateWeight):
         err_in = err_in.contiguous()
         err_out = None
         if not self.first_layer:
-            acc, mx = ops.conv_dgrad_acc(err_in, self.weight_t, self.padding)
+            # the reference builds flip(w).transpose(0,3) here (:404); the kernel reads w in place
+            acc, mx = ops.conv_dgrad_acc(err_in, self.weight, self.padding)
             err_out, self.err_exp, _ = _calc(acc, ops.CALC_ERR, BITWIDTH, ERROR_ROUND_METHOD, 16 * self.layer_id + 1,
                                              exp_tensor(self.err_exp, acc.device), self.weight_exp, mx, False,
                                              SAMPLE_OFFSET * acc[0].numel())

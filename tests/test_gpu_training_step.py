@@ -41,8 +41,6 @@ def build(cfg, seed, dropout, fuse_relu, mu):
     for l, w, e in zip(model.weighted_layers(), weights, wexps):
         l.weight = torch.from_numpy(w).to(DEV)
         l.weight_exp = ti_torch.exp_tensor(e, DEV)
-        if hasattr(l, "refresh_weight_t"):
-            l.refresh_weight_t()
     oracle = O.Net(cfg, weights, wexps, dropout=dropout, mu=mu, seed=seed)
     return model, oracle, rng
 
@@ -64,8 +62,6 @@ def run_steps(cfg, B, seed, dropout, steps, mu, fuse_relu, use_graph, rec=None):
         for i, l in enumerate(model.weighted_layers()):
             assert np.array_equal(l.grad_int32acc.cpu().numpy(), grads[i].astype(np.int32)), f"grad {i} step {step}"
             assert np.array_equal(l.weight.cpu().numpy(), oracle.w[i]), f"weights {i} step {step}"
-            if getattr(l, "weight_t", None) is not None:
-                assert np.array_equal(l.weight_t.cpu().numpy(), O.flip_transpose(oracle.w[i])), f"weight_t {i}"
             if rec is not None:
                 assert crc(l.weight.cpu().numpy()) == rec[f"s{step}_w{i}_crc"]
                 assert crc(l.grad_int32acc.cpu().numpy()) == rec[f"s{step}_g{i}_crc"]
