@@ -102,6 +102,36 @@ NITI_API int niti_conv_wgrad_i8(const int8_t* x, const int8_t* err, int32_t* g32
                        int N, int H, int W, int C, int K, int R, int S, int pad,
                        int32_t* status, void* stream);
 
+/* Convolution and requantisation in ONE pass over the output: TiConv2d.forward's
+ * conv2d_int8 + act_calc (ti_torch.py:391-397) and TiConv2d.backward's error path conv2d_int8 +
+ * err_calc (ti_torch.py:403-407).  The shift depends on the max of the whole int32 tensor, which
+ * is only known when the contraction has finished, so the kernel narrows with a PREDICTED shift
+ * (the one this layer needed last time, state[0]) while it reduces the true max|acc|; a one-thread
+ * kernel then derives the true shift, and only if the prediction was wrong the contraction is
+ * launched again (that launch returns at once otherwise).  The result is always the exact one;
+ * the int32 tensor never touches memory.
+ *   state: device int32[4] owned by the caller, one per layer and direction, zeroed once:
+ *          [0] shift (in: prediction, out: true value), [1] max|acc|, [2] 1 if the last call had
+ *          to redo, [3] number of redos so far.
+ *   kind is ACT for fprop (exp_out = shift + *exp_a + *exp_b) and ERR for dgrad; target 7 bits.
+ * Shapes: niti_conv_*_requant_supported() != 0 (the tensor-core shapes of the entry points above
+ * with 16-byte-multiple output channels); otherwise NITI_ERR_UNSUPPORTED and the caller uses
+ * niti_conv_fprop_i8 / niti_conv_dgrad_i8 + niti_requant_i8.  `scratch` as for niti_conv_fprop_i8.
+ */
+NITI_API int niti_conv_fprop_requant_supported(int C, int K, int R, int S, int pad);
+NITI_API int niti_conv_dgrad_requant_supported(int C, int K, int R, int S, int pad);
+NITI_API int niti_conv_fprop_requant_i8(const int8_t* x, const int8_t* w, int8_t* y8, int32_t* state,
+                       void* scratch, size_t scratch_bytes,
+                       int N, int H, int W, int C, int K, int R, int S, int pad,
+                       int round_mode, const uint64_t* seed, uint32_t rng_stream, uint64_t rng_offset, int relu,
+                       const int32_t* exp_a, const int32_t* exp_b, int32_t* exp_out, int32_t* shift_out,
+                       int32_t* status, void* stream);
+NITI_API int niti_conv_dgrad_requant_i8(const int8_t* err, const int8_t* w, int8_t* e8, int32_t* state,
+                       int N, int H, int W, int C, int K, int R, int S, int pad,
+                       int round_mode, const uint64_t* seed, uint32_t rng_stream, uint64_t rng_offset,
+                       const int32_t* exp_a, const int32_t* exp_b, int32_t* exp_out, int32_t* shift_out,
+                       int32_t* status, void* stream);
+
 /* int8mm_cuda.int8_mm (int8mm.cpp:9-18, int8mm_kernel.cu:8-34) as used by TiLinear
  * (ti_torch.py:241-266), without the padding / .contiguous() copies around it:
  * C32[M][N] = op(A) * op(B); trans_a == 0: A is [M][K], else [K][M];

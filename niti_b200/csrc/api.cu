@@ -84,7 +84,7 @@ extern "C" int niti_conv_fprop_i8(const int8_t* x, const int8_t* w, int32_t* y32
     if (int e = clear_word(maxabs, st)) return e;
     ConvPath path = fprop_path(C, K, R, S, pad);
     if (!(aligned16(x) && aligned16(w) && aligned16(y32))) path = CONV_SIMT;
-    if (path == CONV_TC) return umma_conv(x, w, y32, maxabs, N, H, W, C, K, R, S, pad, 0, status, st);
+    if (path == CONV_TC) return umma_conv(x, w, y32, maxabs, N, H, W, C, K, R, S, pad, 0, nullptr, status, st);
     if (path == CONV_THIN) {
         const size_t m = static_cast<size_t>(N) * H * W;
         if (!scratch || !aligned16(scratch) || scratch_bytes < niti_conv_fprop_scratch_bytes(N, H, W, C, K, R, S)) return NITI_ERR_SCRATCH;
@@ -92,7 +92,7 @@ extern "C" int niti_conv_fprop_i8(const int8_t* x, const int8_t* w, int32_t* y32
         int8_t* wp = xcol + align_up(m * 32, 1024);
         if (int e = im2col32(x, xcol, N, H, W, C, R, S, pad, st)) return e;
         if (int e = pad_rows32(w, wp, K, R * S * C, st)) return e;
-        return umma_gemm(xcol, wp, y32, maxabs, static_cast<int>(m), K, 32, 0, 1, 1, status, st);
+        return umma_gemm(xcol, wp, y32, maxabs, static_cast<int>(m), K, 32, 0, 1, 1, nullptr, status, st);
     }
     return simt_conv_fprop(x, w, y32, maxabs, N, H, W, C, K, R, S, pad, st);
 }
@@ -104,7 +104,7 @@ extern "C" int niti_conv_dgrad_i8(const int8_t* err, const int8_t* w, int32_t* e
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (int e = clear_word(maxabs, st)) return e;
     if (K % 128 == 0 && C % 16 == 0 && aligned16(err) && aligned16(w) && aligned16(e32))
-        return umma_conv(err, w, e32, maxabs, N, H, W, C, K, R, S, pad, 1, status, st);
+        return umma_conv(err, w, e32, maxabs, N, H, W, C, K, R, S, pad, 1, nullptr, status, st);
     return simt_conv_dgrad(err, w, e32, maxabs, N, H, W, C, K, R, S, pad, st);
 }
 
@@ -143,7 +143,7 @@ extern "C" int niti_conv_wgrad_i8(const int8_t* x, const int8_t* err, int32_t* g
     int32_t* partial = reinterpret_cast<int32_t*>(xcol + align_up(m * 32, 1024));
     const int splits = umma_gemm_splits(K, 32, static_cast<int>(m));
     if (int e = im2col32(x, xcol, N, H, W, C, R, S, pad, st)) return e;
-    if (int e = umma_gemm(err, xcol, partial, nullptr, K, 32, static_cast<int>(m), 1, 0, splits, status, st)) return e;
+    if (int e = umma_gemm(err, xcol, partial, nullptr, K, 32, static_cast<int>(m), 1, 0, splits, nullptr, status, st)) return e;
     return reduce_rows32(partial, splits, K, R * S * C, g32, maxabs, st);
 }
 
@@ -155,6 +155,67 @@ extern "C" int niti_gemm_i8(const int8_t* A, const int8_t* B, int32_t* C32, uint
     const int pitch_a = trans_a ? M : K, pitch_b = trans_b ? K : N;
     const bool tc = pitch_a % 16 == 0 && pitch_b % 16 == 0 && N % 4 == 0 && M >= 64 && N >= 32 && K >= 32 && aligned16(A) &&
                     aligned16(B) && aligned16(C32);
-    if (tc) return umma_gemm(A, B, C32, maxabs, M, N, K, trans_a, trans_b, 1, status, st);
+    if (tc) return umma_gemm(A, B, C32, maxabs, M, N, K, trans_a, trans_b, 1, nullptr, status, st);
     return simt_gemm(A, B, C32, maxabs, M, N, K, trans_a, trans_b, st);
+}
+
+// ---------------------------------------------------------------- contraction + requantisation in one pass
+static int fused_conv(const int8_t* in, const int8_t* w, int8_t* out8, int32_t* state, void* scratch, size_t scratch_bytes,
+                      int N, int H, int W, int C, int K, int R, int S, int pad, int flip, int kind, int round_mode,
+                      const uint64_t* seed, uint32_t rng_stream, uint64_t rng_offset, int relu, const int32_t* exp_a,
+                      const int32_t* exp_b, int32_t* exp_out, int32_t* shift_out, int32_t* status, cudaStream_t st) {
+    FusedArgs f{state, 0, round_mode, relu, reinterpret_cast<const unsigned long long*>(seed), rng_stream, rng_offset};
+    unsigned* maxabs = reinterpret_cast<unsigned*>(state + 1);
+    const bool thin = !flip && fprop_path(C, K, R, S, pad) == CONV_THIN;
+    const size_t m = static_cast<size_t>(N) * H * W;
+    int8_t* xcol = static_cast<int8_t*>(scratch);
+    int8_t* wp = thin ? xcol + align_up(m * 32, 1024) : nullptr;
+    if (thin) {
+        if (!scratch || !aligned16(scratch) || scratch_bytes < niti_conv_fprop_scratch_bytes(N, H, W, C, K, R, S)) return NITI_ERR_SCRATCH;
+        if (int e = im2col32(in, xcol, N, H, W, C, R, S, pad, st)) return e;
+        if (int e = pad_rows32(w, wp, K, R * S * C, st)) return e;
+    }
+    if (int e = clear_word(maxabs, st)) return e;
+    for (int pass = 0; pass < 2; ++pass) {
+        f.only_if_redo = pass;
+        int rc = thin ? umma_gemm(xcol, wp, out8, maxabs, static_cast<int>(m), K, 32, 0, 1, 1, &f, status, st)
+                      : umma_conv(in, w, out8, maxabs, N, H, W, C, K, R, S, pad, flip, &f, status, st);
+        if (rc) return rc;
+        if (pass == 0)
+            if (int e = requant_verify(state, kind, 7, exp_a, exp_b, exp_out, shift_out, st)) return e;
+    }
+    return NITI_OK;
+}
+
+extern "C" int niti_conv_fprop_requant_supported(int C, int K, int R, int S, int pad) {
+    const ConvPath p = fprop_path(C, K, R, S, pad);
+    return (p == CONV_TC || p == CONV_THIN) && K % 16 == 0;
+}
+extern "C" int niti_conv_dgrad_requant_supported(int C, int K, int R, int S, int pad) {
+    return same_padding(R, S, pad) && K % 128 == 0 && C % 16 == 0;
+}
+
+extern "C" int niti_conv_fprop_requant_i8(const int8_t* x, const int8_t* w, int8_t* y8, int32_t* state, void* scratch,
+                                          size_t scratch_bytes, int N, int H, int W, int C, int K, int R, int S, int pad,
+                                          int round_mode, const uint64_t* seed, uint32_t rng_stream, uint64_t rng_offset,
+                                          int relu, const int32_t* exp_a, const int32_t* exp_b, int32_t* exp_out,
+                                          int32_t* shift_out, int32_t* status, void* stream) {
+    NITI_REQUIRE(x && w && y8 && state && N > 0 && H > 0 && W > 0 && C > 0 && K > 0 && R > 0 && S > 0 && pad >= 0);
+    NITI_REQUIRE(round_mode >= 0 && round_mode <= 2 && (seed || round_mode != NITI_ROUND_STOCHASTIC));
+    NITI_REQUIRE(aligned16(x) && aligned16(w) && aligned16(y8));
+    if (!niti_conv_fprop_requant_supported(C, K, R, S, pad)) return NITI_ERR_UNSUPPORTED;
+    return fused_conv(x, w, y8, state, scratch, scratch_bytes, N, H, W, C, K, R, S, pad, 0, NITI_CALC_ACT, round_mode, seed,
+                      rng_stream, rng_offset, relu, exp_a, exp_b, exp_out, shift_out, status, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int niti_conv_dgrad_requant_i8(const int8_t* err, const int8_t* w, int8_t* e8, int32_t* state, int N, int H, int W,
+                                          int C, int K, int R, int S, int pad, int round_mode, const uint64_t* seed,
+                                          uint32_t rng_stream, uint64_t rng_offset, const int32_t* exp_a, const int32_t* exp_b,
+                                          int32_t* exp_out, int32_t* shift_out, int32_t* status, void* stream) {
+    NITI_REQUIRE(err && w && e8 && state && N > 0 && H > 0 && W > 0 && C > 0 && K > 0 && R > 0 && S > 0 && pad >= 0);
+    NITI_REQUIRE(round_mode >= 0 && round_mode <= 2 && (seed || round_mode != NITI_ROUND_STOCHASTIC));
+    NITI_REQUIRE(aligned16(err) && aligned16(w) && aligned16(e8));
+    if (!niti_conv_dgrad_requant_supported(C, K, R, S, pad)) return NITI_ERR_UNSUPPORTED;
+    return fused_conv(err, w, e8, state, nullptr, 0, N, H, W, C, K, R, S, pad, 1, NITI_CALC_ERR, round_mode, seed, rng_stream,
+                      rng_offset, 0, exp_a, exp_b, exp_out, shift_out, status, static_cast<cudaStream_t>(stream));
 }

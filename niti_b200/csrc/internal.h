@@ -10,12 +10,23 @@ namespace niti {
 int set_cuda_error(cudaError_t e);
 int set_cuda_error_text(const char* text);
 
-// tensor-core (tcgen05) paths, umma_kernels.cu
+// Requantisation fused into a contraction's epilogue: the kernel narrows with the shift it finds in
+// state[0]; `only_if_redo` launches are no-ops unless state[2] is set (see requant_verify).
+struct FusedArgs {
+    const int32_t* state;
+    int only_if_redo;
+    int mode, relu;
+    const unsigned long long* seed;
+    unsigned rng_stream;
+    unsigned long long rng_offset;
+};
+
+// tensor-core (tcgen05) paths, umma_kernels.cu; `out` is int32 (fused == null) or int8
 int umma_gemm_splits(int M, int N, int K);
-int umma_gemm(const int8_t* A, const int8_t* B, int32_t* C32, unsigned* maxabs, int M, int N, int K,
-              int trans_a, int trans_b, int splits, int32_t* status, cudaStream_t st);
-int umma_conv(const int8_t* x, const int8_t* w, int32_t* y32, unsigned* maxabs, int Nimg, int H, int W, int C, int K,
-              int R, int S, int pad, int flip, int32_t* status, cudaStream_t st);
+int umma_gemm(const int8_t* A, const int8_t* B, void* out, unsigned* maxabs, int M, int N, int K, int trans_a,
+              int trans_b, int splits, const FusedArgs* fused, int32_t* status, cudaStream_t st);
+int umma_conv(const int8_t* x, const int8_t* w, void* out, unsigned* maxabs, int Nimg, int H, int W, int C, int K,
+              int R, int S, int pad, int flip, const FusedArgs* fused, int32_t* status, cudaStream_t st);
 size_t umma_wgrad_scratch_bytes(int Nimg, int H, int W, int C, int K, int R, int S);
 int umma_conv_wgrad_partials(const int8_t* x, const int8_t* err, int32_t* partial, int* splits_out, int Nimg, int H,
                              int W, int C, int K, int R, int S, int pad, int32_t* status, cudaStream_t st);
@@ -33,5 +44,9 @@ int reduce_partials(const int32_t* partial, int splits, long long n, int32_t* ou
 int reduce_rows32(const int32_t* partial, int splits, int rows, int cols_out, int32_t* out, unsigned* maxabs, cudaStream_t st);
 int im2col32(const int8_t* x, int8_t* xcol, int Nimg, int H, int W, int C, int R, int S, int pad, cudaStream_t st);
 int pad_rows32(const int8_t* w, int8_t* wp, int K, int rsc, cudaStream_t st);
+// state = {shift applied, max|acc|, redo flag, redo count}: derive the true shift from state[1],
+// set state[2] = (true != state[0]), store the true shift in state[0], write exponent / shift outputs
+int requant_verify(int32_t* state, int kind, int target_bits, const int32_t* exp_a, const int32_t* exp_b,
+                   int32_t* exp_out, int32_t* shift_out, cudaStream_t st);
 
 }  // namespace niti

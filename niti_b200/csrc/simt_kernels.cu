@@ -96,6 +96,23 @@ requant_kernel(const int32_t* __restrict__ acc, int8_t* __restrict__ out, const 
     }
 }
 
+__global__ void requant_verify_kernel(int32_t* state, int kind, int target_bits, const int32_t* exp_a, const int32_t* exp_b,
+                                      int32_t* exp_out, int32_t* shift_out) {
+    bool zero_out;
+    const int shift = shift_for(static_cast<unsigned>(state[1]), kind, target_bits, &zero_out);
+    const int redo = shift != state[0];
+    state[2] = redo;
+    state[3] += redo;
+    state[0] = shift;
+    if (exp_out) *exp_out = shift + (exp_a ? *exp_a : 0) + (exp_b ? *exp_b : 0);
+    if (shift_out) *shift_out = shift;
+}
+int requant_verify(int32_t* state, int kind, int target_bits, const int32_t* exp_a, const int32_t* exp_b,
+                   int32_t* exp_out, int32_t* shift_out, cudaStream_t st) {
+    requant_verify_kernel<<<1, 1, 0, st>>>(state, kind, target_bits, exp_a, exp_b, exp_out, shift_out);
+    return set_cuda_error(cudaGetLastError());
+}
+
 __global__ void __launch_bounds__(256)
 absmax_kernel(const int32_t* __restrict__ acc, long long n, unsigned* maxabs) {
     unsigned m = 0;
@@ -178,29 +195,35 @@ int reduce_rows32(const int32_t* partial, int splits, int rows, int cols_out, in
 
 // Thin convolutions (R*S*C <= 32, the 3-channel first layer) run as GEMMs over an explicit patch
 // matrix: xcol[pixel][32] holds the R*S*C bytes of the pixel's receptive field, zero padded.
+// One thread per pixel: walks the receptive field in (r, s, c) order, packs the bytes into eight
+// words and writes the 32-byte row with two 16-byte stores.
 __global__ void __launch_bounds__(256)
-im2col32_kernel(const int8_t* __restrict__ x, uint32_t* __restrict__ xcol, int Nimg, int H, int W, int C, int R, int S, int pad) {
+im2col32_kernel(const int8_t* __restrict__ x, uint4* __restrict__ xcol, int Nimg, int H, int W, int C, int R, int S, int pad) {
     const int rsc = R * S * C;
-    const long long total = static_cast<long long>(Nimg) * H * W * 8;  // 8 words of 4 bytes per pixel
-    for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
-         i += static_cast<long long>(gridDim.x) * blockDim.x) {
-        const int t = static_cast<int>(i & 7);
-        const long long pix = i >> 3;
+    const long long pixels = static_cast<long long>(Nimg) * H * W;
+    for (long long pix = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; pix < pixels;
+         pix += static_cast<long long>(gridDim.x) * blockDim.x) {
         const int wq = static_cast<int>(pix % W);
         const int hq = static_cast<int>((pix / W) % H);
         const long long n = pix / (static_cast<long long>(W) * H);
-        uint32_t v = 0;
+        uint32_t word[8];
+        int c = 0, sx = 0, r = 0;
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            const int e = t * 4 + j;
-            if (e < rsc) {
-                const int c = e % C, sx = (e / C) % S, r = e / (C * S);
-                const int hh = hq + r - pad, ww = wq + sx - pad;
-                if (hh >= 0 && hh < H && ww >= 0 && ww < W)
-                    v |= static_cast<uint32_t>(static_cast<uint8_t>(x[((n * H + hh) * W + ww) * C + c])) << (8 * j);
+        for (int t = 0; t < 8; ++t) {
+            uint32_t v = 0;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                if (t * 4 + j < rsc) {
+                    const int hh = hq + r - pad, ww = wq + sx - pad;
+                    if (hh >= 0 && hh < H && ww >= 0 && ww < W)
+                        v |= static_cast<uint32_t>(static_cast<uint8_t>(__ldg(x + ((n * H + hh) * W + ww) * C + c))) << (8 * j);
+                    if (++c == C) { c = 0; if (++sx == S) { sx = 0; ++r; } }
+                }
             }
+            word[t] = v;
         }
-        xcol[i] = v;
+        xcol[pix * 2] = make_uint4(word[0], word[1], word[2], word[3]);
+        xcol[pix * 2 + 1] = make_uint4(word[4], word[5], word[6], word[7]);
     }
 }
 // w[K][rsc] -> wp[K][32], zero padded
@@ -209,8 +232,8 @@ __global__ void pad_rows32_kernel(const int8_t* __restrict__ w, int8_t* __restri
     if (i < K * 32) { const int k = i >> 5, e = i & 31; wp[i] = e < rsc ? w[k * rsc + e] : int8_t(0); }
 }
 int im2col32(const int8_t* x, int8_t* xcol, int Nimg, int H, int W, int C, int R, int S, int pad, cudaStream_t st) {
-    const long long total = static_cast<long long>(Nimg) * H * W * 8;
-    im2col32_kernel<<<blocks_for(total, 256, sm_count_simt() * 16), 256, 0, st>>>(x, reinterpret_cast<uint32_t*>(xcol), Nimg, H, W, C, R, S, pad);
+    const long long total = static_cast<long long>(Nimg) * H * W;
+    im2col32_kernel<<<blocks_for(total, 256, sm_count_simt() * 16), 256, 0, st>>>(x, reinterpret_cast<uint4*>(xcol), Nimg, H, W, C, R, S, pad);
     return set_cuda_error(cudaGetLastError());
 }
 int pad_rows32(const int8_t* w, int8_t* wp, int K, int rsc, cudaStream_t st) {
@@ -668,11 +691,40 @@ gemm_generic_kernel(const int8_t* __restrict__ A, const int8_t* __restrict__ B, 
     }
     warp_atomic_max(maxabs, mx);
 }
+// GEMM with B stored [K][N], N % 4 == 0: each thread produces four adjacent outputs from 32-bit
+// loads of B (FC error e*W and FC gradient e^T*a: short reductions, wide outputs).
+__global__ void __launch_bounds__(256)
+gemm_bn4_kernel(const int8_t* __restrict__ A, const int8_t* __restrict__ B, int32_t* __restrict__ C32, unsigned* maxabs,
+                int M, int N, int K, int trans_a) {
+    unsigned mx = 0;
+    const int n4 = N >> 2;
+    const long long sa_m = trans_a ? 1 : K, sa_k = trans_a ? M : 1;
+    for (long long o = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; o < static_cast<long long>(M) * n4;
+         o += static_cast<long long>(gridDim.x) * blockDim.x) {
+        const long long m = o / n4;
+        const int nq = static_cast<int>(o % n4);
+        const uint32_t* bp = reinterpret_cast<const uint32_t*>(B) + nq;
+        const int8_t* ap = A + m * sa_m;
+        int a0 = 0, a1 = 0, a2 = 0, a3 = 0;
+#pragma unroll 4
+        for (int k = 0; k < K; ++k) {
+            const int a = ap[k * sa_k];
+            const uint32_t b = __ldg(bp + static_cast<long long>(k) * n4);
+            a0 += a * static_cast<int8_t>(b); a1 += a * static_cast<int8_t>(b >> 8);
+            a2 += a * static_cast<int8_t>(b >> 16); a3 += a * static_cast<int8_t>(b >> 24);
+        }
+        reinterpret_cast<int4*>(C32)[o] = make_int4(a0, a1, a2, a3);
+        mx = max(max(mx, iabs_u(a0)), max(iabs_u(a1), max(iabs_u(a2), iabs_u(a3))));
+    }
+    warp_atomic_max(maxabs, mx);
+}
 int simt_gemm(const int8_t* A, const int8_t* B, int32_t* C32, unsigned* maxabs, int M, int N, int K, int trans_a,
               int trans_b, cudaStream_t st) {
     const long long outs = static_cast<long long>(M) * N;
     if (!trans_a && trans_b && K >= 256)
         gemm_kk_kernel<<<blocks_for(outs * 32, 256, sm_count_simt() * 16), 256, 0, st>>>(A, B, C32, maxabs, M, N, K);
+    else if (!trans_b && N % 4 == 0 && reinterpret_cast<uintptr_t>(B) % 4 == 0 && reinterpret_cast<uintptr_t>(C32) % 16 == 0)
+        gemm_bn4_kernel<<<blocks_for(outs / 4, 128, sm_count_simt() * 32), 128, 0, st>>>(A, B, C32, maxabs, M, N, K, trans_a);
     else
         gemm_generic_kernel<<<blocks_for(outs, 256, sm_count_simt() * 32), 256, 0, st>>>(A, B, C32, maxabs, M, N, K, trans_a, trans_b);
     return set_cuda_error(cudaGetLastError());

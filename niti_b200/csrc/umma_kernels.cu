@@ -23,6 +23,7 @@
 
 #include "internal.h"
 #include "ptx.cuh"
+#include "requant.cuh"
 
 namespace niti {
 
@@ -45,7 +46,7 @@ __device__ __forceinline__ void stage_row(uint32_t buf, int row, const uint32_t 
 }
 
 // ------------------------------------------------------------------------------------------------
-// GEMM / convolution forward (and error-backward, which is a forward conv over flipped weights)
+// GEMM / convolution forward / error-backward
 // ------------------------------------------------------------------------------------------------
 struct GemmParams {
     int conv;              // 0: plain GEMM, 1: implicit-GEMM convolution (A tile = 4-D box of pixels)
@@ -62,17 +63,28 @@ struct GemmParams {
     int BW, BH, BI;        // pixels of one tile along w, h and images; BW*BH*BI <= 128
     int tiles_w, tiles_h;
     int cblocks;           // reduction channels / 128
-    unsigned* maxabs;      // may be null (split-K partials)
+    unsigned* maxabs;      // max|acc| is reduced into this word; may be null (split-K partials)
     int32_t* status;
+    // fused requantisation (FUSED kernels): int8 output narrowed by the shift in state[0]
+    const int32_t* state;  // [0] shift to apply, [2] "redo" flag of the verification kernel
+    int only_if_redo;      // 1: this launch does nothing unless state[2] != 0
+    int mode, relu;
+    const unsigned long long* seed;
+    unsigned rng_stream;
+    unsigned long long rng_offset;
 };
 
-template <int BN>
+constexpr int GEMM_THREADS = 320;  // producer warp, MMA warp, two epilogue warpgroups of 4 warps
+
+template <int BN, bool FUSED>
 struct GemmCfg {
     static constexpr int B_STAGE_BYTES = BN * ROW_BYTES;
     static constexpr int STAGE_BYTES = PANEL_BYTES + B_STAGE_BYTES;
-    static constexpr int STAGES = (192 * 1024) / STAGE_BYTES;
+    // staging per epilogue warpgroup: one 128 x 128 int8 tile (fused) or two 128 x 32 int32 tiles
+    static constexpr int EPI_GROUP_BYTES = FUSED ? EPI_CHUNK_BYTES : 2 * EPI_CHUNK_BYTES;
+    static constexpr int EPI_BYTES = 2 * EPI_GROUP_BYTES;
+    static constexpr int STAGES = (224 * 1024 - EPI_BYTES) / STAGE_BYTES;
     static constexpr int TMEM_COLS = 2 * BN;  // two accumulators; 256 or 512 columns
-    static constexpr int EPI_BYTES = 2 * EPI_CHUNK_BYTES;  // double-buffered 128 x 32 int32 staging tile
     static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + EPI_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
 };
 
@@ -83,12 +95,34 @@ __device__ __forceinline__ void report_abort(int32_t* status, int code, int role
     }
 }
 
-template <int BN>
-__global__ void __launch_bounds__(UMMA_THREADS, 1)
+// Four accumulators of one row -> four int8 packed in a word (NITI's shift, see requant.cuh).
+__device__ __forceinline__ uint32_t narrow4(const uint32_t* v, int shift, int mode, int relu, const uint32_t* rnd) {
+    uint32_t w = 0;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const int x = static_cast<int>(v[j]);
+        int y;
+        if (mode == ROUND_NEAREST && shift > 0) {
+            // round half away from zero on |x|, clamp to 127; with ReLU negatives are zero anyway
+            const int t = min(static_cast<int>((static_cast<uint32_t>(x < 0 ? -x : x) + (1u << (shift - 1))) >> shift), 127);
+            y = x < 0 ? (relu ? 0 : -t) : t;
+        } else {
+            y = narrow(x, shift, mode, rnd[j]);
+            if (relu && y < 0) y = 0;
+        }
+        w |= static_cast<uint32_t>(static_cast<uint8_t>(y)) << (8 * j);
+    }
+    return w;
+}
+
+template <int BN, bool FUSED>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
 umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                  const __grid_constant__ CUtensorMap tmC, const GemmParams p) {
-    using Cfg = GemmCfg<BN>;
+    using Cfg = GemmCfg<BN, FUSED>;
     constexpr int STAGES = Cfg::STAGES;
+    if (FUSED && p.only_if_redo && p.state[2] == 0) return;  // prediction was right: nothing to redo
+
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* epi_smem = smem + STAGES * Cfg::STAGE_BYTES;
@@ -200,27 +234,39 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             }
         }
     } else {
-        // ------------------------------------------------------------------ epilogue (4 warps)
-        // Per 32-column chunk: TMEM -> registers (max|acc| on the way) -> swizzled shared-memory
-        // staging tile -> one TMA store.  Two staging tiles, so a store drains while the next
-        // chunk is read.  The store clips rows/columns outside the tensor.
-        const int q = warp & 3;  // TMEM lanes [32q, 32q+32) are the ones this warp may read
+        // ------------------------------------------------------------------ epilogue (2 x 4 warps)
+        // Warpgroup g takes this CTA's tiles g, g+2, g+4, ... (accumulator g), so the epilogues of
+        // two consecutive tiles overlap each other and the main loop.  Per group of 128 output
+        // columns: four tcgen05.ld and ONE wait, the accumulator is handed back as soon as its
+        // last columns sit in registers, max|acc| is tracked in registers, rows go to swizzled
+        // staging tiles and leave through TMA stores (which clip rows/columns outside the tensor).
+        //   plain kernels: int32 out, two rounds of two 128 x 32 staging tiles per column group;
+        //   FUSED kernels: int8 out, narrowed with the shift in state[0], one 128 x 128-byte tile.
+        const int grp = (warp - 2) >> 2;  // epilogue warpgroup 0 / 1
+        const int q = warp & 3;           // TMEM lanes [32q, 32q+32) are the ones this warp may read
         const int row_in_tile = q * 32 + lane;
-        const bool leader = threadIdx.x == 64;
-        unsigned local_max = 0;
-        uint32_t chunk_ctr = 0;
-        int it = 0;
-        for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++it) {
-            const int acc = it & 1; const uint32_t aph = (it >> 1) & 1u;
+        const int bar_id = EPI_BARRIER + grp;
+        const bool leader = (threadIdx.x == 64 + grp * 128);
+        const uint32_t buf = smem_u32(epi_smem) + grp * Cfg::EPI_GROUP_BYTES;
+        int shift = 0;
+        unsigned long long seed = 0;
+        if (FUSED) {
+            shift = p.state[0];
+            if (p.mode == ROUND_STOCHASTIC && shift > 0) seed = *p.seed;
+        }
+        int vmax[4] = {0, 0, 0, 0}, vmin[4] = {0, 0, 0, 0};
+        int i2 = 0;
+        for (int tile = blockIdx.x + grp * gridDim.x; tile < total_tiles; tile += 2 * gridDim.x, ++i2) {
+            const int acc = grp; const uint32_t aph = i2 & 1u;
             const uint32_t failed = mbar_wait(smem_u32(&tfull_bar[acc]), aph, abort_flag) ? 0u : 1u;
-            if (barrier_or(EPI_BARRIER, 128, failed)) {  // same verdict in all 128 threads
+            if (barrier_or(bar_id, 128, failed)) {  // same verdict in all 128 threads of the warpgroup
                 if (failed) report_abort(p.status, 4, 2);
                 break;
             }
             tc_fence_after();
             const int split = tile / mn_tiles, mn = tile % mn_tiles;
             const int m_t = mn / p.n_tiles, n_t = mn % p.n_tiles;
-            bool valid; int cy, cz, cw;
+            bool valid; int cy, cz, cw; long long row_lin;
             if (p.conv) {
                 const int tw = m_t % p.tiles_w, th = (m_t / p.tiles_w) % p.tiles_h, tn = m_t / (p.tiles_w * p.tiles_h);
                 const int w = tw * p.BW + row_in_tile % p.BW;
@@ -228,39 +274,95 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                 const int n = tn * p.BI + row_in_tile / (p.BW * p.BH);
                 valid = row_in_tile < p.BW * p.BH * p.BI && w < p.W && h < p.H && n < p.Nimg;
                 cy = tw * p.BW; cz = th * p.BH; cw = tn * p.BI;
+                row_lin = (static_cast<long long>(n) * p.H + h) * p.W + w;
             } else {
-                valid = m_t * BLOCK_M + row_in_tile < p.M;
+                row_lin = static_cast<long long>(m_t) * BLOCK_M + row_in_tile;
+                valid = row_lin < p.M;
                 cy = m_t * BLOCK_M; cz = split; cw = 0;
             }
             const int col0 = n_t * BN;
             const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(acc * BN);
 #pragma unroll 1
-            for (int c = 0; c < BN && col0 + c < p.N; c += 32) {
-                const uint32_t buf = smem_u32(epi_smem) + (chunk_ctr & 1u) * EPI_CHUNK_BYTES;
-                if (leader) bulk_wait_read<1>();  // the store that last used this tile has read it
-                named_barrier(EPI_BARRIER, 128);
-                uint32_t v[32];
-                tmem_ld_32x32(taddr + c, v);
-                tmem_ld_wait();
-                if (valid) {
-                    const int lim = p.N - (col0 + c);
+            for (int g0 = 0; g0 < BN && col0 + g0 < p.N; g0 += 128) {
+                uint32_t v[4][32];
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) {
-                        const int x = static_cast<int>(v[j]);
-                        if (j < lim) local_max = max(local_max, static_cast<unsigned>(x < 0 ? -x : x));
+                for (int j = 0; j < 4; ++j) tmem_ld_32x32(taddr + g0 + j * 32, v[j]);
+                tmem_ld_wait();
+                if (g0 + 128 >= BN || col0 + g0 + 128 >= p.N) {  // last group: the accumulator is free again
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(smem_u32(&tempty_bar[acc]));
+                }
+                const int lim = p.N - (col0 + g0);
+                if (valid) {
+                    // max|x| = max(max x, -min x): short chains of 3-input min/max
+                    if (lim >= 128) {
+#pragma unroll
+                        for (int j = 0; j < 4; ++j)
+#pragma unroll
+                            for (int i = 0; i < 32; i += 2) {
+                                vmax[j] = __vimax3_s32(vmax[j], static_cast<int>(v[j][i]), static_cast<int>(v[j][i + 1]));
+                                vmin[j] = __vimin3_s32(vmin[j], static_cast<int>(v[j][i]), static_cast<int>(v[j][i + 1]));
+                            }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 4; ++j)
+#pragma unroll
+                            for (int i = 0; i < 32; ++i)
+                                if (j * 32 + i < lim) {
+                                    vmax[0] = max(vmax[0], static_cast<int>(v[j][i]));
+                                    vmin[0] = min(vmin[0], static_cast<int>(v[j][i]));
+                                }
                     }
                 }
-                stage_row(buf, row_in_tile, v);
-                fence_proxy_async();
-                named_barrier(EPI_BARRIER, 128);
-                if (leader) { tma_store_4d(&tmC, buf, col0 + c, cy, cz, cw); bulk_commit(); }
-                ++chunk_ctr;
+                if constexpr (FUSED) {
+                    uint32_t packed[32];
+                    const unsigned long long e0 = p.rng_offset + static_cast<unsigned long long>(row_lin) * p.N + (col0 + g0);
+                    const bool stochastic = p.mode == ROUND_STOCHASTIC && shift > 0;
+#pragma unroll
+                    for (int j = 0; j < 4; ++j)
+#pragma unroll
+                        for (int i = 0; i < 32; i += 4) {
+                            uint32_t rnd[4] = {0, 0, 0, 0};
+                            if (stochastic) {
+                                const unsigned long long e = e0 + j * 32 + i;
+                                if ((e & 3ull) == 0) random_block(seed, p.rng_stream, e >> 2, rnd);
+                                else {
+#pragma unroll
+                                    for (int t = 0; t < 4; ++t) rnd[t] = random_word(seed, p.rng_stream, e + t);
+                                }
+                            }
+                            packed[j * 8 + (i >> 2)] = narrow4(&v[j][i], shift, p.mode, p.relu, rnd);
+                        }
+                    if (leader) bulk_wait_read<0>();  // the previous store has read the staging tile
+                    named_barrier(bar_id, 128);
+                    stage_row(buf, row_in_tile, packed);
+                    fence_proxy_async();
+                    named_barrier(bar_id, 128);
+                    if (leader) { tma_store_4d(&tmC, buf, col0 + g0, cy, cz, cw); bulk_commit(); }
+                } else {
+#pragma unroll
+                    for (int half = 0; half < 2; ++half) {
+                        if (col0 + g0 + half * 64 >= p.N) break;
+                        if (leader) bulk_wait_read<0>();  // the previous round's stores have read the staging tiles
+                        named_barrier(bar_id, 128);
+                        stage_row(buf, row_in_tile, v[2 * half]);
+                        stage_row(buf + EPI_CHUNK_BYTES, row_in_tile, v[2 * half + 1]);
+                        fence_proxy_async();
+                        named_barrier(bar_id, 128);
+                        if (leader) {
+                            tma_store_4d(&tmC, buf, col0 + g0 + half * 64, cy, cz, cw);
+                            if (col0 + g0 + half * 64 + 32 < p.N) tma_store_4d(&tmC, buf + EPI_CHUNK_BYTES, col0 + g0 + half * 64 + 32, cy, cz, cw);
+                            bulk_commit();
+                        }
+                    }
+                }
             }
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(smem_u32(&tempty_bar[acc]));
         }
         if (leader) bulk_wait<0>();
+        const int hi = max(max(vmax[0], vmax[1]), max(vmax[2], vmax[3]));
+        const int lo = min(min(vmin[0], vmin[1]), min(vmin[2], vmin[3]));
+        unsigned local_max = max(static_cast<unsigned>(hi), static_cast<unsigned>(-static_cast<long long>(lo)));
         local_max = __reduce_max_sync(0xFFFFFFFFu, local_max);
         if (lane == 0 && local_max != 0 && p.maxabs != nullptr) atomicMax(p.maxabs, local_max);
     }
@@ -298,7 +400,7 @@ struct WgradParams {
 constexpr int WG_MAX_S = 3;
 constexpr int WG_STAGE_BYTES = (1 + WG_MAX_S) * PANEL_BYTES;  // 64 KB
 constexpr int WG_STAGES = 3;
-constexpr int WG_SMEM_BYTES = WG_STAGES * WG_STAGE_BYTES + 2 * EPI_CHUNK_BYTES + 1024 + 256;
+constexpr int WG_SMEM_BYTES = WG_STAGES * WG_STAGE_BYTES + 1024 + 256;
 constexpr int WG_TMEM_COLS = 512;
 
 __global__ void __launch_bounds__(UMMA_THREADS, 1)
@@ -306,8 +408,7 @@ umma_wgrad_kernel(const __grid_constant__ CUtensorMap tmErr, const __grid_consta
                   const __grid_constant__ CUtensorMap tmP, const WgradParams p) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    uint8_t* epi_smem = smem + WG_STAGES * WG_STAGE_BYTES;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(epi_smem + 2 * EPI_CHUNK_BYTES);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + WG_STAGES * WG_STAGE_BYTES);
     uint64_t* full_bar = bars;
     uint64_t* empty_bar = bars + WG_STAGES;
     uint64_t* tfull_bar = bars + 2 * WG_STAGES;
@@ -383,8 +484,10 @@ umma_wgrad_kernel(const __grid_constant__ CUtensorMap tmErr, const __grid_consta
             if (ok) umma_commit(smem_u32(&tfull_bar[0]));
         }
     } else {
-        // partial[split][k][r][s][c] viewed as a rank-4 tensor (c, r*S+s, k, split): one TMA store
-        // per (tap, 32-channel chunk) writes 128 k-rows of 32 int32
+        // partial[split][k][r][s][c] viewed as a rank-4 tensor (c, r*S+s, k, split): per tap, four TMA
+        // stores of 128 k-rows x 32 channels.  Once the last MMA has completed the operand stages
+        // are dead, so stage `sx` serves as the staging area of tap `sx` (64 KB = 4 tiles each) and
+        // no store ever waits for another.
         const int q = warp & 3;
         const int row_in_tile = q * 32 + lane;
         const bool leader = threadIdx.x == 64;
@@ -393,21 +496,21 @@ umma_wgrad_kernel(const __grid_constant__ CUtensorMap tmErr, const __grid_consta
             if (failed) report_abort(p.status, 14, 2);
         } else {
             tc_fence_after();
-            uint32_t chunk_ctr = 0;
             for (int sx = 0; sx < p.S; ++sx) {
-#pragma unroll 1
-                for (int c = 0; c < 128 && ct * 128 + c < p.C; c += 32) {
-                    const uint32_t buf = smem_u32(epi_smem) + (chunk_ctr & 1u) * EPI_CHUNK_BYTES;
-                    if (leader) bulk_wait_read<1>();
-                    named_barrier(EPI_BARRIER, 128);
-                    uint32_t v[32];
-                    tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + sx * 128 + c, v);
-                    tmem_ld_wait();
-                    stage_row(buf, row_in_tile, v);
-                    fence_proxy_async();
-                    named_barrier(EPI_BARRIER, 128);
-                    if (leader) { tma_store_4d(&tmP, buf, ct * 128 + c, r * p.S + sx, kt * 128, split); bulk_commit(); }
-                    ++chunk_ctr;
+                const uint32_t buf = smem_u32(smem + sx * WG_STAGE_BYTES);
+                uint32_t v[4][32];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + sx * 128 + j * 32, v[j]);
+                tmem_ld_wait();
+#pragma unroll
+                for (int j = 0; j < 4; ++j) stage_row(buf + j * EPI_CHUNK_BYTES, row_in_tile, v[j]);
+                fence_proxy_async();
+                named_barrier(EPI_BARRIER, 128);
+                if (leader) {
+#pragma unroll
+                    for (int j = 0; j < 4; ++j)
+                        if (ct * 128 + j * 32 < p.C) tma_store_4d(&tmP, buf + j * EPI_CHUNK_BYTES, ct * 128 + j * 32, r * p.S + sx, kt * 128, split);
+                    bulk_commit();
                 }
             }
             if (leader) bulk_wait<0>();
@@ -476,16 +579,26 @@ static int sm_count() {
     return n;
 }
 
-template <int BN>
-static int launch_gemm_bn(const CUtensorMap& a, const CUtensorMap& b, const CUtensorMap& c, const GemmParams& p,
-                          cudaStream_t st) {
-    using Cfg = GemmCfg<BN>;
-    cudaError_t e = cudaFuncSetAttribute(umma_gemm_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
+template <int BN, bool FUSED>
+static int launch_gemm_inst(const CUtensorMap& a, const CUtensorMap& b, const CUtensorMap& c, const GemmParams& p,
+                            cudaStream_t st) {
+    using Cfg = GemmCfg<BN, FUSED>;
+    cudaError_t e = cudaFuncSetAttribute(umma_gemm_kernel<BN, FUSED>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
     if (e != cudaSuccess) return set_cuda_error(e);
     int grid = p.m_tiles * p.n_tiles * p.splits;
     if (grid > sm_count()) grid = sm_count();
-    umma_gemm_kernel<BN><<<grid, UMMA_THREADS, Cfg::SMEM_BYTES, st>>>(a, b, c, p);
+    umma_gemm_kernel<BN, FUSED><<<grid, GEMM_THREADS, Cfg::SMEM_BYTES, st>>>(a, b, c, p);
     return set_cuda_error(cudaGetLastError());
+}
+static int launch_gemm(int bn, bool fused, const CUtensorMap& a, const CUtensorMap& b, const CUtensorMap& c,
+                       const GemmParams& p, cudaStream_t st) {
+    if (fused) return bn == 256 ? launch_gemm_inst<256, true>(a, b, c, p, st) : launch_gemm_inst<128, true>(a, b, c, p, st);
+    return bn == 256 ? launch_gemm_inst<256, false>(a, b, c, p, st) : launch_gemm_inst<128, false>(a, b, c, p, st);
+}
+static void set_fused(GemmParams* p, const FusedArgs* f) {
+    if (!f) return;
+    p->state = f->state; p->only_if_redo = f->only_if_redo; p->mode = f->mode; p->relu = f->relu;
+    p->seed = f->seed; p->rng_stream = f->rng_stream; p->rng_offset = f->rng_offset;
 }
 
 // Pixels of one 128-row tile: as much of a row as fits, then rows, then images.
@@ -507,9 +620,10 @@ int umma_gemm_splits(int M, int N, int K) {
     return splits < 1 ? 1 : splits;
 }
 
-// C32[splits][M][N] (splits == 1: the result itself) = op(A) * op(B) over disjoint reduction ranges
-int umma_gemm(const int8_t* A, const int8_t* B, int32_t* C32, unsigned* maxabs, int M, int N, int K,
-              int trans_a, int trans_b, int splits, int32_t* status, cudaStream_t st) {
+// out[splits][M][N] (splits == 1: the result itself) = op(A) * op(B) over disjoint reduction ranges.
+// `fused` == null: int32 out; otherwise int8 out narrowed by the shift in fused->state[0] (splits must be 1).
+int umma_gemm(const int8_t* A, const int8_t* B, void* out, unsigned* maxabs, int M, int N, int K, int trans_a,
+              int trans_b, int splits, const FusedArgs* fused, int32_t* status, cudaStream_t st) {
     CUtensorMap ma, mb, mc;
     const int a_mn = trans_a ? 1 : 0, b_mn = trans_b ? 0 : 1;
     const int bn = (N > 128) ? 256 : 128;
@@ -519,25 +633,27 @@ int umma_gemm(const int8_t* A, const int8_t* B, int32_t* C32, unsigned* maxabs, 
         if (int e = encode_map(&ma, A, false, 2, dims, str, box)) return e;
         if (b_mn) { dims[0] = N; dims[1] = K; str[0] = N; box[1] = 128; } else { dims[0] = K; dims[1] = N; str[0] = K; box[1] = bn; }
         if (int e = encode_map(&mb, B, false, 2, dims, str, box)) return e;
+        const uint64_t es = fused ? 1 : 4;
         uint64_t dc[4] = {(uint64_t)N, (uint64_t)M, (uint64_t)splits, 1};
-        uint64_t sc[3] = {(uint64_t)N * 4, (uint64_t)M * N * 4, (uint64_t)splits * M * N * 4};
-        uint32_t bc[4] = {32, 128, 1, 1};
-        if (int e = encode_map(&mc, C32, true, 4, dc, sc, bc)) return e;
+        uint64_t sc[3] = {(uint64_t)N * es, (uint64_t)M * N * es, (uint64_t)splits * M * N * es};
+        uint32_t bc[4] = {fused ? 128u : 32u, 128, 1, 1};
+        if (int e = encode_map(&mc, out, !fused, 4, dc, sc, bc)) return e;
     }
     GemmParams p{};
     p.conv = 0; p.M = M; p.N = N; p.num_kb = (K + 127) / 128; p.splits = splits;
     p.m_tiles = (M + 127) / 128; p.n_tiles = (N + bn - 1) / bn;
     p.a_mn = a_mn; p.b_mn = b_mn; p.a_bytes = PANEL_BYTES;
     p.maxabs = splits > 1 ? nullptr : maxabs; p.status = status;
-    return bn == 256 ? launch_gemm_bn<256>(ma, mb, mc, p, st) : launch_gemm_bn<128>(ma, mb, mc, p, st);
+    set_fused(&p, fused);
+    return launch_gemm(bn, fused != nullptr, ma, mb, mc, p, st);
 }
 
 // Forward convolution (flip == 0: x [N,H,W,C] with w [K,R,S,C] -> [N,H,W,K]) or error-backward
 // (flip == 1: err [N,H,W,K] with the same w -> [N,H,W,C]); "same" padding, stride 1.
 // Forward reads w rows as the N operand (K-major); backward reads the very same tensor as the
 // reduction operand (MN-major: 128 k rows of 128 c bytes per tap), so no transposed copy exists.
-int umma_conv(const int8_t* x, const int8_t* w, int32_t* y32, unsigned* maxabs, int Nimg, int H, int W, int C, int K,
-              int R, int S, int pad, int flip, int32_t* status, cudaStream_t st) {
+int umma_conv(const int8_t* x, const int8_t* w, void* out, unsigned* maxabs, int Nimg, int H, int W, int C, int K,
+              int R, int S, int pad, int flip, const FusedArgs* fused, int32_t* status, cudaStream_t st) {
     CUtensorMap ma, mb, mc;
     const int red = flip ? K : C;   // reduction channels per tap
     const int outc = flip ? C : K;  // output channels
@@ -553,10 +669,11 @@ int umma_conv(const int8_t* x, const int8_t* w, int32_t* y32, unsigned* maxabs, 
         uint64_t s2[1] = {(uint64_t)R * S * C};
         uint32_t b2[2] = {128, flip ? 128u : (uint32_t)bn};
         if (int e = encode_map(&mb, w, false, 2, d2, s2, b2)) return e;
+        const uint64_t es = fused ? 1 : 4;
         uint64_t dc[4] = {(uint64_t)outc, (uint64_t)W, (uint64_t)H, (uint64_t)Nimg};
-        uint64_t sc[3] = {(uint64_t)outc * 4, (uint64_t)W * outc * 4, (uint64_t)H * W * outc * 4};
-        uint32_t bc[4] = {32, (uint32_t)p.BW, (uint32_t)p.BH, (uint32_t)p.BI};
-        if (int e = encode_map(&mc, y32, true, 4, dc, sc, bc)) return e;
+        uint64_t sc[3] = {(uint64_t)outc * es, (uint64_t)W * outc * es, (uint64_t)H * W * outc * es};
+        uint32_t bc[4] = {fused ? 128u : 32u, (uint32_t)p.BW, (uint32_t)p.BH, (uint32_t)p.BI};
+        if (int e = encode_map(&mc, out, !fused, 4, dc, sc, bc)) return e;
     }
     p.conv = 1; p.flip = flip; p.splits = 1;
     p.H = H; p.W = W; p.S = S; p.pad = pad; p.Nimg = Nimg; p.tapstride = C;
@@ -567,7 +684,8 @@ int umma_conv(const int8_t* x, const int8_t* w, int32_t* y32, unsigned* maxabs, 
     p.m_tiles = p.tiles_w * p.tiles_h * tiles_n; p.n_tiles = (outc + bn - 1) / bn;
     p.a_mn = 0; p.b_mn = flip ? 1 : 0; p.a_bytes = p.BW * p.BH * p.BI * ROW_BYTES;
     p.maxabs = maxabs; p.status = status;
-    return bn == 256 ? launch_gemm_bn<256>(ma, mb, mc, p, st) : launch_gemm_bn<128>(ma, mb, mc, p, st);
+    set_fused(&p, fused);
+    return launch_gemm(bn, fused != nullptr, ma, mb, mc, p, st);
 }
 
 static void wgrad_plan(int Nimg, int H, int W, int C, int K, int R, WgradParams* p) {

@@ -284,11 +284,23 @@ class TiConv2d(UpdateWeight):
         self.stride = stride
         self.padding = padding
         self.fuse_relu = fuse_relu
+        # shift predictions of the fused conv + requantisation kernels (forward, error-backward)
+        self._fwd_state = None
+        self._bwd_state = None
 
     def forward(self, input):
         self.act, self.act_in_exp = input
+        K, R, S, C = self.weight.shape
+        per = self.act.shape[1] * self.act.shape[2] * K
+        if FUSE_REQUANT and self.stride == 1 and ops.conv_fprop_fused_supported(C, K, R, S, self.padding):
+            # conv2d_int8 + act_calc (:393-395) in one kernel; see ops.conv_fprop_fused
+            if self._fwd_state is None:
+                self._fwd_state = ops.new_requant_state(self.act.device)
+            out, exp_out, _ = ops.conv_fprop_fused(self.act, self.weight, self._fwd_state, self.padding, _mode(ACT_ROUND_METHOD),
+                                                   RNG_SEED(self.act.device), 16 * self.layer_id, SAMPLE_OFFSET * per,
+                                                   self.fuse_relu, exp_tensor(self.act_in_exp, self.act.device), self.weight_exp)
+            return out, exp_out
         acc, mx = ops.conv_fprop_acc(self.act, self.weight, self.padding, self.stride)
-        per = acc[0].numel()
         return act_calc(acc, self.act_in_exp, mx, 16 * self.layer_id, self.fuse_relu, SAMPLE_OFFSET * per, self.weight_exp)
 
     def backward(self, input):
@@ -296,11 +308,21 @@ class TiConv2d(UpdateWeight):
         err_in = err_in.contiguous()
         err_out = None
         if not self.first_layer:
-            # the reference builds flip(w).transpose(0,3) here (:404); the kernel reads w in place
-            acc, mx = ops.conv_dgrad_acc(err_in, self.weight, self.padding)
-            err_out, self.err_exp, _ = _calc(acc, ops.CALC_ERR, BITWIDTH, ERROR_ROUND_METHOD, 16 * self.layer_id + 1,
-                                             exp_tensor(self.err_exp, acc.device), self.weight_exp, mx, False,
-                                             SAMPLE_OFFSET * acc[0].numel())
+            # the reference builds flip(w).transpose(0,3) here (:404); the kernels read w in place
+            K, R, S, C = self.weight.shape
+            per = self.act[0].numel()
+            if FUSE_REQUANT and ops.conv_dgrad_fused_supported(C, K, R, S, self.padding):
+                if self._bwd_state is None:
+                    self._bwd_state = ops.new_requant_state(err_in.device)
+                err_out, self.err_exp, _ = ops.conv_dgrad_fused(err_in, self.weight, self._bwd_state, self.padding,
+                                                                _mode(ERROR_ROUND_METHOD), RNG_SEED(err_in.device),
+                                                                16 * self.layer_id + 1, SAMPLE_OFFSET * per,
+                                                                exp_tensor(self.err_exp, err_in.device), self.weight_exp)
+            else:
+                acc, mx = ops.conv_dgrad_acc(err_in, self.weight, self.padding)
+                err_out, self.err_exp, _ = _calc(acc, ops.CALC_ERR, BITWIDTH, ERROR_ROUND_METHOD, 16 * self.layer_id + 1,
+                                                 exp_tensor(self.err_exp, acc.device), self.weight_exp, mx, False,
+                                                 SAMPLE_OFFSET * per)
         K, R, S, C = self.weight.shape
         self.grad_int32acc, self.grad_maxabs = ops.conv_wgrad_acc(self.act, err_in, R, S, self.padding, out=self.grad_buffer)
         if not self.defer_update:
@@ -334,6 +356,7 @@ ERROR_ROUND_METHOD = RoundShift
 GRAD_ROUND_METHOD = PstoShift
 WEIGHT_INIT_METHOD = UniformWeights
 
+FUSE_REQUANT = True    # convolutions narrow to int8 inside their own kernel (predicted shift, verified, redone if wrong)
 GRAD_BITWIDTH = 5      # the reference's training loop injects this per epoch (main.py:73-77)
 TRAINING = True        # likewise (main.py:147-149)
 SAMPLE_OFFSET = 0      # global index of this process's first sample (data-parallel shards)

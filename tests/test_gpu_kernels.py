@@ -209,3 +209,37 @@ def test_quantize_input():
         x8, e = ops.quantize_input(cu(x))
         assert_same(x8, np.ascontiguousarray(want8.transpose(0, 2, 3, 1)), "input quantisation")
         assert int(e.item()) == want_e
+
+
+# ----------------------------------------------------------------------------- fused conv + requantisation
+@pytest.mark.parametrize("N,H,W,C,K", [(4, 32, 32, 128, 128), (3, 16, 16, 128, 256), (5, 8, 8, 256, 512), (2, 12, 20, 128, 144),
+                                        (4, 32, 32, 3, 128), (9, 4, 4, 256, 128)])
+@pytest.mark.parametrize("mode,relu", [(0, True), (0, False), (1, False), (2, True)])
+def test_conv_fused_requant(N, H, W, C, K, mode, relu):
+    """Predicted-shift kernels: first call mispredicts (state starts at 0) and must redo, the second
+    call predicts right; both must equal conv + act_calc / err_calc of the oracle."""
+    rng = np.random.default_rng(N + H + C + K + mode)
+    x, w = rnd8(rng, (N, H, W, C)), rnd8(rng, (K, 3, 3, C))
+    seed = ops.seed_tensor(31, DEV)
+    acc = O.conv_fprop(x, w)
+    words = philox.random_u32_tensor(31, 5, acc.shape, offset=64)
+    want, want_e, want_s = O.act_calc(acc, -3 + -9, mode, words)
+    if relu:
+        want = O.relu_fwd(want)
+    st = ops.new_requant_state(DEV)
+    ea, eb = torch.tensor(-3, dtype=torch.int32, device=DEV), torch.tensor(-9, dtype=torch.int32, device=DEV)
+    for call in range(2):
+        y8, e, s = ops.conv_fprop_fused(cu(x), cu(w), st, 1, mode, seed, 5, 64, relu, ea, eb)
+        assert_same(y8, want, f"fused fprop call {call}")
+        assert int(e.item()) == want_e and int(s.item()) == want_s
+        assert st.tolist()[2:] == [1 if (call == 0 and want_s != 0) else 0, 1 if want_s != 0 else 0]
+    if C % 16 == 0 and K % 128 == 0:
+        err = rnd8(rng, (N, H, W, K))
+        acc = O.conv_dgrad(err, w)
+        words = philox.random_u32_tensor(31, 6, acc.shape, offset=128)
+        want, want_s = O.err_calc(acc, mode, words)
+        st = ops.new_requant_state(DEV)
+        for call in range(2):
+            e8, e, s = ops.conv_dgrad_fused(cu(err), cu(w), st, 1, mode, seed, 6, 128, ea, eb)
+            assert_same(e8, want, f"fused dgrad call {call}")
+            assert int(s.item()) == want_s and int(e.item()) == want_s - 12
