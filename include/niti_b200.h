@@ -106,13 +106,13 @@ NITI_API int niti_conv_wgrad_i8(const int8_t* x, const int8_t* err, int32_t* g32
  * conv2d_int8 + act_calc (ti_torch.py:391-397) and TiConv2d.backward's error path conv2d_int8 +
  * err_calc (ti_torch.py:403-407).  The shift depends on the max of the whole int32 tensor, which
  * is only known when the contraction has finished, so the kernel narrows with a PREDICTED shift
- * (the one this layer needed last time, state[0]) while it reduces the true max|acc|; a one-thread
- * kernel then derives the true shift, and only if the prediction was wrong the contraction is
- * launched again (that launch returns at once otherwise).  The result is always the exact one;
- * the int32 tensor never touches memory.
- *   state: device int32[4] owned by the caller, one per layer and direction, zeroed once:
- *          [0] shift (in: prediction, out: true value), [1] max|acc|, [2] 1 if the last call had
- *          to redo, [3] number of redos so far.
+ * (the one this layer needed last time, state[0]) while it reduces the true max|acc|; the thread
+ * block that finishes last derives the true shift, and only if the prediction was wrong the
+ * contraction is launched again (that second launch returns at once otherwise).  The result is
+ * always the exact one; the int32 tensor never touches memory.
+ *   state: device int32[8] owned by the caller, one per layer and direction, zeroed once:
+ *          [0] shift (in: prediction, out: true value), [1] max|acc| (zero between calls), [2] 1 if
+ *          the last call had to redo, [3] number of redos so far, [4] block ticket (zero between calls).
  *   kind is ACT for fprop (exp_out = shift + *exp_a + *exp_b) and ERR for dgrad; target 7 bits.
  * Shapes: niti_conv_*_requant_supported() != 0 (the tensor-core shapes of the entry points above
  * with 16-byte-multiple output channels); otherwise NITI_ERR_UNSUPPORTED and the caller uses

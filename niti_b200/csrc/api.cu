@@ -164,8 +164,8 @@ static int fused_conv(const int8_t* in, const int8_t* w, int8_t* out8, int32_t* 
                       int N, int H, int W, int C, int K, int R, int S, int pad, int flip, int kind, int round_mode,
                       const uint64_t* seed, uint32_t rng_stream, uint64_t rng_offset, int relu, const int32_t* exp_a,
                       const int32_t* exp_b, int32_t* exp_out, int32_t* shift_out, int32_t* status, cudaStream_t st) {
-    FusedArgs f{state, 0, round_mode, relu, reinterpret_cast<const unsigned long long*>(seed), rng_stream, rng_offset};
-    unsigned* maxabs = reinterpret_cast<unsigned*>(state + 1);
+    FusedArgs f{state, 0, round_mode, relu, reinterpret_cast<const unsigned long long*>(seed), rng_stream, rng_offset,
+                kind, 7, exp_a, exp_b, exp_out, shift_out};
     const bool thin = !flip && fprop_path(C, K, R, S, pad) == CONV_THIN;
     const size_t m = static_cast<size_t>(N) * H * W;
     int8_t* xcol = static_cast<int8_t*>(scratch);
@@ -175,14 +175,12 @@ static int fused_conv(const int8_t* in, const int8_t* w, int8_t* out8, int32_t* 
         if (int e = im2col32(in, xcol, N, H, W, C, R, S, pad, st)) return e;
         if (int e = pad_rows32(w, wp, K, R * S * C, st)) return e;
     }
-    if (int e = clear_word(maxabs, st)) return e;
+    // first launch: narrow with the predicted shift, reduce max|acc|, verify; second launch: redo if it was wrong
     for (int pass = 0; pass < 2; ++pass) {
         f.only_if_redo = pass;
-        int rc = thin ? umma_gemm(xcol, wp, out8, maxabs, static_cast<int>(m), K, 32, 0, 1, 1, &f, status, st)
-                      : umma_conv(in, w, out8, maxabs, N, H, W, C, K, R, S, pad, flip, &f, status, st);
+        int rc = thin ? umma_gemm(xcol, wp, out8, nullptr, static_cast<int>(m), K, 32, 0, 1, 1, &f, status, st)
+                      : umma_conv(in, w, out8, nullptr, N, H, W, C, K, R, S, pad, flip, &f, status, st);
         if (rc) return rc;
-        if (pass == 0)
-            if (int e = requant_verify(state, kind, 7, exp_a, exp_b, exp_out, shift_out, st)) return e;
     }
     return NITI_OK;
 }

@@ -11,14 +11,16 @@ int set_cuda_error(cudaError_t e);
 int set_cuda_error_text(const char* text);
 
 // Requantisation fused into a contraction's epilogue: the kernel narrows with the shift it finds in
-// state[0]; `only_if_redo` launches are no-ops unless state[2] is set (see requant_verify).
+// state[0] and its last CTA verifies that shift; `only_if_redo` launches are no-ops unless state[2] is set.
 struct FusedArgs {
-    const int32_t* state;
+    int32_t* state;        // {shift, max|acc|, redo flag, redo count, CTA ticket, -, -, -}
     int only_if_redo;
     int mode, relu;
     const unsigned long long* seed;
     unsigned rng_stream;
     unsigned long long rng_offset;
+    int kind, target_bits;
+    const int32_t* exp_a; const int32_t* exp_b; int32_t* exp_out; int32_t* shift_out;
 };
 
 // tensor-core (tcgen05) paths, umma_kernels.cu; `out` is int32 (fused == null) or int8
@@ -44,9 +46,5 @@ int reduce_partials(const int32_t* partial, int splits, long long n, int32_t* ou
 int reduce_rows32(const int32_t* partial, int splits, int rows, int cols_out, int32_t* out, unsigned* maxabs, cudaStream_t st);
 int im2col32(const int8_t* x, int8_t* xcol, int Nimg, int H, int W, int C, int R, int S, int pad, cudaStream_t st);
 int pad_rows32(const int8_t* w, int8_t* wp, int K, int rsc, cudaStream_t st);
-// state = {shift applied, max|acc|, redo flag, redo count}: derive the true shift from state[1],
-// set state[2] = (true != state[0]), store the true shift in state[0], write exponent / shift outputs
-int requant_verify(int32_t* state, int kind, int target_bits, const int32_t* exp_a, const int32_t* exp_b,
-                   int32_t* exp_out, int32_t* shift_out, cudaStream_t st);
 
 }  // namespace niti

@@ -96,23 +96,6 @@ requant_kernel(const int32_t* __restrict__ acc, int8_t* __restrict__ out, const 
     }
 }
 
-__global__ void requant_verify_kernel(int32_t* state, int kind, int target_bits, const int32_t* exp_a, const int32_t* exp_b,
-                                      int32_t* exp_out, int32_t* shift_out) {
-    bool zero_out;
-    const int shift = shift_for(static_cast<unsigned>(state[1]), kind, target_bits, &zero_out);
-    const int redo = shift != state[0];
-    state[2] = redo;
-    state[3] += redo;
-    state[0] = shift;
-    if (exp_out) *exp_out = shift + (exp_a ? *exp_a : 0) + (exp_b ? *exp_b : 0);
-    if (shift_out) *shift_out = shift;
-}
-int requant_verify(int32_t* state, int kind, int target_bits, const int32_t* exp_a, const int32_t* exp_b,
-                   int32_t* exp_out, int32_t* shift_out, cudaStream_t st) {
-    requant_verify_kernel<<<1, 1, 0, st>>>(state, kind, target_bits, exp_a, exp_b, exp_out, shift_out);
-    return set_cuda_error(cudaGetLastError());
-}
-
 __global__ void __launch_bounds__(256)
 absmax_kernel(const int32_t* __restrict__ acc, long long n, unsigned* maxabs) {
     unsigned m = 0;

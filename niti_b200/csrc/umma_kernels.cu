@@ -65,9 +65,15 @@ struct GemmParams {
     int cblocks;           // reduction channels / 128
     unsigned* maxabs;      // max|acc| is reduced into this word; may be null (split-K partials)
     int32_t* status;
-    // fused requantisation (FUSED kernels): int8 output narrowed by the shift in state[0]
-    const int32_t* state;  // [0] shift to apply, [2] "redo" flag of the verification kernel
-    int only_if_redo;      // 1: this launch does nothing unless state[2] != 0
+    int split_cols;        // 1: both epilogue warpgroups share every tile (alternate 128-column groups); 0: they alternate tiles
+    // fused requantisation (FUSED kernels): int8 output narrowed by the shift in state[0].
+    // state = {shift, max|acc|, redo flag, redo count, finished-CTA ticket}; the last CTA of a first
+    // launch derives the true shift from max|acc|, publishes it with the exponent / shift outputs and
+    // raises the redo flag when the applied shift was wrong.
+    int32_t* state;
+    int only_if_redo;      // 1: this launch does nothing unless state[2] != 0, and verifies nothing
+    int kind, target_bits;
+    const int32_t* exp_a; const int32_t* exp_b; int32_t* exp_out; int32_t* shift_out;
     int mode, relu;
     const unsigned long long* seed;
     unsigned rng_stream;
@@ -96,27 +102,37 @@ __device__ __forceinline__ void report_abort(int32_t* status, int code, int role
 }
 
 // Four accumulators of one row -> four int8 packed in a word (NITI's shift, see requant.cuh).
+// Round-to-nearest (the default of activations and errors) gets a short branch-free form:
+// round half away from zero on |x|, clamp to 127, restore the sign (ReLU: negatives become 0).
+template <bool RELU>
+__device__ __forceinline__ uint32_t narrow4_nearest(const uint32_t* v, int shift, int half) {
+    int y[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const int x = static_cast<int>(v[j]);
+        if (RELU) {
+            y[j] = min((max(x, 0) + half) >> shift, 127);
+        } else {
+            const int sgn = x >> 31;
+            const int t = min(((x ^ sgn) - sgn + half) >> shift, 127);
+            y[j] = (t ^ sgn) - sgn;
+        }
+    }
+    return __byte_perm(__byte_perm(y[0], y[1], 0x0040), __byte_perm(y[2], y[3], 0x0040), 0x5410);
+}
 __device__ __forceinline__ uint32_t narrow4(const uint32_t* v, int shift, int mode, int relu, const uint32_t* rnd) {
     uint32_t w = 0;
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
-        const int x = static_cast<int>(v[j]);
-        int y;
-        if (mode == ROUND_NEAREST && shift > 0) {
-            // round half away from zero on |x|, clamp to 127; with ReLU negatives are zero anyway
-            const int t = min(static_cast<int>((static_cast<uint32_t>(x < 0 ? -x : x) + (1u << (shift - 1))) >> shift), 127);
-            y = x < 0 ? (relu ? 0 : -t) : t;
-        } else {
-            y = narrow(x, shift, mode, rnd[j]);
-            if (relu && y < 0) y = 0;
-        }
+        int y = narrow(static_cast<int>(v[j]), shift, mode, rnd[j]);
+        if (relu && y < 0) y = 0;
         w |= static_cast<uint32_t>(static_cast<uint8_t>(y)) << (8 * j);
     }
     return w;
 }
 
 template <int BN, bool FUSED>
-__global__ void __launch_bounds__(GEMM_THREADS, 1)
+__global__ void __launch_bounds__(GEMM_THREADS, 1)  // 10 warps: 3 on one scheduler -> at most 168 registers per thread
 umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                  const __grid_constant__ CUtensorMap tmC, const GemmParams p) {
     using Cfg = GemmCfg<BN, FUSED>;
@@ -139,7 +155,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < STAGES; ++i) { mbar_init(smem_u32(&full_bar[i]), 1); mbar_init(smem_u32(&empty_bar[i]), 1); }
-        for (int i = 0; i < 2; ++i) { mbar_init(smem_u32(&tfull_bar[i]), 1); mbar_init(smem_u32(&tempty_bar[i]), 4); }
+        for (int i = 0; i < 2; ++i) { mbar_init(smem_u32(&tfull_bar[i]), 1); mbar_init(smem_u32(&tempty_bar[i]), p.split_cols ? 8 : 4); }
         *abort_flag = 0;
         fence_barrier_init();
         tma_prefetch_desc(&tmA);
@@ -235,9 +251,11 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         }
     } else {
         // ------------------------------------------------------------------ epilogue (2 x 4 warps)
-        // Warpgroup g takes this CTA's tiles g, g+2, g+4, ... (accumulator g), so the epilogues of
-        // two consecutive tiles overlap each other and the main loop.  Per group of 128 output
-        // columns: four tcgen05.ld and ONE wait, the accumulator is handed back as soon as its
+        // Two warpgroups.  With several tiles per CTA they alternate tiles (warpgroup g owns
+        // accumulator g), so the epilogues of consecutive tiles overlap each other and the main
+        // loop; with one or two wide tiles per CTA (split_cols) they share every tile, each taking
+        // alternate 128-column groups, which halves the serial tail.  Per group of 128 columns:
+        // four tcgen05.ld and ONE wait, the accumulator is handed back as soon as the warpgroup's
         // last columns sit in registers, max|acc| is tracked in registers, rows go to swizzled
         // staging tiles and leave through TMA stores (which clip rows/columns outside the tensor).
         //   plain kernels: int32 out, two rounds of two 128 x 32 staging tiles per column group;
@@ -254,10 +272,13 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             shift = p.state[0];
             if (p.mode == ROUND_STOCHASTIC && shift > 0) seed = *p.seed;
         }
+        const bool fast = FUSED && p.mode == ROUND_NEAREST && shift > 0;
+        const int half = shift > 0 ? 1 << (shift - 1) : 0;
         int vmax[4] = {0, 0, 0, 0}, vmin[4] = {0, 0, 0, 0};
-        int i2 = 0;
-        for (int tile = blockIdx.x + grp * gridDim.x; tile < total_tiles; tile += 2 * gridDim.x, ++i2) {
-            const int acc = grp; const uint32_t aph = i2 & 1u;
+        const int tile_step = p.split_cols ? gridDim.x : 2 * gridDim.x;
+        int it = p.split_cols ? 0 : grp;
+        for (int tile = blockIdx.x + (p.split_cols ? 0 : grp * gridDim.x); tile < total_tiles; tile += tile_step, it += (p.split_cols ? 1 : 2)) {
+            const int acc = it & 1; const uint32_t aph = (it >> 1) & 1u;
             const uint32_t failed = mbar_wait(smem_u32(&tfull_bar[acc]), aph, abort_flag) ? 0u : 1u;
             if (barrier_or(bar_id, 128, failed)) {  // same verdict in all 128 threads of the warpgroup
                 if (failed) report_abort(p.status, 4, 2);
@@ -282,16 +303,20 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             }
             const int col0 = n_t * BN;
             const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(acc * BN);
+            // column groups of this warpgroup: all of them, or every other one when the tile is shared
+            const int g_first = p.split_cols ? grp * 128 : 0, g_step = p.split_cols ? 256 : 128;
+            bool released = false;
 #pragma unroll 1
-            for (int g0 = 0; g0 < BN && col0 + g0 < p.N; g0 += 128) {
+            for (int g0 = g_first; g0 < BN && col0 + g0 < p.N; g0 += g_step) {
                 uint32_t v[4][32];
 #pragma unroll
                 for (int j = 0; j < 4; ++j) tmem_ld_32x32(taddr + g0 + j * 32, v[j]);
                 tmem_ld_wait();
-                if (g0 + 128 >= BN || col0 + g0 + 128 >= p.N) {  // last group: the accumulator is free again
+                if (g0 + g_step >= BN || col0 + g0 + g_step >= p.N) {  // this warpgroup's last group of the tile
                     tc_fence_before();
                     __syncwarp();
                     if (lane == 0) mbar_arrive(smem_u32(&tempty_bar[acc]));
+                    released = true;
                 }
                 const int lim = p.N - (col0 + g0);
                 if (valid) {
@@ -317,23 +342,37 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                 }
                 if constexpr (FUSED) {
                     uint32_t packed[32];
-                    const unsigned long long e0 = p.rng_offset + static_cast<unsigned long long>(row_lin) * p.N + (col0 + g0);
-                    const bool stochastic = p.mode == ROUND_STOCHASTIC && shift > 0;
+                    if (fast) {
+                        if (p.relu) {
 #pragma unroll
-                    for (int j = 0; j < 4; ++j)
+                            for (int j = 0; j < 4; ++j)
 #pragma unroll
-                        for (int i = 0; i < 32; i += 4) {
-                            uint32_t rnd[4] = {0, 0, 0, 0};
-                            if (stochastic) {
-                                const unsigned long long e = e0 + j * 32 + i;
-                                if ((e & 3ull) == 0) random_block(seed, p.rng_stream, e >> 2, rnd);
-                                else {
+                                for (int i = 0; i < 32; i += 4) packed[j * 8 + (i >> 2)] = narrow4_nearest<true>(&v[j][i], shift, half);
+                        } else {
 #pragma unroll
-                                    for (int t = 0; t < 4; ++t) rnd[t] = random_word(seed, p.rng_stream, e + t);
-                                }
-                            }
-                            packed[j * 8 + (i >> 2)] = narrow4(&v[j][i], shift, p.mode, p.relu, rnd);
+                            for (int j = 0; j < 4; ++j)
+#pragma unroll
+                                for (int i = 0; i < 32; i += 4) packed[j * 8 + (i >> 2)] = narrow4_nearest<false>(&v[j][i], shift, half);
                         }
+                    } else {
+                        const unsigned long long e0 = p.rng_offset + static_cast<unsigned long long>(row_lin) * p.N + (col0 + g0);
+                        const bool stochastic = p.mode == ROUND_STOCHASTIC && shift > 0;
+#pragma unroll
+                        for (int j = 0; j < 4; ++j)
+#pragma unroll
+                            for (int i = 0; i < 32; i += 4) {
+                                uint32_t rnd[4] = {0, 0, 0, 0};
+                                if (stochastic) {
+                                    const unsigned long long e = e0 + j * 32 + i;
+                                    if ((e & 3ull) == 0) random_block(seed, p.rng_stream, e >> 2, rnd);
+                                    else {
+#pragma unroll
+                                        for (int t = 0; t < 4; ++t) rnd[t] = random_word(seed, p.rng_stream, e + t);
+                                    }
+                                }
+                                packed[j * 8 + (i >> 2)] = narrow4(&v[j][i], shift, p.mode, p.relu, rnd);
+                            }
+                    }
                     if (leader) bulk_wait_read<0>();  // the previous store has read the staging tile
                     named_barrier(bar_id, 128);
                     stage_row(buf, row_in_tile, packed);
@@ -342,21 +381,26 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                     if (leader) { tma_store_4d(&tmC, buf, col0 + g0, cy, cz, cw); bulk_commit(); }
                 } else {
 #pragma unroll
-                    for (int half = 0; half < 2; ++half) {
-                        if (col0 + g0 + half * 64 >= p.N) break;
+                    for (int half_i = 0; half_i < 2; ++half_i) {
+                        if (col0 + g0 + half_i * 64 >= p.N) break;
                         if (leader) bulk_wait_read<0>();  // the previous round's stores have read the staging tiles
                         named_barrier(bar_id, 128);
-                        stage_row(buf, row_in_tile, v[2 * half]);
-                        stage_row(buf + EPI_CHUNK_BYTES, row_in_tile, v[2 * half + 1]);
+                        stage_row(buf, row_in_tile, v[2 * half_i]);
+                        stage_row(buf + EPI_CHUNK_BYTES, row_in_tile, v[2 * half_i + 1]);
                         fence_proxy_async();
                         named_barrier(bar_id, 128);
                         if (leader) {
-                            tma_store_4d(&tmC, buf, col0 + g0 + half * 64, cy, cz, cw);
-                            if (col0 + g0 + half * 64 + 32 < p.N) tma_store_4d(&tmC, buf + EPI_CHUNK_BYTES, col0 + g0 + half * 64 + 32, cy, cz, cw);
+                            tma_store_4d(&tmC, buf, col0 + g0 + half_i * 64, cy, cz, cw);
+                            if (col0 + g0 + half_i * 64 + 32 < p.N) tma_store_4d(&tmC, buf + EPI_CHUNK_BYTES, col0 + g0 + half_i * 64 + 32, cy, cz, cw);
                             bulk_commit();
                         }
                     }
                 }
+            }
+            if (!released) {  // a shared tile none of whose column groups fell to this warpgroup
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(smem_u32(&tempty_bar[acc]));
             }
         }
         if (leader) bulk_wait<0>();
@@ -365,6 +409,28 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         unsigned local_max = max(static_cast<unsigned>(hi), static_cast<unsigned>(-static_cast<long long>(lo)));
         local_max = __reduce_max_sync(0xFFFFFFFFu, local_max);
         if (lane == 0 && local_max != 0 && p.maxabs != nullptr) atomicMax(p.maxabs, local_max);
+        if (FUSED && !p.only_if_redo) {
+            // the CTA that finishes last turns max|acc| into the true shift and checks the prediction
+            __threadfence();
+            named_barrier(EPI_BARRIER + 2, 256);
+            if (threadIdx.x == 64) {
+                int32_t* st = p.state;
+                if (atomicAdd(&st[4], 1) == static_cast<int>(gridDim.x) - 1) {
+                    __threadfence();
+                    bool zero_out;
+                    const unsigned m = static_cast<unsigned>(atomicMax(reinterpret_cast<unsigned*>(&st[1]), 0u));
+                    const int true_shift = shift_for(m, p.kind, p.target_bits, &zero_out);
+                    const int redo = true_shift != st[0];
+                    st[2] = redo;
+                    st[3] += redo;
+                    st[0] = true_shift;
+                    st[1] = 0;  // ready for the next call
+                    st[4] = 0;
+                    if (p.exp_out) *p.exp_out = true_shift + (p.exp_a ? *p.exp_a : 0) + (p.exp_b ? *p.exp_b : 0);
+                    if (p.shift_out) *p.shift_out = true_shift;
+                }
+            }
+        }
     }
 
     // ---------------------------------------------------------------------- teardown
@@ -599,6 +665,10 @@ static void set_fused(GemmParams* p, const FusedArgs* f) {
     if (!f) return;
     p->state = f->state; p->only_if_redo = f->only_if_redo; p->mode = f->mode; p->relu = f->relu;
     p->seed = f->seed; p->rng_stream = f->rng_stream; p->rng_offset = f->rng_offset;
+    p->kind = f->kind; p->target_bits = f->target_bits;
+    p->exp_a = f->exp_a; p->exp_b = f->exp_b; p->exp_out = f->exp_out; p->shift_out = f->shift_out;
+    // max|acc| lives in state[1]; a redo launch must leave it alone (the last CTA of the first launch zeroed it)
+    p->maxabs = f->only_if_redo ? nullptr : reinterpret_cast<unsigned*>(f->state + 1);
 }
 
 // Pixels of one 128-row tile: as much of a row as fits, then rows, then images.
@@ -644,6 +714,7 @@ int umma_gemm(const int8_t* A, const int8_t* B, void* out, unsigned* maxabs, int
     p.m_tiles = (M + 127) / 128; p.n_tiles = (N + bn - 1) / bn;
     p.a_mn = a_mn; p.b_mn = b_mn; p.a_bytes = PANEL_BYTES;
     p.maxabs = splits > 1 ? nullptr : maxabs; p.status = status;
+    p.split_cols = (bn == 256 && p.m_tiles * p.n_tiles * splits <= 2 * sm_count()) ? 1 : 0;
     set_fused(&p, fused);
     return launch_gemm(bn, fused != nullptr, ma, mb, mc, p, st);
 }
@@ -684,6 +755,7 @@ int umma_conv(const int8_t* x, const int8_t* w, void* out, unsigned* maxabs, int
     p.m_tiles = p.tiles_w * p.tiles_h * tiles_n; p.n_tiles = (outc + bn - 1) / bn;
     p.a_mn = 0; p.b_mn = flip ? 1 : 0; p.a_bytes = p.BW * p.BH * p.BI * ROW_BYTES;
     p.maxabs = maxabs; p.status = status;
+    p.split_cols = (bn == 256 && p.m_tiles * p.n_tiles <= 2 * sm_count()) ? 1 : 0;
     set_fused(&p, fused);
     return launch_gemm(bn, fused != nullptr, ma, mb, mc, p, st);
 }

@@ -98,9 +98,9 @@ def conv_fprop_acc(x, w, pad=1, stride=1):
 
 
 def new_requant_state(device):
-    """int32[4] a fused conv + requantisation call keeps per layer and direction:
-    [0] shift (prediction in, true value out), [1] max|acc|, [2] redo flag, [3] redo count."""
-    return torch.zeros(4, dtype=torch.int32, device=device)
+    """int32[8] a fused conv + requantisation call keeps per layer and direction:
+    [0] shift (prediction in, true value out), [1] max|acc|, [2] redo flag, [3] redo count, [4] block ticket."""
+    return torch.zeros(8, dtype=torch.int32, device=device)
 
 
 def conv_fprop_fused_supported(C, K, R, S, pad):
@@ -122,7 +122,7 @@ def conv_fprop_fused(x, w, state, pad=1, mode=ROUND_NEAREST, seed=None, rng_stre
     shift_out = torch.empty((), dtype=torch.int32, device=x.device)
     nbytes = lib.niti_conv_fprop_scratch_bytes(N, H, W, C, K, R, S)
     sc = scratch(x.device, nbytes) if nbytes else None
-    _call("niti_conv_fprop_requant_i8", 5 if nbytes else 3, 2 * N * H * W * K * R * S * C, x.numel() + w.numel() + y8.numel(),
+    _call("niti_conv_fprop_requant_i8", 4 if nbytes else 2, 2 * N * H * W * K * R * S * C, x.numel() + w.numel() + y8.numel(),
           lib.niti_conv_fprop_requant_i8, _p(x), _p(w), _p(y8), _p(state), _p(sc), sc.numel() if nbytes else 0,
           N, H, W, C, K, R, S, pad, mode, _p(seed), rng_stream, rng_offset, int(relu), _p(exp_a), _p(exp_b),
           _p(exp_out), _p(shift_out), _p(status_word(x.device)), _st())
@@ -137,7 +137,7 @@ def conv_dgrad_fused(err, w, state, pad=1, mode=ROUND_NEAREST, seed=None, rng_st
     e8 = torch.empty((N, H, W, C), dtype=torch.int8, device=err.device)
     exp_out = torch.empty((), dtype=torch.int32, device=err.device)
     shift_out = torch.empty((), dtype=torch.int32, device=err.device)
-    _call("niti_conv_dgrad_requant_i8", 3, 2 * N * H * W * K * R * S * C, err.numel() + w.numel() + e8.numel(),
+    _call("niti_conv_dgrad_requant_i8", 2, 2 * N * H * W * K * R * S * C, err.numel() + w.numel() + e8.numel(),
           lib.niti_conv_dgrad_requant_i8, _p(err), _p(w), _p(e8), _p(state), N, H, W, C, K, R, S, pad, mode, _p(seed),
           rng_stream, rng_offset, _p(exp_a), _p(exp_b), _p(exp_out), _p(shift_out), _p(status_word(err.device)), _st())
     return e8, exp_out, shift_out

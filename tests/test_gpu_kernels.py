@@ -232,7 +232,7 @@ def test_conv_fused_requant(N, H, W, C, K, mode, relu):
         y8, e, s = ops.conv_fprop_fused(cu(x), cu(w), st, 1, mode, seed, 5, 64, relu, ea, eb)
         assert_same(y8, want, f"fused fprop call {call}")
         assert int(e.item()) == want_e and int(s.item()) == want_s
-        assert st.tolist()[2:] == [1 if (call == 0 and want_s != 0) else 0, 1 if want_s != 0 else 0]
+        assert st.tolist()[1:5] == [0, 1 if (call == 0 and want_s != 0) else 0, 1 if want_s != 0 else 0, 0]
     if C % 16 == 0 and K % 128 == 0:
         err = rnd8(rng, (N, H, W, K))
         acc = O.conv_dgrad(err, w)
