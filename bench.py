@@ -369,6 +369,107 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+# ------------------------------------------------------------------------------------------------
+# single kernel cases (profiling) and the GEMM / conv sweep
+# ------------------------------------------------------------------------------------------------
+def time_graph(fn, reps=10):
+    """Average device time of fn(): `reps` back-to-back calls replayed from a CUDA graph, CUDA events around the replay."""
+    import torch
+    fn(); fn()
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        for _ in range(reps):
+            fn()
+    g.replay()
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    g.replay()
+    b.record()
+    torch.cuda.synchronize()
+    return a.elapsed_time(b) * 1e-3 / reps
+
+
+def make_case(name, shape):
+    """Returns (callable, algorithmic ops, algorithmic bytes) for one kernel case on cuda:0.
+    conv cases: shape = N,H,W,C,K (3x3, pad 1); gemm cases: shape = M,N,K."""
+    import torch
+    from niti_b200 import ops
+    dev = torch.device("cuda", 0)
+    g = torch.Generator().manual_seed(7)
+
+    def r8(*s):
+        return torch.randint(-127, 128, s, dtype=torch.int8, generator=g).to(dev)
+
+    if name.startswith("gemm"):
+        M, N, K = shape
+        ta, tb = {"gemm_tn": (False, True), "gemm_nn": (False, False), "gemm_tn_a": (True, False)}[name]
+        a, b = r8(*((K, M) if ta else (M, K))), r8(*((N, K) if tb else (K, N)))
+        return (lambda: ops.gemm_acc(a, b, ta, tb)), 2 * M * N * K, M * K + N * K + 4 * M * N
+    N, H, W, C, K = shape
+    x, w, err = r8(N, H, W, C), r8(K, 3, 3, C), r8(N, H, W, K)
+    gop = 2 * N * H * W * K * 9 * C
+    ea = torch.zeros((), dtype=torch.int32, device=dev)
+    if name == "conv_fprop_fused":
+        st = ops.new_requant_state(dev)
+        return (lambda: ops.conv_fprop_fused(x, w, st, 1, 0, None, 0, 0, True, ea, ea)), gop, x.numel() + w.numel() + N * H * W * K
+    if name == "conv_dgrad_fused":
+        st = ops.new_requant_state(dev)
+        return (lambda: ops.conv_dgrad_fused(err, w, st, 1, 0, None, 0, 0, ea, ea)), gop, err.numel() + w.numel() + x.numel()
+    if name == "conv_fprop":
+        return (lambda: ops.conv_fprop_acc(x, w)), gop, x.numel() + w.numel() + 4 * N * H * W * K
+    if name == "conv_dgrad":
+        return (lambda: ops.conv_dgrad_acc(err, w)), gop, err.numel() + w.numel() + 4 * x.numel()
+    if name == "conv_wgrad":
+        return (lambda: ops.conv_wgrad_acc(x, err)), gop, x.numel() + err.numel() + 4 * w.numel()
+    raise SystemExit(f"unknown case {name}")
+
+
+def run_case(args):
+    import torch
+    from niti_b200 import ops
+    torch.cuda.set_device(0)
+    shape = tuple(int(v) for v in args.shape.split(","))
+    fn, aops, abytes = make_case(args.case, shape)
+    if args.plain_launches:
+        for _ in range(args.plain_launches):  # eager launches only: what a profiler should see
+            fn()
+        torch.cuda.synchronize()
+        ops.check_status("cuda:0")
+        print(json.dumps({"case": args.case, "shape": shape, "launched": args.plain_launches}))
+        return
+    t = time_graph(fn)
+    ops.check_status("cuda:0")
+    print(json.dumps({"case": args.case, "shape": shape, "us": t * 1e6, "tops": aops / t / 1e12, "gbs": abytes / t / 1e9}))
+
+
+def run_sweep(args):
+    import torch
+    from niti_b200 import ops
+    torch.cuda.set_device(0)
+    _, bf16_sus, bf16_burst, src = measured_peaks()
+    for n in (1024, 4096, 8192, 16384):
+        a = torch.randint(-127, 128, (n, n), dtype=torch.int8).cuda()
+        t_lib = time_graph(lambda: torch._int_mm(a, a), reps=3 if n > 8192 else 10)
+        for name in ("gemm_tn", "gemm_nn", "gemm_tn_a"):
+            fn, aops, _ = make_case(name, (n, n, n))
+            t = time_graph(fn, reps=3 if n > 8192 else 10)
+            print(json.dumps({"case": name, "n": n, "us": t * 1e6, "tops": aops / t / 1e12, "frac_of_2x_bf16_burst": aops / t / 1e12 / (2 * bf16_burst),
+                              "cublaslt_int_mm_tops": 2 * n ** 3 / t_lib / 1e12}), flush=True)
+        del a
+    for c in (64, 256, 512):
+        for hw in (8, 16, 32):
+            for name in ("conv_fprop_fused", "conv_dgrad_fused", "conv_wgrad"):
+                if c % 128 and name != "conv_wgrad":
+                    name = name.replace("_fused", "")
+                fn, aops, _ = make_case(name, (256, hw, hw, c, c))
+                t = time_graph(fn, reps=3)
+                print(json.dumps({"case": name, "C=K": c, "HW": hw, "batch": 256, "us": t * 1e6, "tops": aops / t / 1e12,
+                                  "frac_of_2x_bf16_burst": aops / t / 1e12 / (2 * bf16_burst)}), flush=True)
+    ops.check_status("cuda:0")
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -376,7 +477,15 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--case", help="time one kernel case instead of the training step (see make_case)")
+    ap.add_argument("--shape", default="128,16,16,256,256")
+    ap.add_argument("--plain-launches", type=int, default=0, help="with --case: just launch it this many times (for ncu)")
+    ap.add_argument("--sweep", action="store_true", help="GEMM and conv roofline sweep, one JSON line per case")
     args = ap.parse_args()
+    if args.case:
+        return run_case(args)
+    if args.sweep:
+        return run_sweep(args)
     if args.impl == "reference":
         run_reference(args)
     else:

@@ -110,3 +110,19 @@ def test_full_training_steps(golden_dir, name):
     got = oracle_net_record(rec)
     for k, v in got.items():
         assert np.array_equal(np.asarray(v), rec[k]), k
+
+
+def test_philox_known_answers():
+    """Philox4x32-10 known-answer vectors of the Random123 distribution (zero, all-ones, pi digits)."""
+    def run(c, k):
+        return [int(v[0]) for v in philox.philox4x32_10([c[0]], [c[1]], [c[2]], [c[3]], k[0], k[1])]
+    assert run((0, 0, 0, 0), (0, 0)) == [0x6627e8d5, 0xe169c58d, 0xbc57ac4c, 0x9b00dbd8]
+    f = 0xFFFFFFFF
+    assert run((f, f, f, f), (f, f)) == [0x408f276d, 0x41c83b0e, 0xa20bc7c6, 0x6d5451fd]
+    assert run((0x243f6a88, 0x85a308d3, 0x13198a2e, 0x03707344), (0xa4093822, 0x299f31d0)) == \
+        [0xd16cfe09, 0x94fdcceb, 0x5001e420, 0x24126ea1]
+    # element -> word mapping: element idx uses counter (idx >> 2) and lane idx & 3
+    w = philox.random_u32_tensor(5, 9, (8,), offset=2)
+    blk = philox.philox4x32_10([0, 1, 2], [0, 0, 0], [9, 9, 9], [0, 0, 0], 5, 0)
+    flat = [int(blk[l][b]) for b in range(3) for l in range(4)]
+    assert [int(v) for v in w] == flat[2:10]
