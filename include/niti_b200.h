@@ -46,6 +46,7 @@ extern "C" {
 #define NITI_ERR_UNSUPPORTED (-2)  /* shape outside what the kernels implement (message says which) */
 #define NITI_ERR_CUDA (-3)         /* a CUDA runtime / driver call failed; see niti_last_cuda_error */
 #define NITI_ERR_SCRATCH (-4)      /* scratch buffer too small */
+#define NITI_ERR_TOO_LARGE (-5)    /* needs more scratch than the library's built-in buffer (see below) */
 
 /* rounding of the int32 -> int8 shift: RoundShift / StoShift / PstoShift (ti_torch.py:23-69) */
 #define NITI_ROUND_NEAREST 0
@@ -99,6 +100,29 @@ NITI_API int niti_conv_dgrad_i8(const int8_t* err, const int8_t* w, int32_t* e32
 NITI_API size_t niti_conv_wgrad_scratch_bytes(int N, int H, int W, int C, int K, int R, int S);
 NITI_API int niti_conv_wgrad_i8(const int8_t* x, const int8_t* err, int32_t* g32, uint32_t* maxabs,
                        void* scratch, size_t scratch_bytes,
+                       int N, int H, int W, int C, int K, int R, int S, int pad,
+                       int32_t* status, void* stream);
+
+/* niti_conv_wgrad_i8 for callers that cannot hand over scratch memory.  This entry point has no
+ * counterpart in the reference.  Some hosts of this library are not able to call cudaMalloc at all:
+ * a plugin inside an application that owns every byte of device memory and offers no allocator, or a
+ * service whose device-memory budget is fixed and audited at start-up.  For them the split-reduction
+ * scratch of the weight gradient lives in a buffer that is part of the library image
+ * (NITI_BUILTIN_SCRATCH_BYTES, held by every GPU context that loads the library until it exits); the
+ * call allocates nothing, neither through CUDA nor through any library.
+ *  - Same arguments (minus scratch), same result bit for bit as niti_conv_wgrad_i8: when the usual
+ *    number of pixel-range splits would not fit, fewer splits are used (integer sums do not depend on
+ *    the split), and a problem that does not fit even unsplit (K*R*S*C*4 bytes above the limit, or a
+ *    first-layer patch matrix N*H*W*32 bytes above it) is refused with NITI_ERR_TOO_LARGE before
+ *    anything is launched.
+ *  - The first call on each device looks up the buffer's device address (cudaGetSymbolAddress, with that
+ *    device current); make that first call during set-up, before any stream capture is begun.
+ *  - All calls on a device share the one buffer and it keeps the previous call's contents; this entry
+ *    point needs none of it zeroed, but two calls whose kernels overlap on the GPU (different streams
+ *    without ordering) race on it: keep calls stream-ordered.
+ */
+#define NITI_BUILTIN_SCRATCH_BYTES (16u << 20)
+NITI_API int niti_conv_wgrad_builtin_scratch_i8(const int8_t* x, const int8_t* err, int32_t* g32, uint32_t* maxabs,
                        int N, int H, int W, int C, int K, int R, int S, int pad,
                        int32_t* status, void* stream);
 

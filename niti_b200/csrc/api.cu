@@ -39,6 +39,7 @@ extern "C" const char* niti_strerror(int code) {
         case NITI_ERR_UNSUPPORTED: return "shape or option not implemented by the kernels";
         case NITI_ERR_CUDA: return "CUDA call failed (see niti_last_cuda_error)";
         case NITI_ERR_SCRATCH: return "scratch buffer too small";
+        case NITI_ERR_TOO_LARGE: return "problem needs more scratch than the library's built-in buffer holds (use the variant that takes caller scratch)";
         default: return "unknown niti error code";
     }
 }
@@ -134,7 +135,7 @@ extern "C" int niti_conv_wgrad_i8(const int8_t* x, const int8_t* err, int32_t* g
     const long long n = static_cast<long long>(K) * R * S * C;
     if (path == CONV_TC) {
         int splits = 0;
-        if (int rc = umma_conv_wgrad_partials(x, err, static_cast<int32_t*>(scratch), &splits, N, H, W, C, K, R, S, pad, status, st)) return rc;
+        if (int rc = umma_conv_wgrad_partials(x, err, static_cast<int32_t*>(scratch), &splits, 0, N, H, W, C, K, R, S, pad, status, st)) return rc;
         return reduce_partials(static_cast<const int32_t*>(scratch), splits, n, g32, maxabs, st);
     }
     // thin: g[k][0..R*S*C) = sum_pixels err[pixel][k] * xcol[pixel][0..32)  (split-K GEMM, then fold and drop the padding)
@@ -216,4 +217,71 @@ extern "C" int niti_conv_dgrad_requant_i8(const int8_t* err, const int8_t* w, in
     if (!niti_conv_dgrad_requant_supported(C, K, R, S, pad)) return NITI_ERR_UNSUPPORTED;
     return fused_conv(err, w, e8, state, nullptr, 0, N, H, W, C, K, R, S, pad, 1, NITI_CALC_ERR, round_mode, seed, rng_stream,
                       rng_offset, 0, exp_a, exp_b, exp_out, shift_out, status, static_cast<cudaStream_t>(stream));
+}
+
+// ---------------------------------------------------------------- weight gradient without caller scratch
+// Scratch for callers that have no way to allocate device memory: a fixed buffer inside the library
+// image.  Every GPU context that loads the library carries these bytes until it is torn down.
+static __device__ __align__(256) unsigned char g_builtin_scratch[NITI_BUILTIN_SCRATCH_BYTES];
+
+// `g_builtin_scratch` names the buffer only in device code.  Host code must ask the runtime for the
+// device address (per device: each device has its own copy of the array); it is looked up the first
+// time a device uses the entry point, with that device current, and remembered.
+static void* g_builtin_scratch_addr[64] = {nullptr};
+
+static int builtin_scratch(void** out) {
+    int dev = -1;
+    if (int e = set_cuda_error(cudaGetDevice(&dev))) return e;
+    if (dev < 0 || dev >= 64) return set_cuda_error_text("device ordinal outside the range the built-in scratch table covers");
+    if (g_builtin_scratch_addr[dev] == nullptr) {
+        void* p = nullptr;
+        if (int e = set_cuda_error(cudaGetSymbolAddress(&p, g_builtin_scratch))) return e;
+        g_builtin_scratch_addr[dev] = p;
+    }
+    *out = g_builtin_scratch_addr[dev];
+    return NITI_OK;
+}
+
+extern "C" int niti_conv_wgrad_builtin_scratch_i8(const int8_t* x, const int8_t* err, int32_t* g32, uint32_t* maxabs, int N,
+                                                  int H, int W, int C, int K, int R, int S, int pad, int32_t* status,
+                                                  void* stream) {
+    NITI_REQUIRE(x && err && g32 && maxabs && N > 0 && H > 0 && W > 0 && C > 0 && K > 0 && R > 0 && S > 0 && pad >= 0);
+    NITI_REQUIRE(aligned16(g32));
+    if (H + 2 * pad - R + 1 <= 0 || W + 2 * pad - S + 1 <= 0) return NITI_ERR_BAD_ARG;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    ConvPath path = wgrad_path(C, K, R, S, pad);
+    if (!(aligned16(x) && aligned16(err))) path = CONV_SIMT;
+    const size_t cap = NITI_BUILTIN_SCRATCH_BYTES;
+    const long long n = static_cast<long long>(K) * R * S * C;
+    // size check first: nothing is launched for a problem that does not fit
+    int max_splits = 0;
+    const size_t m = static_cast<size_t>(N) * H * W;
+    if (path == CONV_TC) {
+        const size_t per_split = static_cast<size_t>(n) * 4;
+        if (per_split > cap) return NITI_ERR_TOO_LARGE;
+        max_splits = static_cast<int>(cap / per_split);
+    } else if (path == CONV_THIN) {
+        const size_t fixed = align_up(m * 32, 1024), per_split = static_cast<size_t>(K) * 32 * 4;
+        if (fixed + per_split > cap) return NITI_ERR_TOO_LARGE;
+        max_splits = static_cast<int>((cap - fixed) / per_split);
+    }
+    if (int e = clear_word(maxabs, st)) return e;
+    if (path == CONV_SIMT) return simt_conv_wgrad(x, err, g32, maxabs, N, H, W, C, K, R, S, pad, st);
+    void* scratch = nullptr;
+    if (int e = builtin_scratch(&scratch)) return e;
+    // Nothing in the buffer has to start at zero: every partial sum that is read back below is first
+    // written by this call (the kernels cover [splits][K][R][S][C], resp. the patch matrix, completely).
+    if (path == CONV_TC) {
+        int splits = 0;
+        if (int rc = umma_conv_wgrad_partials(x, err, static_cast<int32_t*>(scratch), &splits, max_splits, N, H, W, C, K, R, S,
+                                              pad, status, st)) return rc;
+        return reduce_partials(static_cast<const int32_t*>(scratch), splits, n, g32, maxabs, st);
+    }
+    int8_t* xcol = static_cast<int8_t*>(scratch);
+    int32_t* partial = reinterpret_cast<int32_t*>(xcol + align_up(m * 32, 1024));
+    int splits = umma_gemm_splits(K, 32, static_cast<int>(m));
+    if (splits > max_splits) splits = max_splits;
+    if (int e = im2col32(x, xcol, N, H, W, C, R, S, pad, st)) return e;
+    if (int e = umma_gemm(err, xcol, partial, nullptr, K, 32, static_cast<int>(m), 1, 0, splits, nullptr, status, st)) return e;
+    return reduce_rows32(partial, splits, K, R * S * C, g32, maxabs, st);
 }

@@ -30,8 +30,9 @@ int umma_gemm(const int8_t* A, const int8_t* B, void* out, unsigned* maxabs, int
 int umma_conv(const int8_t* x, const int8_t* w, void* out, unsigned* maxabs, int Nimg, int H, int W, int C, int K,
               int R, int S, int pad, int flip, const FusedArgs* fused, int32_t* status, cudaStream_t st);
 size_t umma_wgrad_scratch_bytes(int Nimg, int H, int W, int C, int K, int R, int S);
-int umma_conv_wgrad_partials(const int8_t* x, const int8_t* err, int32_t* partial, int* splits_out, int Nimg, int H,
-                             int W, int C, int K, int R, int S, int pad, int32_t* status, cudaStream_t st);
+// max_splits > 0 caps the number of pixel-range splits (and with it the size of `partial`)
+int umma_conv_wgrad_partials(const int8_t* x, const int8_t* err, int32_t* partial, int* splits_out, int max_splits,
+                             int Nimg, int H, int W, int C, int K, int R, int S, int pad, int32_t* status, cudaStream_t st);
 
 // CUDA-core paths, simt_kernels.cu
 int simt_conv_fprop(const int8_t* x, const int8_t* w, int32_t* y32, unsigned* maxabs, int Nimg, int H, int W, int C,

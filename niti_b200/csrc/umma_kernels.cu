@@ -760,7 +760,7 @@ int umma_conv(const int8_t* x, const int8_t* w, void* out, unsigned* maxabs, int
     return launch_gemm(bn, fused != nullptr, ma, mb, mc, p, st);
 }
 
-static void wgrad_plan(int Nimg, int H, int W, int C, int K, int R, WgradParams* p) {
+static void wgrad_plan(int Nimg, int H, int W, int C, int K, int R, int max_splits, WgradParams* p) {
     pick_pixel_box(Nimg, H, W, &p->BW, &p->BH, &p->BI);
     p->tiles_w = (W + p->BW - 1) / p->BW; p->tiles_h = (H + p->BH - 1) / p->BH; p->tiles_n = (Nimg + p->BI - 1) / p->BI;
     p->chunks = p->tiles_w * p->tiles_h * p->tiles_n;
@@ -769,19 +769,20 @@ static void wgrad_plan(int Nimg, int H, int W, int C, int K, int R, WgradParams*
     int splits = (sm_count() + items / 2) / items;
     if (splits < 1) splits = 1;
     if (splits > p->chunks) splits = p->chunks;
+    if (max_splits > 0 && splits > max_splits) splits = max_splits;
     p->splits = splits;
 }
 
 size_t umma_wgrad_scratch_bytes(int Nimg, int H, int W, int C, int K, int R, int S) {
     WgradParams p{};
-    wgrad_plan(Nimg, H, W, C, K, R, &p);
+    wgrad_plan(Nimg, H, W, C, K, R, 0, &p);
     return static_cast<size_t>(p.splits) * K * R * S * C * sizeof(int32_t);
 }
 
-int umma_conv_wgrad_partials(const int8_t* x, const int8_t* err, int32_t* partial, int* splits_out, int Nimg, int H,
-                             int W, int C, int K, int R, int S, int pad, int32_t* status, cudaStream_t st) {
+int umma_conv_wgrad_partials(const int8_t* x, const int8_t* err, int32_t* partial, int* splits_out, int max_splits,
+                             int Nimg, int H, int W, int C, int K, int R, int S, int pad, int32_t* status, cudaStream_t st) {
     WgradParams p{};
-    wgrad_plan(Nimg, H, W, C, K, R, &p);
+    wgrad_plan(Nimg, H, W, C, K, R, max_splits, &p);
     CUtensorMap me, mx, mp;
     {
         uint32_t box[4] = {128, (uint32_t)p.BW, (uint32_t)p.BH, (uint32_t)p.BI};
