@@ -58,6 +58,13 @@ extern "C" {
 #define NITI_CALC_ERR 1
 #define NITI_CALC_GRAD 2
 
+/* Process-wide tuning switch; returns the previous value (or NITI_ERR_BAD_ARG for an unknown option).
+ * NITI_OPT_ACCUMULATOR_PARKING (default 1): let the fused conv + requantisation entry points use the
+ * single-launch kernel that keeps all accumulators in tensor memory across a grid barrier whenever
+ * the problem is small enough; 0 forces the predict / verify / redo kernels.  Results are identical. */
+#define NITI_OPT_ACCUMULATOR_PARKING 1
+NITI_API int niti_set_option(int option, int value);
+
 NITI_API int niti_version(void);
 NITI_API const char* niti_strerror(int code);
 /* text of the last CUDA error seen by this thread inside the library ("" if none) */
@@ -69,7 +76,7 @@ NITI_API const char* niti_last_cuda_error(void);
  * cutlassconv_kernel.cu:38-319) as called from conv2d_int8 (ti_torch.py:178-192).
  * x [N][H][W][C], w [K][R][S][C] -> y32 [N][P][Q][K], cross-correlation, stride 1, P = H+2*pad-R+1.
  * Unlike the reference no channel padding to 16 is needed (C = 3 is accepted).  *maxabs = max |y32|.
- * Kernel choice: implicit GEMM on the tensor cores when C % 128 == 0 (and R = S = 2*pad+1, K % 4 == 0);
+ * Kernel choice: implicit GEMM on the tensor cores when C % 16 == 0 (and R = S = 2*pad+1, K % 4 == 0);
  * R*S*C <= 32 (3-channel first layer) goes through a patch matrix in `scratch`
  * (niti_conv_fprop_scratch_bytes, 0 for the other paths; scratch may then be NULL) and the
  * tensor-core GEMM; anything else runs on CUDA cores.
@@ -84,7 +91,7 @@ NITI_API int niti_conv_fprop_i8(const int8_t* x, const int8_t* w, int32_t* y32, 
  * conv2d_int8(err, flip(w,[1,2]).transpose(0,3)) (ti_torch.py:403-405) WITHOUT the flipped,
  * transposed copy of the weights: the kernel reads w [K][R][S][C] in place (as the reduction
  * operand, taps mirrored).  err [N][H][W][K] -> e32 [N][H][W][C]; R = S = 2*pad+1.
- * Tensor cores when K % 128 == 0 and C % 16 == 0.
+ * Tensor cores when K % 16 == 0 and C % 16 == 0.
  */
 NITI_API int niti_conv_dgrad_i8(const int8_t* err, const int8_t* w, int32_t* e32, uint32_t* maxabs,
                        int N, int H, int W, int C, int K, int R, int S, int pad,
@@ -133,7 +140,10 @@ NITI_API int niti_conv_wgrad_builtin_scratch_i8(const int8_t* x, const int8_t* e
  * (the one this layer needed last time, state[0]) while it reduces the true max|acc|; the thread
  * block that finishes last derives the true shift, and only if the prediction was wrong the
  * contraction is launched again (that second launch returns at once otherwise).  The result is
- * always the exact one; the int32 tensor never touches memory.
+ * always the exact one; the int32 tensor never touches memory.  When the whole output is at most
+ * 148 x (512 / tile width) tiles, all accumulators fit in tensor memory at once and a single
+ * cooperative launch does it without any prediction: reduce max, grid barrier, narrow (state[0]
+ * still receives the shift; state[2] stays 0).
  *   state: device int32[8] owned by the caller, one per layer and direction, zeroed once:
  *          [0] shift (in: prediction, out: true value), [1] max|acc| (zero between calls), [2] 1 if
  *          the last call had to redo, [3] number of redos so far, [4] block ticket (zero between calls).

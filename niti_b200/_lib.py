@@ -20,6 +20,7 @@ lib = C.CDLL(LIB_PATH)
 _p, _i, _i64, _u64, _u32, _sz = C.c_void_p, C.c_int, C.c_int64, C.c_uint64, C.c_uint32, C.c_size_t
 
 SIGNATURES = {
+    "niti_set_option": (_i, [_i, _i]),
     "niti_version": (_i, []),
     "niti_strerror": (C.c_char_p, [_i]),
     "niti_last_cuda_error": (C.c_char_p, []),

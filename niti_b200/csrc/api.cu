@@ -45,12 +45,20 @@ extern "C" const char* niti_strerror(int code) {
 }
 extern "C" const char* niti_last_cuda_error(void) { return g_cuda_error; }
 
+// tuning switches (process-wide): see niti_set_option
+static int g_opt_parking = 1;
+
+extern "C" int niti_set_option(int option, int value) {
+    if (option == NITI_OPT_ACCUMULATOR_PARKING) { const int old = g_opt_parking; g_opt_parking = value ? 1 : 0; return old; }
+    return NITI_ERR_BAD_ARG;
+}
+
 static int clear_word(uint32_t* p, cudaStream_t st) { return set_cuda_error(cudaMemsetAsync(p, 0, 4, st)); }
 
 static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
-// Which kernel family takes a convolution.  TC: implicit GEMM on the tensor cores (reduction
-// channels in 128-byte blocks).  THIN: R*S*C <= 32 (the 3-channel first layer): explicit patch
+// Which kernel family takes a convolution.  TC: implicit GEMM on the tensor cores (channels in
+// 128-byte blocks; channel counts that are multiples of 16 ride on TMA zero fill).  THIN: R*S*C <= 32 (the 3-channel first layer): explicit patch
 // matrix + tensor-core GEMM.  Otherwise the CUDA-core kernels.
 enum ConvPath { CONV_SIMT = 0, CONV_TC = 1, CONV_THIN = 2 };
 
@@ -58,14 +66,14 @@ static bool same_padding(int R, int S, int pad) { return R == 2 * pad + 1 && S =
 
 static ConvPath fprop_path(int C, int K, int R, int S, int pad) {
     if (!same_padding(R, S, pad) || K % 4 != 0) return CONV_SIMT;
-    if (C % 128 == 0) return CONV_TC;
     if (R * S * C <= 32) return CONV_THIN;
+    if (C % 16 == 0) return CONV_TC;
     return CONV_SIMT;
 }
 static ConvPath wgrad_path(int C, int K, int R, int S, int pad) {
     if (!same_padding(R, S, pad) || K % 16 != 0) return CONV_SIMT;
-    if (C % 128 == 0 && S <= 3) return CONV_TC;
     if (R * S * C <= 32) return CONV_THIN;
+    if (C % 16 == 0 && S <= 3) return CONV_TC;
     return CONV_SIMT;
 }
 
@@ -104,7 +112,7 @@ extern "C" int niti_conv_dgrad_i8(const int8_t* err, const int8_t* w, int32_t* e
     if (!same_padding(R, S, pad)) return NITI_ERR_UNSUPPORTED;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (int e = clear_word(maxabs, st)) return e;
-    if (K % 128 == 0 && C % 16 == 0 && aligned16(err) && aligned16(w) && aligned16(e32))
+    if (K % 16 == 0 && C % 16 == 0 && aligned16(err) && aligned16(w) && aligned16(e32))
         return umma_conv(err, w, e32, maxabs, N, H, W, C, K, R, S, pad, 1, nullptr, status, st);
     return simt_conv_dgrad(err, w, e32, maxabs, N, H, W, C, K, R, S, pad, st);
 }
@@ -165,7 +173,7 @@ static int fused_conv(const int8_t* in, const int8_t* w, int8_t* out8, int32_t* 
                       int N, int H, int W, int C, int K, int R, int S, int pad, int flip, int kind, int round_mode,
                       const uint64_t* seed, uint32_t rng_stream, uint64_t rng_offset, int relu, const int32_t* exp_a,
                       const int32_t* exp_b, int32_t* exp_out, int32_t* shift_out, int32_t* status, cudaStream_t st) {
-    FusedArgs f{state, 0, round_mode, relu, reinterpret_cast<const unsigned long long*>(seed), rng_stream, rng_offset,
+    FusedArgs f{state, 0, 0, round_mode, relu, reinterpret_cast<const unsigned long long*>(seed), rng_stream, rng_offset,
                 kind, 7, exp_a, exp_b, exp_out, shift_out};
     const bool thin = !flip && fprop_path(C, K, R, S, pad) == CONV_THIN;
     const size_t m = static_cast<size_t>(N) * H * W;
@@ -175,6 +183,11 @@ static int fused_conv(const int8_t* in, const int8_t* w, int8_t* out8, int32_t* 
         if (!scratch || !aligned16(scratch) || scratch_bytes < niti_conv_fprop_scratch_bytes(N, H, W, C, K, R, S)) return NITI_ERR_SCRATCH;
         if (int e = im2col32(in, xcol, N, H, W, C, R, S, pad, st)) return e;
         if (int e = pad_rows32(w, wp, K, R * S * C, st)) return e;
+    }
+    // Few enough output tiles for every accumulator to stay in tensor memory: one exact launch.
+    if (g_opt_parking && !thin && umma_conv_fits_parked(N, H, W, flip ? C : K)) {
+        f.parked = 1;
+        return umma_conv(in, w, out8, nullptr, N, H, W, C, K, R, S, pad, flip, &f, status, st);
     }
     // first launch: narrow with the predicted shift, reduce max|acc|, verify; second launch: redo if it was wrong
     for (int pass = 0; pass < 2; ++pass) {
@@ -191,7 +204,7 @@ extern "C" int niti_conv_fprop_requant_supported(int C, int K, int R, int S, int
     return (p == CONV_TC || p == CONV_THIN) && K % 16 == 0;
 }
 extern "C" int niti_conv_dgrad_requant_supported(int C, int K, int R, int S, int pad) {
-    return same_padding(R, S, pad) && K % 128 == 0 && C % 16 == 0;
+    return same_padding(R, S, pad) && K % 16 == 0 && C % 16 == 0;
 }
 
 extern "C" int niti_conv_fprop_requant_i8(const int8_t* x, const int8_t* w, int8_t* y8, int32_t* state, void* scratch,

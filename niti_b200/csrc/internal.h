@@ -13,8 +13,9 @@ int set_cuda_error_text(const char* text);
 // Requantisation fused into a contraction's epilogue: the kernel narrows with the shift it finds in
 // state[0] and its last CTA verifies that shift; `only_if_redo` launches are no-ops unless state[2] is set.
 struct FusedArgs {
-    int32_t* state;        // {shift, max|acc|, redo flag, redo count, CTA ticket, -, -, -}
+    int32_t* state;        // {shift, max|acc|, redo flag, redo count, exit ticket, barrier arrivals, -, -}
     int only_if_redo;
+    int parked;            // 1: accumulator-parking kernel (exact in one launch; needs umma_conv_fits_parked)
     int mode, relu;
     const unsigned long long* seed;
     unsigned rng_stream;
@@ -29,6 +30,7 @@ int umma_gemm(const int8_t* A, const int8_t* B, void* out, unsigned* maxabs, int
               int trans_b, int splits, const FusedArgs* fused, int32_t* status, cudaStream_t st);
 int umma_conv(const int8_t* x, const int8_t* w, void* out, unsigned* maxabs, int Nimg, int H, int W, int C, int K,
               int R, int S, int pad, int flip, const FusedArgs* fused, int32_t* status, cudaStream_t st);
+bool umma_conv_fits_parked(int Nimg, int H, int W, int outc);
 size_t umma_wgrad_scratch_bytes(int Nimg, int H, int W, int C, int K, int R, int S);
 // max_splits > 0 caps the number of pixel-range splits (and with it the size of `partial`)
 int umma_conv_wgrad_partials(const int8_t* x, const int8_t* err, int32_t* partial, int* splits_out, int max_splits,

@@ -21,6 +21,7 @@
 #include <cstdint>
 #include <cstdio>
 
+#include "../../include/niti_b200.h"
 #include "internal.h"
 #include "ptx.cuh"
 #include "requant.cuh"
@@ -62,7 +63,8 @@ struct GemmParams {
     int tapstride;         // elements between consecutive taps in a filter row
     int BW, BH, BI;        // pixels of one tile along w, h and images; BW*BH*BI <= 128
     int tiles_w, tiles_h;
-    int cblocks;           // reduction channels / 128
+    int cblocks;           // 128-byte blocks per tap: ceil(reduction channels / 128)
+    int red;               // reduction channels per tap (conv) -- the last block of a tap may be partial
     unsigned* maxabs;      // max|acc| is reduced into this word; may be null (split-K partials)
     int32_t* status;
     int split_cols;        // 1: both epilogue warpgroups share every tile (alternate 128-column groups); 0: they alternate tiles
@@ -131,6 +133,184 @@ __device__ __forceinline__ uint32_t narrow4(const uint32_t* v, int shift, int mo
     return w;
 }
 
+// ---- warp roles shared by the streaming kernel and the accumulator-parking kernel -------------
+// TMA producer (one thread): fills the stage ring for every tile of this CTA, in tile order.
+template <int BN, int STAGES, int STAGE_BYTES>
+__device__ __forceinline__ void producer_role(uint8_t* smem, uint64_t* full_bar, uint64_t* empty_bar, const CUtensorMap* tmA,
+                                              const CUtensorMap* tmB, const GemmParams& p, volatile int* abort_flag) {
+    const int mn_tiles = p.m_tiles * p.n_tiles;
+    const int total_tiles = mn_tiles * p.splits;
+    int s = 0; uint32_t ph = 0; bool ok = true;
+    for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+        const int split = tile / mn_tiles, mn = tile % mn_tiles;
+        const int m_t = mn / p.n_tiles, n_t = mn % p.n_tiles;
+        const int kb_lo = static_cast<int>(static_cast<long long>(split) * p.num_kb / p.splits);
+        const int kb_hi = static_cast<int>(static_cast<long long>(split + 1) * p.num_kb / p.splits);
+        int tw = 0, th = 0, tn = 0;
+        if (p.conv) { tw = m_t % p.tiles_w; th = (m_t / p.tiles_w) % p.tiles_h; tn = m_t / (p.tiles_w * p.tiles_h); }
+        for (int kb = kb_lo; kb < kb_hi; ++kb) {
+            if (!mbar_wait(smem_u32(&empty_bar[s]), ph ^ 1u, abort_flag)) { ok = false; report_abort(p.status, 1, 0); break; }
+            const uint32_t fb = smem_u32(&full_bar[s]);
+            const uint32_t sa = smem_u32(smem + s * STAGE_BYTES);
+            const uint32_t sb = sa + PANEL_BYTES;
+            mbar_arrive_expect_tx(fb, static_cast<uint32_t>(p.a_bytes + BN * ROW_BYTES));
+            if (p.conv) {
+                const int tap = kb / p.cblocks, cb = kb % p.cblocks;
+                const int r = tap / p.S, sx = tap % p.S;
+                const int dx = p.flip ? p.pad - sx : sx - p.pad, dy = p.flip ? p.pad - r : r - p.pad;
+                tma_load_4d(sa, tmA, fb, cb * ROW_BYTES, tw * p.BW + dx, th * p.BH + dy, tn * p.BI);
+                if (p.b_mn) {
+#pragma unroll
+                    for (int pn = 0; pn < BN / 128; ++pn)
+                        tma_load_2d(sb + pn * PANEL_BYTES, tmB, fb, tap * p.tapstride + n_t * BN + pn * 128, cb * 128);
+                } else {
+                    tma_load_2d(sb, tmB, fb, tap * p.tapstride + cb * ROW_BYTES, n_t * BN);
+                }
+            } else {
+                if (p.a_mn) tma_load_2d(sa, tmA, fb, m_t * BLOCK_M, kb * 128);
+                else        tma_load_2d(sa, tmA, fb, kb * ROW_BYTES, m_t * BLOCK_M);
+                if (p.b_mn) {
+#pragma unroll
+                    for (int pn = 0; pn < BN / 128; ++pn)
+                        tma_load_2d(sb + pn * PANEL_BYTES, tmB, fb, n_t * BN + pn * 128, kb * 128);
+                } else {
+                    tma_load_2d(sb, tmB, fb, kb * ROW_BYTES, n_t * BN);
+                }
+            }
+            if (++s == STAGES) { s = 0; ph ^= 1u; }
+        }
+    }
+}
+
+// MMA issuer (one thread).  Streaming: two accumulators used alternately, each handed back by the
+// epilogue (tempty).  PARKED: tile i of this CTA accumulates into TMEM columns [i*BN, (i+1)*BN) and
+// stays there until the kernel ends, so no accumulator is ever waited for.
+template <int BN, int STAGES, int STAGE_BYTES, bool PARKED>
+__device__ __forceinline__ void mma_role(uint8_t* smem, uint64_t* full_bar, uint64_t* empty_bar, uint64_t* tfull_bar,
+                                         uint64_t* tempty_bar, uint32_t tmem_base, const GemmParams& p, volatile int* abort_flag) {
+    const int mn_tiles = p.m_tiles * p.n_tiles;
+    const int total_tiles = mn_tiles * p.splits;
+    const uint32_t idesc = make_idesc_i8(BLOCK_M, BN, p.a_mn, p.b_mn);
+    int s = 0; uint32_t ph = 0; bool ok = true; int it = 0;
+    for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x, ++it) {
+        const int acc = PARKED ? it : (it & 1);
+        if (!PARKED) {
+            const uint32_t aph = (it >> 1) & 1u;
+            if (!mbar_wait(smem_u32(&tempty_bar[acc]), aph ^ 1u, abort_flag)) { report_abort(p.status, 2, 1); break; }
+            tc_fence_after();
+        }
+        const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BN);
+        const int split = tile / mn_tiles;
+        const int kb_lo = static_cast<int>(static_cast<long long>(split) * p.num_kb / p.splits);
+        const int kb_hi = static_cast<int>(static_cast<long long>(split + 1) * p.num_kb / p.splits);
+        for (int kb = kb_lo; kb < kb_hi; ++kb) {
+            if (!mbar_wait(smem_u32(&full_bar[s]), ph, abort_flag)) { ok = false; report_abort(p.status, 3, 1); break; }
+            tc_fence_after();
+            const uint32_t sa = smem_u32(smem + s * STAGE_BYTES);
+            const uint32_t sb = sa + PANEL_BYTES;
+            const uint64_t a0 = p.a_mn ? make_smem_desc(sa, PANEL_BYTES, 1024, SWIZZLE_128B_CODE)
+                                       : make_smem_desc(sa, 16, 1024, SWIZZLE_128B_CODE);
+            const uint64_t b0 = p.b_mn ? make_smem_desc(sb, PANEL_BYTES, 1024, SWIZZLE_128B_CODE)
+                                       : make_smem_desc(sb, 16, 1024, SWIZZLE_128B_CODE);
+            const uint32_t a_step = p.a_mn ? 32u * ROW_BYTES : 32u;
+            const uint32_t b_step = p.b_mn ? 32u * ROW_BYTES : 32u;
+            // a conv tap whose channel count is not a multiple of 128 ends in a partial block:
+            // issue only the MMAs (K = 32 each) that cover real channels (the rest is TMA zero fill)
+            int nmma = 4;
+            if (p.conv) { const int left = p.red - (kb % p.cblocks) * 128; nmma = left >= 128 ? 4 : (left + 31) >> 5; }
+#pragma unroll
+            for (int k = 0; k < 4; ++k)
+                if (k < nmma)
+                    umma_i8(d_tmem, desc_advance(a0, k * a_step), desc_advance(b0, k * b_step), idesc,
+                            static_cast<uint32_t>(kb != kb_lo || k != 0));
+            umma_commit(smem_u32(&empty_bar[s]));
+            if (++s == STAGES) { s = 0; ph ^= 1u; }
+        }
+        if (ok) umma_commit(smem_u32(&tfull_bar[acc]));
+    }
+}
+
+// Output row of an epilogue thread: validity, TMA store coordinates of its tile, linear row index.
+struct RowInfo { bool valid; int cy, cz, cw; long long row_lin; };
+__device__ __forceinline__ RowInfo row_info(const GemmParams& p, int m_t, int split, int row_in_tile) {
+    RowInfo r;
+    if (p.conv) {
+        const int tw = m_t % p.tiles_w, th = (m_t / p.tiles_w) % p.tiles_h, tn = m_t / (p.tiles_w * p.tiles_h);
+        const int w = tw * p.BW + row_in_tile % p.BW;
+        const int h = th * p.BH + (row_in_tile / p.BW) % p.BH;
+        const int n = tn * p.BI + row_in_tile / (p.BW * p.BH);
+        r.valid = row_in_tile < p.BW * p.BH * p.BI && w < p.W && h < p.H && n < p.Nimg;
+        r.cy = tw * p.BW; r.cz = th * p.BH; r.cw = tn * p.BI;
+        r.row_lin = (static_cast<long long>(n) * p.H + h) * p.W + w;
+    } else {
+        r.row_lin = static_cast<long long>(m_t) * BLOCK_M + row_in_tile;
+        r.valid = r.row_lin < p.M;
+        r.cy = m_t * BLOCK_M; r.cz = split; r.cw = 0;
+    }
+    return r;
+}
+// max|x| = max(max x, -min x) over the first `lim` of 128 accumulators: short chains of 3-input min/max
+__device__ __forceinline__ void track_minmax(const uint32_t (&v)[4][32], int lim, int (&vmax)[4], int (&vmin)[4]) {
+    if (lim >= 128) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+#pragma unroll
+            for (int i = 0; i < 32; i += 2) {
+                vmax[j] = __vimax3_s32(vmax[j], static_cast<int>(v[j][i]), static_cast<int>(v[j][i + 1]));
+                vmin[j] = __vimin3_s32(vmin[j], static_cast<int>(v[j][i]), static_cast<int>(v[j][i + 1]));
+            }
+    } else {
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+                if (j * 32 + i < lim) {
+                    vmax[0] = max(vmax[0], static_cast<int>(v[j][i]));
+                    vmin[0] = min(vmin[0], static_cast<int>(v[j][i]));
+                }
+    }
+}
+__device__ __forceinline__ unsigned fold_minmax(const int (&vmax)[4], const int (&vmin)[4]) {
+    const int hi = max(max(vmax[0], vmax[1]), max(vmax[2], vmax[3]));
+    const int lo = min(min(vmin[0], vmin[1]), min(vmin[2], vmin[3]));
+    return max(static_cast<unsigned>(hi), static_cast<unsigned>(-static_cast<long long>(lo)));
+}
+// 128 accumulators of one row -> 32 words of packed int8
+__device__ __forceinline__ void narrow_row(const uint32_t (&v)[4][32], uint32_t (&packed)[32], int shift, int mode, int relu,
+                                           unsigned long long seed, unsigned rng_stream, unsigned long long e0) {
+    if (mode == ROUND_NEAREST && shift > 0) {
+        const int half = 1 << (shift - 1);
+        if (relu) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+#pragma unroll
+                for (int i = 0; i < 32; i += 4) packed[j * 8 + (i >> 2)] = narrow4_nearest<true>(&v[j][i], shift, half);
+        } else {
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+#pragma unroll
+                for (int i = 0; i < 32; i += 4) packed[j * 8 + (i >> 2)] = narrow4_nearest<false>(&v[j][i], shift, half);
+        }
+    } else {
+        const bool stochastic = mode == ROUND_STOCHASTIC && shift > 0;
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+#pragma unroll
+            for (int i = 0; i < 32; i += 4) {
+                uint32_t rnd[4] = {0, 0, 0, 0};
+                if (stochastic) {
+                    const unsigned long long e = e0 + j * 32 + i;
+                    if ((e & 3ull) == 0) random_block(seed, rng_stream, e >> 2, rnd);
+                    else {
+#pragma unroll
+                        for (int t = 0; t < 4; ++t) rnd[t] = random_word(seed, rng_stream, e + t);
+                    }
+                }
+                packed[j * 8 + (i >> 2)] = narrow4(&v[j][i], shift, mode, relu, rnd);
+            }
+    }
+}
+
 template <int BN, bool FUSED>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)  // 10 warps: 3 on one scheduler -> at most 168 registers per thread
 umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
@@ -172,83 +352,9 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     const int total_tiles = mn_tiles * p.splits;
 
     if (warp == 0) {
-        // ------------------------------------------------------------------ TMA producer
-        if (lane == 0) {
-            int s = 0; uint32_t ph = 0; bool ok = true;
-            for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
-                const int split = tile / mn_tiles, mn = tile % mn_tiles;
-                const int m_t = mn / p.n_tiles, n_t = mn % p.n_tiles;
-                const int kb_lo = static_cast<int>(static_cast<long long>(split) * p.num_kb / p.splits);
-                const int kb_hi = static_cast<int>(static_cast<long long>(split + 1) * p.num_kb / p.splits);
-                int tw = 0, th = 0, tn = 0;
-                if (p.conv) { tw = m_t % p.tiles_w; th = (m_t / p.tiles_w) % p.tiles_h; tn = m_t / (p.tiles_w * p.tiles_h); }
-                for (int kb = kb_lo; kb < kb_hi; ++kb) {
-                    if (!mbar_wait(smem_u32(&empty_bar[s]), ph ^ 1u, abort_flag)) { ok = false; report_abort(p.status, 1, 0); break; }
-                    const uint32_t fb = smem_u32(&full_bar[s]);
-                    const uint32_t sa = smem_u32(smem + s * Cfg::STAGE_BYTES);
-                    const uint32_t sb = sa + PANEL_BYTES;
-                    mbar_arrive_expect_tx(fb, static_cast<uint32_t>(p.a_bytes + Cfg::B_STAGE_BYTES));
-                    if (p.conv) {
-                        const int tap = kb / p.cblocks, cb = kb % p.cblocks;
-                        const int r = tap / p.S, sx = tap % p.S;
-                        const int dx = p.flip ? p.pad - sx : sx - p.pad, dy = p.flip ? p.pad - r : r - p.pad;
-                        tma_load_4d(sa, &tmA, fb, cb * ROW_BYTES, tw * p.BW + dx, th * p.BH + dy, tn * p.BI);
-                        if (p.b_mn) {
-#pragma unroll
-                            for (int pn = 0; pn < BN / 128; ++pn)
-                                tma_load_2d(sb + pn * PANEL_BYTES, &tmB, fb, tap * p.tapstride + n_t * BN + pn * 128, cb * 128);
-                        } else {
-                            tma_load_2d(sb, &tmB, fb, tap * p.tapstride + cb * ROW_BYTES, n_t * BN);
-                        }
-                    } else {
-                        if (p.a_mn) tma_load_2d(sa, &tmA, fb, m_t * BLOCK_M, kb * 128);
-                        else        tma_load_2d(sa, &tmA, fb, kb * ROW_BYTES, m_t * BLOCK_M);
-                        if (p.b_mn) {
-#pragma unroll
-                            for (int pn = 0; pn < BN / 128; ++pn)
-                                tma_load_2d(sb + pn * PANEL_BYTES, &tmB, fb, n_t * BN + pn * 128, kb * 128);
-                        } else {
-                            tma_load_2d(sb, &tmB, fb, kb * ROW_BYTES, n_t * BN);
-                        }
-                    }
-                    if (++s == STAGES) { s = 0; ph ^= 1u; }
-                }
-            }
-        }
+        if (lane == 0) producer_role<BN, STAGES, Cfg::STAGE_BYTES>(smem, full_bar, empty_bar, &tmA, &tmB, p, abort_flag);
     } else if (warp == 1) {
-        // ------------------------------------------------------------------ MMA issuer
-        if (lane == 0) {
-            const uint32_t idesc = make_idesc_i8(BLOCK_M, BN, p.a_mn, p.b_mn);
-            int s = 0; uint32_t ph = 0; bool ok = true; int it = 0;
-            for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x, ++it) {
-                const int acc = it & 1; const uint32_t aph = (it >> 1) & 1u;
-                if (!mbar_wait(smem_u32(&tempty_bar[acc]), aph ^ 1u, abort_flag)) { report_abort(p.status, 2, 1); break; }
-                tc_fence_after();
-                const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BN);
-                const int split = tile / mn_tiles;
-                const int kb_lo = static_cast<int>(static_cast<long long>(split) * p.num_kb / p.splits);
-                const int kb_hi = static_cast<int>(static_cast<long long>(split + 1) * p.num_kb / p.splits);
-                for (int kb = kb_lo; kb < kb_hi; ++kb) {
-                    if (!mbar_wait(smem_u32(&full_bar[s]), ph, abort_flag)) { ok = false; report_abort(p.status, 3, 1); break; }
-                    tc_fence_after();
-                    const uint32_t sa = smem_u32(smem + s * Cfg::STAGE_BYTES);
-                    const uint32_t sb = sa + PANEL_BYTES;
-                    const uint64_t a0 = p.a_mn ? make_smem_desc(sa, PANEL_BYTES, 1024, SWIZZLE_128B_CODE)
-                                               : make_smem_desc(sa, 16, 1024, SWIZZLE_128B_CODE);
-                    const uint64_t b0 = p.b_mn ? make_smem_desc(sb, PANEL_BYTES, 1024, SWIZZLE_128B_CODE)
-                                               : make_smem_desc(sb, 16, 1024, SWIZZLE_128B_CODE);
-                    const uint32_t a_step = p.a_mn ? 32u * ROW_BYTES : 32u;
-                    const uint32_t b_step = p.b_mn ? 32u * ROW_BYTES : 32u;
-#pragma unroll
-                    for (int k = 0; k < 4; ++k)
-                        umma_i8(d_tmem, desc_advance(a0, k * a_step), desc_advance(b0, k * b_step), idesc,
-                                static_cast<uint32_t>(kb != kb_lo || k != 0));
-                    umma_commit(smem_u32(&empty_bar[s]));
-                    if (++s == STAGES) { s = 0; ph ^= 1u; }
-                }
-                if (ok) umma_commit(smem_u32(&tfull_bar[acc]));
-            }
-        }
+        if (lane == 0) mma_role<BN, STAGES, Cfg::STAGE_BYTES, false>(smem, full_bar, empty_bar, tfull_bar, tempty_bar, tmem_base, p, abort_flag);
     } else {
         // ------------------------------------------------------------------ epilogue (2 x 4 warps)
         // Two warpgroups.  With several tiles per CTA they alternate tiles (warpgroup g owns
@@ -441,6 +547,179 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         tc_fence_after();
         __syncwarp();
         tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
+// Exact single-pass requantisation for problems whose accumulators all fit in tensor memory:
+// every CTA owns at most 512 / BN output tiles and PARKS their int32 accumulators in TMEM.  After
+// its main loops a CTA reduces max|acc| of its tiles into the global word, all CTAs meet at a grid
+// barrier (cooperative launch: all resident; bounded spin), read the now final max, derive the true
+// shift and only then narrow their parked accumulators to int8.  No prediction, no second launch,
+// no int32 in memory.  state = {shift out, max|acc|, redo flag (cleared), redo count, exit ticket,
+// barrier arrivals}; words 1, 4 and 5 are zero between calls.
+// ------------------------------------------------------------------------------------------------
+template <int BN>
+struct ParkedCfg {
+    static constexpr int STAGE_BYTES = PANEL_BYTES + BN * ROW_BYTES;
+    static constexpr int EPI_GROUP_BYTES = EPI_CHUNK_BYTES;  // one 128 x 128 int8 staging tile per warpgroup
+    static constexpr int EPI_BYTES = 2 * EPI_GROUP_BYTES;
+    static constexpr int STAGES = (224 * 1024 - EPI_BYTES) / STAGE_BYTES;
+    static constexpr int MAX_TILES = 512 / BN;
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + EPI_BYTES + 1024 + 256;
+};
+
+constexpr unsigned long long GRID_BARRIER_LIMIT_NS = 500000000ull;  // 0.5 s
+
+template <int BN>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+umma_parked_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                   const __grid_constant__ CUtensorMap tmC, const GemmParams p) {
+    using Cfg = ParkedCfg<BN>;
+    constexpr int STAGES = Cfg::STAGES;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t* epi_smem = smem + STAGES * Cfg::STAGE_BYTES;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(epi_smem + Cfg::EPI_BYTES);
+    uint64_t* full_bar = bars;
+    uint64_t* empty_bar = bars + STAGES;
+    uint64_t* tfull_bar = bars + 2 * STAGES;  // one per parked tile (up to 4)
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    volatile int* shift_slot = reinterpret_cast<volatile int*>(tmem_slot + 2);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < STAGES; ++i) { mbar_init(smem_u32(&full_bar[i]), 1); mbar_init(smem_u32(&empty_bar[i]), 1); }
+        for (int i = 0; i < 4; ++i) mbar_init(smem_u32(&tfull_bar[i]), 1);
+        *abort_flag = 0;
+        fence_barrier_init();
+        tma_prefetch_desc(&tmA);
+        tma_prefetch_desc(&tmB);
+        tma_prefetch_desc(&tmC);
+    }
+    if (warp == 1) { tmem_alloc(smem_u32(tmem_slot), 512); tmem_relinquish(); }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    const int mn_tiles = p.m_tiles * p.n_tiles;
+    const int total_tiles = mn_tiles * p.splits;
+
+    if (warp == 0) {
+        if (lane == 0) producer_role<BN, STAGES, Cfg::STAGE_BYTES>(smem, full_bar, empty_bar, &tmA, &tmB, p, abort_flag);
+    } else if (warp == 1) {
+        if (lane == 0) mma_role<BN, STAGES, Cfg::STAGE_BYTES, true>(smem, full_bar, empty_bar, tfull_bar, nullptr, tmem_base, p, abort_flag);
+    } else {
+        // Work units of the epilogue: (tile of this CTA, 128-column group); the two warpgroups take
+        // alternate units, the same ones in both passes.
+        const int grp = (warp - 2) >> 2;
+        const int q = warp & 3;
+        const int row_in_tile = q * 32 + lane;
+        const int bar_id = EPI_BARRIER + grp;
+        const bool leader = (threadIdx.x == 64 + grp * 128);
+        const uint32_t buf = smem_u32(epi_smem) + grp * Cfg::EPI_GROUP_BYTES;
+        constexpr int CG = BN / 128;
+        int my_tiles = 0;
+        for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) ++my_tiles;
+        const int units = my_tiles * CG;
+
+        // ---- pass 1: max|acc| of this CTA's tiles
+        int vmax[4] = {0, 0, 0, 0}, vmin[4] = {0, 0, 0, 0};
+        bool ok = true;
+        for (int u = grp; u < units; u += 2) {
+            const int it = u / CG, g0 = (u % CG) * 128;
+            const int tile = blockIdx.x + it * gridDim.x;
+            const uint32_t failed = mbar_wait(smem_u32(&tfull_bar[it]), 0, abort_flag) ? 0u : 1u;
+            if (barrier_or(bar_id, 128, failed)) { if (failed) report_abort(p.status, 4, 2); ok = false; break; }
+            tc_fence_after();
+            const int mn = tile % mn_tiles, m_t = mn / p.n_tiles, n_t = mn % p.n_tiles;
+            const RowInfo ri = row_info(p, m_t, tile / mn_tiles, row_in_tile);
+            const int col = n_t * BN + g0;
+            if (col >= p.N) continue;
+            uint32_t v[4][32];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + it * BN + g0 + j * 32, v[j]);
+            tmem_ld_wait();
+            if (ri.valid) track_minmax(v, p.N - col, vmax, vmin);
+        }
+        unsigned local_max = __reduce_max_sync(0xFFFFFFFFu, fold_minmax(vmax, vmin));
+        int32_t* st = p.state;
+        if (lane == 0 && local_max != 0) atomicMax(reinterpret_cast<unsigned*>(&st[1]), local_max);
+
+        // ---- grid barrier: every CTA has contributed its maximum
+        __threadfence();
+        named_barrier(EPI_BARRIER + 2, 256);
+        if (threadIdx.x == 64) {
+            atomicAdd(&st[5], 1);
+            const unsigned long long t0 = global_timer_ns();
+            bool arrived = false;
+            for (unsigned spin = 0;; ++spin) {
+                if (atomicAdd(&st[5], 0) >= static_cast<int>(gridDim.x)) { arrived = true; break; }
+                if ((spin & 63) == 63) {
+                    if (*abort_flag || global_timer_ns() - t0 > GRID_BARRIER_LIMIT_NS) break;
+                    __nanosleep(200);
+                }
+            }
+            __threadfence();
+            bool zero_out;
+            const unsigned m = atomicMax(reinterpret_cast<unsigned*>(&st[1]), 0u);
+            *shift_slot = arrived ? shift_for(m, p.kind, p.target_bits, &zero_out) : -1;
+            if (!arrived) { *abort_flag = 1; report_abort(p.status, 5, 2); }
+        }
+        named_barrier(EPI_BARRIER + 2, 256);
+        const int shift = *shift_slot;
+
+        // ---- pass 2: narrow the parked accumulators with the true shift
+        if (ok && shift >= 0) {
+            unsigned long long seed = 0;
+            if (p.mode == ROUND_STOCHASTIC && shift > 0) seed = *p.seed;
+            for (int u = grp; u < units; u += 2) {
+                const int it = u / CG, g0 = (u % CG) * 128;
+                const int tile = blockIdx.x + it * gridDim.x;
+                const int mn = tile % mn_tiles, m_t = mn / p.n_tiles, n_t = mn % p.n_tiles;
+                const RowInfo ri = row_info(p, m_t, tile / mn_tiles, row_in_tile);
+                const int col = n_t * BN + g0;
+                if (col >= p.N) continue;
+                uint32_t v[4][32];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + it * BN + g0 + j * 32, v[j]);
+                tmem_ld_wait();
+                uint32_t packed[32];
+                narrow_row(v, packed, shift, p.mode, p.relu, seed, p.rng_stream,
+                           p.rng_offset + static_cast<unsigned long long>(ri.row_lin) * p.N + col);
+                if (leader) bulk_wait_read<0>();
+                named_barrier(bar_id, 128);
+                stage_row(buf, row_in_tile, packed);
+                fence_proxy_async();
+                named_barrier(bar_id, 128);
+                if (leader) { tma_store_4d(&tmC, buf, col, ri.cy, ri.cz, ri.cw); bulk_commit(); }
+            }
+            if (leader) bulk_wait<0>();
+        }
+        // ---- the CTA that leaves last publishes the shift and clears the words for the next call
+        named_barrier(EPI_BARRIER + 2, 256);
+        if (threadIdx.x == 64) {
+            if (atomicAdd(&st[4], 1) == static_cast<int>(gridDim.x) - 1) {
+                __threadfence();
+                const int s_out = shift < 0 ? 0 : shift;
+                st[0] = s_out; st[2] = 0; st[1] = 0; st[5] = 0; st[4] = 0;
+                if (p.exp_out) *p.exp_out = s_out + (p.exp_a ? *p.exp_a : 0) + (p.exp_b ? *p.exp_b : 0);
+                if (p.shift_out) *p.shift_out = s_out;
+            }
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        if (*abort_flag) __nanosleep(200000);
+        tc_fence_after();
+        __syncwarp();
+        tmem_dealloc(tmem_base, 512);
     }
 }
 
@@ -661,6 +940,25 @@ static int launch_gemm(int bn, bool fused, const CUtensorMap& a, const CUtensorM
     if (fused) return bn == 256 ? launch_gemm_inst<256, true>(a, b, c, p, st) : launch_gemm_inst<128, true>(a, b, c, p, st);
     return bn == 256 ? launch_gemm_inst<256, false>(a, b, c, p, st) : launch_gemm_inst<128, false>(a, b, c, p, st);
 }
+template <int BN>
+static int launch_parked_inst(const CUtensorMap& a, const CUtensorMap& b, const CUtensorMap& c, const GemmParams& p,
+                              cudaStream_t st) {
+    using Cfg = ParkedCfg<BN>;
+    cudaError_t e = cudaFuncSetAttribute(umma_parked_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
+    if (e != cudaSuccess) return set_cuda_error(e);
+    int grid = p.m_tiles * p.n_tiles * p.splits;
+    if (grid > sm_count()) grid = sm_count();
+    // cooperative launch: the grid barrier inside needs every CTA resident at the same time
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(grid); cfg.blockDim = dim3(GEMM_THREADS); cfg.dynamicSmemBytes = Cfg::SMEM_BYTES; cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeCooperative; attr[0].val.cooperative = 1;
+    cfg.attrs = attr; cfg.numAttrs = 1;
+    return set_cuda_error(cudaLaunchKernelEx(&cfg, umma_parked_kernel<BN>, a, b, c, p));
+}
+// all accumulators of the problem fit in the tensor memory of one wave of CTAs
+static bool fits_parked(int bn, int tiles) { return tiles <= sm_count() * (512 / bn); }
+
 static void set_fused(GemmParams* p, const FusedArgs* f) {
     if (!f) return;
     p->state = f->state; p->only_if_redo = f->only_if_redo; p->mode = f->mode; p->relu = f->relu;
@@ -750,14 +1048,26 @@ int umma_conv(const int8_t* x, const int8_t* w, void* out, unsigned* maxabs, int
     p.H = H; p.W = W; p.S = S; p.pad = pad; p.Nimg = Nimg; p.tapstride = C;
     p.tiles_w = (W + p.BW - 1) / p.BW; p.tiles_h = (H + p.BH - 1) / p.BH;
     const int tiles_n = (Nimg + p.BI - 1) / p.BI;
-    p.cblocks = red / 128;
+    p.cblocks = (red + 127) / 128; p.red = red;
     p.M = Nimg * H * W; p.N = outc; p.num_kb = R * S * p.cblocks;
     p.m_tiles = p.tiles_w * p.tiles_h * tiles_n; p.n_tiles = (outc + bn - 1) / bn;
     p.a_mn = 0; p.b_mn = flip ? 1 : 0; p.a_bytes = p.BW * p.BH * p.BI * ROW_BYTES;
     p.maxabs = maxabs; p.status = status;
     p.split_cols = (bn == 256 && p.m_tiles * p.n_tiles <= 2 * sm_count()) ? 1 : 0;
     set_fused(&p, fused);
+    if (fused && fused->parked) {
+        if (!fits_parked(bn, p.m_tiles * p.n_tiles)) return NITI_ERR_UNSUPPORTED;
+        return bn == 256 ? launch_parked_inst<256>(ma, mb, mc, p, st) : launch_parked_inst<128>(ma, mb, mc, p, st);
+    }
     return launch_gemm(bn, fused != nullptr, ma, mb, mc, p, st);
+}
+
+bool umma_conv_fits_parked(int Nimg, int H, int W, int outc) {
+    int bw, bh, bi;
+    pick_pixel_box(Nimg, H, W, &bw, &bh, &bi);
+    const int bn = (outc > 128) ? 256 : 128;
+    const int m_tiles = ((W + bw - 1) / bw) * ((H + bh - 1) / bh) * ((Nimg + bi - 1) / bi);
+    return fits_parked(bn, m_tiles * ((outc + bn - 1) / bn));
 }
 
 static void wgrad_plan(int Nimg, int H, int W, int C, int K, int R, int max_splits, WgradParams* p) {

@@ -97,6 +97,11 @@ def conv_fprop_acc(x, w, pad=1, stride=1):
     return y32, mx
 
 
+def set_accumulator_parking(enabled):
+    """Switch the single-launch (accumulators parked in tensor memory) fused kernels on or off; returns the old setting."""
+    return bool(lib.niti_set_option(1, int(bool(enabled))))
+
+
 def new_requant_state(device):
     """int32[8] a fused conv + requantisation call keeps per layer and direction:
     [0] shift (prediction in, true value out), [1] max|acc|, [2] redo flag, [3] redo count, [4] block ticket."""
@@ -165,7 +170,7 @@ def conv_wgrad_acc(x, err, R=3, S=3, pad=1, out=None):
     mx = torch.empty(1, dtype=torch.int32, device=x.device)
     nbytes = lib.niti_conv_wgrad_scratch_bytes(N, H, W, C, K, R, S)
     sc = scratch(x.device, nbytes)
-    _call("niti_conv_wgrad_i8", 2 if C % 128 == 0 else 3, 2 * N * H * W * K * R * S * C, x.numel() + err.numel() + 4 * g32.numel(),
+    _call("niti_conv_wgrad_i8", 2 if C % 16 == 0 else 3, 2 * N * H * W * K * R * S * C, x.numel() + err.numel() + 4 * g32.numel(),
           lib.niti_conv_wgrad_i8, _p(x), _p(err), _p(g32), _p(mx), _p(sc), sc.numel(), N, H, W, C, K, R, S, pad,
           _p(status_word(x.device)), _st())
     return g32, mx

@@ -66,6 +66,8 @@ CONV_CASES = [
     (2, 8, 8, 128, 128), (4, 32, 32, 128, 128), (3, 16, 16, 128, 256), (5, 8, 8, 256, 512), (9, 4, 4, 256, 128),
     (2, 12, 20, 128, 144), (1, 2, 2, 128, 128), (16, 2, 2, 128, 128),
     (4, 32, 32, 3, 128), (3, 8, 8, 3, 32), (2, 8, 8, 16, 32), (2, 6, 10, 5, 7),
+    # channel counts that are multiples of 16 but not of 128: partial 128-byte blocks, TMA zero fill
+    (6, 16, 16, 64, 64), (3, 8, 8, 192, 64), (2, 8, 8, 48, 80), (4, 8, 8, 64, 320),
 ]
 
 
@@ -213,11 +215,22 @@ def test_quantize_input():
 
 # ----------------------------------------------------------------------------- fused conv + requantisation
 @pytest.mark.parametrize("N,H,W,C,K", [(4, 32, 32, 128, 128), (3, 16, 16, 128, 256), (5, 8, 8, 256, 512), (2, 12, 20, 128, 144),
-                                        (4, 32, 32, 3, 128), (9, 4, 4, 256, 128)])
+                                        (4, 32, 32, 3, 128), (9, 4, 4, 256, 128), (6, 16, 16, 64, 64), (2, 8, 8, 48, 80)])
 @pytest.mark.parametrize("mode,relu", [(0, True), (0, False), (1, False), (2, True)])
-def test_conv_fused_requant(N, H, W, C, K, mode, relu):
-    """Predicted-shift kernels: first call mispredicts (state starts at 0) and must redo, the second
-    call predicts right; both must equal conv + act_calc / err_calc of the oracle."""
+@pytest.mark.parametrize("parking", [False, True])
+def test_conv_fused_requant(N, H, W, C, K, mode, relu, parking):
+    """Fused conv + requantisation against conv + act_calc / err_calc of the oracle.
+    parking=False: predicted-shift kernels; the first call mispredicts (state starts at 0) and must
+    redo, the second call predicts right.  parking=True: accumulators parked in tensor memory across
+    a grid barrier, exact in one launch (all of these shapes are small enough)."""
+    old = ops.set_accumulator_parking(parking)
+    try:
+        _fused_case(N, H, W, C, K, mode, relu, parking and C * 9 > 32)
+    finally:
+        ops.set_accumulator_parking(old)
+
+
+def _fused_case(N, H, W, C, K, mode, relu, parked):
     rng = np.random.default_rng(N + H + C + K + mode)
     x, w = rnd8(rng, (N, H, W, C)), rnd8(rng, (K, 3, 3, C))
     seed = ops.seed_tensor(31, DEV)
@@ -232,8 +245,9 @@ def test_conv_fused_requant(N, H, W, C, K, mode, relu):
         y8, e, s = ops.conv_fprop_fused(cu(x), cu(w), st, 1, mode, seed, 5, 64, relu, ea, eb)
         assert_same(y8, want, f"fused fprop call {call}")
         assert int(e.item()) == want_e and int(s.item()) == want_s
-        assert st.tolist()[1:5] == [0, 1 if (call == 0 and want_s != 0) else 0, 1 if want_s != 0 else 0, 0]
-    if C % 16 == 0 and K % 128 == 0:
+        redo_now, redos = (0, 0) if parked else (1 if (call == 0 and want_s != 0) else 0, 1 if want_s != 0 else 0)
+        assert st.tolist()[1:6] == [0, redo_now, redos, 0, 0] and st.tolist()[0] == want_s
+    if C % 16 == 0 and K % 16 == 0:
         err = rnd8(rng, (N, H, W, K))
         acc = O.conv_dgrad(err, w)
         words = philox.random_u32_tensor(31, 6, acc.shape, offset=128)

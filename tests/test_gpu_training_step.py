@@ -85,6 +85,13 @@ def test_vgg7_three_steps_graph_replay():
     run_steps([128, 128, "M", 256, 256, "M", 512, 512, "M"], 8, 4321, True, 3, 5, True, True)
 
 
+@pytest.mark.parametrize("name,B", [("vgg9_wide", 2), ("vgg13", 4), (8, 2)])
+def test_other_layer_lists_one_step(name, B):
+    """The layer lists of the benchmark's other configurations (incl. the 64-channel VGG-13 layers) and the
+    reference's depth-8 table, one step each."""
+    run_steps(list(ti_vgg.cifar_cfg[name]), B, 99, True, 1, 5, True, False)
+
+
 def test_stochastic_act_err_grad_rounding():
     saved = ti_torch.ACT_ROUND_METHOD, ti_torch.ERROR_ROUND_METHOD, ti_torch.GRAD_ROUND_METHOD
     try:
