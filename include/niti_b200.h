@@ -202,10 +202,13 @@ NITI_API int niti_absmax_i32(const int32_t* acc, int64_t n, uint32_t* maxabs, vo
  * int8pool_cuda.int8_pool / int8_pool_backward (int8pool.cpp, int8pool_kernel.cu:28-138) as
  * used by TiMaxpool2d (ti_torch.py:292-316); int8 throughout (no fp16 copies), pad 0.
  * Backward recomputes the window maximum from x and routes dy to the first position, scanning
- * rows then columns, that holds it.
+ * rows then columns, that holds it.  relu_mask != 0 additionally zeroes dx where x <= 0, i.e. it
+ * applies the TiReLU.backward (ti_torch.py:281-290) of a ReLU whose output x is (x > 0 exactly where
+ * the ReLU's input was > 0), saving that layer's separate pass.
  */
 NITI_API int niti_maxpool_fwd_i8(const int8_t* x, int8_t* y, int N, int H, int W, int C, int k, int stride, void* stream);
-NITI_API int niti_maxpool_bwd_i8(const int8_t* x, const int8_t* dy, int8_t* dx, int N, int H, int W, int C, int k, int stride, void* stream);
+NITI_API int niti_maxpool_bwd_i8(const int8_t* x, const int8_t* dy, int8_t* dx, int N, int H, int W, int C, int k, int stride,
+                        int relu_mask, void* stream);
 /* TiReLU.forward / backward (ti_torch.py:268-290) */
 NITI_API int niti_relu_fwd_i8(const int8_t* x, int8_t* y, int64_t n, void* stream);
 NITI_API int niti_relu_bwd_i8(const int8_t* act, const int8_t* err, int8_t* out, int64_t n, void* stream);

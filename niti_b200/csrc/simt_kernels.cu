@@ -250,9 +250,11 @@ maxpool2_fwd_kernel(const uint4* __restrict__ x, uint4* __restrict__ y, int Nimg
     }
 }
 
-__device__ __forceinline__ void route4(unsigned a, unsigned b, unsigned d, unsigned e, unsigned dy,
+// relu_mask: the position that receives dy holds the window maximum m, so "x > 0 there" is "m > 0"
+__device__ __forceinline__ void route4(unsigned a, unsigned b, unsigned d, unsigned e, unsigned dy, int relu_mask,
                                        unsigned& oa, unsigned& ob, unsigned& od, unsigned& oe) {
     const unsigned m = __vmaxs4(__vmaxs4(a, b), __vmaxs4(d, e));
+    if (relu_mask) dy &= __vcmpgts4(m, 0);
     const unsigned ha = __vcmpeq4(a, m);
     const unsigned hb = __vcmpeq4(b, m) & ~ha;
     const unsigned hd = __vcmpeq4(d, m) & ~(ha | hb);
@@ -262,7 +264,7 @@ __device__ __forceinline__ void route4(unsigned a, unsigned b, unsigned d, unsig
 
 __global__ void __launch_bounds__(256)
 maxpool2_bwd_kernel(const uint4* __restrict__ x, const uint4* __restrict__ dy, uint4* __restrict__ dx, int Nimg, int H,
-                    int W, int C16, int P, int Q) {
+                    int W, int C16, int P, int Q, int relu_mask) {
     const long long total = static_cast<long long>(Nimg) * P * Q * C16;
     for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
          i += static_cast<long long>(gridDim.x) * blockDim.x) {
@@ -276,10 +278,10 @@ maxpool2_bwd_kernel(const uint4* __restrict__ x, const uint4* __restrict__ dy, u
         uint4 a = __ldg(x + base), b = __ldg(x + base + C16), d = __ldg(x + base + row), e = __ldg(x + base + row + C16);
         uint4 g = __ldg(dy + i);
         uint4 oa, ob, od, oe;
-        route4(a.x, b.x, d.x, e.x, g.x, oa.x, ob.x, od.x, oe.x);
-        route4(a.y, b.y, d.y, e.y, g.y, oa.y, ob.y, od.y, oe.y);
-        route4(a.z, b.z, d.z, e.z, g.z, oa.z, ob.z, od.z, oe.z);
-        route4(a.w, b.w, d.w, e.w, g.w, oa.w, ob.w, od.w, oe.w);
+        route4(a.x, b.x, d.x, e.x, g.x, relu_mask, oa.x, ob.x, od.x, oe.x);
+        route4(a.y, b.y, d.y, e.y, g.y, relu_mask, oa.y, ob.y, od.y, oe.y);
+        route4(a.z, b.z, d.z, e.z, g.z, relu_mask, oa.z, ob.z, od.z, oe.z);
+        route4(a.w, b.w, d.w, e.w, g.w, relu_mask, oa.w, ob.w, od.w, oe.w);
         dx[base] = oa; dx[base + C16] = ob; dx[base + row] = od; dx[base + row + C16] = oe;
     }
 }
@@ -303,7 +305,7 @@ __global__ void maxpool_fwd_generic(const int8_t* __restrict__ x, int8_t* __rest
     }
 }
 __global__ void maxpool_bwd_generic(const int8_t* __restrict__ x, const int8_t* __restrict__ dy, int8_t* __restrict__ dx,
-                                    int Nimg, int H, int W, int C, int k, int stride, int P, int Q) {
+                                    int Nimg, int H, int W, int C, int k, int stride, int P, int Q, int relu_mask) {
     const long long total = static_cast<long long>(Nimg) * H * W * C;
     for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
          i += static_cast<long long>(gridDim.x) * blockDim.x) {
@@ -324,7 +326,7 @@ __global__ void maxpool_bwd_generic(const int8_t* __restrict__ x, const int8_t* 
                         int v = x[((static_cast<long long>(n) * H + p * stride + a) * W + q * stride + b) * C + c];
                         if (v > m) { m = v; am = a; bm = b; }
                     }
-                if (p * stride + am == h && q * stride + bm == w)
+                if (p * stride + am == h && q * stride + bm == w && (!relu_mask || m > 0))
                     sum += dy[((static_cast<long long>(n) * P + p) * Q + q) * C + c];
             }
         dx[i] = static_cast<int8_t>(sum);
@@ -369,6 +371,36 @@ dropout_kernel(const int8_t* __restrict__ x, int8_t* __restrict__ y, long long r
          i += static_cast<long long>(gridDim.x) * blockDim.x) {
         const unsigned long long f = static_cast<unsigned long long>(i % features);
         y[i] = (random_word(seed, rng_stream, f) & 1u) ? x[i] : int8_t(0);
+    }
+}
+// features % 16 == 0: one thread owns 16 features (four generator blocks, drawn once) and walks a strip of
+// rows with 16-byte accesses; the mask depends on the feature only.
+constexpr int DROPOUT_ROWS_PER_THREAD = 8;
+__global__ void __launch_bounds__(256)
+dropout16_kernel(const uint4* __restrict__ x, uint4* __restrict__ y, long long rows, long long f16,
+                 const unsigned long long* seed_p, unsigned rng_stream) {
+    const unsigned long long seed = *seed_p;
+    const long long strips = (rows + DROPOUT_ROWS_PER_THREAD - 1) / DROPOUT_ROWS_PER_THREAD;
+    const long long total = strips * f16;
+    for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+         i += static_cast<long long>(gridDim.x) * blockDim.x) {
+        const long long fq = i % f16, strip = i / f16;
+        uint32_t m[4];
+#pragma unroll
+        for (int b = 0; b < 4; ++b) {
+            uint32_t w[4];
+            random_block(seed, rng_stream, static_cast<unsigned long long>(fq) * 4 + b, w);
+            m[b] = ((w[0] & 1u) ? 0xFFu : 0u) | ((w[1] & 1u) ? 0xFF00u : 0u) | ((w[2] & 1u) ? 0xFF0000u : 0u) |
+                   ((w[3] & 1u) ? 0xFF000000u : 0u);
+        }
+        const long long r0 = strip * DROPOUT_ROWS_PER_THREAD;
+#pragma unroll
+        for (int r = 0; r < DROPOUT_ROWS_PER_THREAD; ++r)
+            if (r0 + r < rows) {
+                uint4 v = __ldg(x + (r0 + r) * f16 + fq);
+                v.x &= m[0]; v.y &= m[1]; v.z &= m[2]; v.w &= m[3];
+                y[(r0 + r) * f16 + fq] = v;
+            }
     }
 }
 
@@ -689,7 +721,7 @@ gemm_bn4_kernel(const int8_t* __restrict__ A, const int8_t* __restrict__ B, int3
         const uint32_t* bp = reinterpret_cast<const uint32_t*>(B) + nq;
         const int8_t* ap = A + m * sa_m;
         int a0 = 0, a1 = 0, a2 = 0, a3 = 0;
-#pragma unroll 4
+#pragma unroll 16
         for (int k = 0; k < K; ++k) {
             const int a = ap[k * sa_k];
             const uint32_t b = __ldg(bp + static_cast<long long>(k) * n4);
@@ -758,7 +790,7 @@ extern "C" int niti_maxpool_fwd_i8(const int8_t* x, int8_t* y, int N, int H, int
 }
 
 extern "C" int niti_maxpool_bwd_i8(const int8_t* x, const int8_t* dy, int8_t* dx, int N, int H, int W, int C, int k,
-                                   int stride, void* stream) {
+                                   int stride, int relu_mask, void* stream) {
     NITI_REQUIRE(x && dy && dx && N > 0 && H >= k && W >= k && C > 0 && k > 0 && stride > 0);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const int P = (H - k) / stride + 1, Q = (W - k) / stride + 1;
@@ -766,10 +798,10 @@ extern "C" int niti_maxpool_bwd_i8(const int8_t* x, const int8_t* dy, int8_t* dx
     if (k == 2 && stride == 2 && C % 16 == 0 && H % 2 == 0 && W % 2 == 0 && al) {
         const long long total = static_cast<long long>(N) * P * Q * (C / 16);
         maxpool2_bwd_kernel<<<blocks_for(total, 256, sm_count_simt() * 16), 256, 0, st>>>(
-            reinterpret_cast<const uint4*>(x), reinterpret_cast<const uint4*>(dy), reinterpret_cast<uint4*>(dx), N, H, W, C / 16, P, Q);
+            reinterpret_cast<const uint4*>(x), reinterpret_cast<const uint4*>(dy), reinterpret_cast<uint4*>(dx), N, H, W, C / 16, P, Q, relu_mask);
     } else {
         const long long total = static_cast<long long>(N) * H * W * C;
-        maxpool_bwd_generic<<<blocks_for(total, 256, sm_count_simt() * 16), 256, 0, st>>>(x, dy, dx, N, H, W, C, k, stride, P, Q);
+        maxpool_bwd_generic<<<blocks_for(total, 256, sm_count_simt() * 16), 256, 0, st>>>(x, dy, dx, N, H, W, C, k, stride, P, Q, relu_mask);
     }
     return set_cuda_error(cudaGetLastError());
 }
@@ -788,8 +820,15 @@ extern "C" int niti_relu_bwd_i8(const int8_t* act, const int8_t* err, int8_t* ou
 extern "C" int niti_dropout_i8(const int8_t* x, int8_t* y, int64_t rows, int64_t features, const uint64_t* seed,
                                uint32_t rng_stream, void* stream) {
     NITI_REQUIRE(x && y && seed && rows >= 0 && features > 0);
-    dropout_kernel<<<blocks_for(rows * features, 256, sm_count_simt() * 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(
-        x, y, rows, features, reinterpret_cast<const unsigned long long*>(seed), rng_stream);
+    if (features % 16 == 0 && (reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y)) % 16 == 0) {
+        const long long work = ((rows + DROPOUT_ROWS_PER_THREAD - 1) / DROPOUT_ROWS_PER_THREAD) * (features / 16);
+        dropout16_kernel<<<blocks_for(work, 128, sm_count_simt() * 8), 128, 0, static_cast<cudaStream_t>(stream)>>>(
+            reinterpret_cast<const uint4*>(x), reinterpret_cast<uint4*>(y), rows, features / 16,
+            reinterpret_cast<const unsigned long long*>(seed), rng_stream);
+    } else {
+        dropout_kernel<<<blocks_for(rows * features, 256, sm_count_simt() * 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+            x, y, rows, features, reinterpret_cast<const unsigned long long*>(seed), rng_stream);
+    }
     return set_cuda_error(cudaGetLastError());
 }
 

@@ -959,6 +959,14 @@ static int launch_parked_inst(const CUtensorMap& a, const CUtensorMap& b, const 
 // all accumulators of the problem fit in the tensor memory of one wave of CTAs
 static bool fits_parked(int bn, int tiles) { return tiles <= sm_count() * (512 / bn); }
 
+// Output tile width: 256 columns halve the A-operand traffic, but when that leaves fewer tiles than
+// half the SMs, 128-column tiles put twice as many SMs to work.
+static int pick_bn(int m_tiles, int n_cols) {
+    if (n_cols <= 128) return 128;
+    const int tiles256 = m_tiles * ((n_cols + 255) / 256);
+    return tiles256 * 2 <= sm_count() ? 128 : 256;
+}
+
 static void set_fused(GemmParams* p, const FusedArgs* f) {
     if (!f) return;
     p->state = f->state; p->only_if_redo = f->only_if_redo; p->mode = f->mode; p->relu = f->relu;
@@ -1026,9 +1034,9 @@ int umma_conv(const int8_t* x, const int8_t* w, void* out, unsigned* maxabs, int
     CUtensorMap ma, mb, mc;
     const int red = flip ? K : C;   // reduction channels per tap
     const int outc = flip ? C : K;  // output channels
-    const int bn = (outc > 128) ? 256 : 128;
     GemmParams p{};
     pick_pixel_box(Nimg, H, W, &p.BW, &p.BH, &p.BI);
+    const int bn = pick_bn(((W + p.BW - 1) / p.BW) * ((H + p.BH - 1) / p.BH) * ((Nimg + p.BI - 1) / p.BI), outc);
     {
         uint64_t dims[4] = {(uint64_t)red, (uint64_t)W, (uint64_t)H, (uint64_t)Nimg};
         uint64_t str[3] = {(uint64_t)red, (uint64_t)W * red, (uint64_t)H * W * red};
@@ -1065,8 +1073,8 @@ int umma_conv(const int8_t* x, const int8_t* w, void* out, unsigned* maxabs, int
 bool umma_conv_fits_parked(int Nimg, int H, int W, int outc) {
     int bw, bh, bi;
     pick_pixel_box(Nimg, H, W, &bw, &bh, &bi);
-    const int bn = (outc > 128) ? 256 : 128;
     const int m_tiles = ((W + bw - 1) / bw) * ((H + bh - 1) / bh) * ((Nimg + bi - 1) / bi);
+    const int bn = pick_bn(m_tiles, outc);
     return fits_parked(bn, m_tiles * ((outc + bn - 1) / bn));
 }
 

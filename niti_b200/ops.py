@@ -220,11 +220,12 @@ def maxpool_fwd(x, k=2, stride=2):
     return y
 
 
-def maxpool_bwd(x, dy, k=2, stride=2):
+def maxpool_bwd(x, dy, k=2, stride=2, relu_mask=False):
+    """dx of max pooling; relu_mask also applies the backward of the ReLU that produced x (zero where x <= 0)."""
     _need_cuda(x, dy)
     N, H, W, C = x.shape
     dx = torch.empty_like(x)
-    _call("niti_maxpool_bwd_i8", 1, 0, 2 * x.numel() + dy.numel(), lib.niti_maxpool_bwd_i8, _p(x), _p(dy), _p(dx), N, H, W, C, k, stride, _st())
+    _call("niti_maxpool_bwd_i8", 1, 0, 2 * x.numel() + dy.numel(), lib.niti_maxpool_bwd_i8, _p(x), _p(dy), _p(dx), N, H, W, C, k, stride, int(relu_mask), _st())
     return dx
 
 

@@ -200,6 +200,9 @@ class TiReLU(Module):
     def __init__(self, fused=False):
         super(TiReLU, self).__init__()
         self.fused = fused
+        # set by a model builder when the next layer (a TiMaxpool2d with relu_backward_fused) applies this
+        # ReLU's backward mask itself
+        self.backward_in_next_layer = False
 
     def forward(self, input):
         act_in, exp_in = input
@@ -209,6 +212,8 @@ class TiReLU(Module):
 
     def backward(self, input):
         err_in, err_exp = input
+        if self.backward_in_next_layer:
+            return err_in, err_exp
         act, _ = self.act_in
         return ops.relu_bwd(act, err_in.contiguous()), err_exp
 
@@ -223,6 +228,9 @@ class TiMaxpool2d(Module):
         self.kernel_size = kernel_size
         self.stride = stride
         self.padding = padding
+        # True when this layer's input is the output of a TiReLU whose backward mask is applied here
+        # (x > 0 on the ReLU's output exactly where its input was > 0): one pass instead of two
+        self.relu_backward_fused = False
 
     def forward(self, input):
         self.act_in, exp_in = input
@@ -231,7 +239,8 @@ class TiMaxpool2d(Module):
 
     def backward(self, input):
         err_in, err_exp = input
-        return ops.maxpool_bwd(self.act_in, err_in.contiguous(), self.kernel_size, self.stride), err_exp
+        return ops.maxpool_bwd(self.act_in, err_in.contiguous(), self.kernel_size, self.stride,
+                               self.relu_backward_fused), err_exp
 
 
 class TiFlat(Module):

@@ -35,7 +35,12 @@ class TiVGG_cifar(TiNet):
         image_size = 32
         for idx, x in enumerate(cfg):
             if x == 'M':
-                layers += [TiMaxpool2d(2, 2)]
+                pool = TiMaxpool2d(2, 2)
+                if fuse_relu and layers and isinstance(layers[-1], TiReLU):
+                    # conv -> ReLU -> pool: the pool's backward also applies the ReLU's mask
+                    layers[-1].backward_in_next_layer = True
+                    pool.relu_backward_fused = True
+                layers += [pool]
                 image_size = image_size // 2
             else:
                 layers += [TiConv2d(in_channels, x, first_layer=(idx == 0), fuse_relu=fuse_relu),

@@ -161,6 +161,7 @@ def test_maxpool_relu(shape):
     assert_same(y, O.maxpool_fwd(x), "maxpool fwd")
     dy = rnd8(rng, y.shape)
     assert_same(ops.maxpool_bwd(cu(x), cu(dy)), O.maxpool_bwd(x, dy), "maxpool bwd")
+    assert_same(ops.maxpool_bwd(cu(x), cu(dy), relu_mask=True), O.relu_bwd(x, O.maxpool_bwd(x, dy)), "maxpool bwd + relu mask")
     x2 = rnd8(rng, shape, -128, 128)
     assert_same(ops.relu_fwd(cu(x2)), O.relu_fwd(x2), "relu fwd")
     e = rnd8(rng, shape)
@@ -173,6 +174,7 @@ def test_maxpool_generic_window():
     assert_same(ops.maxpool_fwd(cu(x), 3, 2), O.maxpool_fwd(x, 3, 2), "maxpool 3/2 fwd")
     dy = rnd8(rng, (2, 4, 4, 4), -30, 31)
     assert_same(ops.maxpool_bwd(cu(x), cu(dy), 3, 2), O.maxpool_bwd(x, dy, 3, 2), "maxpool 3/2 bwd")
+    assert_same(ops.maxpool_bwd(cu(x), cu(dy), 3, 2, True), O.relu_bwd(x, O.maxpool_bwd(x, dy, 3, 2)), "maxpool 3/2 bwd + relu mask")
 
 
 def test_dropout():
