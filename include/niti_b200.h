@@ -63,6 +63,13 @@ extern "C" {
  * single-launch kernel that keeps all accumulators in tensor memory across a grid barrier whenever
  * the problem is small enough; 0 forces the predict / verify / redo kernels.  Results are identical. */
 #define NITI_OPT_ACCUMULATOR_PARKING 1
+/* NITI_OPT_WGRAD_TMA_REDUCE (default 1): the tensor-core weight gradient adds every thread block's tiles
+ * straight into the zeroed gradient with TMA reductions at the L2; 0: partial sums per pixel range go to
+ * scratch and a second kernel folds them.  Same integers either way. */
+#define NITI_OPT_WGRAD_TMA_REDUCE 2
+/* NITI_OPT_STAGE_CAP (default 0 = all): use at most this many shared-memory stages in the GEMM / conv
+ * main loops (measurement aid: separates latency-bound from bandwidth-bound behaviour). */
+#define NITI_OPT_STAGE_CAP 3
 NITI_API int niti_set_option(int option, int value);
 
 NITI_API int niti_version(void);
@@ -101,8 +108,9 @@ NITI_API int niti_conv_dgrad_i8(const int8_t* err, const int8_t* w, int32_t* e32
  * first-layer group-conv form conv2d_weight_int8 (ti_torch.py:194-233, int8conv_kernel.cu:248-334):
  * g32[k][r][s][c] = sum_{n,p,q} err[n][p][q][k] * x[n][p+r-pad][q+s-pad][c], exact int32, read
  * straight from the NHWC tensors (no transposes).  On the tensor-core paths the reduction over
- * pixels is split across thread blocks; partial sums go through `scratch`
- * (niti_conv_wgrad_scratch_bytes) and a second kernel folds them and reduces *maxabs = max |g32|.
+ * pixels is split across thread blocks, which add their tiles into g32 with TMA reductions (exact,
+ * order-independent); the first-layer path and the NITI_OPT_WGRAD_TMA_REDUCE = 0 mode put partial
+ * sums in `scratch` (niti_conv_wgrad_scratch_bytes) and fold them.  *maxabs = max |g32|.
  */
 NITI_API size_t niti_conv_wgrad_scratch_bytes(int N, int H, int W, int C, int K, int R, int S);
 NITI_API int niti_conv_wgrad_i8(const int8_t* x, const int8_t* err, int32_t* g32, uint32_t* maxabs,

@@ -47,9 +47,12 @@ extern "C" const char* niti_last_cuda_error(void) { return g_cuda_error; }
 
 // tuning switches (process-wide): see niti_set_option
 static int g_opt_parking = 1;
+static int g_opt_wgrad_reduce = 1;
 
 extern "C" int niti_set_option(int option, int value) {
     if (option == NITI_OPT_ACCUMULATOR_PARKING) { const int old = g_opt_parking; g_opt_parking = value ? 1 : 0; return old; }
+    if (option == NITI_OPT_STAGE_CAP) { const int old = g_stage_cap; g_stage_cap = value < 0 ? 0 : value; return old; }
+    if (option == NITI_OPT_WGRAD_TMA_REDUCE) { const int old = g_opt_wgrad_reduce; g_opt_wgrad_reduce = value ? 1 : 0; return old; }
     return NITI_ERR_BAD_ARG;
 }
 
@@ -120,7 +123,7 @@ extern "C" int niti_conv_dgrad_i8(const int8_t* err, const int8_t* w, int32_t* e
 extern "C" size_t niti_conv_wgrad_scratch_bytes(int N, int H, int W, int C, int K, int R, int S) {
     if (N <= 0 || H <= 0 || W <= 0 || C <= 0 || K <= 0 || R <= 0 || S <= 0) return 0;
     const ConvPath path = wgrad_path(C, K, R, S, (R - 1) / 2);
-    if (path == CONV_TC) return umma_wgrad_scratch_bytes(N, H, W, C, K, R, S);
+    if (path == CONV_TC) return g_opt_wgrad_reduce ? 16 : umma_wgrad_scratch_bytes(N, H, W, C, K, R, S);
     if (path == CONV_THIN) {
         const size_t m = static_cast<size_t>(N) * H * W;
         return align_up(m * 32, 1024) + static_cast<size_t>(umma_gemm_splits(K, 32, static_cast<int>(m))) * K * 32 * 4;
@@ -143,6 +146,13 @@ extern "C" int niti_conv_wgrad_i8(const int8_t* x, const int8_t* err, int32_t* g
     const long long n = static_cast<long long>(K) * R * S * C;
     if (path == CONV_TC) {
         int splits = 0;
+        if (g_opt_wgrad_reduce) {
+            // zero the gradient, let every thread block add its tiles into it at the L2 (TMA reductions), then one
+            // pass for max|g|: no partial sums in memory, no folding kernel
+            if (int e = set_cuda_error(cudaMemsetAsync(g32, 0, static_cast<size_t>(n) * 4, st))) return e;
+            if (int rc = umma_conv_wgrad_partials(x, err, g32, &splits, 0, N, H, W, C, K, R, S, pad, status, st, 1)) return rc;
+            return absmax_i32(g32, n, maxabs, st);
+        }
         if (int rc = umma_conv_wgrad_partials(x, err, static_cast<int32_t*>(scratch), &splits, 0, N, H, W, C, K, R, S, pad, status, st)) return rc;
         return reduce_partials(static_cast<const int32_t*>(scratch), splits, n, g32, maxabs, st);
     }

@@ -24,6 +24,8 @@ struct FusedArgs {
     const int32_t* exp_a; const int32_t* exp_b; int32_t* exp_out; int32_t* shift_out;
 };
 
+extern int g_stage_cap;  // experiments: cap on the shared-memory stages the GEMM / conv kernels use (0 = all)
+
 // tensor-core (tcgen05) paths, umma_kernels.cu; `out` is int32 (fused == null) or int8
 int umma_gemm_splits(int M, int N, int K);
 int umma_gemm(const int8_t* A, const int8_t* B, void* out, unsigned* maxabs, int M, int N, int K, int trans_a,
@@ -33,8 +35,11 @@ int umma_conv(const int8_t* x, const int8_t* w, void* out, unsigned* maxabs, int
 bool umma_conv_fits_parked(int Nimg, int H, int W, int outc);
 size_t umma_wgrad_scratch_bytes(int Nimg, int H, int W, int C, int K, int R, int S);
 // max_splits > 0 caps the number of pixel-range splits (and with it the size of `partial`)
+// direct == 1: `partial` is the zeroed gradient and the CTAs add into it (TMA reduction) instead of storing partials
 int umma_conv_wgrad_partials(const int8_t* x, const int8_t* err, int32_t* partial, int* splits_out, int max_splits,
-                             int Nimg, int H, int W, int C, int K, int R, int S, int pad, int32_t* status, cudaStream_t st);
+                             int Nimg, int H, int W, int C, int K, int R, int S, int pad, int32_t* status, cudaStream_t st,
+                             int direct = 0);
+int absmax_i32(const int32_t* acc, long long n, unsigned* maxabs, cudaStream_t st);  // reduces into *maxabs (not cleared)
 
 // CUDA-core paths, simt_kernels.cu
 int simt_conv_fprop(const int8_t* x, const int8_t* w, int32_t* y32, unsigned* maxabs, int Nimg, int H, int W, int C,

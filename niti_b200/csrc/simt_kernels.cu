@@ -111,6 +111,11 @@ absmax_kernel(const int32_t* __restrict__ acc, long long n, unsigned* maxabs) {
     warp_atomic_max(maxabs, m);
 }
 
+int absmax_i32(const int32_t* acc, long long n, unsigned* maxabs, cudaStream_t st) {
+    absmax_kernel<<<blocks_for(n / 4 + 1, 256, sm_count_simt() * 8), 256, 0, st>>>(acc, n, maxabs);
+    return set_cuda_error(cudaGetLastError());
+}
+
 // out[i] = sum over splits of partial[s][i]; max|out| reduced into *maxabs.
 // Block = 64 int4 columns x 4 split groups: each thread sums every fourth split (loads of different
 // splits are independent, so several are in flight), the groups meet in shared memory.

@@ -67,6 +67,7 @@ struct GemmParams {
     int red;               // reduction channels per tap (conv) -- the last block of a tap may be partial
     unsigned* maxabs;      // max|acc| is reduced into this word; may be null (split-K partials)
     int32_t* status;
+    int nstages;           // stages of the ring actually used (<= the compiled maximum; tuning / experiments)
     int split_cols;        // 1: both epilogue warpgroups share every tile (alternate 128-column groups); 0: they alternate tiles
     // fused requantisation (FUSED kernels): int8 output narrowed by the shift in state[0].
     // state = {shift, max|acc|, redo flag, redo count, finished-CTA ticket}; the last CTA of a first
@@ -140,6 +141,7 @@ __device__ __forceinline__ void producer_role(uint8_t* smem, uint64_t* full_bar,
                                               const CUtensorMap* tmB, const GemmParams& p, volatile int* abort_flag) {
     const int mn_tiles = p.m_tiles * p.n_tiles;
     const int total_tiles = mn_tiles * p.splits;
+    const int nst = (p.nstages > 0 && p.nstages < STAGES) ? p.nstages : STAGES;
     int s = 0; uint32_t ph = 0; bool ok = true;
     for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
         const int split = tile / mn_tiles, mn = tile % mn_tiles;
@@ -177,7 +179,7 @@ __device__ __forceinline__ void producer_role(uint8_t* smem, uint64_t* full_bar,
                     tma_load_2d(sb, tmB, fb, kb * ROW_BYTES, n_t * BN);
                 }
             }
-            if (++s == STAGES) { s = 0; ph ^= 1u; }
+            if (++s == nst) { s = 0; ph ^= 1u; }
         }
     }
 }
@@ -191,6 +193,7 @@ __device__ __forceinline__ void mma_role(uint8_t* smem, uint64_t* full_bar, uint
     const int mn_tiles = p.m_tiles * p.n_tiles;
     const int total_tiles = mn_tiles * p.splits;
     const uint32_t idesc = make_idesc_i8(BLOCK_M, BN, p.a_mn, p.b_mn);
+    const int nst = (p.nstages > 0 && p.nstages < STAGES) ? p.nstages : STAGES;
     int s = 0; uint32_t ph = 0; bool ok = true; int it = 0;
     for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x, ++it) {
         const int acc = PARKED ? it : (it & 1);
@@ -224,7 +227,7 @@ __device__ __forceinline__ void mma_role(uint8_t* smem, uint64_t* full_bar, uint
                     umma_i8(d_tmem, desc_advance(a0, k * a_step), desc_advance(b0, k * b_step), idesc,
                             static_cast<uint32_t>(kb != kb_lo || k != 0));
             umma_commit(smem_u32(&empty_bar[s]));
-            if (++s == STAGES) { s = 0; ph ^= 1u; }
+            if (++s == nst) { s = 0; ph ^= 1u; }
         }
         if (ok) umma_commit(smem_u32(&tfull_bar[acc]));
     }
@@ -740,6 +743,7 @@ struct WgradParams {
     int mma_per_chunk;     // ceil(rows / 32)
     int32_t* partial;      // [splits][K*R*S*C]
     int32_t* status;
+    int reduce_direct;     // 1: every CTA adds its tiles straight into the (zeroed) gradient with TMA reductions
 };
 
 constexpr int WG_MAX_S = 3;
@@ -854,7 +858,10 @@ umma_wgrad_kernel(const __grid_constant__ CUtensorMap tmErr, const __grid_consta
                 if (leader) {
 #pragma unroll
                     for (int j = 0; j < 4; ++j)
-                        if (ct * 128 + j * 32 < p.C) tma_store_4d(&tmP, buf + j * EPI_CHUNK_BYTES, ct * 128 + j * 32, r * p.S + sx, kt * 128, split);
+                        if (ct * 128 + j * 32 < p.C) {
+                            if (p.reduce_direct) tma_reduce_add_4d(&tmP, buf + j * EPI_CHUNK_BYTES, ct * 128 + j * 32, r * p.S + sx, kt * 128, 0);
+                            else tma_store_4d(&tmP, buf + j * EPI_CHUNK_BYTES, ct * 128 + j * 32, r * p.S + sx, kt * 128, split);
+                        }
                     bulk_commit();
                 }
             }
@@ -967,7 +974,10 @@ static int pick_bn(int m_tiles, int n_cols) {
     return tiles256 * 2 <= sm_count() ? 128 : 256;
 }
 
+int g_stage_cap = 0;  // 0: use every compiled stage
+
 static void set_fused(GemmParams* p, const FusedArgs* f) {
+    p->nstages = g_stage_cap;
     if (!f) return;
     p->state = f->state; p->only_if_redo = f->only_if_redo; p->mode = f->mode; p->relu = f->relu;
     p->seed = f->seed; p->rng_stream = f->rng_stream; p->rng_offset = f->rng_offset;
@@ -1097,10 +1107,14 @@ size_t umma_wgrad_scratch_bytes(int Nimg, int H, int W, int C, int K, int R, int
     return static_cast<size_t>(p.splits) * K * R * S * C * sizeof(int32_t);
 }
 
+// partial != null, direct == 0: CTA (split, tile) stores its sums to partial[split] (the caller folds them);
+// direct == 1: `partial` is the gradient itself, zeroed by the caller, and every CTA adds into it.
 int umma_conv_wgrad_partials(const int8_t* x, const int8_t* err, int32_t* partial, int* splits_out, int max_splits,
-                             int Nimg, int H, int W, int C, int K, int R, int S, int pad, int32_t* status, cudaStream_t st) {
+                             int Nimg, int H, int W, int C, int K, int R, int S, int pad, int32_t* status, cudaStream_t st,
+                             int direct) {
     WgradParams p{};
     wgrad_plan(Nimg, H, W, C, K, R, max_splits, &p);
+    p.reduce_direct = direct;
     CUtensorMap me, mx, mp;
     {
         uint32_t box[4] = {128, (uint32_t)p.BW, (uint32_t)p.BH, (uint32_t)p.BI};
@@ -1110,7 +1124,7 @@ int umma_conv_wgrad_partials(const int8_t* x, const int8_t* err, int32_t* partia
         uint64_t dx[4] = {(uint64_t)C, (uint64_t)W, (uint64_t)H, (uint64_t)Nimg};
         uint64_t sx[3] = {(uint64_t)C, (uint64_t)W * C, (uint64_t)H * W * C};
         if (int e = encode_map(&mx, x, false, 4, dx, sx, box)) return e;
-        uint64_t dp[4] = {(uint64_t)C, (uint64_t)R * S, (uint64_t)K, (uint64_t)p.splits};
+        uint64_t dp[4] = {(uint64_t)C, (uint64_t)R * S, (uint64_t)K, (uint64_t)(direct ? 1 : p.splits)};
         uint64_t sp[3] = {(uint64_t)C * 4, (uint64_t)R * S * C * 4, (uint64_t)K * R * S * C * 4};
         uint32_t bp[4] = {32, 1, 128, 1};
         if (int e = encode_map(&mp, partial, true, 4, dp, sp, bp)) return e;

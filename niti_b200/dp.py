@@ -48,6 +48,20 @@ class GradBucket:
             dist.all_reduce(self.flat, op=dist.ReduceOp.SUM, group=group)
         return self.flat
 
+    def comm_groups(self, min_bytes=4 << 20):
+        """Contiguous runs of layers to all-reduce together, in the order their gradients become ready in the
+        backward pass (last layer first); small neighbours are merged so no message is tiny.  Returns
+        [(first_layer, last_layer, flat_start, flat_end)] with first_layer the one that is ready LAST."""
+        groups, hi = [], len(self.shapes) - 1
+        while hi >= 0:
+            lo = hi
+            end = self.flat.numel() if hi == len(self.shapes) - 1 else self.offsets[hi + 1]
+            while lo > 0 and (end - self.offsets[lo]) * 4 < min_bytes:
+                lo -= 1
+            groups.append((lo, hi, self.offsets[lo], end))
+            hi = lo - 1
+        return groups
+
     def checksum(self):
         """Order-independent digest used to assert that replicas hold identical values."""
         f = self.flat.to(torch.int64)

@@ -102,6 +102,12 @@ def set_accumulator_parking(enabled):
     return bool(lib.niti_set_option(1, int(bool(enabled))))
 
 
+def set_wgrad_tma_reduce(enabled):
+    """Tensor-core weight gradient: add tiles into the gradient with TMA reductions (default) or go through
+    partial sums in scratch; returns the old setting."""
+    return bool(lib.niti_set_option(2, int(bool(enabled))))
+
+
 def new_requant_state(device):
     """int32[8] a fused conv + requantisation call keeps per layer and direction:
     [0] shift (prediction in, true value out), [1] max|acc|, [2] redo flag, [3] redo count, [4] block ticket."""

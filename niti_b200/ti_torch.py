@@ -27,6 +27,7 @@ class UpdateWeight(Module):
     layer_id = 0          # index among the weighted layers; selects the random-bit streams
     grad_buffer = None    # optional preallocated int32 view the weight gradient is written into
     defer_update = False  # data-parallel trainers sum gradients across ranks before updating
+    grad_ready = None     # optional callback(layer), called as soon as grad_int32acc has been enqueued
 
     def weight_update(self):
         """vanilla SGD on int8 weights: w <- clamp(w - grad_calc(grad_int32acc, GRAD_BITWIDTH))"""
@@ -187,6 +188,8 @@ class TiLinear(UpdateWeight):
                                          exp_tensor(err_exp, acc.device), self.weight_exp, mx, False,
                                          SAMPLE_OFFSET * acc.shape[1])
         self.grad_int32acc, self.grad_maxabs = ops.gemm_acc(err_in, act, trans_a=True, out=self.grad_buffer)
+        if self.grad_ready is not None:
+            self.grad_ready(self)
         if not self.defer_update:
             self.weight_update()
         return err_out, self.err_exp
@@ -334,6 +337,8 @@ class TiConv2d(UpdateWeight):
                                                  SAMPLE_OFFSET * per)
         K, R, S, C = self.weight.shape
         self.grad_int32acc, self.grad_maxabs = ops.conv_wgrad_acc(self.act, err_in, R, S, self.padding, out=self.grad_buffer)
+        if self.grad_ready is not None:
+            self.grad_ready(self)
         if not self.defer_update:
             self.weight_update()
         if not self.first_layer:

@@ -98,3 +98,17 @@ def test_two_rank_step_matches_replica_sum():
         total = g if total is None else {i: total[i] + g[i] for i in g}
     net.apply_grads(total, step=0)
     assert [w.tobytes() for w in net.w] == results[0][2]
+
+
+def test_comm_groups_cover_bucket_in_backward_order():
+    shapes = [(128, 3, 3, 3), (128, 3, 3, 128), (256, 3, 3, 128), (256, 3, 3, 256), (512, 3, 3, 256), (512, 3, 3, 512), (10, 8192)]
+    b = GradBucket(shapes, "cpu")
+    groups = b.comm_groups(min_bytes=4 << 20)
+    # last layers first, contiguous, disjoint, covering the whole flat buffer, no small message except possibly the last
+    assert groups[0][1] == len(shapes) - 1 and groups[-1][0] == 0
+    assert all(g[0] <= g[1] for g in groups)
+    assert all(a[0] == b_[1] + 1 for a, b_ in zip(groups, groups[1:]))
+    assert groups[0][3] == b.flat.numel() and groups[-1][2] == 0
+    assert all(a[2] == b_[3] for a, b_ in zip(groups, groups[1:]))
+    assert all((g[3] - g[2]) * 4 >= 4 << 20 for g in groups[:-1])
+    assert GradBucket([(4, 4)], "cpu").comm_groups() == [(0, 0, 0, 16)]

@@ -92,13 +92,18 @@ def test_conv_dgrad(N, H, W, C, K):
 
 
 @pytest.mark.parametrize("N,H,W,C,K", CONV_CASES)
-def test_conv_wgrad(N, H, W, C, K):
+@pytest.mark.parametrize("tma_reduce", [True, False])
+def test_conv_wgrad(N, H, W, C, K, tma_reduce):
     rng = np.random.default_rng(N + H * 3 + C * 5 + K + 2)
     x, err = rnd8(rng, (N, H, W, C)), rnd8(rng, (N, H, W, K))
     want = O.conv_wgrad(x, err)
-    g32, mx = ops.conv_wgrad_acc(cu(x), cu(err))
-    assert_same(g32, want.astype(np.int32), "conv wgrad accumulators")
-    assert int(mx.item()) == int(np.abs(want).max())
+    old = ops.set_wgrad_tma_reduce(tma_reduce)
+    try:
+        g32, mx = ops.conv_wgrad_acc(cu(x), cu(err))
+        assert_same(g32, want.astype(np.int32), "conv wgrad accumulators")
+        assert int(mx.item()) == int(np.abs(want).max())
+    finally:
+        ops.set_wgrad_tma_reduce(old)
 
 
 def test_conv_rejects_stride():
