@@ -70,6 +70,10 @@ extern "C" {
 /* NITI_OPT_STAGE_CAP (default 0 = all): use at most this many shared-memory stages in the GEMM / conv
  * main loops (measurement aid: separates latency-bound from bandwidth-bound behaviour). */
 #define NITI_OPT_STAGE_CAP 3
+/* NITI_OPT_CTA_PAIRS (bit 0: GEMMs, bit 1: convolutions; default 1): run the kernels as pairs of
+ * thread blocks that issue 256-row MMAs together (tcgen05 cta_group::2), each fetching half of the B
+ * operand, which cuts the L2 -> shared-memory traffic per output; 0: one thread block per 128-row tile. */
+#define NITI_OPT_CTA_PAIRS 4
 NITI_API int niti_set_option(int option, int value);
 
 NITI_API int niti_version(void);

@@ -51,6 +51,7 @@ static int g_opt_wgrad_reduce = 1;
 
 extern "C" int niti_set_option(int option, int value) {
     if (option == NITI_OPT_ACCUMULATOR_PARKING) { const int old = g_opt_parking; g_opt_parking = value ? 1 : 0; return old; }
+    if (option == NITI_OPT_CTA_PAIRS) { const int old = g_two_cta; g_two_cta = value & 3; return old; }
     if (option == NITI_OPT_STAGE_CAP) { const int old = g_stage_cap; g_stage_cap = value < 0 ? 0 : value; return old; }
     if (option == NITI_OPT_WGRAD_TMA_REDUCE) { const int old = g_opt_wgrad_reduce; g_opt_wgrad_reduce = value ? 1 : 0; return old; }
     return NITI_ERR_BAD_ARG;
@@ -195,7 +196,7 @@ static int fused_conv(const int8_t* in, const int8_t* w, int8_t* out8, int32_t* 
         if (int e = pad_rows32(w, wp, K, R * S * C, st)) return e;
     }
     // Few enough output tiles for every accumulator to stay in tensor memory: one exact launch.
-    if (g_opt_parking && !thin && umma_conv_fits_parked(N, H, W, flip ? C : K)) {
+    if (g_opt_parking && !thin && umma_conv_fits_parked(N, H, W, flip ? C : K, flip)) {
         f.parked = 1;
         return umma_conv(in, w, out8, nullptr, N, H, W, C, K, R, S, pad, flip, &f, status, st);
     }

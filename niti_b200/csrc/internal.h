@@ -24,6 +24,7 @@ struct FusedArgs {
     const int32_t* exp_a; const int32_t* exp_b; int32_t* exp_out; int32_t* shift_out;
 };
 
+extern int g_two_cta;    // CTA pairs (cta_group::2) where the shape allows: bit 0 for GEMMs, bit 1 for convolutions
 extern int g_stage_cap;  // experiments: cap on the shared-memory stages the GEMM / conv kernels use (0 = all)
 
 // tensor-core (tcgen05) paths, umma_kernels.cu; `out` is int32 (fused == null) or int8
@@ -32,7 +33,7 @@ int umma_gemm(const int8_t* A, const int8_t* B, void* out, unsigned* maxabs, int
               int trans_b, int splits, const FusedArgs* fused, int32_t* status, cudaStream_t st);
 int umma_conv(const int8_t* x, const int8_t* w, void* out, unsigned* maxabs, int Nimg, int H, int W, int C, int K,
               int R, int S, int pad, int flip, const FusedArgs* fused, int32_t* status, cudaStream_t st);
-bool umma_conv_fits_parked(int Nimg, int H, int W, int outc);
+bool umma_conv_fits_parked(int Nimg, int H, int W, int outc, int flip);
 size_t umma_wgrad_scratch_bytes(int Nimg, int H, int W, int C, int K, int R, int S);
 // max_splits > 0 caps the number of pixel-range splits (and with it the size of `partial`)
 // direct == 1: `partial` is the zeroed gradient and the CTAs add into it (TMA reduction) instead of storing partials

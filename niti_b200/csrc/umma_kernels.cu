@@ -85,9 +85,9 @@ struct GemmParams {
 
 constexpr int GEMM_THREADS = 320;  // producer warp, MMA warp, two epilogue warpgroups of 4 warps
 
-template <int BN, bool FUSED>
+template <int BN, bool FUSED, bool TWO = false>
 struct GemmCfg {
-    static constexpr int B_STAGE_BYTES = BN * ROW_BYTES;
+    static constexpr int B_STAGE_BYTES = (TWO ? BN / 2 : BN) * ROW_BYTES;  // a CTA of a pair holds half of the B columns
     static constexpr int STAGE_BYTES = PANEL_BYTES + B_STAGE_BYTES;
     // staging per epilogue warpgroup: one 128 x 128 int8 tile (fused) or two 128 x 32 int32 tiles
     static constexpr int EPI_GROUP_BYTES = FUSED ? EPI_CHUNK_BYTES : 2 * EPI_CHUNK_BYTES;
@@ -136,47 +136,72 @@ __device__ __forceinline__ uint32_t narrow4(const uint32_t* v, int shift, int mo
 
 // ---- warp roles shared by the streaming kernel and the accumulator-parking kernel -------------
 // TMA producer (one thread): fills the stage ring for every tile of this CTA, in tile order.
-template <int BN, int STAGES, int STAGE_BYTES>
+// TWO: this CTA is half of a CTA pair (cluster ranks 0/1).  Tiles are 256 rows high: rank r owns rows
+// [128 r, 128 r + 128) of the pair's tile (m tile 2*pair_m + r) and columns [r BN/2, (r+1) BN/2) of the B
+// operand; all byte counts are reported to rank 0's "full" barrier, which its MMA thread waits on.
+template <int BN, int STAGES, int STAGE_BYTES, bool TWO>
 __device__ __forceinline__ void producer_role(uint8_t* smem, uint64_t* full_bar, uint64_t* empty_bar, const CUtensorMap* tmA,
                                               const CUtensorMap* tmB, const GemmParams& p, volatile int* abort_flag) {
     const int mn_tiles = p.m_tiles * p.n_tiles;
     const int total_tiles = mn_tiles * p.splits;
+    const uint32_t rank = TWO ? cluster_ctarank() : 0u;
+    const int first = TWO ? static_cast<int>(blockIdx.x >> 1) : static_cast<int>(blockIdx.x);
+    const int step = TWO ? static_cast<int>(gridDim.x >> 1) : static_cast<int>(gridDim.x);
+    constexpr int BNH = TWO ? BN / 2 : BN;  // B columns this CTA loads
     const int nst = (p.nstages > 0 && p.nstages < STAGES) ? p.nstages : STAGES;
     int s = 0; uint32_t ph = 0; bool ok = true;
-    for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+    for (int tile = first; ok && tile < total_tiles; tile += step) {
         const int split = tile / mn_tiles, mn = tile % mn_tiles;
-        const int m_t = mn / p.n_tiles, n_t = mn % p.n_tiles;
+        const int m_t = TWO ? 2 * (mn / p.n_tiles) + static_cast<int>(rank) : mn / p.n_tiles, n_t = mn % p.n_tiles;
         const int kb_lo = static_cast<int>(static_cast<long long>(split) * p.num_kb / p.splits);
         const int kb_hi = static_cast<int>(static_cast<long long>(split + 1) * p.num_kb / p.splits);
         int tw = 0, th = 0, tn = 0;
         if (p.conv) { tw = m_t % p.tiles_w; th = (m_t / p.tiles_w) % p.tiles_h; tn = m_t / (p.tiles_w * p.tiles_h); }
+        const int ncol = n_t * BN + static_cast<int>(rank) * BNH;  // first B column of this CTA
         for (int kb = kb_lo; kb < kb_hi; ++kb) {
             if (!mbar_wait(smem_u32(&empty_bar[s]), ph ^ 1u, abort_flag)) { ok = false; report_abort(p.status, 1, 0); break; }
-            const uint32_t fb = smem_u32(&full_bar[s]);
             const uint32_t sa = smem_u32(smem + s * STAGE_BYTES);
             const uint32_t sb = sa + PANEL_BYTES;
-            mbar_arrive_expect_tx(fb, static_cast<uint32_t>(p.a_bytes + BN * ROW_BYTES));
+            uint32_t fb = smem_u32(&full_bar[s]);
+            if (TWO) {
+                if (rank == 0) mbar_arrive_expect_tx(fb, 2u * static_cast<uint32_t>(p.a_bytes + BNH * ROW_BYTES));
+                fb = mapa_u32(fb, 0);
+            } else {
+                mbar_arrive_expect_tx(fb, static_cast<uint32_t>(p.a_bytes + BN * ROW_BYTES));
+            }
             if (p.conv) {
                 const int tap = kb / p.cblocks, cb = kb % p.cblocks;
                 const int r = tap / p.S, sx = tap % p.S;
                 const int dx = p.flip ? p.pad - sx : sx - p.pad, dy = p.flip ? p.pad - r : r - p.pad;
-                tma_load_4d(sa, tmA, fb, cb * ROW_BYTES, tw * p.BW + dx, th * p.BH + dy, tn * p.BI);
+                if (TWO) tma_load_4d_pair(sa, tmA, fb, cb * ROW_BYTES, tw * p.BW + dx, th * p.BH + dy, tn * p.BI);
+                else     tma_load_4d(sa, tmA, fb, cb * ROW_BYTES, tw * p.BW + dx, th * p.BH + dy, tn * p.BI);
                 if (p.b_mn) {
 #pragma unroll
-                    for (int pn = 0; pn < BN / 128; ++pn)
-                        tma_load_2d(sb + pn * PANEL_BYTES, tmB, fb, tap * p.tapstride + n_t * BN + pn * 128, cb * 128);
+                    for (int pn = 0; pn < BNH / 128; ++pn) {
+                        if (TWO) tma_load_2d_pair(sb + pn * PANEL_BYTES, tmB, fb, tap * p.tapstride + ncol + pn * 128, cb * 128);
+                        else     tma_load_2d(sb + pn * PANEL_BYTES, tmB, fb, tap * p.tapstride + ncol + pn * 128, cb * 128);
+                    }
                 } else {
-                    tma_load_2d(sb, tmB, fb, tap * p.tapstride + cb * ROW_BYTES, n_t * BN);
+                    if (TWO) tma_load_2d_pair(sb, tmB, fb, tap * p.tapstride + cb * ROW_BYTES, ncol);
+                    else     tma_load_2d(sb, tmB, fb, tap * p.tapstride + cb * ROW_BYTES, ncol);
                 }
             } else {
-                if (p.a_mn) tma_load_2d(sa, tmA, fb, m_t * BLOCK_M, kb * 128);
-                else        tma_load_2d(sa, tmA, fb, kb * ROW_BYTES, m_t * BLOCK_M);
+                if (TWO) {
+                    if (p.a_mn) tma_load_2d_pair(sa, tmA, fb, m_t * BLOCK_M, kb * 128);
+                    else        tma_load_2d_pair(sa, tmA, fb, kb * ROW_BYTES, m_t * BLOCK_M);
+                } else {
+                    if (p.a_mn) tma_load_2d(sa, tmA, fb, m_t * BLOCK_M, kb * 128);
+                    else        tma_load_2d(sa, tmA, fb, kb * ROW_BYTES, m_t * BLOCK_M);
+                }
                 if (p.b_mn) {
 #pragma unroll
-                    for (int pn = 0; pn < BN / 128; ++pn)
-                        tma_load_2d(sb + pn * PANEL_BYTES, tmB, fb, n_t * BN + pn * 128, kb * 128);
+                    for (int pn = 0; pn < BNH / 128; ++pn) {
+                        if (TWO) tma_load_2d_pair(sb + pn * PANEL_BYTES, tmB, fb, ncol + pn * 128, kb * 128);
+                        else     tma_load_2d(sb + pn * PANEL_BYTES, tmB, fb, ncol + pn * 128, kb * 128);
+                    }
                 } else {
-                    tma_load_2d(sb, tmB, fb, kb * ROW_BYTES, n_t * BN);
+                    if (TWO) tma_load_2d_pair(sb, tmB, fb, kb * ROW_BYTES, ncol);
+                    else     tma_load_2d(sb, tmB, fb, kb * ROW_BYTES, ncol);
                 }
             }
             if (++s == nst) { s = 0; ph ^= 1u; }
@@ -187,15 +212,19 @@ __device__ __forceinline__ void producer_role(uint8_t* smem, uint64_t* full_bar,
 // MMA issuer (one thread).  Streaming: two accumulators used alternately, each handed back by the
 // epilogue (tempty).  PARKED: tile i of this CTA accumulates into TMEM columns [i*BN, (i+1)*BN) and
 // stays there until the kernel ends, so no accumulator is ever waited for.
-template <int BN, int STAGES, int STAGE_BYTES, bool PARKED>
+// TWO: run by rank 0 of a CTA pair only; M = 256 MMAs over both CTAs' shared and tensor memory, and every
+// completion (stage free, accumulator full) is signalled to both CTAs.
+template <int BN, int STAGES, int STAGE_BYTES, bool PARKED, bool TWO>
 __device__ __forceinline__ void mma_role(uint8_t* smem, uint64_t* full_bar, uint64_t* empty_bar, uint64_t* tfull_bar,
                                          uint64_t* tempty_bar, uint32_t tmem_base, const GemmParams& p, volatile int* abort_flag) {
     const int mn_tiles = p.m_tiles * p.n_tiles;
     const int total_tiles = mn_tiles * p.splits;
-    const uint32_t idesc = make_idesc_i8(BLOCK_M, BN, p.a_mn, p.b_mn);
+    const uint32_t idesc = make_idesc_i8(TWO ? 2 * BLOCK_M : BLOCK_M, BN, p.a_mn, p.b_mn);
     const int nst = (p.nstages > 0 && p.nstages < STAGES) ? p.nstages : STAGES;
+    const int first = TWO ? static_cast<int>(blockIdx.x >> 1) : static_cast<int>(blockIdx.x);
+    const int step = TWO ? static_cast<int>(gridDim.x >> 1) : static_cast<int>(gridDim.x);
     int s = 0; uint32_t ph = 0; bool ok = true; int it = 0;
-    for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x, ++it) {
+    for (int tile = first; ok && tile < total_tiles; tile += step, ++it) {
         const int acc = PARKED ? it : (it & 1);
         if (!PARKED) {
             const uint32_t aph = (it >> 1) & 1u;
@@ -223,13 +252,16 @@ __device__ __forceinline__ void mma_role(uint8_t* smem, uint64_t* full_bar, uint
             if (p.conv) { const int left = p.red - (kb % p.cblocks) * 128; nmma = left >= 128 ? 4 : (left + 31) >> 5; }
 #pragma unroll
             for (int k = 0; k < 4; ++k)
-                if (k < nmma)
-                    umma_i8(d_tmem, desc_advance(a0, k * a_step), desc_advance(b0, k * b_step), idesc,
-                            static_cast<uint32_t>(kb != kb_lo || k != 0));
-            umma_commit(smem_u32(&empty_bar[s]));
+                if (k < nmma) {
+                    if (TWO) umma_i8_pair(d_tmem, desc_advance(a0, k * a_step), desc_advance(b0, k * b_step), idesc,
+                                          static_cast<uint32_t>(kb != kb_lo || k != 0));
+                    else     umma_i8(d_tmem, desc_advance(a0, k * a_step), desc_advance(b0, k * b_step), idesc,
+                                     static_cast<uint32_t>(kb != kb_lo || k != 0));
+                }
+            if (TWO) umma_commit_pair(smem_u32(&empty_bar[s])); else umma_commit(smem_u32(&empty_bar[s]));
             if (++s == nst) { s = 0; ph ^= 1u; }
         }
-        if (ok) umma_commit(smem_u32(&tfull_bar[acc]));
+        if (ok) { if (TWO) umma_commit_pair(smem_u32(&tfull_bar[acc])); else umma_commit(smem_u32(&tfull_bar[acc])); }
     }
 }
 
@@ -314,11 +346,11 @@ __device__ __forceinline__ void narrow_row(const uint32_t (&v)[4][32], uint32_t 
     }
 }
 
-template <int BN, bool FUSED>
+template <int BN, bool FUSED, bool TWO>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)  // 10 warps: 3 on one scheduler -> at most 168 registers per thread
 umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                  const __grid_constant__ CUtensorMap tmC, const GemmParams p) {
-    using Cfg = GemmCfg<BN, FUSED>;
+    using Cfg = GemmCfg<BN, FUSED, TWO>;
     constexpr int STAGES = Cfg::STAGES;
     if (FUSED && p.only_if_redo && p.state[2] == 0) return;  // prediction was right: nothing to redo
 
@@ -335,29 +367,37 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
+    const uint32_t rank = TWO ? cluster_ctarank() : 0u;  // rank 0 of a pair issues the MMAs and owns the barriers the MMA thread waits on
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < STAGES; ++i) { mbar_init(smem_u32(&full_bar[i]), 1); mbar_init(smem_u32(&empty_bar[i]), 1); }
-        for (int i = 0; i < 2; ++i) { mbar_init(smem_u32(&tfull_bar[i]), 1); mbar_init(smem_u32(&tempty_bar[i]), p.split_cols ? 8 : 4); }
+        for (int i = 0; i < 2; ++i) { mbar_init(smem_u32(&tfull_bar[i]), 1); mbar_init(smem_u32(&tempty_bar[i]), (p.split_cols ? 8 : 4) * (TWO ? 2 : 1)); }
         *abort_flag = 0;
         fence_barrier_init();
         tma_prefetch_desc(&tmA);
         tma_prefetch_desc(&tmB);
         tma_prefetch_desc(&tmC);
     }
-    if (warp == 1) { tmem_alloc(smem_u32(tmem_slot), Cfg::TMEM_COLS); tmem_relinquish(); }
+    if (warp == 1) {
+        if (TWO) { tmem_alloc_pair(smem_u32(tmem_slot), Cfg::TMEM_COLS); tmem_relinquish_pair(); }
+        else     { tmem_alloc(smem_u32(tmem_slot), Cfg::TMEM_COLS); tmem_relinquish(); }
+    }
     tc_fence_before();
     __syncthreads();
+    if (TWO) cluster_sync_all();  // the partner's barriers exist before anything is signalled across the pair
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
-    const int mn_tiles = p.m_tiles * p.n_tiles;
+    const int mn_tiles = p.m_tiles * p.n_tiles;  // TWO: m_tiles counts 256-row tiles of the pair
     const int total_tiles = mn_tiles * p.splits;
+    const int cta_first = TWO ? static_cast<int>(blockIdx.x >> 1) : static_cast<int>(blockIdx.x);
+    const int cta_step = TWO ? static_cast<int>(gridDim.x >> 1) : static_cast<int>(gridDim.x);
 
     if (warp == 0) {
-        if (lane == 0) producer_role<BN, STAGES, Cfg::STAGE_BYTES>(smem, full_bar, empty_bar, &tmA, &tmB, p, abort_flag);
+        if (lane == 0) producer_role<BN, STAGES, Cfg::STAGE_BYTES, TWO>(smem, full_bar, empty_bar, &tmA, &tmB, p, abort_flag);
     } else if (warp == 1) {
-        if (lane == 0) mma_role<BN, STAGES, Cfg::STAGE_BYTES, false>(smem, full_bar, empty_bar, tfull_bar, tempty_bar, tmem_base, p, abort_flag);
+        if (lane == 0 && rank == 0)
+            mma_role<BN, STAGES, Cfg::STAGE_BYTES, false, TWO>(smem, full_bar, empty_bar, tfull_bar, tempty_bar, tmem_base, p, abort_flag);
     } else {
         // ------------------------------------------------------------------ epilogue (2 x 4 warps)
         // Two warpgroups.  With several tiles per CTA they alternate tiles (warpgroup g owns
@@ -384,9 +424,9 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         const bool fast = FUSED && p.mode == ROUND_NEAREST && shift > 0;
         const int half = shift > 0 ? 1 << (shift - 1) : 0;
         int vmax[4] = {0, 0, 0, 0}, vmin[4] = {0, 0, 0, 0};
-        const int tile_step = p.split_cols ? gridDim.x : 2 * gridDim.x;
+        const int tile_step = p.split_cols ? cta_step : 2 * cta_step;
         int it = p.split_cols ? 0 : grp;
-        for (int tile = blockIdx.x + (p.split_cols ? 0 : grp * gridDim.x); tile < total_tiles; tile += tile_step, it += (p.split_cols ? 1 : 2)) {
+        for (int tile = cta_first + (p.split_cols ? 0 : grp * cta_step); tile < total_tiles; tile += tile_step, it += (p.split_cols ? 1 : 2)) {
             const int acc = it & 1; const uint32_t aph = (it >> 1) & 1u;
             const uint32_t failed = mbar_wait(smem_u32(&tfull_bar[acc]), aph, abort_flag) ? 0u : 1u;
             if (barrier_or(bar_id, 128, failed)) {  // same verdict in all 128 threads of the warpgroup
@@ -395,7 +435,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             }
             tc_fence_after();
             const int split = tile / mn_tiles, mn = tile % mn_tiles;
-            const int m_t = mn / p.n_tiles, n_t = mn % p.n_tiles;
+            const int m_t = TWO ? 2 * (mn / p.n_tiles) + static_cast<int>(rank) : mn / p.n_tiles, n_t = mn % p.n_tiles;
             bool valid; int cy, cz, cw; long long row_lin;
             if (p.conv) {
                 const int tw = m_t % p.tiles_w, th = (m_t / p.tiles_w) % p.tiles_h, tn = m_t / (p.tiles_w * p.tiles_h);
@@ -424,7 +464,10 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                 if (g0 + g_step >= BN || col0 + g0 + g_step >= p.N) {  // this warpgroup's last group of the tile
                     tc_fence_before();
                     __syncwarp();
-                    if (lane == 0) mbar_arrive(smem_u32(&tempty_bar[acc]));
+                    if (lane == 0) {
+                        if (TWO) mbar_arrive_cluster(mapa_u32(smem_u32(&tempty_bar[acc]), 0));
+                        else     mbar_arrive(smem_u32(&tempty_bar[acc]));
+                    }
                     released = true;
                 }
                 const int lim = p.N - (col0 + g0);
@@ -509,7 +552,10 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             if (!released) {  // a shared tile none of whose column groups fell to this warpgroup
                 tc_fence_before();
                 __syncwarp();
-                if (lane == 0) mbar_arrive(smem_u32(&tempty_bar[acc]));
+                if (lane == 0) {
+                        if (TWO) mbar_arrive_cluster(mapa_u32(smem_u32(&tempty_bar[acc]), 0));
+                        else     mbar_arrive(smem_u32(&tempty_bar[acc]));
+                    }
             }
         }
         if (leader) bulk_wait<0>();
@@ -545,11 +591,12 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     // ---------------------------------------------------------------------- teardown
     tc_fence_before();
     __syncthreads();
+    if (TWO) cluster_sync_all();  // the partner may still signal this CTA's barriers / have MMAs reading its memory
     if (warp == 1) {
         if (*abort_flag) __nanosleep(200000);  // let copies and MMAs already in flight land
         tc_fence_after();
         __syncwarp();
-        tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+        if (TWO) tmem_dealloc_pair(tmem_base, Cfg::TMEM_COLS); else tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
     }
 }
 
@@ -562,9 +609,9 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 // no int32 in memory.  state = {shift out, max|acc|, redo flag (cleared), redo count, exit ticket,
 // barrier arrivals}; words 1, 4 and 5 are zero between calls.
 // ------------------------------------------------------------------------------------------------
-template <int BN>
+template <int BN, bool TWO = false>
 struct ParkedCfg {
-    static constexpr int STAGE_BYTES = PANEL_BYTES + BN * ROW_BYTES;
+    static constexpr int STAGE_BYTES = PANEL_BYTES + (TWO ? BN / 2 : BN) * ROW_BYTES;
     static constexpr int EPI_GROUP_BYTES = EPI_CHUNK_BYTES;  // one 128 x 128 int8 staging tile per warpgroup
     static constexpr int EPI_BYTES = 2 * EPI_GROUP_BYTES;
     static constexpr int STAGES = (224 * 1024 - EPI_BYTES) / STAGE_BYTES;
@@ -574,11 +621,11 @@ struct ParkedCfg {
 
 constexpr unsigned long long GRID_BARRIER_LIMIT_NS = 500000000ull;  // 0.5 s
 
-template <int BN>
+template <int BN, bool TWO>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 umma_parked_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                    const __grid_constant__ CUtensorMap tmC, const GemmParams p) {
-    using Cfg = ParkedCfg<BN>;
+    using Cfg = ParkedCfg<BN, TWO>;
     constexpr int STAGES = Cfg::STAGES;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -593,6 +640,7 @@ umma_parked_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
+    const uint32_t rank = TWO ? cluster_ctarank() : 0u;
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < STAGES; ++i) { mbar_init(smem_u32(&full_bar[i]), 1); mbar_init(smem_u32(&empty_bar[i]), 1); }
@@ -603,19 +651,26 @@ umma_parked_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
         tma_prefetch_desc(&tmB);
         tma_prefetch_desc(&tmC);
     }
-    if (warp == 1) { tmem_alloc(smem_u32(tmem_slot), 512); tmem_relinquish(); }
+    if (warp == 1) {
+        if (TWO) { tmem_alloc_pair(smem_u32(tmem_slot), 512); tmem_relinquish_pair(); }
+        else     { tmem_alloc(smem_u32(tmem_slot), 512); tmem_relinquish(); }
+    }
     tc_fence_before();
     __syncthreads();
+    if (TWO) cluster_sync_all();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
-    const int mn_tiles = p.m_tiles * p.n_tiles;
+    const int mn_tiles = p.m_tiles * p.n_tiles;  // TWO: m_tiles counts 256-row tiles of the pair
     const int total_tiles = mn_tiles * p.splits;
+    const int cta_first = TWO ? static_cast<int>(blockIdx.x >> 1) : static_cast<int>(blockIdx.x);
+    const int cta_step = TWO ? static_cast<int>(gridDim.x >> 1) : static_cast<int>(gridDim.x);
 
     if (warp == 0) {
-        if (lane == 0) producer_role<BN, STAGES, Cfg::STAGE_BYTES>(smem, full_bar, empty_bar, &tmA, &tmB, p, abort_flag);
+        if (lane == 0) producer_role<BN, STAGES, Cfg::STAGE_BYTES, TWO>(smem, full_bar, empty_bar, &tmA, &tmB, p, abort_flag);
     } else if (warp == 1) {
-        if (lane == 0) mma_role<BN, STAGES, Cfg::STAGE_BYTES, true>(smem, full_bar, empty_bar, tfull_bar, nullptr, tmem_base, p, abort_flag);
+        if (lane == 0 && rank == 0)
+            mma_role<BN, STAGES, Cfg::STAGE_BYTES, true, TWO>(smem, full_bar, empty_bar, tfull_bar, nullptr, tmem_base, p, abort_flag);
     } else {
         // Work units of the epilogue: (tile of this CTA, 128-column group); the two warpgroups take
         // alternate units, the same ones in both passes.
@@ -627,7 +682,7 @@ umma_parked_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
         const uint32_t buf = smem_u32(epi_smem) + grp * Cfg::EPI_GROUP_BYTES;
         constexpr int CG = BN / 128;
         int my_tiles = 0;
-        for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) ++my_tiles;
+        for (int tile = cta_first; tile < total_tiles; tile += cta_step) ++my_tiles;
         const int units = my_tiles * CG;
 
         // ---- pass 1: max|acc| of this CTA's tiles
@@ -635,11 +690,12 @@ umma_parked_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
         bool ok = true;
         for (int u = grp; u < units; u += 2) {
             const int it = u / CG, g0 = (u % CG) * 128;
-            const int tile = blockIdx.x + it * gridDim.x;
+            const int tile = cta_first + it * cta_step;
             const uint32_t failed = mbar_wait(smem_u32(&tfull_bar[it]), 0, abort_flag) ? 0u : 1u;
             if (barrier_or(bar_id, 128, failed)) { if (failed) report_abort(p.status, 4, 2); ok = false; break; }
             tc_fence_after();
-            const int mn = tile % mn_tiles, m_t = mn / p.n_tiles, n_t = mn % p.n_tiles;
+            const int mn = tile % mn_tiles, n_t = mn % p.n_tiles;
+            const int m_t = TWO ? 2 * (mn / p.n_tiles) + static_cast<int>(rank) : mn / p.n_tiles;
             const RowInfo ri = row_info(p, m_t, tile / mn_tiles, row_in_tile);
             const int col = n_t * BN + g0;
             if (col >= p.N) continue;
@@ -682,8 +738,9 @@ umma_parked_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
             if (p.mode == ROUND_STOCHASTIC && shift > 0) seed = *p.seed;
             for (int u = grp; u < units; u += 2) {
                 const int it = u / CG, g0 = (u % CG) * 128;
-                const int tile = blockIdx.x + it * gridDim.x;
-                const int mn = tile % mn_tiles, m_t = mn / p.n_tiles, n_t = mn % p.n_tiles;
+                const int tile = cta_first + it * cta_step;
+                const int mn = tile % mn_tiles, n_t = mn % p.n_tiles;
+            const int m_t = TWO ? 2 * (mn / p.n_tiles) + static_cast<int>(rank) : mn / p.n_tiles;
                 const RowInfo ri = row_info(p, m_t, tile / mn_tiles, row_in_tile);
                 const int col = n_t * BN + g0;
                 if (col >= p.N) continue;
@@ -718,11 +775,12 @@ umma_parked_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
 
     tc_fence_before();
     __syncthreads();
+    if (TWO) cluster_sync_all();
     if (warp == 1) {
         if (*abort_flag) __nanosleep(200000);
         tc_fence_after();
         __syncwarp();
-        tmem_dealloc(tmem_base, 512);
+        if (TWO) tmem_dealloc_pair(tmem_base, 512); else tmem_dealloc(tmem_base, 512);
     }
 }
 
@@ -934,37 +992,70 @@ static int sm_count() {
 template <int BN, bool FUSED>
 static int launch_gemm_inst(const CUtensorMap& a, const CUtensorMap& b, const CUtensorMap& c, const GemmParams& p,
                             cudaStream_t st) {
-    using Cfg = GemmCfg<BN, FUSED>;
-    cudaError_t e = cudaFuncSetAttribute(umma_gemm_kernel<BN, FUSED>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
+    using Cfg = GemmCfg<BN, FUSED, false>;
+    cudaError_t e = cudaFuncSetAttribute(umma_gemm_kernel<BN, FUSED, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
     if (e != cudaSuccess) return set_cuda_error(e);
     int grid = p.m_tiles * p.n_tiles * p.splits;
     if (grid > sm_count()) grid = sm_count();
-    umma_gemm_kernel<BN, FUSED><<<grid, GEMM_THREADS, Cfg::SMEM_BYTES, st>>>(a, b, c, p);
+    umma_gemm_kernel<BN, FUSED, false><<<grid, GEMM_THREADS, Cfg::SMEM_BYTES, st>>>(a, b, c, p);
     return set_cuda_error(cudaGetLastError());
 }
-static int launch_gemm(int bn, bool fused, const CUtensorMap& a, const CUtensorMap& b, const CUtensorMap& c,
+// CTA pairs: clusters of two CTAs, p.m_tiles counts 256-row tiles
+template <int BN, bool FUSED>
+static int launch_gemm_pair_inst(const CUtensorMap& a, const CUtensorMap& b, const CUtensorMap& c, const GemmParams& p,
+                                 cudaStream_t st) {
+    using Cfg = GemmCfg<BN, FUSED, true>;
+    cudaError_t e = cudaFuncSetAttribute(umma_gemm_kernel<BN, FUSED, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
+    if (e != cudaSuccess) return set_cuda_error(e);
+    int pairs = p.m_tiles * p.n_tiles * p.splits;
+    if (pairs > sm_count() / 2) pairs = sm_count() / 2;
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(2 * pairs); cfg.blockDim = dim3(GEMM_THREADS); cfg.dynamicSmemBytes = Cfg::SMEM_BYTES; cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr; cfg.numAttrs = 1;
+    return set_cuda_error(cudaLaunchKernelEx(&cfg, umma_gemm_kernel<BN, FUSED, true>, a, b, c, p));
+}
+static int launch_gemm(int bn, bool fused, bool pair, const CUtensorMap& a, const CUtensorMap& b, const CUtensorMap& c,
                        const GemmParams& p, cudaStream_t st) {
+    if (pair) {
+        if (fused) return bn == 256 ? launch_gemm_pair_inst<256, true>(a, b, c, p, st) : launch_gemm_pair_inst<128, true>(a, b, c, p, st);
+        return bn == 256 ? launch_gemm_pair_inst<256, false>(a, b, c, p, st) : launch_gemm_pair_inst<128, false>(a, b, c, p, st);
+    }
     if (fused) return bn == 256 ? launch_gemm_inst<256, true>(a, b, c, p, st) : launch_gemm_inst<128, true>(a, b, c, p, st);
     return bn == 256 ? launch_gemm_inst<256, false>(a, b, c, p, st) : launch_gemm_inst<128, false>(a, b, c, p, st);
 }
-template <int BN>
+// CTA pairs (M = 256 MMAs, B operand split between the two CTAs): bit 0 enables them for GEMMs, bit 1 for
+// convolutions.  Measured on B200: +20 % on large GEMMs (2.2 -> 2.7 POP/s at 8192^3), nothing on the
+// convolutions (their A tiles are re-read per filter tap and dominate), hence the default.
+int g_two_cta = 1;
+// a pair needs two 128-row tiles to share a B tile; an MN-major B splits only at 128-column panels
+static bool pair_ok(int m_tiles, int bn, int b_mn, int conv) {
+    return (g_two_cta & (conv ? 2 : 1)) && m_tiles >= 2 && (!b_mn || bn == 256);
+}
+template <int BN, bool TWO>
 static int launch_parked_inst(const CUtensorMap& a, const CUtensorMap& b, const CUtensorMap& c, const GemmParams& p,
                               cudaStream_t st) {
-    using Cfg = ParkedCfg<BN>;
-    cudaError_t e = cudaFuncSetAttribute(umma_parked_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
+    using Cfg = ParkedCfg<BN, TWO>;
+    cudaError_t e = cudaFuncSetAttribute(umma_parked_kernel<BN, TWO>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
     if (e != cudaSuccess) return set_cuda_error(e);
-    int grid = p.m_tiles * p.n_tiles * p.splits;
-    if (grid > sm_count()) grid = sm_count();
+    int grid = p.m_tiles * p.n_tiles * p.splits;  // TWO: pairs
+    if (TWO) { if (grid > sm_count() / 2) grid = sm_count() / 2; grid *= 2; }
+    else if (grid > sm_count()) grid = sm_count();
     // cooperative launch: the grid barrier inside needs every CTA resident at the same time
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3(grid); cfg.blockDim = dim3(GEMM_THREADS); cfg.dynamicSmemBytes = Cfg::SMEM_BYTES; cfg.stream = st;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeCooperative; attr[0].val.cooperative = 1;
-    cfg.attrs = attr; cfg.numAttrs = 1;
-    return set_cuda_error(cudaLaunchKernelEx(&cfg, umma_parked_kernel<BN>, a, b, c, p));
+    attr[1].id = cudaLaunchAttributeClusterDimension;
+    attr[1].val.clusterDim.x = 2; attr[1].val.clusterDim.y = 1; attr[1].val.clusterDim.z = 1;
+    cfg.attrs = attr; cfg.numAttrs = TWO ? 2 : 1;
+    return set_cuda_error(cudaLaunchKernelEx(&cfg, umma_parked_kernel<BN, TWO>, a, b, c, p));
 }
-// all accumulators of the problem fit in the tensor memory of one wave of CTAs
-static bool fits_parked(int bn, int tiles) { return tiles <= sm_count() * (512 / bn); }
+// all accumulators of the problem fit in the tensor memory of one wave of CTAs (units: 128-row tiles,
+// or 256-row pair tiles on sm/2 pairs)
+static bool fits_parked(int bn, int tiles, bool pair) { return tiles <= (pair ? sm_count() / 2 : sm_count()) * (512 / bn); }
 
 // Output tile width: 256 columns halve the A-operand traffic, but when that leaves fewer tiles than
 // half the SMs, 128-column tiles put twice as many SMs to work.
@@ -1013,11 +1104,12 @@ int umma_gemm(const int8_t* A, const int8_t* B, void* out, unsigned* maxabs, int
     CUtensorMap ma, mb, mc;
     const int a_mn = trans_a ? 1 : 0, b_mn = trans_b ? 0 : 1;
     const int bn = (N > 128) ? 256 : 128;
+    const bool pair = pair_ok((M + 127) / 128, bn, b_mn, 0);
     {
         uint64_t dims[2], str[1]; uint32_t box[2] = {128, 128};
         if (a_mn) { dims[0] = M; dims[1] = K; str[0] = M; } else { dims[0] = K; dims[1] = M; str[0] = K; }
         if (int e = encode_map(&ma, A, false, 2, dims, str, box)) return e;
-        if (b_mn) { dims[0] = N; dims[1] = K; str[0] = N; box[1] = 128; } else { dims[0] = K; dims[1] = N; str[0] = K; box[1] = bn; }
+        if (b_mn) { dims[0] = N; dims[1] = K; str[0] = N; box[1] = 128; } else { dims[0] = K; dims[1] = N; str[0] = K; box[1] = pair ? bn / 2 : bn; }
         if (int e = encode_map(&mb, B, false, 2, dims, str, box)) return e;
         const uint64_t es = fused ? 1 : 4;
         uint64_t dc[4] = {(uint64_t)N, (uint64_t)M, (uint64_t)splits, 1};
@@ -1028,11 +1120,12 @@ int umma_gemm(const int8_t* A, const int8_t* B, void* out, unsigned* maxabs, int
     GemmParams p{};
     p.conv = 0; p.M = M; p.N = N; p.num_kb = (K + 127) / 128; p.splits = splits;
     p.m_tiles = (M + 127) / 128; p.n_tiles = (N + bn - 1) / bn;
+    if (pair) p.m_tiles = (p.m_tiles + 1) / 2;
     p.a_mn = a_mn; p.b_mn = b_mn; p.a_bytes = PANEL_BYTES;
     p.maxabs = splits > 1 ? nullptr : maxabs; p.status = status;
-    p.split_cols = (bn == 256 && p.m_tiles * p.n_tiles * splits <= 2 * sm_count()) ? 1 : 0;
+    p.split_cols = (bn == 256 && p.m_tiles * p.n_tiles * splits <= 2 * (pair ? sm_count() / 2 : sm_count())) ? 1 : 0;
     set_fused(&p, fused);
-    return launch_gemm(bn, fused != nullptr, ma, mb, mc, p, st);
+    return launch_gemm(bn, fused != nullptr, pair, ma, mb, mc, p, st);
 }
 
 // Forward convolution (flip == 0: x [N,H,W,C] with w [K,R,S,C] -> [N,H,W,K]) or error-backward
@@ -1046,7 +1139,10 @@ int umma_conv(const int8_t* x, const int8_t* w, void* out, unsigned* maxabs, int
     const int outc = flip ? C : K;  // output channels
     GemmParams p{};
     pick_pixel_box(Nimg, H, W, &p.BW, &p.BH, &p.BI);
-    const int bn = pick_bn(((W + p.BW - 1) / p.BW) * ((H + p.BH - 1) / p.BH) * ((Nimg + p.BI - 1) / p.BI), outc);
+    const int all_m_tiles = ((W + p.BW - 1) / p.BW) * ((H + p.BH - 1) / p.BH) * ((Nimg + p.BI - 1) / p.BI);
+    const int bn = pick_bn(all_m_tiles, outc);
+    const bool parked = fused && fused->parked;
+    const bool pair = pair_ok(all_m_tiles, bn, flip ? 1 : 0, 1);
     {
         uint64_t dims[4] = {(uint64_t)red, (uint64_t)W, (uint64_t)H, (uint64_t)Nimg};
         uint64_t str[3] = {(uint64_t)red, (uint64_t)W * red, (uint64_t)H * W * red};
@@ -1054,7 +1150,7 @@ int umma_conv(const int8_t* x, const int8_t* w, void* out, unsigned* maxabs, int
         if (int e = encode_map(&ma, x, false, 4, dims, str, box)) return e;
         uint64_t d2[2] = {(uint64_t)R * S * C, (uint64_t)K};
         uint64_t s2[1] = {(uint64_t)R * S * C};
-        uint32_t b2[2] = {128, flip ? 128u : (uint32_t)bn};
+        uint32_t b2[2] = {128, flip ? 128u : (uint32_t)(pair ? bn / 2 : bn)};
         if (int e = encode_map(&mb, w, false, 2, d2, s2, b2)) return e;
         const uint64_t es = fused ? 1 : 4;
         uint64_t dc[4] = {(uint64_t)outc, (uint64_t)W, (uint64_t)H, (uint64_t)Nimg};
@@ -1069,23 +1165,26 @@ int umma_conv(const int8_t* x, const int8_t* w, void* out, unsigned* maxabs, int
     p.cblocks = (red + 127) / 128; p.red = red;
     p.M = Nimg * H * W; p.N = outc; p.num_kb = R * S * p.cblocks;
     p.m_tiles = p.tiles_w * p.tiles_h * tiles_n; p.n_tiles = (outc + bn - 1) / bn;
+    if (pair) p.m_tiles = (p.m_tiles + 1) / 2;
     p.a_mn = 0; p.b_mn = flip ? 1 : 0; p.a_bytes = p.BW * p.BH * p.BI * ROW_BYTES;
     p.maxabs = maxabs; p.status = status;
-    p.split_cols = (bn == 256 && p.m_tiles * p.n_tiles <= 2 * sm_count()) ? 1 : 0;
+    p.split_cols = (bn == 256 && p.m_tiles * p.n_tiles <= 2 * (pair ? sm_count() / 2 : sm_count())) ? 1 : 0;
     set_fused(&p, fused);
-    if (fused && fused->parked) {
-        if (!fits_parked(bn, p.m_tiles * p.n_tiles)) return NITI_ERR_UNSUPPORTED;
-        return bn == 256 ? launch_parked_inst<256>(ma, mb, mc, p, st) : launch_parked_inst<128>(ma, mb, mc, p, st);
+    if (parked) {
+        if (!fits_parked(bn, p.m_tiles * p.n_tiles, pair)) return NITI_ERR_UNSUPPORTED;
+        if (pair) return bn == 256 ? launch_parked_inst<256, true>(ma, mb, mc, p, st) : launch_parked_inst<128, true>(ma, mb, mc, p, st);
+        return bn == 256 ? launch_parked_inst<256, false>(ma, mb, mc, p, st) : launch_parked_inst<128, false>(ma, mb, mc, p, st);
     }
-    return launch_gemm(bn, fused != nullptr, ma, mb, mc, p, st);
+    return launch_gemm(bn, fused != nullptr, pair, ma, mb, mc, p, st);
 }
 
-bool umma_conv_fits_parked(int Nimg, int H, int W, int outc) {
+bool umma_conv_fits_parked(int Nimg, int H, int W, int outc, int flip) {
     int bw, bh, bi;
     pick_pixel_box(Nimg, H, W, &bw, &bh, &bi);
     const int m_tiles = ((W + bw - 1) / bw) * ((H + bh - 1) / bh) * ((Nimg + bi - 1) / bi);
     const int bn = pick_bn(m_tiles, outc);
-    return fits_parked(bn, m_tiles * ((outc + bn - 1) / bn));
+    const bool pair = pair_ok(m_tiles, bn, flip, 1);
+    return fits_parked(bn, (pair ? (m_tiles + 1) / 2 : m_tiles) * ((outc + bn - 1) / bn), pair);
 }
 
 static void wgrad_plan(int Nimg, int H, int W, int C, int K, int R, int max_splits, WgradParams* p) {

@@ -102,6 +102,14 @@ def set_accumulator_parking(enabled):
     return bool(lib.niti_set_option(1, int(bool(enabled))))
 
 
+def set_cta_pairs(mask):
+    """CTA pairs (tcgen05 cta_group::2): bit 0 for GEMMs (default on), bit 1 for convolutions (default off);
+    True = both, False = none.  Returns the old mask."""
+    if isinstance(mask, bool):
+        mask = 3 if mask else 0
+    return lib.niti_set_option(4, int(mask))
+
+
 def set_wgrad_tma_reduce(enabled):
     """Tensor-core weight gradient: add tiles into the gradient with TMA reductions (default) or go through
     partial sums in scratch; returns the old setting."""

@@ -264,3 +264,32 @@ def _fused_case(N, H, W, C, K, mode, relu, parked):
             e8, e, s = ops.conv_dgrad_fused(cu(err), cu(w), st, 1, mode, seed, 6, 128, ea, eb)
             assert_same(e8, want, f"fused dgrad call {call}")
             assert int(s.item()) == want_s and int(e.item()) == want_s - 12
+
+
+# ----------------------------------------------------------------------------- single-CTA variants
+@pytest.mark.parametrize("pairs", [0, 3])
+def test_cta_pair_and_single_cta_kernels_match(pairs):
+    """CTA pairs (cta_group::2) are the default for GEMMs and optional for convolutions; with the option
+    switch at 0 (one CTA per tile everywhere) and at 3 (pairs wherever shapes allow) the integers must be the same."""
+    old = ops.set_cta_pairs(pairs)
+    try:
+        rng = np.random.default_rng(12)
+        for (M, N, K, ta, tb) in [(384, 256, 512, 0, 1), (256, 256, 384, 0, 0), (256, 384, 512, 1, 0)]:
+            a = rnd8(rng, (K, M) if ta else (M, K))
+            b = rnd8(rng, (N, K) if tb else (K, N))
+            c32, mx = ops.gemm_acc(cu(a), cu(b), bool(ta), bool(tb))
+            assert_same(c32, O.int8_mm(a.T if ta else a, b.T if tb else b).astype(np.int32), "gemm, single CTA")
+        x, w, err = rnd8(rng, (5, 8, 8, 256)), rnd8(rng, (512, 3, 3, 256)), rnd8(rng, (5, 8, 8, 512))
+        assert_same(ops.conv_fprop_acc(cu(x), cu(w))[0], O.conv_fprop(x, w).astype(np.int32), "conv fprop, single CTA")
+        assert_same(ops.conv_dgrad_acc(cu(err), cu(w))[0], O.conv_dgrad(err, w).astype(np.int32), "conv dgrad, single CTA")
+        for parking in (False, True):
+            oldp = ops.set_accumulator_parking(parking)
+            st = ops.new_requant_state(DEV)
+            want, want_e, _ = O.act_calc(O.conv_fprop(x, w), 0)
+            for _ in range(2):
+                y8, e, s = ops.conv_fprop_fused(cu(x), cu(w), st, 1, 0, None, 0, 0, False,
+                                                torch.zeros((), dtype=torch.int32, device=DEV), None)
+                assert_same(y8, want, f"fused conv, pairs={pairs}, parking={parking}")
+            ops.set_accumulator_parking(oldp)
+    finally:
+        ops.set_cta_pairs(old)
