@@ -240,6 +240,45 @@ NITI_API int niti_loss_i8(const int8_t* out8, const int32_t* out_exp, const int6
 NITI_API int niti_update_i8(int8_t* w, const int32_t* g32, const uint32_t* maxabs, int64_t n,
                    int mu, int round_mode, const uint64_t* seed, uint32_t rng_stream, void* stream);
 
+/* The classifier head of a training step in one (cooperative) kernel: TiDropout.forward
+ * (ti_torch.py:439-455), TiLinear.forward (:241-253), TiLoss.forward (ti_loss.py:6-36), TiLinear.backward
+ * (:255-266) with UpdateWeight.weight_update (:16-21), and TiDropout.backward.  Same integers as the calls
+ *   niti_dropout_i8, niti_gemm_i8 (x W^T), niti_requant_i8 (act), niti_loss_i8, niti_gemm_i8 (err W),
+ *   niti_requant_i8 (err), niti_gemm_i8 (err^T x), niti_update_i8, niti_dropout_i8
+ * made one after the other with the streams / offsets named below.
+ *   x [B][F] int8 features (before dropout), *exp_x their exponent; w [J][F] int8 (updated in place when
+ *   `update` != 0), *exp_w; target int64 [B];
+ *   out8 [B][J] logits with *exp_out; err8 [B][J] the loss's error (exponent 0);
+ *   e8 [B][F] the error handed to the layer before the head (dropout bits applied), *exp_err;
+ *   g32 [J][F] the weight gradient's accumulators, *grad_maxabs = max |g32|.
+ *   dropout != 0: one keep bit per feature from stream dropout_stream (and the +1 on the exponent);
+ *   bits: target bit-width of activations and errors (7); mu: of the gradient;
+ *   act / err / grad rounding draw from streams layer_stream, layer_stream + 1, layer_stream + 2 with the
+ *   element indices niti_requant_i8 / niti_update_i8 would use (samples offset by sample_offset);
+ *   the loss's StoShift draws from loss_stream.
+ * scratch: niti_fc_head_scratch_bytes(B, F, J) bytes, 16-byte aligned.  Shapes: J <= 16, F % 16 == 0 and
+ * J * F small enough for shared memory (niti_fc_head_supported says).  status: int32[4] or null; a grid
+ * barrier that is not met within 0.5 s writes code 6 there and the kernel returns. */
+typedef struct niti_fc_head_args {
+    const int8_t* x; const int32_t* exp_x;
+    int8_t* w; const int32_t* exp_w;
+    const int64_t* target;
+    int8_t* out8; int32_t* exp_out;
+    int8_t* err8;
+    int8_t* e8; int32_t* exp_err;
+    int32_t* g32; uint32_t* grad_maxabs;
+    void* scratch; size_t scratch_bytes;
+    int32_t B, F, J;
+    int32_t dropout, bits, act_round, err_round, grad_round, mu, update;
+    const uint64_t* seed;
+    uint32_t layer_stream, dropout_stream, loss_stream;
+    uint64_t sample_offset;
+    int32_t* status;
+} niti_fc_head_args;
+NITI_API int niti_fc_head_supported(int B, int F, int J);
+NITI_API size_t niti_fc_head_scratch_bytes(int B, int F, int J);
+NITI_API int niti_fc_head_train_i8(const niti_fc_head_args* args, void* stream);
+
 /* TiFloatToInt8 + the NCHW -> NHWC permute of TiNet.forward (ti_torch.py:341-356, ti_net.py:18-19):
  * x f32 [N][C][H][W] -> x8 int8 [N][H][W][C], *exp_out = ceil(log2(max|x|)) - 7.
  * `scratch` is one uint32 word (cleared by the call). */

@@ -45,7 +45,23 @@ SIGNATURES = {
     "niti_loss_i8": (_i, [_p, _p, _p, _p, _i, _i, _p, _u32, _u64, _p]),
     "niti_update_i8": (_i, [_p, _p, _p, _i64, _i, _i, _p, _u32, _p]),
     "niti_quantize_input_f32": (_i, [_p, _p, _p, _p, _i, _i, _i, _i, _p]),
+    "niti_fc_head_supported": (_i, [_i, _i, _i]),
+    "niti_fc_head_scratch_bytes": (_sz, [_i, _i, _i]),
+    "niti_fc_head_train_i8": (_i, [_p, _p]),
 }
+
+
+class FcHeadArgs(C.Structure):
+    """niti_fc_head_args of include/niti_b200.h"""
+    _fields_ = [("x", _p), ("exp_x", _p), ("w", _p), ("exp_w", _p), ("target", _p), ("out8", _p), ("exp_out", _p),
+                ("err8", _p), ("e8", _p), ("exp_err", _p), ("g32", _p), ("grad_maxabs", _p),
+                ("scratch", _p), ("scratch_bytes", _sz), ("B", C.c_int32), ("F", C.c_int32), ("J", C.c_int32),
+                ("dropout", C.c_int32), ("bits", C.c_int32), ("act_round", C.c_int32), ("err_round", C.c_int32),
+                ("grad_round", C.c_int32), ("mu", C.c_int32), ("update", C.c_int32), ("seed", _p),
+                ("layer_stream", _u32), ("dropout_stream", _u32), ("loss_stream", _u32), ("sample_offset", _u64),
+                ("status", _p)]
+
+
 
 for _name, (_res, _args) in SIGNATURES.items():
     _fn = getattr(lib, _name)

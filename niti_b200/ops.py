@@ -7,7 +7,9 @@ int32 CUDA tensors so that nothing here reads a value back to the host.
 """
 import torch
 
-from ._lib import lib, check
+import ctypes
+
+from ._lib import lib, check, FcHeadArgs
 
 ROUND_NEAREST, ROUND_STOCHASTIC, ROUND_PSEUDO_STOCHASTIC = 0, 1, 2
 CALC_ACT, CALC_ERR, CALC_GRAD = 0, 1, 2
@@ -272,6 +274,38 @@ def loss_err(out8, out_exp, target, seed, rng_stream=0xFFFF, sample_offset=0):
     _call("niti_loss_i8", 1, 0, 2 * out8.numel(), lib.niti_loss_i8, _p(out8), _p(out_exp), _p(target), _p(err),
           out8.shape[0], out8.shape[1], _p(seed), rng_stream, sample_offset, _st())
     return err
+
+
+def fc_head_supported(B, F, J):
+    return bool(lib.niti_fc_head_supported(B, F, J))
+
+
+def fc_head_train(x, exp_x, w, exp_w, target, seed, layer_stream, *, dropout=True, bits=7, act_mode=ROUND_NEAREST,
+                  err_mode=ROUND_NEAREST, grad_mode=ROUND_PSEUDO_STOCHASTIC, mu=5, update=True, sample_offset=0,
+                  g32=None, dropout_stream=0xFFFE, loss_stream=0xFFFF):
+    """Dropout + FC forward + loss error + FC backward (+ update of w in place) in one kernel.
+    Returns (out8, exp_out, err8, e8, exp_err, g32, grad_maxabs)."""
+    _need_cuda(x, exp_x, w, exp_w, target, seed, g32)
+    B, F = x.shape
+    J = w.shape[0]
+    assert x.dtype == torch.int8 and w.dtype == torch.int8 and target.dtype == torch.int64 and w.shape[1] == F
+    dev = x.device
+    out8 = torch.empty((B, J), dtype=torch.int8, device=dev)
+    err8 = torch.empty((B, J), dtype=torch.int8, device=dev)
+    e8 = torch.empty_like(x)
+    exps = torch.empty(2, dtype=torch.int32, device=dev)
+    if g32 is None:
+        g32 = torch.empty((J, F), dtype=torch.int32, device=dev)
+    gm = torch.empty(1, dtype=torch.int32, device=dev)
+    nbytes = lib.niti_fc_head_scratch_bytes(B, F, J)
+    sc = torch.empty(nbytes, dtype=torch.uint8, device=dev)
+    a = FcHeadArgs(_p(x), _p(exp_x), _p(w), _p(exp_w), _p(target), _p(out8), exps[0:1].data_ptr(), _p(err8), _p(e8),
+                   exps[1:2].data_ptr(), _p(g32), _p(gm), _p(sc), nbytes, B, F, J, int(dropout), bits, act_mode, err_mode,
+                   grad_mode, mu, int(update), _p(seed), layer_stream, dropout_stream, loss_stream, sample_offset,
+                   _p(status_word(dev)))
+    _call("niti_fc_head_train_i8", 1, 6 * B * F * J, 2 * x.numel() + 6 * w.numel(), lib.niti_fc_head_train_i8,
+          ctypes.byref(a), _st())
+    return out8, exps[0], err8, e8, exps[1], g32, gm
 
 
 def update(w, g32, maxabs, mu, mode=ROUND_PSEUDO_STOCHASTIC, seed=None, rng_stream=0):

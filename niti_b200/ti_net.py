@@ -5,8 +5,9 @@ import collections
 import torch
 from torch.nn.modules import Module
 
+from . import ops, ti_torch
 from .ti_loss import TiLoss
-from .ti_torch import RangeEstimate, TiFloatToInt8, exp_tensor
+from .ti_torch import RangeEstimate, TiDropout, TiFloatToInt8, TiLinear, exp_tensor
 
 
 class TiNet(Module):
@@ -46,6 +47,53 @@ class TiNet(Module):
                     x = block.backward(x)
             else:
                 x = layer.backward(x)
+
+    def _fusable_head(self, batch):
+        """(number of head layers, has dropout) if the network ends in [TiDropout,] TiLinear of a size the
+        one-kernel classifier head takes, else None."""
+        layers = list(self.forward_layers)
+        if not (ti_torch.FUSE_HEAD and ti_torch.TRAINING and layers and isinstance(layers[-1], TiLinear)):
+            return None
+        drop = len(layers) >= 2 and isinstance(layers[-2], TiDropout)
+        J, F = layers[-1].weight.shape
+        if len(layers) - (2 if drop else 1) < 1 or not ops.fc_head_supported(batch, F, J):
+            return None
+        return (2 if drop else 1), drop
+
+    def train_step(self, x, target):
+        """forward(x) followed by backward(target), with the same results; when the network ends in
+        [TiDropout,] TiLinear the whole classifier head (dropout, FC forward, loss, FC backward, update)
+        runs as one kernel instead of eleven."""
+        head = self._fusable_head(x.shape[0])
+        if head is None:
+            out = self.forward(x)
+            self.backward(target)
+            return out
+        n_head, drop = head
+        layers = list(self.forward_layers)
+        body, lin = layers[:-n_head], layers[-1]
+        h = TiFloatToInt8(x)
+        for l in body:
+            h = l(h)
+        feat, feat_exp = h
+        dev = feat.device
+        lin.act_in = h
+        out8, out_exp, err8, e8, err_exp, g32, gm = ops.fc_head_train(
+            feat.contiguous(), exp_tensor(feat_exp, dev), lin.weight, lin.weight_exp,
+            target.to(device=dev, dtype=torch.int64).contiguous(), ti_torch.RNG_SEED(dev), 16 * lin.layer_id,
+            dropout=drop, bits=ti_torch.BITWIDTH, act_mode=ti_torch._mode(ti_torch.ACT_ROUND_METHOD),
+            err_mode=ti_torch._mode(ti_torch.ERROR_ROUND_METHOD), grad_mode=ti_torch._mode(ti_torch.GRAD_ROUND_METHOD),
+            mu=ti_torch.GRAD_BITWIDTH, update=not lin.defer_update, sample_offset=ti_torch.SAMPLE_OFFSET,
+            g32=lin.grad_buffer)
+        self.out, self.out_exp = out8, out_exp
+        self.loss.out_grad = err8
+        lin.grad_int32acc, lin.grad_maxabs, lin.err_exp = g32, gm, err_exp
+        if lin.grad_ready is not None:
+            lin.grad_ready(lin)
+        e = (e8, err_exp)
+        for l in reversed(body):
+            e = l.backward(e)
+        return self.out, self.out_exp
 
     def state_dict(self):
         """Same keys as the reference (ti_net.py:34-41): layers.<idx>.weight / .weight_exp."""

@@ -371,6 +371,7 @@ GRAD_ROUND_METHOD = PstoShift
 WEIGHT_INIT_METHOD = UniformWeights
 
 FUSE_REQUANT = True    # convolutions narrow to int8 inside their own kernel (predicted shift, verified, redone if wrong)
+FUSE_HEAD = True       # TiNet.train_step runs [dropout,] FC, loss, FC backward and update as one kernel
 GRAD_BITWIDTH = 5      # the reference's training loop injects this per epoch (main.py:73-77)
 TRAINING = True        # likewise (main.py:147-149)
 SAMPLE_OFFSET = 0      # global index of this process's first sample (data-parallel shards)

@@ -64,8 +64,7 @@ class Trainer:
 
     # ------------------------------------------------------------------ pieces of one step
     def _forward_backward(self):
-        self.model(self.x)
-        self.model.backward(self.t)
+        self.model.train_step(self.x, self.t)
 
     def _update(self):
         if self.world > 1:

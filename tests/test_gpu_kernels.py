@@ -293,3 +293,61 @@ def test_cta_pair_and_single_cta_kernels_match(pairs):
             ops.set_accumulator_parking(oldp)
     finally:
         ops.set_cta_pairs(old)
+
+
+# ----------------------------------------------------------------------------- fused classifier head
+HEAD_CASES = [
+    # B, F, J, dropout, (act, err, grad) rounding, exp_x, exp_w, sample_offset
+    (128, 8192, 10, True, (0, 0, 2), -5, -8, 0),
+    (128, 8192, 10, True, (1, 1, 1), -9, -9, 256),
+    (4, 512, 10, True, (0, 0, 2), -6, -7, 0),
+    (37, 2048, 16, False, (0, 1, 0), -2, -5, 37),
+    (200, 1024, 3, True, (2, 2, 2), -12, -10, 0),
+    (300, 160, 10, False, (0, 0, 2), 0, -3, 11),
+]
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("B,F,J,dropout,modes,exp_x,exp_w,offset", HEAD_CASES)
+def test_fc_head_one_kernel_matches_the_separate_calls(B, F, J, dropout, modes, exp_x, exp_w, offset):
+    """The one-kernel classifier head against the chain of calls it replaces (each of which is checked
+    against the oracle above): dropout, FC forward, requantise, loss, FC error-backward, requantise,
+    weight gradient, update, dropout backward."""
+    rng = np.random.default_rng(B * 7 + F + J)
+    act_mode, err_mode, grad_mode = modes
+    x = cu(rnd8(rng, (B, F), 0, 128))
+    w = cu(rnd8(rng, (J, F), -40, 41))
+    tgt = cu(rng.integers(0, J, size=B).astype(np.int64))
+    seed = ops.seed_tensor(99 + B, DEV)
+    ex = torch.tensor(exp_x, dtype=torch.int32, device=DEV)
+    ew = torch.tensor(exp_w, dtype=torch.int32, device=DEV)
+    stream = 16 * 6
+    assert ops.fc_head_supported(B, F, J)
+
+    xd = ops.dropout(x, seed, 0xFFFE) if dropout else x
+    e_in = ex + 1 if dropout else ex
+    acc, mx = ops.gemm_acc(xd, w, trans_b=True)
+    out8, out_exp, _ = ops.requant(acc, mx, ops.CALC_ACT, 7, act_mode, seed, stream, offset * J, exp_a=e_in, exp_b=ew)
+    err8 = ops.loss_err(out8, out_exp, tgt, seed, 0xFFFF, offset)
+    acc2, mx2 = ops.gemm_acc(err8, w)
+    zero = torch.zeros((), dtype=torch.int32, device=DEV)
+    e8, err_exp, _ = ops.requant(acc2, mx2, ops.CALC_ERR, 7, err_mode, seed, stream + 1, offset * F, exp_a=zero, exp_b=ew)
+    if dropout:
+        e8 = ops.dropout(e8, seed, 0xFFFE)
+    g32, gm = ops.gemm_acc(err8, xd, trans_a=True)
+    w_sep = w.clone()
+    ops.update(w_sep, g32, gm, 5, grad_mode, seed, stream + 2)
+
+    for update in (False, True):
+        w_one = w.clone()
+        got = ops.fc_head_train(x, ex, w_one, ew, tgt, seed, stream, dropout=dropout, act_mode=act_mode, err_mode=err_mode,
+                                grad_mode=grad_mode, mu=5, update=update, sample_offset=offset)
+        o8, oexp, l8, b8, bexp, gg, gmax = got
+        assert_same(o8, out8.cpu().numpy(), "head: logits")
+        assert int(oexp) == int(out_exp)
+        assert_same(l8, err8.cpu().numpy(), "head: loss error")
+        assert_same(b8, e8.cpu().numpy(), "head: error to the features")
+        assert int(bexp) == int(err_exp)
+        assert_same(gg, g32.cpu().numpy(), "head: weight gradient")
+        assert int(gmax) == int(gm)
+        assert_same(w_one, (w_sep if update else w).cpu().numpy(), f"head: weights, update={update}")
