@@ -114,7 +114,8 @@ NITI_API int niti_conv_dgrad_i8(const int8_t* err, const int8_t* w, int32_t* e32
  * straight from the NHWC tensors (no transposes).  On the tensor-core paths the reduction over
  * pixels is split across thread blocks, which add their tiles into g32 with TMA reductions (exact,
  * order-independent); the first-layer path and the NITI_OPT_WGRAD_TMA_REDUCE = 0 mode put partial
- * sums in `scratch` (niti_conv_wgrad_scratch_bytes) and fold them.  *maxabs = max |g32|.
+ * sums in `scratch` (niti_conv_wgrad_scratch_bytes) and fold them.  *maxabs = max |g32|; maxabs may
+ * be null when the caller finds the maximum later (niti_update_multi_i8 does).
  */
 NITI_API size_t niti_conv_wgrad_scratch_bytes(int N, int H, int W, int C, int K, int R, int S);
 NITI_API int niti_conv_wgrad_i8(const int8_t* x, const int8_t* err, int32_t* g32, uint32_t* maxabs,
@@ -239,6 +240,17 @@ NITI_API int niti_loss_i8(const int8_t* out8, const int32_t* out_exp, const int6
  * *maxabs = max |g32| (from niti_conv_wgrad_i8 / niti_gemm_i8 / niti_absmax_i32). */
 NITI_API int niti_update_i8(int8_t* w, const int32_t* g32, const uint32_t* maxabs, int64_t n,
                    int mu, int round_mode, const uint64_t* seed, uint32_t rng_stream, void* stream);
+
+/* Every weighted layer's update in one (cooperative) launch: for each item max |g32| is found, written to
+ * *maxabs when that is not null, and w updated exactly as niti_update_i8 would with that maximum and the
+ * item's rng_stream.  scratch: niti_update_multi_scratch_bytes() bytes.  status as in niti_fc_head_train_i8
+ * (code 7).  No counterpart in the reference, which updates layer by layer (ti_torch.py:16-21). */
+typedef struct niti_update_item {
+    int8_t* w; const int32_t* g32; uint32_t* maxabs; int64_t n; uint32_t rng_stream;
+} niti_update_item;
+NITI_API size_t niti_update_multi_scratch_bytes(void);
+NITI_API int niti_update_multi_i8(const niti_update_item* items, int count, int mu, int round_mode, const uint64_t* seed,
+                         void* scratch, size_t scratch_bytes, int32_t* status, void* stream);
 
 /* The classifier head of a training step in one (cooperative) kernel: TiDropout.forward
  * (ti_torch.py:439-455), TiLinear.forward (:241-253), TiLoss.forward (ti_loss.py:6-36), TiLinear.backward

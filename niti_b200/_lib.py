@@ -45,10 +45,17 @@ SIGNATURES = {
     "niti_loss_i8": (_i, [_p, _p, _p, _p, _i, _i, _p, _u32, _u64, _p]),
     "niti_update_i8": (_i, [_p, _p, _p, _i64, _i, _i, _p, _u32, _p]),
     "niti_quantize_input_f32": (_i, [_p, _p, _p, _p, _i, _i, _i, _i, _p]),
+    "niti_update_multi_scratch_bytes": (_sz, []),
+    "niti_update_multi_i8": (_i, [_p, _i, _i, _i, _p, _p, _sz, _p, _p]),
     "niti_fc_head_supported": (_i, [_i, _i, _i]),
     "niti_fc_head_scratch_bytes": (_sz, [_i, _i, _i]),
     "niti_fc_head_train_i8": (_i, [_p, _p]),
 }
+
+
+class UpdateItem(C.Structure):
+    """niti_update_item of include/niti_b200.h"""
+    _fields_ = [("w", _p), ("g32", _p), ("maxabs", _p), ("n", _i64), ("rng_stream", _u32)]
 
 
 class FcHeadArgs(C.Structure):

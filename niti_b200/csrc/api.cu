@@ -135,11 +135,12 @@ extern "C" size_t niti_conv_wgrad_scratch_bytes(int N, int H, int W, int C, int 
 extern "C" int niti_conv_wgrad_i8(const int8_t* x, const int8_t* err, int32_t* g32, uint32_t* maxabs, void* scratch,
                                   size_t scratch_bytes, int N, int H, int W, int C, int K, int R, int S, int pad,
                                   int32_t* status, void* stream) {
-    NITI_REQUIRE(x && err && g32 && maxabs && N > 0 && H > 0 && W > 0 && C > 0 && K > 0 && R > 0 && S > 0 && pad >= 0);
+    NITI_REQUIRE(x && err && g32 && N > 0 && H > 0 && W > 0 && C > 0 && K > 0 && R > 0 && S > 0 && pad >= 0);
     NITI_REQUIRE(aligned16(g32));
     if (H + 2 * pad - R + 1 <= 0 || W + 2 * pad - S + 1 <= 0) return NITI_ERR_BAD_ARG;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    if (int e = clear_word(maxabs, st)) return e;
+    if (maxabs != nullptr)  // null: the caller finds max|g32| later (niti_update_multi_i8 does)
+        if (int e = clear_word(maxabs, st)) return e;
     ConvPath path = wgrad_path(C, K, R, S, pad);
     if (!(aligned16(x) && aligned16(err))) path = CONV_SIMT;
     if (path == CONV_SIMT) return simt_conv_wgrad(x, err, g32, maxabs, N, H, W, C, K, R, S, pad, st);
@@ -152,7 +153,7 @@ extern "C" int niti_conv_wgrad_i8(const int8_t* x, const int8_t* err, int32_t* g
             // pass for max|g|: no partial sums in memory, no folding kernel
             if (int e = set_cuda_error(cudaMemsetAsync(g32, 0, static_cast<size_t>(n) * 4, st))) return e;
             if (int rc = umma_conv_wgrad_partials(x, err, g32, &splits, 0, N, H, W, C, K, R, S, pad, status, st, 1)) return rc;
-            return absmax_i32(g32, n, maxabs, st);
+            return maxabs != nullptr ? absmax_i32(g32, n, maxabs, st) : NITI_OK;
         }
         if (int rc = umma_conv_wgrad_partials(x, err, static_cast<int32_t*>(scratch), &splits, 0, N, H, W, C, K, R, S, pad, status, st)) return rc;
         return reduce_partials(static_cast<const int32_t*>(scratch), splits, n, g32, maxabs, st);

@@ -1,0 +1,43 @@
+// A bounded barrier across the thread blocks of a cooperative launch (all blocks co-resident).
+#pragma once
+#include <cstdint>
+
+namespace niti {
+
+constexpr unsigned long long GRID_WAIT_LIMIT_NS = 500000000ull;  // 0.5 s
+
+__device__ __forceinline__ unsigned long long grid_timer_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+
+// Every block calls this with the same, monotonically growing `target` (blocks x number of the barrier);
+// `counter` starts at zero.  Returns false when the other blocks did not arrive within the limit: the
+// caller must then leave the kernel (status, when given, receives {code, block, target}).
+__device__ __forceinline__ bool bounded_grid_barrier(int32_t* counter, int target, int32_t* status, int code, int* flag) {
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        __threadfence();
+        atomicAdd(counter, 1);
+        const unsigned long long t0 = grid_timer_ns();
+        bool arrived = false;
+        for (unsigned spin = 0;; ++spin) {
+            if (atomicAdd(counter, 0) >= target) { arrived = true; break; }
+            if ((spin & 31) == 31) {
+                if (grid_timer_ns() - t0 > GRID_WAIT_LIMIT_NS) break;
+                __nanosleep(100);
+            }
+        }
+        __threadfence();
+        *flag = arrived ? 1 : 0;
+        if (!arrived && status != nullptr && atomicCAS(status, 0, code) == 0) {
+            status[1] = static_cast<int32_t>(blockIdx.x);
+            status[2] = target;
+        }
+    }
+    __syncthreads();
+    return *flag != 0;
+}
+
+}  // namespace niti

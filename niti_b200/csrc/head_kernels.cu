@@ -16,6 +16,7 @@
 #include "internal.h"
 #include "requant.cuh"
 #include "loss_math.cuh"
+#include "grid_barrier.cuh"
 
 namespace niti {
 namespace {
@@ -24,7 +25,6 @@ constexpr int HEAD_THREADS = 256;
 constexpr int HEAD_MAX_CLASSES = 16;
 constexpr int HEAD_RED_INTS = 16 * 16 * 16;  // [batch group][class][feature of the chunk]
 constexpr size_t HEAD_MAX_SMEM = 200 * 1024;
-constexpr unsigned long long HEAD_BARRIER_LIMIT_NS = 500000000ull;
 
 struct HeadParams {
     const int8_t* x; const int32_t* exp_x; int8_t* w; const int32_t* exp_w; const long long* target;
@@ -38,11 +38,6 @@ struct HeadParams {
     int32_t* status;
 };
 
-__device__ __forceinline__ unsigned long long head_timer_ns() {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    return t;
-}
 __device__ __forceinline__ unsigned iabs32(int x) { return static_cast<unsigned>(x < 0 ? -x : x); }
 // four mask bits -> four bytes of 0xFF / 0x00
 __device__ __forceinline__ uint32_t expand4(unsigned b) {
@@ -52,32 +47,6 @@ __device__ __forceinline__ long long warp_sum_ll(long long v) {
 #pragma unroll
     for (int off = 16; off > 0; off >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, off);
     return v;
-}
-
-// All blocks of the (cooperative) grid meet; false if the others did not arrive in time.
-__device__ bool head_barrier(int32_t* counter, int target, int32_t* status, int* flag) {
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        __threadfence();
-        atomicAdd(counter, 1);
-        const unsigned long long t0 = head_timer_ns();
-        bool arrived = false;
-        for (unsigned spin = 0;; ++spin) {
-            if (atomicAdd(counter, 0) >= target) { arrived = true; break; }
-            if ((spin & 31) == 31) {
-                if (head_timer_ns() - t0 > HEAD_BARRIER_LIMIT_NS) break;
-                __nanosleep(100);
-            }
-        }
-        __threadfence();
-        *flag = arrived ? 1 : 0;
-        if (!arrived && status != nullptr && atomicCAS(status, 0, 6) == 0) {
-            status[1] = static_cast<int32_t>(blockIdx.x);
-            status[2] = target;
-        }
-    }
-    __syncthreads();
-    return *flag != 0;
 }
 
 // e[k] = sum_j err[j] * W[j][16 c + k]: one 16-feature chunk of the error that goes back to the features
@@ -171,7 +140,7 @@ __global__ void __launch_bounds__(HEAD_THREADS, 1) fc_head_kernel(const HeadPara
         }
         __syncthreads();
     }
-    if (!head_barrier(&p.state[3], G, p.status, sFlag)) return;
+    if (!bounded_grid_barrier(&p.state[3], G, p.status, 6, sFlag)) return;
 
     // ---- logits to int8, then the loss's error: one warp per sample, one lane per class
     const int exp_w = *p.exp_w;
@@ -228,7 +197,7 @@ __global__ void __launch_bounds__(HEAD_THREADS, 1) fc_head_kernel(const HeadPara
             }
         }
     }
-    if (!head_barrier(&p.state[3], 2 * G, p.status, sFlag)) return;
+    if (!bounded_grid_barrier(&p.state[3], 2 * G, p.status, 6, sFlag)) return;
 
     // ---- every block needs every sample's error
     for (int i = t; i < B * J; i += HEAD_THREADS) sErr[i] = __ldcg(reinterpret_cast<const signed char*>(p.err8) + i);
@@ -279,7 +248,7 @@ __global__ void __launch_bounds__(HEAD_THREADS, 1) fc_head_kernel(const HeadPara
         m = __reduce_max_sync(0xFFFFFFFFu, m);
         if (lane == 0 && m != 0) atomicMax(&umax[2], m);
     }
-    if (!head_barrier(&p.state[3], 3 * G, p.status, sFlag)) return;
+    if (!bounded_grid_barrier(&p.state[3], 3 * G, p.status, 6, sFlag)) return;
 
     // ---- error to the features: recompute, narrow with the tensor-wide shift, apply the dropout bits
     {

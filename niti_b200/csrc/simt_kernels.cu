@@ -10,6 +10,7 @@
 #include "internal.h"
 #include "requant.cuh"
 #include "loss_math.cuh"
+#include "grid_barrier.cuh"
 
 namespace niti {
 
@@ -34,7 +35,7 @@ __device__ __forceinline__ unsigned iabs_u(int x) { return static_cast<unsigned>
 
 __device__ __forceinline__ void warp_atomic_max(unsigned* dst, unsigned v) {
     v = __reduce_max_sync(0xFFFFFFFFu, v);
-    if ((threadIdx.x & 31) == 0 && v != 0) atomicMax(dst, v);
+    if ((threadIdx.x & 31) == 0 && v != 0 && dst != nullptr) atomicMax(dst, v);
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -500,6 +501,67 @@ update_kernel(int8_t* __restrict__ w, const int32_t* __restrict__ g32, const uns
     }
 }
 
+// All weighted layers of a step in one cooperative launch: max|g32| of every layer, a grid barrier, then
+// every layer's update with its own shift.  The second read of the gradients comes from L2.
+constexpr int UPDATE_MULTI_MAX = 16;
+struct UpdateItem { int8_t* w; const int32_t* g32; unsigned* maxabs; long long n; unsigned rng_stream; };
+struct UpdateMultiParams {
+    UpdateItem item[UPDATE_MULTI_MAX];
+    int count, mu, mode;
+    const unsigned long long* seed;
+    int32_t* state;  // [count] maxima, [UPDATE_MULTI_MAX] barrier arrivals; zero at launch
+    int32_t* status;
+};
+__global__ void __launch_bounds__(256)
+update_multi_kernel(const UpdateMultiParams p) {
+    __shared__ int flag;
+    const long long tid = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
+    const long long nthreads = static_cast<long long>(gridDim.x) * blockDim.x;
+    unsigned* umax = reinterpret_cast<unsigned*>(p.state);
+    for (int l = 0; l < p.count; ++l) {
+        const UpdateItem& it = p.item[l];
+        unsigned m = 0;
+        const long long groups = it.n >> 2;
+        for (long long g = tid; g < groups; g += nthreads) {
+            const int4 v = reinterpret_cast<const int4*>(it.g32)[g];
+            m = max(max(m, iabs_u(v.x)), max(iabs_u(v.y), max(iabs_u(v.z), iabs_u(v.w))));
+        }
+        for (long long i = (groups << 2) + tid; i < it.n; i += nthreads) m = max(m, iabs_u(it.g32[i]));
+        warp_atomic_max(&umax[l], m);
+    }
+    if (!bounded_grid_barrier(&p.state[UPDATE_MULTI_MAX], static_cast<int>(gridDim.x), p.status, 7, &flag)) return;
+    const unsigned long long seed = (p.mode == ROUND_STOCHASTIC) ? *p.seed : 0ull;
+    for (int l = 0; l < p.count; ++l) {
+        const UpdateItem& it = p.item[l];
+        const unsigned mx = __ldcg(&umax[l]);
+        if (tid == 0 && it.maxabs != nullptr) *it.maxabs = mx;
+        bool zero_out;
+        const int shift = shift_for(mx, CALC_GRAD, p.mu, &zero_out);
+        const bool stochastic = (p.mode == ROUND_STOCHASTIC) && shift > 0;
+        const long long groups = it.n >> 2;
+        for (long long g = tid; g < groups; g += nthreads) {
+            const int4 gv = __ldcs(reinterpret_cast<const int4*>(it.g32) + g);
+            const uint32_t wv = reinterpret_cast<const uint32_t*>(it.w)[g];
+            uint32_t rnd[4] = {0, 0, 0, 0};
+            if (stochastic) random_block(seed, it.rng_stream, static_cast<unsigned long long>(g), rnd);
+            const int gx[4] = {gv.x, gv.y, gv.z, gv.w};
+            uint32_t o = 0;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int g8 = zero_out ? 0 : narrow(gx[j], shift, p.mode, rnd[j]);
+                const int wj = static_cast<int8_t>(wv >> (8 * j));
+                o |= static_cast<uint32_t>(static_cast<uint8_t>(clamp127(wj - g8))) << (8 * j);
+            }
+            reinterpret_cast<uint32_t*>(it.w)[g] = o;
+        }
+        for (long long i = (groups << 2) + tid; i < it.n; i += nthreads) {
+            const uint32_t rnd = stochastic ? random_word(seed, it.rng_stream, static_cast<unsigned long long>(i)) : 0u;
+            const int g8 = zero_out ? 0 : narrow(it.g32[i], shift, p.mode, rnd);
+            it.w[i] = static_cast<int8_t>(clamp127(static_cast<int>(it.w[i]) - g8));
+        }
+    }
+}
+
 // ------------------------------------------------------------------------------------------------
 // input quantisation (ti_torch.py:341-356 + the permute of ti_net.py:19)
 // ------------------------------------------------------------------------------------------------
@@ -677,7 +739,7 @@ gemm_kk_kernel(const int8_t* __restrict__ A, const int8_t* __restrict__ B, int32
         acc = __reduce_add_sync(0xFFFFFFFFu, acc);
         if (lane == 0) { C32[o] = acc; mx = max(mx, iabs_u(acc)); }
     }
-    if (lane == 0 && mx != 0) atomicMax(maxabs, mx);
+    if (lane == 0 && mx != 0 && maxabs != nullptr) atomicMax(maxabs, mx);
 }
 // GEMM, any majors: one thread per output element, consecutive threads along N.
 __global__ void __launch_bounds__(256)
@@ -840,6 +902,47 @@ extern "C" int niti_update_i8(int8_t* w, const int32_t* g32, const uint32_t* max
     update_kernel<<<blocks_for(n / 4 + 1, 256, sm_count_simt() * 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(
         w, g32, maxabs, n, mu, round_mode, reinterpret_cast<const unsigned long long*>(seed), rng_stream);
     return set_cuda_error(cudaGetLastError());
+}
+
+extern "C" size_t niti_update_multi_scratch_bytes(void) { return 2 * UPDATE_MULTI_MAX * sizeof(int32_t); }
+
+extern "C" int niti_update_multi_i8(const niti_update_item* items, int count, int mu, int round_mode, const uint64_t* seed,
+                                    void* scratch, size_t scratch_bytes, int32_t* status, void* stream) {
+    NITI_REQUIRE(items && count > 0 && round_mode >= 0 && round_mode <= 2 && scratch);
+    NITI_REQUIRE(seed || round_mode != NITI_ROUND_STOCHASTIC);
+    if (scratch_bytes < niti_update_multi_scratch_bytes()) return NITI_ERR_SCRATCH;
+    for (int i = 0; i < count; ++i) {
+        NITI_REQUIRE(items[i].w && items[i].g32 && items[i].n > 0);
+        NITI_REQUIRE(reinterpret_cast<uintptr_t>(items[i].w) % 4 == 0 && reinterpret_cast<uintptr_t>(items[i].g32) % 16 == 0);
+    }
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    static int blocks_per_sm = 0;
+    if (blocks_per_sm == 0) {
+        int n = 0;
+        if (int e = set_cuda_error(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, update_multi_kernel, 256, 0))) return e;
+        blocks_per_sm = n < 1 ? 1 : (n > 4 ? 4 : n);
+    }
+    for (int first = 0; first < count; first += UPDATE_MULTI_MAX) {
+        UpdateMultiParams p;
+        p.count = count - first < UPDATE_MULTI_MAX ? count - first : UPDATE_MULTI_MAX;
+        long long total = 0;
+        for (int i = 0; i < p.count; ++i) {
+            const niti_update_item& it = items[first + i];
+            p.item[i] = UpdateItem{it.w, it.g32, it.maxabs, it.n, it.rng_stream};
+            total += it.n;
+        }
+        p.mu = mu; p.mode = round_mode;
+        p.seed = reinterpret_cast<const unsigned long long*>(seed);
+        p.state = static_cast<int32_t*>(scratch);
+        p.status = status;
+        if (int e = set_cuda_error(cudaMemsetAsync(scratch, 0, niti_update_multi_scratch_bytes(), st))) return e;
+        const int grid = blocks_for(total / 4 + 1, 256, sm_count_simt() * blocks_per_sm);
+        void* args[] = {&p};
+        if (int e = set_cuda_error(cudaLaunchCooperativeKernel(reinterpret_cast<const void*>(update_multi_kernel), dim3(grid),
+                                                               dim3(256), args, 0, st)))
+            return e;
+    }
+    return NITI_OK;
 }
 
 extern "C" int niti_quantize_input_f32(const float* x, int8_t* x8, int32_t* exp_out, uint32_t* scratch, int N, int C,

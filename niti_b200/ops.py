@@ -9,7 +9,7 @@ import torch
 
 import ctypes
 
-from ._lib import lib, check, FcHeadArgs
+from ._lib import lib, check, FcHeadArgs, UpdateItem
 
 ROUND_NEAREST, ROUND_STOCHASTIC, ROUND_PSEUDO_STOCHASTIC = 0, 1, 2
 CALC_ACT, CALC_ERR, CALC_GRAD = 0, 1, 2
@@ -178,12 +178,13 @@ def conv_dgrad_acc(err, w, pad=1):
     return e32, mx
 
 
-def conv_wgrad_acc(x, err, R=3, S=3, pad=1, out=None):
+def conv_wgrad_acc(x, err, R=3, S=3, pad=1, out=None, want_max=True):
+    """Weight gradient accumulators and max|g32| (None when want_max is False: update_multi finds it)."""
     _need_cuda(x, err, out)
     N, H, W, C = x.shape
     K = err.shape[3]
     g32 = out if out is not None else torch.empty((K, R, S, C), dtype=torch.int32, device=x.device)
-    mx = torch.empty(1, dtype=torch.int32, device=x.device)
+    mx = torch.empty(1, dtype=torch.int32, device=x.device) if want_max else None
     nbytes = lib.niti_conv_wgrad_scratch_bytes(N, H, W, C, K, R, S)
     sc = scratch(x.device, nbytes)
     _call("niti_conv_wgrad_i8", 2 if C % 16 == 0 else 3, 2 * N * H * W * K * R * S * C, x.numel() + err.numel() + 4 * g32.numel(),
@@ -313,6 +314,25 @@ def update(w, g32, maxabs, mu, mode=ROUND_PSEUDO_STOCHASTIC, seed=None, rng_stre
     _need_cuda(w, g32, maxabs)
     _call("niti_update_i8", 1, 0, 6 * w.numel(), lib.niti_update_i8, _p(w), _p(g32), _p(maxabs),
           w.numel(), mu, mode, _p(seed), rng_stream, _st())
+
+
+def update_multi(ws, g32s, streams, mu, mode=ROUND_PSEUDO_STOCHASTIC, seed=None, want_max=False):
+    """All layers' integer SGD updates in one launch: per layer max|g32| -> shift -> w -= narrow(g32).
+    Returns the per-layer maxima (int32[len(ws)]) when want_max."""
+    _need_cuda(seed, *ws, *g32s)
+    dev = ws[0].device
+    n = len(ws)
+    mx = torch.empty(n, dtype=torch.int32, device=dev) if want_max else None
+    items = (UpdateItem * n)()
+    for i, (w, g, st) in enumerate(zip(ws, g32s, streams)):
+        assert w.dtype == torch.int8 and g.dtype == torch.int32 and g.numel() == w.numel()
+        items[i] = UpdateItem(_p(w), _p(g), mx[i:i + 1].data_ptr() if want_max else None, w.numel(), st)
+    nbytes = lib.niti_update_multi_scratch_bytes()
+    sc = torch.empty(nbytes, dtype=torch.uint8, device=dev)
+    total = sum(w.numel() for w in ws)
+    _call("niti_update_multi_i8", (n + 15) // 16, 0, 10 * total, lib.niti_update_multi_i8, items, n, mu, mode, _p(seed),
+          _p(sc), nbytes, _p(status_word(dev)), _st())
+    return mx
 
 
 def quantize_input(x):

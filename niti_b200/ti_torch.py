@@ -35,6 +35,14 @@ class UpdateWeight(Module):
                    RNG_SEED(self.weight.device), 16 * self.layer_id + 2)
 
 
+def weight_update_all(layers):
+    """The updates of all `layers` (UpdateWeight modules whose grad_int32acc is set) in one launch; each
+    layer's maximum is recomputed from its accumulators, so this also serves gradients summed across ranks."""
+    dev = layers[0].weight.device
+    ops.update_multi([l.weight for l in layers], [l.grad_int32acc for l in layers], [16 * l.layer_id + 2 for l in layers],
+                     GRAD_BITWIDTH, _mode(GRAD_ROUND_METHOD), RNG_SEED(dev))
+
+
 def _fake_max(shift):
     # a max|x| whose bit-width is exactly shift + BITWIDTH, so the kernel picks `shift`
     return 1 << (shift + BITWIDTH)
@@ -336,7 +344,9 @@ class TiConv2d(UpdateWeight):
                                                  exp_tensor(self.err_exp, acc.device), self.weight_exp, mx, False,
                                                  SAMPLE_OFFSET * per)
         K, R, S, C = self.weight.shape
-        self.grad_int32acc, self.grad_maxabs = ops.conv_wgrad_acc(self.act, err_in, R, S, self.padding, out=self.grad_buffer)
+        # a deferred update finds max|g| itself (weight_update_all)
+        self.grad_int32acc, self.grad_maxabs = ops.conv_wgrad_acc(self.act, err_in, R, S, self.padding, out=self.grad_buffer,
+                                                                  want_max=not self.defer_update)
         if self.grad_ready is not None:
             self.grad_ready(self)
         if not self.defer_update:

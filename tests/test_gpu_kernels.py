@@ -351,3 +351,27 @@ def test_fc_head_one_kernel_matches_the_separate_calls(B, F, J, dropout, modes, 
         assert_same(gg, g32.cpu().numpy(), "head: weight gradient")
         assert int(gmax) == int(gm)
         assert_same(w_one, (w_sep if update else w).cpu().numpy(), f"head: weights, update={update}")
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("mode", [0, 1, 2])
+@pytest.mark.parametrize("count", [1, 7, 19])
+def test_update_multi_matches_layer_by_layer(mode, count):
+    """One launch for all layers against absmax + update per layer (the latter is checked against the oracle above)."""
+    rng = np.random.default_rng(100 * mode + count)
+    sizes = [int(rng.integers(1, 40000)) * (4 if i % 3 else 1) + (i % 3 == 0) * 3 for i in range(count)]
+    sizes[0] = 128 * 3 * 3 * 256
+    seed = ops.seed_tensor(321, DEV)
+    ws, gs, want = [], [], []
+    for i, n in enumerate(sizes):
+        w = cu(rnd8(rng, (n,)))
+        scale = [1, 50, 4000, 300000][i % 4]
+        g = cu((rng.integers(-scale, scale + 1, size=n) * (i % 5 != 4)).astype(np.int32))
+        ref = w.clone()
+        mx = ops.absmax(g)
+        ops.update(ref, g, mx, 5, mode, seed, 16 * i + 2)
+        ws.append(w); gs.append(g); want.append((ref, mx))
+    got_mx = ops.update_multi(ws, gs, [16 * i + 2 for i in range(count)], 5, mode, seed, want_max=True)
+    for i in range(count):
+        assert_same(ws[i], want[i][0].cpu().numpy(), f"update_multi layer {i} of {count}, n={sizes[i]}")
+        assert int(got_mx[i]) == int(want[i][1])
