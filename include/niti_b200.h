@@ -74,6 +74,11 @@ extern "C" {
  * thread blocks that issue 256-row MMAs together (tcgen05 cta_group::2), each fetching half of the B
  * operand, which cuts the L2 -> shared-memory traffic per output; 0: one thread block per 128-row tile. */
 #define NITI_OPT_CTA_PAIRS 4
+/* NITI_OPT_COOPERATIVE_LAUNCH (default 1): the kernels that contain a grid barrier (accumulator parking,
+ * classifier head, multi-layer update) are launched cooperatively, i.e. the driver guarantees that all their
+ * thread blocks are resident together.  0: plain launches of the same one-wave grids; a barrier that is not met
+ * (something else held SMs for more than 0.5 s) then ends in the status word's error, never in a hang. */
+#define NITI_OPT_COOPERATIVE_LAUNCH 5
 NITI_API int niti_set_option(int option, int value);
 
 NITI_API int niti_version(void);

@@ -52,6 +52,7 @@ static int g_opt_wgrad_reduce = 1;
 extern "C" int niti_set_option(int option, int value) {
     if (option == NITI_OPT_ACCUMULATOR_PARKING) { const int old = g_opt_parking; g_opt_parking = value ? 1 : 0; return old; }
     if (option == NITI_OPT_CTA_PAIRS) { const int old = g_two_cta; g_two_cta = value & 3; return old; }
+    if (option == NITI_OPT_COOPERATIVE_LAUNCH) { const int old = g_cooperative; g_cooperative = value ? 1 : 0; return old; }
     if (option == NITI_OPT_STAGE_CAP) { const int old = g_stage_cap; g_stage_cap = value < 0 ? 0 : value; return old; }
     if (option == NITI_OPT_WGRAD_TMA_REDUCE) { const int old = g_opt_wgrad_reduce; g_opt_wgrad_reduce = value ? 1 : 0; return old; }
     return NITI_ERR_BAD_ARG;

@@ -12,6 +12,12 @@ __device__ __forceinline__ unsigned long long grid_timer_ns() {
     return t;
 }
 
+__device__ __forceinline__ int ld_acquire_gpu(const int32_t* p) {
+    int v;
+    asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+
 // Every block calls this with the same, monotonically growing `target` (blocks x number of the barrier);
 // `counter` starts at zero.  Returns false when the other blocks did not arrive within the limit: the
 // caller must then leave the kernel (status, when given, receives {code, block, target}).
@@ -23,11 +29,8 @@ __device__ __forceinline__ bool bounded_grid_barrier(int32_t* counter, int targe
         const unsigned long long t0 = grid_timer_ns();
         bool arrived = false;
         for (unsigned spin = 0;; ++spin) {
-            if (atomicAdd(counter, 0) >= target) { arrived = true; break; }
-            if ((spin & 31) == 31) {
-                if (grid_timer_ns() - t0 > GRID_WAIT_LIMIT_NS) break;
-                __nanosleep(100);
-            }
+            if (ld_acquire_gpu(counter) >= target) { arrived = true; break; }  // a load: waiters do not queue at the L2's atomic unit
+            if ((spin & 63) == 63 && grid_timer_ns() - t0 > GRID_WAIT_LIMIT_NS) break;
         }
         __threadfence();
         *flag = arrived ? 1 : 0;

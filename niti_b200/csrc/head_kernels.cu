@@ -49,37 +49,63 @@ __device__ __forceinline__ long long warp_sum_ll(long long v) {
     return v;
 }
 
-// e[k] = sum_j err[j] * W[j][16 c + k]: one 16-feature chunk of the error that goes back to the features
+// max over the block -> one atomic (every thread calls; `scratch` holds 8 words)
+__device__ __forceinline__ void block_max(unsigned* dst, unsigned m, int32_t* scratch) {
+    m = __reduce_max_sync(0xFFFFFFFFu, m);
+    __syncthreads();
+    if ((threadIdx.x & 31) == 0) scratch[threadIdx.x >> 5] = static_cast<int32_t>(m);
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        unsigned x = 0;
+#pragma unroll
+        for (int i = 0; i < HEAD_THREADS / 32; ++i) x = max(x, static_cast<unsigned>(scratch[i]));
+        if (x != 0) atomicMax(dst, x);
+    }
+    __syncthreads();
+}
+
+// e[k] = sum_j err[j] * W[j][16 c + k]: one 16-feature chunk of the error that goes back to the features.
+// The loop over classes stays rolled: this code runs once or twice per launch, so every instruction is an
+// instruction-cache miss and straight-line unrolling costs more than the loop overhead it saves.
 __device__ __forceinline__ void dgrad_chunk(const uint4* sW, const int8_t* err, int J, int F16, int c, int (&e)[16]) {
 #pragma unroll
     for (int k = 0; k < 16; ++k) e[k] = 0;
+#pragma unroll 1
+    for (int j = 0; j < J; ++j) {
+        const int ej = err[j];
+        const uint4 wv = sW[j * F16 + c];
+        const uint32_t ww[4] = {wv.x, wv.y, wv.z, wv.w};
 #pragma unroll
-    for (int j = 0; j < HEAD_MAX_CLASSES; ++j)
-        if (j < J) {
-            const int ej = err[j];
-            const uint4 wv = sW[j * F16 + c];
-            const uint32_t ww[4] = {wv.x, wv.y, wv.z, wv.w};
+        for (int q = 0; q < 4; ++q)
 #pragma unroll
-            for (int q = 0; q < 4; ++q)
-#pragma unroll
-                for (int r = 0; r < 4; ++r) e[q * 4 + r] += ej * static_cast<int>(static_cast<int8_t>(ww[q] >> (8 * r)));
-        }
+            for (int r = 0; r < 4; ++r) e[q * 4 + r] += ej * static_cast<int>(static_cast<int8_t>(ww[q] >> (8 * r)));
+    }
 }
+
+#ifdef NITI_HEAD_TIMING
+#define HEAD_STAMP(i) do { if (blockIdx.x == 0 && threadIdx.x == 0) reinterpret_cast<unsigned long long*>(p.state + 4 + ((p.B * p.J + 1) & ~1))[i] = grid_timer_ns(); } while (0)
+#else
+#define HEAD_STAMP(i) do { } while (0)
+#endif
 
 __global__ void __launch_bounds__(HEAD_THREADS, 1) fc_head_kernel(const HeadParams p) {
     extern __shared__ __align__(16) unsigned char smem[];
     const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
     const int F = p.F, F16 = F >> 4, J = p.J, B = p.B, G = gridDim.x;
-    // shared memory: W [J][F] | keep bits, one uint16 per 16 features | err8 [B][J] | reduction scratch | flag
+    // shared memory: W [J][F] | keep bits, one uint16 per 16 features | err8 [B][J] | err8 transposed | reduction scratch | flag
     uint4* sW = reinterpret_cast<uint4*>(smem);
     size_t off = static_cast<size_t>(J) * F;
     uint16_t* sMask = reinterpret_cast<uint16_t*>(smem + off);
     off = (off + 2 * static_cast<size_t>(F16) + 15) & ~static_cast<size_t>(15);
     int8_t* sErr = reinterpret_cast<int8_t*>(smem + off);
     off = (off + static_cast<size_t>(B) * J + 15) & ~static_cast<size_t>(15);
+    const int S = (((B + 3) >> 2) + 3) & ~3;  // samples per batch group of the weight gradient (a multiple of 4)
+    int8_t* sErrT = reinterpret_cast<int8_t*>(smem + off);  // err8 transposed, [J][4 S], zero beyond B
+    off += static_cast<size_t>(J) * 4 * S;
     int32_t* sRed = reinterpret_cast<int32_t*>(smem + off);
     int* sFlag = reinterpret_cast<int*>(sRed + HEAD_RED_INTS);
 
+    HEAD_STAMP(0);
     const unsigned long long seed = *p.seed;
     unsigned* umax = reinterpret_cast<unsigned*>(p.state);
 
@@ -101,8 +127,10 @@ __global__ void __launch_bounds__(HEAD_THREADS, 1) fc_head_kernel(const HeadPara
         }
     }
     __syncthreads();
+    HEAD_STAMP(1);
 
     // ---- forward GEMM: out32[b][j] = sum_f drop(x)[b][f] * W[j][f], one sample per block at a time
+    unsigned fwd_max = 0;
     for (int b = blockIdx.x; b < B; b += G) {
         int acc[HEAD_MAX_CLASSES];
 #pragma unroll
@@ -131,17 +159,22 @@ __global__ void __launch_bounds__(HEAD_THREADS, 1) fc_head_kernel(const HeadPara
                 if (lane == 0) sRed[warp * HEAD_MAX_CLASSES + j] = v;
             }
         __syncthreads();
-        if (t < J) {
+        if (warp == 0) {
             int v = 0;
+            if (lane < J) {
 #pragma unroll
-            for (int wq = 0; wq < HEAD_THREADS / 32; ++wq) v += sRed[wq * HEAD_MAX_CLASSES + t];
-            p.out32[b * J + t] = v;
-            if (v != 0) atomicMax(&umax[0], iabs32(v));
+                for (int wq = 0; wq < HEAD_THREADS / 32; ++wq) v += sRed[wq * HEAD_MAX_CLASSES + lane];
+                p.out32[b * J + lane] = v;
+            }
+            fwd_max = max(fwd_max, __reduce_max_sync(0xFFFFFFFFu, iabs32(v)));
         }
         __syncthreads();
     }
+    if (t == 0 && fwd_max != 0) atomicMax(&umax[0], fwd_max);  // one atomic per block: they serialise at the L2
+    HEAD_STAMP(2);
     if (!bounded_grid_barrier(&p.state[3], G, p.status, 6, sFlag)) return;
 
+    HEAD_STAMP(3);
     // ---- logits to int8, then the loss's error: one warp per sample, one lane per class
     const int exp_w = *p.exp_w;
     {
@@ -197,10 +230,16 @@ __global__ void __launch_bounds__(HEAD_THREADS, 1) fc_head_kernel(const HeadPara
             }
         }
     }
+    HEAD_STAMP(4);
     if (!bounded_grid_barrier(&p.state[3], 2 * G, p.status, 6, sFlag)) return;
+    HEAD_STAMP(5);
 
     // ---- every block needs every sample's error
     for (int i = t; i < B * J; i += HEAD_THREADS) sErr[i] = __ldcg(reinterpret_cast<const signed char*>(p.err8) + i);
+    for (int i = t; i < J * 4 * S; i += HEAD_THREADS) {
+        const int j = i / (4 * S), b = i % (4 * S);
+        sErrT[i] = b < B ? __ldcg(reinterpret_cast<const signed char*>(p.err8) + b * J + j) : int8_t(0);
+    }
     __syncthreads();
 
     // ---- error-backward GEMM, first pass: only max|e32| (the values are recomputed once the shift is known)
@@ -213,42 +252,64 @@ __global__ void __launch_bounds__(HEAD_THREADS, 1) fc_head_kernel(const HeadPara
 #pragma unroll
                 for (int k = 0; k < 16; ++k) m = max(m, iabs32(e[k]));
             }
-        m = __reduce_max_sync(0xFFFFFFFFu, m);
-        if (lane == 0 && m != 0) atomicMax(&umax[1], m);
+        block_max(&umax[1], m, sRed);
     }
-    // ---- weight gradient g32[j][f] = sum_b err8[b][j] * drop(x)[b][f]: a block owns 16-feature chunks;
-    //      thread = (feature of the chunk, one of 16 batch groups), the groups meet in shared memory
-    const int fl = t & 15, bg = t >> 4;
+    HEAD_STAMP(6);
+    // ---- weight gradient g32[j][f] = sum_b err8[b][j] * drop(x)[b][f].  A block owns 16-feature chunks and takes
+    //      four of them (64 features) per pass: thread = (feature, one of 4 batch groups); the loads of a batch of
+    //      samples are issued together, the groups meet in shared memory.
+    const int fq = t & 63, bq = t >> 6;
     {
         unsigned m = 0;
-        for (int c = blockIdx.x; c < F16; c += G) {
+        for (int c0 = blockIdx.x; c0 < F16; c0 += 4 * G) {
+            const int c = c0 + (fq >> 4) * G, fl = fq & 15;
+            const bool live = c < F16;
             const int f = c * 16 + fl;
             int acc[HEAD_MAX_CLASSES];
 #pragma unroll
             for (int j = 0; j < HEAD_MAX_CLASSES; ++j) acc[j] = 0;
-            if ((sMask[c] >> fl) & 1u)
-                for (int b = bg; b < B; b += 16) {
-                    const int xv = p.x[static_cast<size_t>(b) * F + f];
+            if (live && ((sMask[c] >> fl) & 1u)) {
+                // batch group bq takes samples [bq S, bq S + S): four at a time, packed into one word for __dp4a
+                const int8_t* xp = p.x + f;
+                const uint32_t* eT = reinterpret_cast<const uint32_t*>(sErrT);
+#pragma unroll 1
+                for (int b0 = bq * S; b0 < bq * S + S; b0 += 16) {
+                    uint32_t xb[16];  // sixteen loads in flight
 #pragma unroll
-                    for (int j = 0; j < HEAD_MAX_CLASSES; ++j)
-                        if (j < J) acc[j] += xv * static_cast<int>(sErr[b * J + j]);
+                    for (int u = 0; u < 16; ++u) {
+                        const int b = b0 + u;
+                        xb[u] = (b < B && b < bq * S + S) ? static_cast<uint32_t>(static_cast<uint8_t>(__ldg(xp + static_cast<size_t>(b) * F))) : 0u;
+                    }
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        const int b = b0 + 4 * q;
+                        if (b < bq * S + S) {
+                            const int x4 = static_cast<int>(xb[4 * q] | (xb[4 * q + 1] << 8) | (xb[4 * q + 2] << 16) | (xb[4 * q + 3] << 24));
+#pragma unroll
+                            for (int j = 0; j < HEAD_MAX_CLASSES; ++j)
+                                if (j < J) acc[j] = __dp4a(x4, static_cast<int>(eT[j * S + (b >> 2)]), acc[j]);
+                        }
+                    }
                 }
-#pragma unroll
-            for (int j = 0; j < HEAD_MAX_CLASSES; ++j) sRed[(bg * 16 + j) * 16 + fl] = acc[j];
-            __syncthreads();
-            if (bg < J) {  // thread = (feature, class bg)
-                int v = 0;
-#pragma unroll
-                for (int gq = 0; gq < 16; ++gq) v += sRed[(gq * 16 + bg) * 16 + fl];
-                p.g32[static_cast<size_t>(bg) * F + f] = v;
-                m = max(m, iabs32(v));
             }
             __syncthreads();
+#pragma unroll
+            for (int j = 0; j < HEAD_MAX_CLASSES; ++j) sRed[(bq * 16 + j) * 64 + fq] = acc[j];
+            __syncthreads();
+            if (live)
+                for (int j = bq; j < J; j += 4) {  // thread = (feature, classes bq, bq + 4, ...)
+                    int v = 0;
+#pragma unroll
+                    for (int gq = 0; gq < 4; ++gq) v += sRed[(gq * 16 + j) * 64 + fq];
+                    p.g32[static_cast<size_t>(j) * F + f] = v;
+                    m = max(m, iabs32(v));
+                }
         }
-        m = __reduce_max_sync(0xFFFFFFFFu, m);
-        if (lane == 0 && m != 0) atomicMax(&umax[2], m);
+        block_max(&umax[2], m, sRed);
     }
+    HEAD_STAMP(7);
     if (!bounded_grid_barrier(&p.state[3], 3 * G, p.status, 6, sFlag)) return;
+    HEAD_STAMP(8);
 
     // ---- error to the features: recompute, narrow with the tensor-wide shift, apply the dropout bits
     {
@@ -279,28 +340,35 @@ __global__ void __launch_bounds__(HEAD_THREADS, 1) fc_head_kernel(const HeadPara
                 reinterpret_cast<uint4*>(p.e8)[static_cast<size_t>(b) * F16 + c] = o;
             }
     }
+    HEAD_STAMP(9);
     // ---- the update of the weights this block computed the gradient of
     {
         bool zero_out;
         const unsigned mg = __ldcg(&umax[2]);
         if (blockIdx.x == 0 && t == 0) *p.grad_maxabs = mg;
-        if (p.update && bg < J) {
+        if (p.update) {
             const int shift = shift_for(mg, CALC_GRAD, p.mu, &zero_out);
             const int8_t* sWb = reinterpret_cast<const int8_t*>(sW);
-            for (int c = blockIdx.x; c < F16; c += G) {
-                const size_t i = static_cast<size_t>(bg) * F + c * 16 + fl;
-                const uint32_t rnd = (p.grad_mode == ROUND_STOCHASTIC && shift > 0) ? random_word(seed, p.layer_stream + 2, i) : 0u;
-                const int g8 = zero_out ? 0 : narrow(p.g32[i], shift, p.grad_mode, rnd);
-                p.w[i] = static_cast<int8_t>(clamp127(static_cast<int>(sWb[i]) - g8));
+            for (int c0 = blockIdx.x; c0 < F16; c0 += 4 * G) {
+                const int c = c0 + (fq >> 4) * G;
+                if (c >= F16) continue;
+                for (int j = bq; j < J; j += 4) {
+                    const size_t i = static_cast<size_t>(j) * F + c * 16 + (fq & 15);
+                    const uint32_t rnd = (p.grad_mode == ROUND_STOCHASTIC && shift > 0) ? random_word(seed, p.layer_stream + 2, i) : 0u;
+                    const int g8 = zero_out ? 0 : narrow(p.g32[i], shift, p.grad_mode, rnd);
+                    p.w[i] = static_cast<int8_t>(clamp127(static_cast<int>(sWb[i]) - g8));
+                }
             }
         }
     }
+    HEAD_STAMP(10);
 }
 
 size_t head_smem_bytes(int B, int F, int J) {
     size_t off = static_cast<size_t>(J) * F;
     off = (off + 2 * static_cast<size_t>(F / 16) + 15) & ~static_cast<size_t>(15);
     off = (off + static_cast<size_t>(B) * J + 15) & ~static_cast<size_t>(15);
+    off += static_cast<size_t>(J) * 4 * ((((B + 3) >> 2) + 3) & ~3);
     return off + HEAD_RED_INTS * sizeof(int32_t) + 16;
 }
 
@@ -367,7 +435,10 @@ extern "C" int niti_fc_head_train_i8(const niti_fc_head_args* a, void* stream) {
 
     e = cudaMemsetAsync(p.state, 0, 4 * sizeof(int32_t), st);
     if (e != cudaSuccess) return set_cuda_error(e);
-    void* args[] = {&p};
-    e = cudaLaunchCooperativeKernel(reinterpret_cast<const void*>(fc_head_kernel), dim3(grid), dim3(HEAD_THREADS), args, smem, st);
-    return set_cuda_error(e);
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(grid); cfg.blockDim = dim3(HEAD_THREADS); cfg.dynamicSmemBytes = smem; cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeCooperative; attr[0].val.cooperative = g_cooperative;  // the grid is at most one block per SM
+    cfg.attrs = attr; cfg.numAttrs = 1;
+    return set_cuda_error(cudaLaunchKernelEx(&cfg, fc_head_kernel, p));
 }

@@ -25,6 +25,7 @@ struct FusedArgs {
 };
 
 extern int g_two_cta;    // CTA pairs (cta_group::2) where the shape allows: bit 0 for GEMMs, bit 1 for convolutions
+extern int g_cooperative;  // 1: cooperative launches for the kernels with a grid barrier (see umma_kernels.cu)
 extern int g_stage_cap;  // experiments: cap on the shared-memory stages the GEMM / conv kernels use (0 = all)
 
 // tensor-core (tcgen05) paths, umma_kernels.cu; `out` is int32 (fused == null) or int8

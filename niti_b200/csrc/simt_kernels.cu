@@ -38,6 +38,22 @@ __device__ __forceinline__ void warp_atomic_max(unsigned* dst, unsigned v) {
     if ((threadIdx.x & 31) == 0 && v != 0 && dst != nullptr) atomicMax(dst, v);
 }
 
+// Same for a whole block (every thread must call it): atomics on one address serialise at the L2, so a
+// grid-wide maximum costs one atomic per block, not one per warp.
+__device__ __forceinline__ void block_atomic_max(unsigned* dst, unsigned v) {
+    __shared__ unsigned warp_part[32];
+    v = __reduce_max_sync(0xFFFFFFFFu, v);
+    const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
+    if (l == 0) warp_part[w] = v;
+    __syncthreads();
+    if (w == 0) {
+        unsigned x = l < static_cast<int>((blockDim.x + 31) >> 5) ? warp_part[l] : 0u;
+        x = __reduce_max_sync(0xFFFFFFFFu, x);
+        if (l == 0 && x != 0 && dst != nullptr) atomicMax(dst, x);
+    }
+    __syncthreads();
+}
+
 // ------------------------------------------------------------------------------------------------
 // requantisation: int32 -> int8 by the tensor-wide shift
 // ------------------------------------------------------------------------------------------------
@@ -110,7 +126,7 @@ absmax_kernel(const int32_t* __restrict__ acc, long long n, unsigned* maxabs) {
     for (long long i = (groups << 2) + blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n;
          i += static_cast<long long>(gridDim.x) * blockDim.x)
         m = max(m, iabs_u(acc[i]));
-    warp_atomic_max(maxabs, m);
+    block_atomic_max(maxabs, m);
 }
 
 int absmax_i32(const int32_t* acc, long long n, unsigned* maxabs, cudaStream_t st) {
@@ -512,24 +528,52 @@ struct UpdateMultiParams {
     int32_t* state;  // [count] maxima, [UPDATE_MULTI_MAX] barrier arrivals; zero at launch
     int32_t* status;
 };
+__device__ __forceinline__ unsigned absmax4(const int4 v) {
+    return max(max(iabs_u(v.x), iabs_u(v.y)), max(iabs_u(v.z), iabs_u(v.w)));
+}
+__device__ __forceinline__ uint32_t update_word(const int4 gv, const uint32_t wv, const uint32_t (&rnd)[4], int shift, int mode,
+                                                bool zero_out) {
+    const int gx[4] = {gv.x, gv.y, gv.z, gv.w};
+    uint32_t o = 0;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const int g8 = zero_out ? 0 : narrow(gx[j], shift, mode, rnd[j]);
+        const int wj = static_cast<int8_t>(wv >> (8 * j));
+        o |= static_cast<uint32_t>(static_cast<uint8_t>(clamp127(wj - g8))) << (8 * j);
+    }
+    return o;
+}
 __global__ void __launch_bounds__(256)
 update_multi_kernel(const UpdateMultiParams p) {
     __shared__ int flag;
+    __shared__ unsigned block_max[UPDATE_MULTI_MAX];
     const long long tid = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
     const long long nthreads = static_cast<long long>(gridDim.x) * blockDim.x;
     unsigned* umax = reinterpret_cast<unsigned*>(p.state);
+    if (threadIdx.x < UPDATE_MULTI_MAX) block_max[threadIdx.x] = 0;
+    __syncthreads();
+    // ---- per-layer maxima: four independent 16-byte loads in flight per thread; one global atomic per layer and
+    //      block.  The loop over layers stays rolled: code that runs once per launch is paid for in instruction-cache
+    //      misses, not in issue slots.
+#pragma unroll 1
     for (int l = 0; l < p.count; ++l) {
-        const UpdateItem& it = p.item[l];
         unsigned m = 0;
-        const long long groups = it.n >> 2;
-        for (long long g = tid; g < groups; g += nthreads) {
-            const int4 v = reinterpret_cast<const int4*>(it.g32)[g];
-            m = max(max(m, iabs_u(v.x)), max(iabs_u(v.y), max(iabs_u(v.z), iabs_u(v.w))));
+        const int4* g4 = reinterpret_cast<const int4*>(p.item[l].g32);
+        const long long n = p.item[l].n, groups = n >> 2;
+        long long g = tid;
+        for (; g + 3 * nthreads < groups; g += 4 * nthreads) {
+            const int4 v0 = g4[g], v1 = g4[g + nthreads], v2 = g4[g + 2 * nthreads], v3 = g4[g + 3 * nthreads];
+            m = max(max(m, absmax4(v0)), max(absmax4(v1), max(absmax4(v2), absmax4(v3))));
         }
-        for (long long i = (groups << 2) + tid; i < it.n; i += nthreads) m = max(m, iabs_u(it.g32[i]));
-        warp_atomic_max(&umax[l], m);
+        for (; g < groups; g += nthreads) m = max(m, absmax4(g4[g]));
+        for (long long i = (groups << 2) + tid; i < n; i += nthreads) m = max(m, iabs_u(p.item[l].g32[i]));
+        m = __reduce_max_sync(0xFFFFFFFFu, m);
+        if ((threadIdx.x & 31) == 0 && m != 0) atomicMax(&block_max[l], m);
     }
+    __syncthreads();
+    if (threadIdx.x < p.count && block_max[threadIdx.x] != 0) atomicMax(&umax[threadIdx.x], block_max[threadIdx.x]);
     if (!bounded_grid_barrier(&p.state[UPDATE_MULTI_MAX], static_cast<int>(gridDim.x), p.status, 7, &flag)) return;
+    // ---- the updates
     const unsigned long long seed = (p.mode == ROUND_STOCHASTIC) ? *p.seed : 0ull;
     for (int l = 0; l < p.count; ++l) {
         const UpdateItem& it = p.item[l];
@@ -539,20 +583,24 @@ update_multi_kernel(const UpdateMultiParams p) {
         const int shift = shift_for(mx, CALC_GRAD, p.mu, &zero_out);
         const bool stochastic = (p.mode == ROUND_STOCHASTIC) && shift > 0;
         const long long groups = it.n >> 2;
-        for (long long g = tid; g < groups; g += nthreads) {
-            const int4 gv = __ldcs(reinterpret_cast<const int4*>(it.g32) + g);
-            const uint32_t wv = reinterpret_cast<const uint32_t*>(it.w)[g];
+        const int4* g4 = reinterpret_cast<const int4*>(it.g32);
+        uint32_t* w4 = reinterpret_cast<uint32_t*>(it.w);
+        long long g = tid;
+        for (; g + nthreads < groups; g += 2 * nthreads) {  // two groups per iteration: their loads go out together
+            const int4 ga = __ldcs(g4 + g), gb = __ldcs(g4 + g + nthreads);
+            const uint32_t wa = w4[g], wb = w4[g + nthreads];
+            uint32_t ra[4] = {0, 0, 0, 0}, rb[4] = {0, 0, 0, 0};
+            if (stochastic) {
+                random_block(seed, it.rng_stream, static_cast<unsigned long long>(g), ra);
+                random_block(seed, it.rng_stream, static_cast<unsigned long long>(g + nthreads), rb);
+            }
+            w4[g] = update_word(ga, wa, ra, shift, p.mode, zero_out);
+            w4[g + nthreads] = update_word(gb, wb, rb, shift, p.mode, zero_out);
+        }
+        for (; g < groups; g += nthreads) {
             uint32_t rnd[4] = {0, 0, 0, 0};
             if (stochastic) random_block(seed, it.rng_stream, static_cast<unsigned long long>(g), rnd);
-            const int gx[4] = {gv.x, gv.y, gv.z, gv.w};
-            uint32_t o = 0;
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                const int g8 = zero_out ? 0 : narrow(gx[j], shift, p.mode, rnd[j]);
-                const int wj = static_cast<int8_t>(wv >> (8 * j));
-                o |= static_cast<uint32_t>(static_cast<uint8_t>(clamp127(wj - g8))) << (8 * j);
-            }
-            reinterpret_cast<uint32_t*>(it.w)[g] = o;
+            w4[g] = update_word(__ldcs(g4 + g), w4[g], rnd, shift, p.mode, zero_out);
         }
         for (long long i = (groups << 2) + tid; i < it.n; i += nthreads) {
             const uint32_t rnd = stochastic ? random_word(seed, it.rng_stream, static_cast<unsigned long long>(i)) : 0u;
@@ -570,7 +618,7 @@ __global__ void __launch_bounds__(256) absmax_f32_kernel(const float* __restrict
     for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n;
          i += static_cast<long long>(gridDim.x) * blockDim.x)
         m = max(m, __float_as_uint(fabsf(x[i])));
-    warp_atomic_max(bits, m);
+    block_atomic_max(bits, m);
 }
 __global__ void __launch_bounds__(256)
 quantize_input_kernel(const float* __restrict__ x, int8_t* __restrict__ x8, int32_t* exp_out, const unsigned* bits,
@@ -920,7 +968,7 @@ extern "C" int niti_update_multi_i8(const niti_update_item* items, int count, in
     if (blocks_per_sm == 0) {
         int n = 0;
         if (int e = set_cuda_error(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, update_multi_kernel, 256, 0))) return e;
-        blocks_per_sm = n < 1 ? 1 : (n > 4 ? 4 : n);
+        blocks_per_sm = n < 1 ? 1 : (n > 8 ? 8 : n);
     }
     for (int first = 0; first < count; first += UPDATE_MULTI_MAX) {
         UpdateMultiParams p;
@@ -937,10 +985,12 @@ extern "C" int niti_update_multi_i8(const niti_update_item* items, int count, in
         p.status = status;
         if (int e = set_cuda_error(cudaMemsetAsync(scratch, 0, niti_update_multi_scratch_bytes(), st))) return e;
         const int grid = blocks_for(total / 4 + 1, 256, sm_count_simt() * blocks_per_sm);
-        void* args[] = {&p};
-        if (int e = set_cuda_error(cudaLaunchCooperativeKernel(reinterpret_cast<const void*>(update_multi_kernel), dim3(grid),
-                                                               dim3(256), args, 0, st)))
-            return e;
+        cudaLaunchConfig_t cfg{};
+        cfg.gridDim = dim3(grid); cfg.blockDim = dim3(256); cfg.dynamicSmemBytes = 0; cfg.stream = st;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeCooperative; attr[0].val.cooperative = g_cooperative;  // the grid fits in one wave
+        cfg.attrs = attr; cfg.numAttrs = 1;
+        if (int e = set_cuda_error(cudaLaunchKernelEx(&cfg, update_multi_kernel, p))) return e;
     }
     return NITI_OK;
 }

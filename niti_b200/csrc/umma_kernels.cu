@@ -25,6 +25,7 @@
 #include "internal.h"
 #include "ptx.cuh"
 #include "requant.cuh"
+#include "grid_barrier.cuh"
 
 namespace niti {
 
@@ -364,6 +365,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     uint64_t* tempty_bar = bars + 2 * STAGES + 2;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    volatile unsigned* warp_max = reinterpret_cast<volatile unsigned*>(tmem_slot + 4);  // one word per epilogue warp
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -563,12 +565,19 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         const int lo = min(min(vmin[0], vmin[1]), min(vmin[2], vmin[3]));
         unsigned local_max = max(static_cast<unsigned>(hi), static_cast<unsigned>(-static_cast<long long>(lo)));
         local_max = __reduce_max_sync(0xFFFFFFFFu, local_max);
-        if (lane == 0 && local_max != 0 && p.maxabs != nullptr) atomicMax(p.maxabs, local_max);
+        // one atomic per CTA: atomics on one address serialise at the L2, and there are 8 warps x 148 CTAs
+        if (lane == 0) warp_max[warp - 2] = local_max;
+        named_barrier(EPI_BARRIER + 2, 256);
+        if (threadIdx.x == 64) {
+            unsigned m = 0;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) m = max(m, warp_max[i]);
+            if (m != 0 && p.maxabs != nullptr) atomicMax(p.maxabs, m);
+        }
         if (FUSED && !p.only_if_redo) {
             // the CTA that finishes last turns max|acc| into the true shift and checks the prediction
-            __threadfence();
-            named_barrier(EPI_BARRIER + 2, 256);
             if (threadIdx.x == 64) {
+                __threadfence();
                 int32_t* st = p.state;
                 if (atomicAdd(&st[4], 1) == static_cast<int>(gridDim.x) - 1) {
                     __threadfence();
@@ -637,6 +646,7 @@ umma_parked_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
     volatile int* shift_slot = reinterpret_cast<volatile int*>(tmem_slot + 2);
+    volatile unsigned* warp_max = reinterpret_cast<volatile unsigned*>(tmem_slot + 4);  // one word per epilogue warp
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -707,20 +717,24 @@ umma_parked_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
         }
         unsigned local_max = __reduce_max_sync(0xFFFFFFFFu, fold_minmax(vmax, vmin));
         int32_t* st = p.state;
-        if (lane == 0 && local_max != 0) atomicMax(reinterpret_cast<unsigned*>(&st[1]), local_max);
+        if (lane == 0) warp_max[warp - 2] = local_max;
 
-        // ---- grid barrier: every CTA has contributed its maximum
-        __threadfence();
+        // ---- grid barrier: every CTA has contributed its maximum (one atomic each: atomics on one address
+        //      serialise at the L2; the waiters poll with plain acquire loads for the same reason)
         named_barrier(EPI_BARRIER + 2, 256);
         if (threadIdx.x == 64) {
+            unsigned cta_max = 0;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) cta_max = max(cta_max, warp_max[i]);
+            if (cta_max != 0) atomicMax(reinterpret_cast<unsigned*>(&st[1]), cta_max);
+            __threadfence();
             atomicAdd(&st[5], 1);
             const unsigned long long t0 = global_timer_ns();
             bool arrived = false;
             for (unsigned spin = 0;; ++spin) {
-                if (atomicAdd(&st[5], 0) >= static_cast<int>(gridDim.x)) { arrived = true; break; }
+                if (ld_acquire_gpu(&st[5]) >= static_cast<int>(gridDim.x)) { arrived = true; break; }
                 if ((spin & 63) == 63) {
                     if (*abort_flag || global_timer_ns() - t0 > GRID_BARRIER_LIMIT_NS) break;
-                    __nanosleep(200);
                 }
             }
             __threadfence();
@@ -1047,7 +1061,7 @@ static int launch_parked_inst(const CUtensorMap& a, const CUtensorMap& b, const 
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3(grid); cfg.blockDim = dim3(GEMM_THREADS); cfg.dynamicSmemBytes = Cfg::SMEM_BYTES; cfg.stream = st;
     cudaLaunchAttribute attr[2];
-    attr[0].id = cudaLaunchAttributeCooperative; attr[0].val.cooperative = 1;
+    attr[0].id = cudaLaunchAttributeCooperative; attr[0].val.cooperative = g_cooperative;
     attr[1].id = cudaLaunchAttributeClusterDimension;
     attr[1].val.clusterDim.x = 2; attr[1].val.clusterDim.y = 1; attr[1].val.clusterDim.z = 1;
     cfg.attrs = attr; cfg.numAttrs = TWO ? 2 : 1;
@@ -1066,6 +1080,10 @@ static int pick_bn(int m_tiles, int n_cols) {
 }
 
 int g_stage_cap = 0;  // 0: use every compiled stage
+// 1: kernels with a grid barrier are launched cooperatively (the driver guarantees that all their blocks are
+// resident together).  0: plain launches of grids that fit the device in one wave; co-residency then rests on
+// nothing else occupying the SMs, and a barrier that is not met ends in the bounded wait's error status.
+int g_cooperative = 1;
 
 static void set_fused(GemmParams* p, const FusedArgs* f) {
     p->nstages = g_stage_cap;

@@ -104,6 +104,11 @@ def set_accumulator_parking(enabled):
     return bool(lib.niti_set_option(1, int(bool(enabled))))
 
 
+def set_cooperative_launch(enabled):
+    """Cooperative (default) or plain launches for the kernels with a grid barrier; returns the old setting."""
+    return bool(lib.niti_set_option(5, int(bool(enabled))))
+
+
 def set_cta_pairs(mask):
     """CTA pairs (tcgen05 cta_group::2): bit 0 for GEMMs (default on), bit 1 for convolutions (default off);
     True = both, False = none.  Returns the old mask."""
