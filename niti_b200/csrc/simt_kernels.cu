@@ -523,6 +523,7 @@ constexpr int UPDATE_MULTI_MAX = 16;
 struct UpdateItem { int8_t* w; const int32_t* g32; unsigned* maxabs; long long n; unsigned rng_stream; };
 struct UpdateMultiParams {
     UpdateItem item[UPDATE_MULTI_MAX];
+    int first_block[UPDATE_MULTI_MAX + 1];  // layer l is shared by blocks [first_block[l], first_block[l + 1])
     int count, mu, mode;
     const unsigned long long* seed;
     int32_t* state;  // [count] maxima, [UPDATE_MULTI_MAX] barrier arrivals; zero at launch
@@ -543,70 +544,60 @@ __device__ __forceinline__ uint32_t update_word(const int4 gv, const uint32_t wv
     }
     return o;
 }
+// Every block works on ONE layer (blocks are dealt to the layers in proportion to their sizes on the host), so a
+// block has one chain of loads -> maximum -> atomic before the barrier and one read of its layer's maximum after it.
 __global__ void __launch_bounds__(256)
 update_multi_kernel(const UpdateMultiParams p) {
     __shared__ int flag;
-    __shared__ unsigned block_max[UPDATE_MULTI_MAX];
-    const long long tid = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
-    const long long nthreads = static_cast<long long>(gridDim.x) * blockDim.x;
     unsigned* umax = reinterpret_cast<unsigned*>(p.state);
-    if (threadIdx.x < UPDATE_MULTI_MAX) block_max[threadIdx.x] = 0;
-    __syncthreads();
-    // ---- per-layer maxima: four independent 16-byte loads in flight per thread; one global atomic per layer and
-    //      block.  The loop over layers stays rolled: code that runs once per launch is paid for in instruction-cache
-    //      misses, not in issue slots.
-#pragma unroll 1
-    for (int l = 0; l < p.count; ++l) {
+    int l = 0;
+    while (l + 1 < p.count && static_cast<int>(blockIdx.x) >= p.first_block[l + 1]) ++l;
+    const UpdateItem& it = p.item[l];
+    const long long nthreads = static_cast<long long>(p.first_block[l + 1] - p.first_block[l]) * blockDim.x;
+    const long long tid = static_cast<long long>(static_cast<int>(blockIdx.x) - p.first_block[l]) * blockDim.x + threadIdx.x;
+    const long long groups = it.n >> 2;
+    const int4* g4 = reinterpret_cast<const int4*>(it.g32);
+    {   // ---- the layer's maximum: four independent 16-byte loads in flight per thread, one global atomic per block
         unsigned m = 0;
-        const int4* g4 = reinterpret_cast<const int4*>(p.item[l].g32);
-        const long long n = p.item[l].n, groups = n >> 2;
         long long g = tid;
         for (; g + 3 * nthreads < groups; g += 4 * nthreads) {
             const int4 v0 = g4[g], v1 = g4[g + nthreads], v2 = g4[g + 2 * nthreads], v3 = g4[g + 3 * nthreads];
             m = max(max(m, absmax4(v0)), max(absmax4(v1), max(absmax4(v2), absmax4(v3))));
         }
         for (; g < groups; g += nthreads) m = max(m, absmax4(g4[g]));
-        for (long long i = (groups << 2) + tid; i < n; i += nthreads) m = max(m, iabs_u(p.item[l].g32[i]));
-        m = __reduce_max_sync(0xFFFFFFFFu, m);
-        if ((threadIdx.x & 31) == 0 && m != 0) atomicMax(&block_max[l], m);
+        for (long long i = (groups << 2) + tid; i < it.n; i += nthreads) m = max(m, iabs_u(it.g32[i]));
+        block_atomic_max(&umax[l], m);
     }
-    __syncthreads();
-    if (threadIdx.x < p.count && block_max[threadIdx.x] != 0) atomicMax(&umax[threadIdx.x], block_max[threadIdx.x]);
     if (!bounded_grid_barrier(&p.state[UPDATE_MULTI_MAX], static_cast<int>(gridDim.x), p.status, 7, &flag)) return;
-    // ---- the updates
-    const unsigned long long seed = (p.mode == ROUND_STOCHASTIC) ? *p.seed : 0ull;
-    for (int l = 0; l < p.count; ++l) {
-        const UpdateItem& it = p.item[l];
-        const unsigned mx = __ldcg(&umax[l]);
-        if (tid == 0 && it.maxabs != nullptr) *it.maxabs = mx;
-        bool zero_out;
-        const int shift = shift_for(mx, CALC_GRAD, p.mu, &zero_out);
-        const bool stochastic = (p.mode == ROUND_STOCHASTIC) && shift > 0;
-        const long long groups = it.n >> 2;
-        const int4* g4 = reinterpret_cast<const int4*>(it.g32);
-        uint32_t* w4 = reinterpret_cast<uint32_t*>(it.w);
-        long long g = tid;
-        for (; g + nthreads < groups; g += 2 * nthreads) {  // two groups per iteration: their loads go out together
-            const int4 ga = __ldcs(g4 + g), gb = __ldcs(g4 + g + nthreads);
-            const uint32_t wa = w4[g], wb = w4[g + nthreads];
-            uint32_t ra[4] = {0, 0, 0, 0}, rb[4] = {0, 0, 0, 0};
-            if (stochastic) {
-                random_block(seed, it.rng_stream, static_cast<unsigned long long>(g), ra);
-                random_block(seed, it.rng_stream, static_cast<unsigned long long>(g + nthreads), rb);
-            }
-            w4[g] = update_word(ga, wa, ra, shift, p.mode, zero_out);
-            w4[g + nthreads] = update_word(gb, wb, rb, shift, p.mode, zero_out);
+    // ---- the update
+    const unsigned mx = __ldcg(&umax[l]);
+    if (tid == 0 && it.maxabs != nullptr) *it.maxabs = mx;
+    bool zero_out;
+    const int shift = shift_for(mx, CALC_GRAD, p.mu, &zero_out);
+    const bool stochastic = (p.mode == ROUND_STOCHASTIC) && shift > 0;
+    const unsigned long long seed = stochastic ? *p.seed : 0ull;
+    uint32_t* w4 = reinterpret_cast<uint32_t*>(it.w);
+    long long g = tid;
+    for (; g + nthreads < groups; g += 2 * nthreads) {  // two groups per iteration: their loads go out together
+        const int4 ga = __ldcs(g4 + g), gb = __ldcs(g4 + g + nthreads);
+        const uint32_t wa = w4[g], wb = w4[g + nthreads];
+        uint32_t ra[4] = {0, 0, 0, 0}, rb[4] = {0, 0, 0, 0};
+        if (stochastic) {
+            random_block(seed, it.rng_stream, static_cast<unsigned long long>(g), ra);
+            random_block(seed, it.rng_stream, static_cast<unsigned long long>(g + nthreads), rb);
         }
-        for (; g < groups; g += nthreads) {
-            uint32_t rnd[4] = {0, 0, 0, 0};
-            if (stochastic) random_block(seed, it.rng_stream, static_cast<unsigned long long>(g), rnd);
-            w4[g] = update_word(__ldcs(g4 + g), w4[g], rnd, shift, p.mode, zero_out);
-        }
-        for (long long i = (groups << 2) + tid; i < it.n; i += nthreads) {
-            const uint32_t rnd = stochastic ? random_word(seed, it.rng_stream, static_cast<unsigned long long>(i)) : 0u;
-            const int g8 = zero_out ? 0 : narrow(it.g32[i], shift, p.mode, rnd);
-            it.w[i] = static_cast<int8_t>(clamp127(static_cast<int>(it.w[i]) - g8));
-        }
+        w4[g] = update_word(ga, wa, ra, shift, p.mode, zero_out);
+        w4[g + nthreads] = update_word(gb, wb, rb, shift, p.mode, zero_out);
+    }
+    for (; g < groups; g += nthreads) {
+        uint32_t rnd[4] = {0, 0, 0, 0};
+        if (stochastic) random_block(seed, it.rng_stream, static_cast<unsigned long long>(g), rnd);
+        w4[g] = update_word(__ldcs(g4 + g), w4[g], rnd, shift, p.mode, zero_out);
+    }
+    for (long long i = (groups << 2) + tid; i < it.n; i += nthreads) {
+        const uint32_t rnd = stochastic ? random_word(seed, it.rng_stream, static_cast<unsigned long long>(i)) : 0u;
+        const int g8 = zero_out ? 0 : narrow(it.g32[i], shift, p.mode, rnd);
+        it.w[i] = static_cast<int8_t>(clamp127(static_cast<int>(it.w[i]) - g8));
     }
 }
 
@@ -984,7 +975,18 @@ extern "C" int niti_update_multi_i8(const niti_update_item* items, int count, in
         p.state = static_cast<int32_t*>(scratch);
         p.status = status;
         if (int e = set_cuda_error(cudaMemsetAsync(scratch, 0, niti_update_multi_scratch_bytes(), st))) return e;
-        const int grid = blocks_for(total / 4 + 1, 256, sm_count_simt() * blocks_per_sm);
+        // deal the blocks of one resident wave to the layers in proportion to their sizes (at least one each)
+        const int wave = sm_count_simt() * blocks_per_sm;
+        int grid = 0;
+        for (int i = 0; i < p.count; ++i) {
+            long long share = (static_cast<long long>(wave - p.count) * p.item[i].n) / (total > 0 ? total : 1);
+            const long long useful = (p.item[i].n / 4 + 255) / 256;  // a block per 256 word groups is as fine as it gets
+            if (share > useful - 1) share = useful - 1;
+            if (share < 0) share = 0;
+            p.first_block[i] = grid;
+            grid += 1 + static_cast<int>(share);
+        }
+        p.first_block[p.count] = grid;
         cudaLaunchConfig_t cfg{};
         cfg.gridDim = dim3(grid); cfg.blockDim = dim3(256); cfg.dynamicSmemBytes = 0; cfg.stream = st;
         cudaLaunchAttribute attr[1];

@@ -311,6 +311,71 @@ __device__ __forceinline__ unsigned fold_minmax(const int (&vmax)[4], const int 
     const int lo = min(min(vmin[0], vmin[1]), min(vmin[2], vmin[3]));
     return max(static_cast<unsigned>(hi), static_cast<unsigned>(-static_cast<long long>(lo)));
 }
+// The same two steps on 32 accumulators at a time, for epilogues that run once or twice per launch: there
+// every instruction is fetched cold, so a rolled loop over four 32-column chunks (a quarter of the code, the
+// last three trips from the instruction cache) beats the straight-line 128-column form.
+__device__ __forceinline__ void minmax32(const uint32_t (&v)[32], int lim, int (&vmax)[4], int (&vmin)[4]) {
+    if (lim >= 32) {
+#pragma unroll
+        for (int i = 0; i < 32; i += 4) {
+            vmax[0] = __vimax3_s32(vmax[0], static_cast<int>(v[i]), static_cast<int>(v[i + 1]));
+            vmin[0] = __vimin3_s32(vmin[0], static_cast<int>(v[i]), static_cast<int>(v[i + 1]));
+            vmax[1] = __vimax3_s32(vmax[1], static_cast<int>(v[i + 2]), static_cast<int>(v[i + 3]));
+            vmin[1] = __vimin3_s32(vmin[1], static_cast<int>(v[i + 2]), static_cast<int>(v[i + 3]));
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < 32; ++i)
+            if (i < lim) {
+                vmax[0] = max(vmax[0], static_cast<int>(v[i]));
+                vmin[0] = min(vmin[0], static_cast<int>(v[i]));
+            }
+    }
+}
+__device__ __forceinline__ void narrow32(const uint32_t (&v)[32], uint32_t (&packed)[8], int shift, int mode, int relu,
+                                         unsigned long long seed, unsigned rng_stream, unsigned long long e0) {
+    if (mode == ROUND_NEAREST && shift > 0) {
+        const int half = 1 << (shift - 1);
+        if (relu) {
+#pragma unroll
+            for (int i = 0; i < 32; i += 4) packed[i >> 2] = narrow4_nearest<true>(&v[i], shift, half);
+        } else {
+#pragma unroll
+            for (int i = 0; i < 32; i += 4) packed[i >> 2] = narrow4_nearest<false>(&v[i], shift, half);
+        }
+    } else {
+        const bool stochastic = mode == ROUND_STOCHASTIC && shift > 0;
+#pragma unroll 1
+        for (int i = 0; i < 32; i += 4) {
+            uint32_t rnd[4] = {0, 0, 0, 0};
+            if (stochastic) {
+                const unsigned long long e = e0 + i;
+                if ((e & 3ull) == 0) random_block(seed, rng_stream, e >> 2, rnd);
+                else {
+#pragma unroll
+                    for (int t = 0; t < 4; ++t) rnd[t] = random_word(seed, rng_stream, e + t);
+                }
+            }
+            uint32_t x[4];
+            // select without dynamic register indexing
+#pragma unroll
+            for (int t = 0; t < 4; ++t) {
+                x[t] = v[t];
+#pragma unroll
+                for (int k = 4; k < 32; k += 4) x[t] = (i == k) ? v[k + t] : x[t];
+            }
+            const uint32_t w = narrow4(x, shift, mode, relu, rnd);
+#pragma unroll
+            for (int k = 0; k < 8; ++k) if (i == 4 * k) packed[k] = w;
+        }
+    }
+}
+// a 32-byte piece (chunk j of the row's 128 bytes) at its 128-byte-swizzled place in the staging tile
+__device__ __forceinline__ void stage_piece(uint32_t buf, int row, int j, const uint32_t (&w)[8]) {
+    const uint32_t base = buf + static_cast<uint32_t>(row) * 128u;
+    st_shared_v4(base + (static_cast<uint32_t>((2 * j) ^ (row & 7)) << 4), w[0], w[1], w[2], w[3]);
+    st_shared_v4(base + (static_cast<uint32_t>((2 * j + 1) ^ (row & 7)) << 4), w[4], w[5], w[6], w[7]);
+}
 // 128 accumulators of one row -> 32 words of packed int8
 __device__ __forceinline__ void narrow_row(const uint32_t (&v)[4][32], uint32_t (&packed)[32], int shift, int mode, int relu,
                                            unsigned long long seed, unsigned rng_stream, unsigned long long e0) {
@@ -709,11 +774,15 @@ umma_parked_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
             const RowInfo ri = row_info(p, m_t, tile / mn_tiles, row_in_tile);
             const int col = n_t * BN + g0;
             if (col >= p.N) continue;
-            uint32_t v[4][32];
-#pragma unroll
-            for (int j = 0; j < 4; ++j) tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + it * BN + g0 + j * 32, v[j]);
-            tmem_ld_wait();
-            if (ri.valid) track_minmax(v, p.N - col, vmax, vmin);
+            const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + it * BN + g0;
+#pragma unroll 1
+            for (int j = 0; j < 4; ++j) {
+                if (col + 32 * j >= p.N) break;
+                uint32_t v[32];
+                tmem_ld_32x32(taddr + j * 32, v);
+                tmem_ld_wait();
+                if (ri.valid) minmax32(v, p.N - col - 32 * j, vmax, vmin);
+            }
         }
         unsigned local_max = __reduce_max_sync(0xFFFFFFFFu, fold_minmax(vmax, vmin));
         int32_t* st = p.state;
@@ -758,16 +827,19 @@ umma_parked_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
                 const RowInfo ri = row_info(p, m_t, tile / mn_tiles, row_in_tile);
                 const int col = n_t * BN + g0;
                 if (col >= p.N) continue;
-                uint32_t v[4][32];
-#pragma unroll
-                for (int j = 0; j < 4; ++j) tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + it * BN + g0 + j * 32, v[j]);
-                tmem_ld_wait();
-                uint32_t packed[32];
-                narrow_row(v, packed, shift, p.mode, p.relu, seed, p.rng_stream,
-                           p.rng_offset + static_cast<unsigned long long>(ri.row_lin) * p.N + col);
-                if (leader) bulk_wait_read<0>();
+                const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + it * BN + g0;
+                const unsigned long long e0 = p.rng_offset + static_cast<unsigned long long>(ri.row_lin) * p.N + col;
+                if (leader) bulk_wait_read<0>();  // the previous store has read the staging tile
                 named_barrier(bar_id, 128);
-                stage_row(buf, row_in_tile, packed);
+#pragma unroll 1
+                for (int j = 0; j < 4; ++j) {
+                    if (col + 32 * j >= p.N) break;  // the store clips these columns
+                    uint32_t v[32], packed[8];
+                    tmem_ld_32x32(taddr + j * 32, v);
+                    tmem_ld_wait();
+                    narrow32(v, packed, shift, p.mode, p.relu, seed, p.rng_stream, e0 + 32 * j);
+                    stage_piece(buf, row_in_tile, j, packed);
+                }
                 fence_proxy_async();
                 named_barrier(bar_id, 128);
                 if (leader) { tma_store_4d(&tmC, buf, col, ri.cy, ri.cz, ri.cw); bulk_commit(); }
