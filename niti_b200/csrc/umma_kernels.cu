@@ -28,6 +28,12 @@
 #include "grid_barrier.cuh"
 
 namespace niti {
+#ifdef NITI_PARKED_TIMING
+__device__ unsigned long long g_dbg_stamps[32];
+#define PARK_STAMP(i) do { if (blockIdx.x == 0) g_dbg_stamps[i] = global_timer_ns(); } while (0)
+#else
+#define PARK_STAMP(i) do { } while (0)
+#endif
 
 constexpr int BLOCK_M = 128;
 constexpr int ROW_BYTES = 128;               // bytes per shared-memory row of an operand tile
@@ -238,6 +244,7 @@ __device__ __forceinline__ void mma_role(uint8_t* smem, uint64_t* full_bar, uint
         const int kb_hi = static_cast<int>(static_cast<long long>(split + 1) * p.num_kb / p.splits);
         for (int kb = kb_lo; kb < kb_hi; ++kb) {
             if (!mbar_wait(smem_u32(&full_bar[s]), ph, abort_flag)) { ok = false; report_abort(p.status, 3, 1); break; }
+            if (PARKED && it == 0 && kb == kb_lo) PARK_STAMP(2);
             tc_fence_after();
             const uint32_t sa = smem_u32(smem + s * STAGE_BYTES);
             const uint32_t sb = sa + PANEL_BYTES;
@@ -264,6 +271,7 @@ __device__ __forceinline__ void mma_role(uint8_t* smem, uint64_t* full_bar, uint
         }
         if (ok) { if (TWO) umma_commit_pair(smem_u32(&tfull_bar[acc])); else umma_commit(smem_u32(&tfull_bar[acc])); }
     }
+    if (PARKED) PARK_STAMP(3);
 }
 
 // Output row of an epilogue thread: validity, TMA store coordinates of its tile, linear row index.
@@ -460,11 +468,15 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     const int cta_first = TWO ? static_cast<int>(blockIdx.x >> 1) : static_cast<int>(blockIdx.x);
     const int cta_step = TWO ? static_cast<int>(gridDim.x >> 1) : static_cast<int>(gridDim.x);
 
+    // Only one lane of warps 0 and 1 works; the others wait at __syncwarp so that each warp reaches the
+    // block-wide barrier of the teardown converged (an aligned barrier executed by a diverged warp is undefined).
     if (warp == 0) {
         if (lane == 0) producer_role<BN, STAGES, Cfg::STAGE_BYTES, TWO>(smem, full_bar, empty_bar, &tmA, &tmB, p, abort_flag);
+        __syncwarp();
     } else if (warp == 1) {
         if (lane == 0 && rank == 0)
             mma_role<BN, STAGES, Cfg::STAGE_BYTES, false, TWO>(smem, full_bar, empty_bar, tfull_bar, tempty_bar, tmem_base, p, abort_flag);
+        __syncwarp();
     } else {
         // ------------------------------------------------------------------ epilogue (2 x 4 warps)
         // Two warpgroups.  With several tiles per CTA they alternate tiles (warpgroup g owns
@@ -625,7 +637,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                     }
             }
         }
-        if (leader) bulk_wait<0>();
+        if (leader) bulk_wait_read<0>();  // shared memory may go once the stores have read it; the writes land by the end of the grid
         const int hi = max(max(vmax[0], vmax[1]), max(vmax[2], vmax[3]));
         const int lo = min(min(vmin[0], vmin[1]), min(vmin[2], vmin[3]));
         unsigned local_max = max(static_cast<unsigned>(hi), static_cast<unsigned>(-static_cast<long long>(lo)));
@@ -701,6 +713,7 @@ umma_parked_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
                    const __grid_constant__ CUtensorMap tmC, const GemmParams p) {
     using Cfg = ParkedCfg<BN, TWO>;
     constexpr int STAGES = Cfg::STAGES;
+    if (threadIdx.x == 0) PARK_STAMP(0);
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* epi_smem = smem + STAGES * Cfg::STAGE_BYTES;
@@ -735,6 +748,7 @@ umma_parked_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
     if (TWO) cluster_sync_all();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    if (threadIdx.x == 0) PARK_STAMP(1);
 
     const int mn_tiles = p.m_tiles * p.n_tiles;  // TWO: m_tiles counts 256-row tiles of the pair
     const int total_tiles = mn_tiles * p.splits;
@@ -743,9 +757,11 @@ umma_parked_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
 
     if (warp == 0) {
         if (lane == 0) producer_role<BN, STAGES, Cfg::STAGE_BYTES, TWO>(smem, full_bar, empty_bar, &tmA, &tmB, p, abort_flag);
+        __syncwarp();  // reach the teardown's block-wide barrier as a converged warp
     } else if (warp == 1) {
         if (lane == 0 && rank == 0)
             mma_role<BN, STAGES, Cfg::STAGE_BYTES, true, TWO>(smem, full_bar, empty_bar, tfull_bar, nullptr, tmem_base, p, abort_flag);
+        __syncwarp();
     } else {
         // Work units of the epilogue: (tile of this CTA, 128-column group); the two warpgroups take
         // alternate units, the same ones in both passes.
@@ -768,6 +784,7 @@ umma_parked_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
             const int tile = cta_first + it * cta_step;
             const uint32_t failed = mbar_wait(smem_u32(&tfull_bar[it]), 0, abort_flag) ? 0u : 1u;
             if (barrier_or(bar_id, 128, failed)) { if (failed) report_abort(p.status, 4, 2); ok = false; break; }
+            if (threadIdx.x == 64 && u == 0) PARK_STAMP(4);
             tc_fence_after();
             const int mn = tile % mn_tiles, n_t = mn % p.n_tiles;
             const int m_t = TWO ? 2 * (mn / p.n_tiles) + static_cast<int>(rank) : mn / p.n_tiles;
@@ -787,6 +804,7 @@ umma_parked_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
         unsigned local_max = __reduce_max_sync(0xFFFFFFFFu, fold_minmax(vmax, vmin));
         int32_t* st = p.state;
         if (lane == 0) warp_max[warp - 2] = local_max;
+        if (threadIdx.x == 64) PARK_STAMP(5);
 
         // ---- grid barrier: every CTA has contributed its maximum (one atomic each: atomics on one address
         //      serialise at the L2; the waiters poll with plain acquire loads for the same reason)
@@ -814,6 +832,7 @@ umma_parked_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
         }
         named_barrier(EPI_BARRIER + 2, 256);
         const int shift = *shift_slot;
+        if (threadIdx.x == 64) PARK_STAMP(6);
 
         // ---- pass 2: narrow the parked accumulators with the true shift
         if (ok && shift >= 0) {
@@ -844,8 +863,9 @@ umma_parked_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
                 named_barrier(bar_id, 128);
                 if (leader) { tma_store_4d(&tmC, buf, col, ri.cy, ri.cz, ri.cw); bulk_commit(); }
             }
-            if (leader) bulk_wait<0>();
+            if (leader) bulk_wait_read<0>();
         }
+        if (threadIdx.x == 64) PARK_STAMP(7);
         // ---- the CTA that leaves last publishes the shift and clears the words for the next call
         named_barrier(EPI_BARRIER + 2, 256);
         if (threadIdx.x == 64) {
@@ -861,6 +881,7 @@ umma_parked_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
 
     tc_fence_before();
     __syncthreads();
+    if (threadIdx.x == 0) PARK_STAMP(8);
     if (TWO) cluster_sync_all();
     if (warp == 1) {
         if (*abort_flag) __nanosleep(200000);
@@ -869,6 +890,13 @@ umma_parked_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
         if (TWO) tmem_dealloc_pair(tmem_base, 512); else tmem_dealloc(tmem_base, 512);
     }
 }
+#ifdef NITI_PARKED_TIMING
+}  // namespace niti
+extern "C" __attribute__((visibility("default"))) int niti_debug_stamps(unsigned long long* out) {
+    return cudaMemcpyFromSymbol(out, niti::g_dbg_stamps, sizeof(niti::g_dbg_stamps)) == cudaSuccess ? 0 : -3;
+}
+namespace niti {
+#endif
 
 // ------------------------------------------------------------------------------------------------
 // Convolution weight gradient: g[k][r][s][c] = sum_pixels err[pixel][k] * x[pixel + (r,s) - pad][c]
@@ -899,6 +927,7 @@ constexpr int WG_TMEM_COLS = 512;
 __global__ void __launch_bounds__(UMMA_THREADS, 1)
 umma_wgrad_kernel(const __grid_constant__ CUtensorMap tmErr, const __grid_constant__ CUtensorMap tmX,
                   const __grid_constant__ CUtensorMap tmP, const WgradParams p) {
+    if (threadIdx.x == 0 && blockIdx.y == 0) PARK_STAMP(10);
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + WG_STAGES * WG_STAGE_BYTES);
@@ -913,7 +942,7 @@ umma_wgrad_kernel(const __grid_constant__ CUtensorMap tmErr, const __grid_consta
 
     // Rows past the box (when a tile holds fewer than 128 pixels) are read by the MMA as part of
     // the reduction: they must be zero.  TMA only ever writes the first box_bytes of a panel.
-    {
+    if ((p.box_bytes / ROW_BYTES) % 32 != 0) {  // full 32-row slabs leave nothing unwritten for the MMAs to read
         int4* z = reinterpret_cast<int4*>(smem);
         for (int i = threadIdx.x; i < WG_STAGES * WG_STAGE_BYTES / 16; i += UMMA_THREADS) z[i] = make_int4(0, 0, 0, 0);
     }
@@ -932,6 +961,7 @@ umma_wgrad_kernel(const __grid_constant__ CUtensorMap tmErr, const __grid_consta
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    if (threadIdx.x == 0 && blockIdx.y == 0) PARK_STAMP(11);
 
     const int split = blockIdx.x;
     const int item = blockIdx.y;
@@ -956,16 +986,30 @@ umma_wgrad_kernel(const __grid_constant__ CUtensorMap tmErr, const __grid_consta
                 if (++s == WG_STAGES) { s = 0; ph ^= 1u; }
             }
         }
+        __syncwarp();  // reach the teardown's block-wide barrier as a converged warp
     } else if (warp == 1) {
         if (lane == 0) {
             const uint32_t idesc = make_idesc_i8(BLOCK_M, 128, 1, 1);
+            const uint32_t idesc2 = make_idesc_i8(BLOCK_M, 256, 1, 1);
             int s = 0; uint32_t ph = 0; bool ok = true;
             for (int ch = chunk_lo; ch < chunk_hi; ++ch) {
                 if (!mbar_wait(smem_u32(&full_bar[s]), ph, abort_flag)) { ok = false; report_abort(p.status, 13, 1); break; }
+                if (ch == chunk_lo && blockIdx.y == 0) PARK_STAMP(12);
                 tc_fence_after();
                 const uint32_t sa = smem_u32(smem + s * WG_STAGE_BYTES);
                 const uint64_t a0 = make_smem_desc(sa, PANEL_BYTES, 1024, SWIZZLE_128B_CODE);
-                for (int sx = 0; sx < p.S; ++sx) {
+                // The taps' x tiles lie one panel apart, which is exactly the layout of an MN-major B operand of
+                // two 128-column panels: two taps go through ONE 256-column MMA (wide MMAs use the tensor pipe
+                // better: measured ~217 cycles for N = 256 against ~146 for N = 128), accumulating into the
+                // adjacent TMEM column blocks of the two taps.
+                int sx = 0;
+                for (; sx + 1 < p.S; sx += 2) {
+                    const uint64_t b0 = make_smem_desc(sa + (1 + sx) * PANEL_BYTES, PANEL_BYTES, 1024, SWIZZLE_128B_CODE);
+                    for (int k = 0; k < p.mma_per_chunk; ++k)
+                        umma_i8(tmem_base + sx * 128, desc_advance(a0, k * 32u * ROW_BYTES), desc_advance(b0, k * 32u * ROW_BYTES),
+                                idesc2, static_cast<uint32_t>(ch != chunk_lo || k != 0));
+                }
+                for (; sx < p.S; ++sx) {
                     const uint64_t b0 = make_smem_desc(sa + (1 + sx) * PANEL_BYTES, PANEL_BYTES, 1024, SWIZZLE_128B_CODE);
                     for (int k = 0; k < p.mma_per_chunk; ++k)
                         umma_i8(tmem_base + sx * 128, desc_advance(a0, k * 32u * ROW_BYTES), desc_advance(b0, k * 32u * ROW_BYTES),
@@ -975,7 +1019,9 @@ umma_wgrad_kernel(const __grid_constant__ CUtensorMap tmErr, const __grid_consta
                 if (++s == WG_STAGES) { s = 0; ph ^= 1u; }
             }
             if (ok) umma_commit(smem_u32(&tfull_bar[0]));
+            if (blockIdx.y == 0) PARK_STAMP(13);
         }
+        __syncwarp();
     } else {
         // partial[split][k][r][s][c] viewed as a rank-4 tensor (c, r*S+s, k, split): per tap, four TMA
         // stores of 128 k-rows x 32 channels.  Once the last MMA has completed the operand stages
@@ -989,6 +1035,7 @@ umma_wgrad_kernel(const __grid_constant__ CUtensorMap tmErr, const __grid_consta
             if (failed) report_abort(p.status, 14, 2);
         } else {
             tc_fence_after();
+            if (leader && blockIdx.y == 0) PARK_STAMP(14);
             for (int sx = 0; sx < p.S; ++sx) {
                 const uint32_t buf = smem_u32(smem + sx * WG_STAGE_BYTES);
                 uint32_t v[4][32];
@@ -1009,7 +1056,9 @@ umma_wgrad_kernel(const __grid_constant__ CUtensorMap tmErr, const __grid_consta
                     bulk_commit();
                 }
             }
-            if (leader) bulk_wait<0>();
+            if (leader && blockIdx.y == 0) PARK_STAMP(15);
+            if (leader) bulk_wait_read<0>();
+            if (leader && blockIdx.y == 0) PARK_STAMP(16);
         }
     }
 
@@ -1283,7 +1332,7 @@ static void wgrad_plan(int Nimg, int H, int W, int C, int K, int R, int max_spli
     p->chunks = p->tiles_w * p->tiles_h * p->tiles_n;
     p->k_tiles = (K + 127) / 128; p->c_tiles = (C + 127) / 128;
     const int items = R * p->k_tiles * p->c_tiles;
-    int splits = (sm_count() + items / 2) / items;
+    int splits = sm_count() / items;  // never more CTAs than SMs: a second wave of a few CTAs would double the time
     if (splits < 1) splits = 1;
     if (splits > p->chunks) splits = p->chunks;
     if (max_splits > 0 && splits > max_splits) splits = max_splits;
