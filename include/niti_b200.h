@@ -127,6 +127,13 @@ NITI_API int niti_conv_wgrad_i8(const int8_t* x, const int8_t* err, int32_t* g32
                        void* scratch, size_t scratch_bytes,
                        int N, int H, int W, int C, int K, int R, int S, int pad,
                        int32_t* status, void* stream);
+/* The same contraction ADDED into g32: g32 += sum err * x, with no clearing pass, no scratch and no maximum.
+ * The caller has zeroed g32 (niti_update_multi_i8 with clear_gradients does) or keeps the gradient of earlier
+ * micro-batches in it.  Tensor-core shapes only (niti_conv_wgrad_accumulate_supported); x, err, g32 16-byte aligned. */
+NITI_API int niti_conv_wgrad_accumulate_supported(int C, int K, int R, int S, int pad);
+NITI_API int niti_conv_wgrad_accumulate_i8(const int8_t* x, const int8_t* err, int32_t* g32,
+                                  int N, int H, int W, int C, int K, int R, int S, int pad,
+                                  int32_t* status, void* stream);
 
 /* niti_conv_wgrad_i8 for callers that cannot hand over scratch memory.  This entry point has no
  * counterpart in the reference.  Some hosts of this library are not able to call cudaMalloc at all:
@@ -249,13 +256,15 @@ NITI_API int niti_update_i8(int8_t* w, const int32_t* g32, const uint32_t* maxab
 /* Every weighted layer's update in one (cooperative) launch: for each item max |g32| is found, written to
  * *maxabs when that is not null, and w updated exactly as niti_update_i8 would with that maximum and the
  * item's rng_stream.  scratch: niti_update_multi_scratch_bytes() bytes.  status as in niti_fc_head_train_i8
- * (code 7).  No counterpart in the reference, which updates layer by layer (ti_torch.py:16-21). */
+ * (code 7).  clear_gradients != 0 also zeroes every g32 after use, which is what niti_conv_wgrad_accumulate_i8
+ * wants to find at the next step.  No counterpart in the reference, which updates layer by layer
+ * (ti_torch.py:16-21). */
 typedef struct niti_update_item {
-    int8_t* w; const int32_t* g32; uint32_t* maxabs; int64_t n; uint32_t rng_stream;
+    int8_t* w; int32_t* g32; uint32_t* maxabs; int64_t n; uint32_t rng_stream;
 } niti_update_item;
 NITI_API size_t niti_update_multi_scratch_bytes(void);
-NITI_API int niti_update_multi_i8(const niti_update_item* items, int count, int mu, int round_mode, const uint64_t* seed,
-                         void* scratch, size_t scratch_bytes, int32_t* status, void* stream);
+NITI_API int niti_update_multi_i8(const niti_update_item* items, int count, int mu, int round_mode, int clear_gradients,
+                         const uint64_t* seed, void* scratch, size_t scratch_bytes, int32_t* status, void* stream);
 
 /* The classifier head of a training step in one (cooperative) kernel: TiDropout.forward
  * (ti_torch.py:439-455), TiLinear.forward (:241-253), TiLoss.forward (ti_loss.py:6-36), TiLinear.backward

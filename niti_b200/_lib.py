@@ -46,7 +46,9 @@ SIGNATURES = {
     "niti_update_i8": (_i, [_p, _p, _p, _i64, _i, _i, _p, _u32, _p]),
     "niti_quantize_input_f32": (_i, [_p, _p, _p, _p, _i, _i, _i, _i, _p]),
     "niti_update_multi_scratch_bytes": (_sz, []),
-    "niti_update_multi_i8": (_i, [_p, _i, _i, _i, _p, _p, _sz, _p, _p]),
+    "niti_update_multi_i8": (_i, [_p, _i, _i, _i, _i, _p, _p, _sz, _p, _p]),
+    "niti_conv_wgrad_accumulate_supported": (_i, [_i] * 5),
+    "niti_conv_wgrad_accumulate_i8": (_i, [_p, _p, _p] + [_i] * 8 + [_p, _p]),
     "niti_fc_head_supported": (_i, [_i, _i, _i]),
     "niti_fc_head_scratch_bytes": (_sz, [_i, _i, _i]),
     "niti_fc_head_train_i8": (_i, [_p, _p]),

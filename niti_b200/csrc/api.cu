@@ -169,6 +169,20 @@ extern "C" int niti_conv_wgrad_i8(const int8_t* x, const int8_t* err, int32_t* g
     return reduce_rows32(partial, splits, K, R * S * C, g32, maxabs, st);
 }
 
+extern "C" int niti_conv_wgrad_accumulate_supported(int C, int K, int R, int S, int pad) {
+    return wgrad_path(C, K, R, S, pad) == CONV_TC ? 1 : 0;
+}
+
+extern "C" int niti_conv_wgrad_accumulate_i8(const int8_t* x, const int8_t* err, int32_t* g32, int N, int H, int W, int C, int K,
+                                             int R, int S, int pad, int32_t* status, void* stream) {
+    NITI_REQUIRE(x && err && g32 && N > 0 && H > 0 && W > 0 && C > 0 && K > 0 && R > 0 && S > 0 && pad >= 0);
+    NITI_REQUIRE(aligned16(g32) && aligned16(x) && aligned16(err));
+    if (H + 2 * pad - R + 1 <= 0 || W + 2 * pad - S + 1 <= 0) return NITI_ERR_BAD_ARG;
+    if (wgrad_path(C, K, R, S, pad) != CONV_TC) return NITI_ERR_UNSUPPORTED;
+    int splits = 0;
+    return umma_conv_wgrad_partials(x, err, g32, &splits, 0, N, H, W, C, K, R, S, pad, status, static_cast<cudaStream_t>(stream), 1);
+}
+
 extern "C" int niti_gemm_i8(const int8_t* A, const int8_t* B, int32_t* C32, uint32_t* maxabs, int M, int N, int K,
                             int trans_a, int trans_b, int32_t* status, void* stream) {
     NITI_REQUIRE(A && B && C32 && maxabs && M > 0 && N > 0 && K > 0);

@@ -520,11 +520,11 @@ update_kernel(int8_t* __restrict__ w, const int32_t* __restrict__ g32, const uns
 // All weighted layers of a step in one cooperative launch: max|g32| of every layer, a grid barrier, then
 // every layer's update with its own shift.  The second read of the gradients comes from L2.
 constexpr int UPDATE_MULTI_MAX = 16;
-struct UpdateItem { int8_t* w; const int32_t* g32; unsigned* maxabs; long long n; unsigned rng_stream; };
+struct UpdateItem { int8_t* w; int32_t* g32; unsigned* maxabs; long long n; unsigned rng_stream; };
 struct UpdateMultiParams {
     UpdateItem item[UPDATE_MULTI_MAX];
     int first_block[UPDATE_MULTI_MAX + 1];  // layer l is shared by blocks [first_block[l], first_block[l + 1])
-    int count, mu, mode;
+    int count, mu, mode, clear;
     const unsigned long long* seed;
     int32_t* state;  // [count] maxima, [UPDATE_MULTI_MAX] barrier arrivals; zero at launch
     int32_t* status;
@@ -588,16 +588,22 @@ update_multi_kernel(const UpdateMultiParams p) {
         }
         w4[g] = update_word(ga, wa, ra, shift, p.mode, zero_out);
         w4[g + nthreads] = update_word(gb, wb, rb, shift, p.mode, zero_out);
+        if (p.clear) {
+            reinterpret_cast<int4*>(it.g32)[g] = make_int4(0, 0, 0, 0);
+            reinterpret_cast<int4*>(it.g32)[g + nthreads] = make_int4(0, 0, 0, 0);
+        }
     }
     for (; g < groups; g += nthreads) {
         uint32_t rnd[4] = {0, 0, 0, 0};
         if (stochastic) random_block(seed, it.rng_stream, static_cast<unsigned long long>(g), rnd);
         w4[g] = update_word(__ldcs(g4 + g), w4[g], rnd, shift, p.mode, zero_out);
+        if (p.clear) reinterpret_cast<int4*>(it.g32)[g] = make_int4(0, 0, 0, 0);
     }
     for (long long i = (groups << 2) + tid; i < it.n; i += nthreads) {
         const uint32_t rnd = stochastic ? random_word(seed, it.rng_stream, static_cast<unsigned long long>(i)) : 0u;
         const int g8 = zero_out ? 0 : narrow(it.g32[i], shift, p.mode, rnd);
         it.w[i] = static_cast<int8_t>(clamp127(static_cast<int>(it.w[i]) - g8));
+        if (p.clear) it.g32[i] = 0;
     }
 }
 
@@ -945,8 +951,8 @@ extern "C" int niti_update_i8(int8_t* w, const int32_t* g32, const uint32_t* max
 
 extern "C" size_t niti_update_multi_scratch_bytes(void) { return 2 * UPDATE_MULTI_MAX * sizeof(int32_t); }
 
-extern "C" int niti_update_multi_i8(const niti_update_item* items, int count, int mu, int round_mode, const uint64_t* seed,
-                                    void* scratch, size_t scratch_bytes, int32_t* status, void* stream) {
+extern "C" int niti_update_multi_i8(const niti_update_item* items, int count, int mu, int round_mode, int clear_gradients,
+                                    const uint64_t* seed, void* scratch, size_t scratch_bytes, int32_t* status, void* stream) {
     NITI_REQUIRE(items && count > 0 && round_mode >= 0 && round_mode <= 2 && scratch);
     NITI_REQUIRE(seed || round_mode != NITI_ROUND_STOCHASTIC);
     if (scratch_bytes < niti_update_multi_scratch_bytes()) return NITI_ERR_SCRATCH;
@@ -970,7 +976,7 @@ extern "C" int niti_update_multi_i8(const niti_update_item* items, int count, in
             p.item[i] = UpdateItem{it.w, it.g32, it.maxabs, it.n, it.rng_stream};
             total += it.n;
         }
-        p.mu = mu; p.mode = round_mode;
+        p.mu = mu; p.mode = round_mode; p.clear = clear_gradients ? 1 : 0;
         p.seed = reinterpret_cast<const unsigned long long*>(seed);
         p.state = static_cast<int32_t*>(scratch);
         p.status = status;

@@ -198,6 +198,22 @@ def conv_wgrad_acc(x, err, R=3, S=3, pad=1, out=None, want_max=True):
     return g32, mx
 
 
+def conv_wgrad_accumulate_supported(C, K, R, S, pad):
+    return bool(lib.niti_conv_wgrad_accumulate_supported(C, K, R, S, pad))
+
+
+def conv_wgrad_accumulate(x, err, g32, R=3, S=3, pad=1):
+    """g32 += weight gradient (no clearing pass: the caller keeps g32 zeroed between steps, see update_multi)."""
+    _need_cuda(x, err, g32)
+    N, H, W, C = x.shape
+    K = err.shape[3]
+    assert g32.dtype == torch.int32 and g32.numel() == K * R * S * C
+    _call("niti_conv_wgrad_accumulate_i8", 1, 2 * N * H * W * K * R * S * C, x.numel() + err.numel() + 4 * g32.numel(),
+          lib.niti_conv_wgrad_accumulate_i8, _p(x), _p(err), _p(g32), N, H, W, C, K, R, S, pad,
+          _p(status_word(x.device)), _st())
+    return g32
+
+
 def gemm_acc(a, b, trans_a=False, trans_b=False, out=None):
     """C32[M,N] = op(a) @ op(b); a is [M,K] ([K,M] if trans_a), b is [K,N] ([N,K] if trans_b)."""
     _need_cuda(a, b, out)
@@ -321,9 +337,9 @@ def update(w, g32, maxabs, mu, mode=ROUND_PSEUDO_STOCHASTIC, seed=None, rng_stre
           w.numel(), mu, mode, _p(seed), rng_stream, _st())
 
 
-def update_multi(ws, g32s, streams, mu, mode=ROUND_PSEUDO_STOCHASTIC, seed=None, want_max=False):
-    """All layers' integer SGD updates in one launch: per layer max|g32| -> shift -> w -= narrow(g32).
-    Returns the per-layer maxima (int32[len(ws)]) when want_max."""
+def update_multi(ws, g32s, streams, mu, mode=ROUND_PSEUDO_STOCHASTIC, seed=None, want_max=False, clear=False):
+    """All layers' integer SGD updates in one launch: per layer max|g32| -> shift -> w -= narrow(g32); `clear`
+    also zeroes the accumulators afterwards.  Returns the per-layer maxima (int32[len(ws)]) when want_max."""
     _need_cuda(seed, *ws, *g32s)
     dev = ws[0].device
     n = len(ws)
@@ -335,7 +351,7 @@ def update_multi(ws, g32s, streams, mu, mode=ROUND_PSEUDO_STOCHASTIC, seed=None,
     nbytes = lib.niti_update_multi_scratch_bytes()
     sc = torch.empty(nbytes, dtype=torch.uint8, device=dev)
     total = sum(w.numel() for w in ws)
-    _call("niti_update_multi_i8", (n + 15) // 16, 0, 10 * total, lib.niti_update_multi_i8, items, n, mu, mode, _p(seed),
+    _call("niti_update_multi_i8", (n + 15) // 16, 0, 10 * total, lib.niti_update_multi_i8, items, n, mu, mode, int(clear), _p(seed),
           _p(sc), nbytes, _p(status_word(dev)), _st())
     return mx
 

@@ -27,6 +27,7 @@ class UpdateWeight(Module):
     layer_id = 0          # index among the weighted layers; selects the random-bit streams
     grad_buffer = None    # optional preallocated int32 view the weight gradient is written into
     defer_update = False  # data-parallel trainers sum gradients across ranks before updating
+    grad_accumulate = False  # the weight gradient is ADDED into grad_buffer, which weight_update_all zeroes after use
     grad_ready = None     # optional callback(layer), called as soon as grad_int32acc has been enqueued
 
     def weight_update(self):
@@ -35,12 +36,13 @@ class UpdateWeight(Module):
                    RNG_SEED(self.weight.device), 16 * self.layer_id + 2)
 
 
-def weight_update_all(layers):
+def weight_update_all(layers, clear=False):
     """The updates of all `layers` (UpdateWeight modules whose grad_int32acc is set) in one launch; each
-    layer's maximum is recomputed from its accumulators, so this also serves gradients summed across ranks."""
+    layer's maximum is recomputed from its accumulators, so this also serves gradients summed across ranks.
+    `clear` zeroes the accumulators afterwards (layers with grad_accumulate add into them at the next step)."""
     dev = layers[0].weight.device
     ops.update_multi([l.weight for l in layers], [l.grad_int32acc for l in layers], [16 * l.layer_id + 2 for l in layers],
-                     GRAD_BITWIDTH, _mode(GRAD_ROUND_METHOD), RNG_SEED(dev))
+                     GRAD_BITWIDTH, _mode(GRAD_ROUND_METHOD), RNG_SEED(dev), clear=clear)
 
 
 def _fake_max(shift):
@@ -344,9 +346,13 @@ class TiConv2d(UpdateWeight):
                                                  exp_tensor(self.err_exp, acc.device), self.weight_exp, mx, False,
                                                  SAMPLE_OFFSET * per)
         K, R, S, C = self.weight.shape
-        # a deferred update finds max|g| itself (weight_update_all)
-        self.grad_int32acc, self.grad_maxabs = ops.conv_wgrad_acc(self.act, err_in, R, S, self.padding, out=self.grad_buffer,
-                                                                  want_max=not self.defer_update)
+        if (self.grad_accumulate and self.defer_update and self.grad_buffer is not None
+                and ops.conv_wgrad_accumulate_supported(C, K, R, S, self.padding)):
+            self.grad_int32acc, self.grad_maxabs = ops.conv_wgrad_accumulate(self.act, err_in, self.grad_buffer, R, S, self.padding), None
+        else:
+            # a deferred update finds max|g| itself (weight_update_all)
+            self.grad_int32acc, self.grad_maxabs = ops.conv_wgrad_acc(self.act, err_in, R, S, self.padding, out=self.grad_buffer,
+                                                                      want_max=not self.defer_update)
         if self.grad_ready is not None:
             self.grad_ready(self)
         if not self.defer_update:

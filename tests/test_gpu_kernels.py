@@ -375,3 +375,35 @@ def test_update_multi_matches_layer_by_layer(mode, count):
     for i in range(count):
         assert_same(ws[i], want[i][0].cpu().numpy(), f"update_multi layer {i} of {count}, n={sizes[i]}")
         assert int(got_mx[i]) == int(want[i][1])
+
+
+@pytest.mark.gpu
+def test_update_multi_can_clear_the_accumulators():
+    rng = np.random.default_rng(5)
+    seed = ops.seed_tensor(1, DEV)
+    ws = [cu(rnd8(rng, (n,))) for n in (4096, 1003)]
+    gs = [cu(rng.integers(-900, 900, size=n).astype(np.int32)) for n in (4096, 1003)]
+    want = []
+    for w, g in zip(ws, gs):
+        ref = w.clone()
+        ops.update(ref, g, ops.absmax(g), 5, 2, seed, 2)
+        want.append(ref.cpu().numpy())
+    ops.update_multi(ws, gs, [2, 2], 5, 2, seed, clear=True)
+    for w, g, r in zip(ws, gs, want):
+        assert_same(w, r, "update_multi with clear: weights")
+        assert int(g.abs().max()) == 0
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("N,H,W,C,K", [(8, 16, 16, 128, 128), (4, 8, 8, 256, 128), (3, 10, 6, 64, 144)])
+def test_conv_wgrad_accumulates_into_the_gradient(N, H, W, C, K):
+    """g32 += weight gradient: twice the same call gives base + 2 * gradient (gradient accumulation over micro-batches)."""
+    rng = np.random.default_rng(N + H + C)
+    x, e = rnd8(rng, (N, H, W, C)), rnd8(rng, (N, H, W, K))
+    assert ops.conv_wgrad_accumulate_supported(C, K, 3, 3, 1)
+    base = rng.integers(-1000, 1000, size=(K, 3, 3, C)).astype(np.int32)
+    g = cu(base.copy())
+    ops.conv_wgrad_accumulate(cu(x), cu(e), g)
+    ops.conv_wgrad_accumulate(cu(x), cu(e), g)
+    want = O.conv_wgrad(x, e, 3, 3, 1)
+    assert_same(g, (base.astype(np.int64) + 2 * want).astype(np.int32), "accumulating weight gradient")

@@ -45,9 +45,10 @@ def build(cfg, seed, dropout, fuse_relu, mu):
     return model, oracle, rng
 
 
-def run_steps(cfg, B, seed, dropout, steps, mu, fuse_relu, use_graph, rec=None):
+def run_steps(cfg, B, seed, dropout, steps, mu, fuse_relu, use_graph, rec=None, keep_gradients=True):
+    """keep_gradients: compare every layer's int32 gradient too (the default trainer zeroes them in its update launch)."""
     model, oracle, rng = build(cfg, seed, dropout, fuse_relu, mu)
-    tr = Trainer(model, B, DEV, use_graph=use_graph, seed=seed, warmup_steps=1)
+    tr = Trainer(model, B, DEV, use_graph=use_graph, seed=seed, warmup_steps=1, keep_gradients=keep_gradients)
     for step in range(steps):
         x = synth_images(rng, B)
         tgt = rng.integers(0, 10, size=B)
@@ -60,11 +61,15 @@ def run_steps(cfg, B, seed, dropout, steps, mu, fuse_relu, use_graph, rec=None):
         assert int(exp_h) == want_e
         assert np.array_equal(model.loss.out_grad.cpu().numpy(), oracle.trace["loss_err"]), f"loss error differs at step {step}"
         for i, l in enumerate(model.weighted_layers()):
-            assert np.array_equal(l.grad_int32acc.cpu().numpy(), grads[i].astype(np.int32)), f"grad {i} step {step}"
+            if keep_gradients:
+                assert np.array_equal(l.grad_int32acc.cpu().numpy(), grads[i].astype(np.int32)), f"grad {i} step {step}"
+            else:
+                assert int(l.grad_int32acc.abs().max()) == 0, "the update launch leaves the accumulators cleared"
             assert np.array_equal(l.weight.cpu().numpy(), oracle.w[i]), f"weights {i} step {step}"
             if rec is not None:
                 assert crc(l.weight.cpu().numpy()) == rec[f"s{step}_w{i}_crc"]
-                assert crc(l.grad_int32acc.cpu().numpy()) == rec[f"s{step}_g{i}_crc"]
+                if keep_gradients:
+                    assert crc(l.grad_int32acc.cpu().numpy()) == rec[f"s{step}_g{i}_crc"]
         if rec is not None:
             assert np.array_equal(out_h.numpy(), rec[f"s{step}_out"]) and int(exp_h) == rec[f"s{step}_out_exp"]
             assert np.array_equal(model.loss.out_grad.cpu().numpy(), rec[f"s{step}_loss_err"])
@@ -80,9 +85,19 @@ def test_against_reference_golden(golden_dir, name, fuse_relu, use_graph):
               fuse_relu, use_graph, rec)
 
 
-def test_vgg7_three_steps_graph_replay():
-    """Eager warm-up step, capture, then replays: the captured step must keep matching the oracle."""
-    run_steps([128, 128, "M", 256, 256, "M", 512, 512, "M"], 8, 4321, True, 3, 5, True, True)
+@pytest.mark.parametrize("keep_gradients", [True, False])
+def test_vgg7_three_steps_graph_replay(keep_gradients):
+    """Eager warm-up step, capture, then replays: the captured step must keep matching the oracle, with the
+    gradients kept for comparison and in the default mode (accumulating weight-gradient kernels, bucket cleared
+    by the update launch)."""
+    run_steps([128, 128, "M", 256, 256, "M", 512, 512, "M"], 8, 4321, True, 3, 5, True, True, keep_gradients=keep_gradients)
+
+
+def test_golden_net_default_trainer_mode(golden_dir):
+    rec = np.load(os.path.join(golden_dir, "net_vgg7_b4.npz"))
+    cfg = ["M" if c == 0 else int(c) for c in rec["cfg"]]
+    run_steps(cfg, int(rec["B"]), int(rec["seed"]), bool(rec["dropout"]), int(rec["steps"]), int(rec["mu"]),
+              True, True, rec, keep_gradients=False)
 
 
 @pytest.mark.parametrize("name,B", [("vgg9_wide", 2), ("vgg13", 4), (8, 2)])
