@@ -28,6 +28,7 @@ class UpdateWeight(Module):
     grad_buffer = None    # optional preallocated int32 view the weight gradient is written into
     defer_update = False  # data-parallel trainers sum gradients across ranks before updating
     grad_accumulate = False  # the weight gradient is ADDED into grad_buffer, which weight_update_all zeroes after use
+    wgrad_stream = None      # optional side stream for the (accumulating) weight-gradient kernel; the owner joins it
     grad_ready = None     # optional callback(layer), called as soon as grad_int32acc has been enqueued
 
     def weight_update(self):
@@ -329,6 +330,10 @@ class TiConv2d(UpdateWeight):
         err_in, self.err_exp = input
         err_in = err_in.contiguous()
         err_out = None
+        fork = None
+        if self.wgrad_stream is not None and not self.first_layer:
+            fork = torch.cuda.Event()
+            fork.record()  # the weight gradient needs only what has been enqueued up to here
         if not self.first_layer:
             # the reference builds flip(w).transpose(0,3) here (:404); the kernels read w in place
             K, R, S, C = self.weight.shape
@@ -348,7 +353,16 @@ class TiConv2d(UpdateWeight):
         K, R, S, C = self.weight.shape
         if (self.grad_accumulate and self.defer_update and self.grad_buffer is not None
                 and ops.conv_wgrad_accumulate_supported(C, K, R, S, self.padding)):
-            self.grad_int32acc, self.grad_maxabs = ops.conv_wgrad_accumulate(self.act, err_in, self.grad_buffer, R, S, self.padding), None
+            if fork is not None:
+                # error-backward and weight gradient are independent: on two streams the SMs one kernel leaves idle
+                # (its last wave, its epilogue) are taken by the other
+                self._wgrad_inputs = (self.act, err_in)  # referenced until the owner of the side stream has joined it
+                self.wgrad_stream.wait_event(fork)
+                with torch.cuda.stream(self.wgrad_stream):
+                    ops.conv_wgrad_accumulate(self.act, err_in, self.grad_buffer, R, S, self.padding)
+                self.grad_int32acc, self.grad_maxabs = self.grad_buffer, None
+            else:
+                self.grad_int32acc, self.grad_maxabs = ops.conv_wgrad_accumulate(self.act, err_in, self.grad_buffer, R, S, self.padding), None
         else:
             # a deferred update finds max|g| itself (weight_update_all)
             self.grad_int32acc, self.grad_maxabs = ops.conv_wgrad_acc(self.act, err_in, R, S, self.padding, out=self.grad_buffer,
