@@ -165,6 +165,11 @@ __device__ __forceinline__ void producer_role(uint8_t* smem, uint64_t* full_bar,
         int tw = 0, th = 0, tn = 0;
         if (p.conv) { tw = m_t % p.tiles_w; th = (m_t / p.tiles_w) % p.tiles_h; tn = m_t / (p.tiles_w * p.tiles_h); }
         const int ncol = n_t * BN + static_cast<int>(rank) * BNH;  // first B column of this CTA
+        // This loop is one thread's serial instruction stream and sets the pace of the whole pipeline: the tap
+        // (r, sx) and channel block cb of a reduction block are kept as running counters, because four integer
+        // divisions per block cost more than the block's MMAs.
+        int cb = 0, sx = 0, r = 0;
+        if (p.conv) { const int tap0 = kb_lo / p.cblocks; cb = kb_lo % p.cblocks; r = tap0 / p.S; sx = tap0 % p.S; }
         for (int kb = kb_lo; kb < kb_hi; ++kb) {
             if (!mbar_wait(smem_u32(&empty_bar[s]), ph ^ 1u, abort_flag)) { ok = false; report_abort(p.status, 1, 0); break; }
             const uint32_t sa = smem_u32(smem + s * STAGE_BYTES);
@@ -177,8 +182,7 @@ __device__ __forceinline__ void producer_role(uint8_t* smem, uint64_t* full_bar,
                 mbar_arrive_expect_tx(fb, static_cast<uint32_t>(p.a_bytes + BN * ROW_BYTES));
             }
             if (p.conv) {
-                const int tap = kb / p.cblocks, cb = kb % p.cblocks;
-                const int r = tap / p.S, sx = tap % p.S;
+                const int tap = r * p.S + sx;
                 const int dx = p.flip ? p.pad - sx : sx - p.pad, dy = p.flip ? p.pad - r : r - p.pad;
                 if (TWO) tma_load_4d_pair(sa, tmA, fb, cb * ROW_BYTES, tw * p.BW + dx, th * p.BH + dy, tn * p.BI);
                 else     tma_load_4d(sa, tmA, fb, cb * ROW_BYTES, tw * p.BW + dx, th * p.BH + dy, tn * p.BI);
@@ -192,6 +196,7 @@ __device__ __forceinline__ void producer_role(uint8_t* smem, uint64_t* full_bar,
                     if (TWO) tma_load_2d_pair(sb, tmB, fb, tap * p.tapstride + cb * ROW_BYTES, ncol);
                     else     tma_load_2d(sb, tmB, fb, tap * p.tapstride + cb * ROW_BYTES, ncol);
                 }
+                if (++cb == p.cblocks) { cb = 0; if (++sx == p.S) { sx = 0; ++r; } }
             } else {
                 if (TWO) {
                     if (p.a_mn) tma_load_2d_pair(sa, tmA, fb, m_t * BLOCK_M, kb * 128);
@@ -230,6 +235,13 @@ __device__ __forceinline__ void mma_role(uint8_t* smem, uint64_t* full_bar, uint
     const int nst = (p.nstages > 0 && p.nstages < STAGES) ? p.nstages : STAGES;
     const int first = TWO ? static_cast<int>(blockIdx.x >> 1) : static_cast<int>(blockIdx.x);
     const int step = TWO ? static_cast<int>(gridDim.x >> 1) : static_cast<int>(gridDim.x);
+    // operand descriptors of stage 0 (a stage's are these advanced by the stage offset) and the K = 32 steps
+    const uint32_t s0 = smem_u32(smem);
+    const uint64_t a_base = p.a_mn ? make_smem_desc(s0, PANEL_BYTES, 1024, SWIZZLE_128B_CODE) : make_smem_desc(s0, 16, 1024, SWIZZLE_128B_CODE);
+    const uint64_t b_base = p.b_mn ? make_smem_desc(s0 + PANEL_BYTES, PANEL_BYTES, 1024, SWIZZLE_128B_CODE)
+                                   : make_smem_desc(s0 + PANEL_BYTES, 16, 1024, SWIZZLE_128B_CODE);
+    const uint32_t a_step = p.a_mn ? 32u * ROW_BYTES : 32u;
+    const uint32_t b_step = p.b_mn ? 32u * ROW_BYTES : 32u;
     int s = 0; uint32_t ph = 0; bool ok = true; int it = 0;
     for (int tile = first; ok && tile < total_tiles; tile += step, ++it) {
         const int acc = PARKED ? it : (it & 1);
@@ -242,22 +254,21 @@ __device__ __forceinline__ void mma_role(uint8_t* smem, uint64_t* full_bar, uint
         const int split = tile / mn_tiles;
         const int kb_lo = static_cast<int>(static_cast<long long>(split) * p.num_kb / p.splits);
         const int kb_hi = static_cast<int>(static_cast<long long>(split + 1) * p.num_kb / p.splits);
+        int cb = p.conv ? kb_lo % p.cblocks : 0;  // channel block within the tap: a running counter, no division per block
         for (int kb = kb_lo; kb < kb_hi; ++kb) {
             if (!mbar_wait(smem_u32(&full_bar[s]), ph, abort_flag)) { ok = false; report_abort(p.status, 3, 1); break; }
             if (PARKED && it == 0 && kb == kb_lo) PARK_STAMP(2);
             tc_fence_after();
-            const uint32_t sa = smem_u32(smem + s * STAGE_BYTES);
-            const uint32_t sb = sa + PANEL_BYTES;
-            const uint64_t a0 = p.a_mn ? make_smem_desc(sa, PANEL_BYTES, 1024, SWIZZLE_128B_CODE)
-                                       : make_smem_desc(sa, 16, 1024, SWIZZLE_128B_CODE);
-            const uint64_t b0 = p.b_mn ? make_smem_desc(sb, PANEL_BYTES, 1024, SWIZZLE_128B_CODE)
-                                       : make_smem_desc(sb, 16, 1024, SWIZZLE_128B_CODE);
-            const uint32_t a_step = p.a_mn ? 32u * ROW_BYTES : 32u;
-            const uint32_t b_step = p.b_mn ? 32u * ROW_BYTES : 32u;
+            const uint64_t a0 = desc_advance(a_base, static_cast<uint32_t>(s) * STAGE_BYTES);
+            const uint64_t b0 = desc_advance(b_base, static_cast<uint32_t>(s) * STAGE_BYTES);
             // a conv tap whose channel count is not a multiple of 128 ends in a partial block:
             // issue only the MMAs (K = 32 each) that cover real channels (the rest is TMA zero fill)
             int nmma = 4;
-            if (p.conv) { const int left = p.red - (kb % p.cblocks) * 128; nmma = left >= 128 ? 4 : (left + 31) >> 5; }
+            if (p.conv) {
+                const int left = p.red - cb * 128;
+                nmma = left >= 128 ? 4 : (left + 31) >> 5;
+                if (++cb == p.cblocks) cb = 0;
+            }
 #pragma unroll
             for (int k = 0; k < 4; ++k)
                 if (k < nmma) {
@@ -974,8 +985,9 @@ umma_wgrad_kernel(const __grid_constant__ CUtensorMap tmErr, const __grid_consta
     if (warp == 0) {
         if (lane == 0) {
             int s = 0; uint32_t ph = 0;
+            // tile coordinates as running counters: this single thread's instruction stream paces the pipeline
+            int tw = chunk_lo % p.tiles_w, th = (chunk_lo / p.tiles_w) % p.tiles_h, tn = chunk_lo / (p.tiles_w * p.tiles_h);
             for (int ch = chunk_lo; ch < chunk_hi; ++ch) {
-                const int tw = ch % p.tiles_w, th = (ch / p.tiles_w) % p.tiles_h, tn = ch / (p.tiles_w * p.tiles_h);
                 if (!mbar_wait(smem_u32(&empty_bar[s]), ph ^ 1u, abort_flag)) { report_abort(p.status, 11, 0); break; }
                 const uint32_t fb = smem_u32(&full_bar[s]);
                 const uint32_t sa = smem_u32(smem + s * WG_STAGE_BYTES);
@@ -984,6 +996,7 @@ umma_wgrad_kernel(const __grid_constant__ CUtensorMap tmErr, const __grid_consta
                 for (int sx = 0; sx < p.S; ++sx)
                     tma_load_4d(sa + (1 + sx) * PANEL_BYTES, &tmX, fb, ct * 128, tw * p.BW + sx - p.pad, th * p.BH + r - p.pad, tn * p.BI);
                 if (++s == WG_STAGES) { s = 0; ph ^= 1u; }
+                if (++tw == p.tiles_w) { tw = 0; if (++th == p.tiles_h) { th = 0; ++tn; } }
             }
         }
         __syncwarp();  // reach the teardown's block-wide barrier as a converged warp
