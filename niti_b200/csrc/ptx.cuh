@@ -61,6 +61,20 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
     return done;
 }
 
+// Non-blocking probe of a phase: lets a loop ask about the NEXT stage before it works on the current one, so that
+// the barrier's shared-memory round trip is hidden behind that work.
+__device__ __forceinline__ uint32_t mbar_test_wait(uint32_t bar, uint32_t parity) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred P;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 P, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, P;\n\t}"
+        : "=r"(done)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return done;
+}
+
 // Bounded wait on an mbarrier phase.  `abort_flag` is a CTA-wide word in shared memory:
 // once any role gives up, every other role's wait returns false on its next poll.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {

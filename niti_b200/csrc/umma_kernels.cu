@@ -142,7 +142,10 @@ __device__ __forceinline__ uint32_t narrow4(const uint32_t* v, int shift, int mo
 }
 
 // ---- warp roles shared by the streaming kernel and the accumulator-parking kernel -------------
-// TMA producer (one thread): fills the stage ring for every tile of this CTA, in tile order.
+// TMA producer: fills the stage ring for every tile of this CTA, in tile order.  The WHOLE warp runs the loop and
+// one lane issues: with warp-uniform control flow the compiler keeps addresses, coordinates and descriptors in
+// uniform registers, which is where the TMA and MMA instructions take their operands from; a loop entered by a
+// single lane pays a register-to-uniform-register move per operand instead (measured: ~100 cycles per MMA issue).
 // TWO: this CTA is half of a CTA pair (cluster ranks 0/1).  Tiles are 256 rows high: rank r owns rows
 // [128 r, 128 r + 128) of the pair's tile (m tile 2*pair_m + r) and columns [r BN/2, (r+1) BN/2) of the B
 // operand; all byte counts are reported to rank 0's "full" barrier, which its MMA thread waits on.
@@ -156,7 +159,9 @@ __device__ __forceinline__ void producer_role(uint8_t* smem, uint64_t* full_bar,
     const int step = TWO ? static_cast<int>(gridDim.x >> 1) : static_cast<int>(gridDim.x);
     constexpr int BNH = TWO ? BN / 2 : BN;  // B columns this CTA loads
     const int nst = (p.nstages > 0 && p.nstages < STAGES) ? p.nstages : STAGES;
+    const bool issuer = (threadIdx.x & 31) == 0;
     int s = 0; uint32_t ph = 0; bool ok = true;
+    bool ready = false;  // the current stage's "empty" phase was already seen complete by the previous iteration's probe
     for (int tile = first; ok && tile < total_tiles; tile += step) {
         const int split = tile / mn_tiles, mn = tile % mn_tiles;
         const int m_t = TWO ? 2 * (mn / p.n_tiles) + static_cast<int>(rank) : mn / p.n_tiles, n_t = mn % p.n_tiles;
@@ -171,17 +176,23 @@ __device__ __forceinline__ void producer_role(uint8_t* smem, uint64_t* full_bar,
         int cb = 0, sx = 0, r = 0;
         if (p.conv) { const int tap0 = kb_lo / p.cblocks; cb = kb_lo % p.cblocks; r = tap0 / p.S; sx = tap0 % p.S; }
         for (int kb = kb_lo; kb < kb_hi; ++kb) {
-            if (!mbar_wait(smem_u32(&empty_bar[s]), ph ^ 1u, abort_flag)) { ok = false; report_abort(p.status, 1, 0); break; }
+            if (!ready && !mbar_wait(smem_u32(&empty_bar[s]), ph ^ 1u, abort_flag)) { ok = false; report_abort(p.status, 1, 0); break; }
+            {   // probe the next stage's "empty" phase while this stage's loads are being issued
+                const int sn = (s + 1 == nst) ? 0 : s + 1;
+                ready = mbar_test_wait(smem_u32(&empty_bar[sn]), (sn == 0 ? ph ^ 1u : ph) ^ 1u) != 0;
+            }
             const uint32_t sa = smem_u32(smem + s * STAGE_BYTES);
             const uint32_t sb = sa + PANEL_BYTES;
             uint32_t fb = smem_u32(&full_bar[s]);
             if (TWO) {
-                if (rank == 0) mbar_arrive_expect_tx(fb, 2u * static_cast<uint32_t>(p.a_bytes + BNH * ROW_BYTES));
+                if (rank == 0 && issuer) mbar_arrive_expect_tx(fb, 2u * static_cast<uint32_t>(p.a_bytes + BNH * ROW_BYTES));
                 fb = mapa_u32(fb, 0);
             } else {
-                mbar_arrive_expect_tx(fb, static_cast<uint32_t>(p.a_bytes + BN * ROW_BYTES));
+                if (issuer) mbar_arrive_expect_tx(fb, static_cast<uint32_t>(p.a_bytes + BN * ROW_BYTES));
             }
-            if (p.conv) {
+            if (!issuer) {
+                // the other lanes only follow the counters
+            } else if (p.conv) {
                 const int tap = r * p.S + sx;
                 const int dx = p.flip ? p.pad - sx : sx - p.pad, dy = p.flip ? p.pad - r : r - p.pad;
                 if (TWO) tma_load_4d_pair(sa, tmA, fb, cb * ROW_BYTES, tw * p.BW + dx, th * p.BH + dy, tn * p.BI);
@@ -196,7 +207,6 @@ __device__ __forceinline__ void producer_role(uint8_t* smem, uint64_t* full_bar,
                     if (TWO) tma_load_2d_pair(sb, tmB, fb, tap * p.tapstride + cb * ROW_BYTES, ncol);
                     else     tma_load_2d(sb, tmB, fb, tap * p.tapstride + cb * ROW_BYTES, ncol);
                 }
-                if (++cb == p.cblocks) { cb = 0; if (++sx == p.S) { sx = 0; ++r; } }
             } else {
                 if (TWO) {
                     if (p.a_mn) tma_load_2d_pair(sa, tmA, fb, m_t * BLOCK_M, kb * 128);
@@ -216,12 +226,13 @@ __device__ __forceinline__ void producer_role(uint8_t* smem, uint64_t* full_bar,
                     else     tma_load_2d(sb, tmB, fb, kb * ROW_BYTES, ncol);
                 }
             }
+            if (p.conv && ++cb == p.cblocks) { cb = 0; if (++sx == p.S) { sx = 0; ++r; } }
             if (++s == nst) { s = 0; ph ^= 1u; }
         }
     }
 }
 
-// MMA issuer (one thread).  Streaming: two accumulators used alternately, each handed back by the
+// MMA issuer: the whole warp runs the loop (uniform control flow, see the producer), lane 0 issues MMAs and commits.  Streaming: two accumulators used alternately, each handed back by the
 // epilogue (tempty).  PARKED: tile i of this CTA accumulates into TMEM columns [i*BN, (i+1)*BN) and
 // stays there until the kernel ends, so no accumulator is ever waited for.
 // TWO: run by rank 0 of a CTA pair only; M = 256 MMAs over both CTAs' shared and tensor memory, and every
@@ -242,7 +253,9 @@ __device__ __forceinline__ void mma_role(uint8_t* smem, uint64_t* full_bar, uint
                                    : make_smem_desc(s0 + PANEL_BYTES, 16, 1024, SWIZZLE_128B_CODE);
     const uint32_t a_step = p.a_mn ? 32u * ROW_BYTES : 32u;
     const uint32_t b_step = p.b_mn ? 32u * ROW_BYTES : 32u;
+    const bool issuer = (threadIdx.x & 31) == 0;
     int s = 0; uint32_t ph = 0; bool ok = true; int it = 0;
+    bool ready = false;  // the current stage's "full" phase was already seen complete by the previous iteration's probe
     for (int tile = first; ok && tile < total_tiles; tile += step, ++it) {
         const int acc = PARKED ? it : (it & 1);
         if (!PARKED) {
@@ -256,9 +269,12 @@ __device__ __forceinline__ void mma_role(uint8_t* smem, uint64_t* full_bar, uint
         const int kb_hi = static_cast<int>(static_cast<long long>(split + 1) * p.num_kb / p.splits);
         int cb = p.conv ? kb_lo % p.cblocks : 0;  // channel block within the tap: a running counter, no division per block
         for (int kb = kb_lo; kb < kb_hi; ++kb) {
-            if (!mbar_wait(smem_u32(&full_bar[s]), ph, abort_flag)) { ok = false; report_abort(p.status, 3, 1); break; }
+            if (!ready && !mbar_wait(smem_u32(&full_bar[s]), ph, abort_flag)) { ok = false; report_abort(p.status, 3, 1); break; }
             if (PARKED && it == 0 && kb == kb_lo) PARK_STAMP(2);
-            tc_fence_after();
+            {   // ask about the next stage now; the answer is needed only after this stage's MMAs have been issued
+                const int sn = (s + 1 == nst) ? 0 : s + 1;
+                ready = mbar_test_wait(smem_u32(&full_bar[sn]), sn == 0 ? ph ^ 1u : ph) != 0;
+            }
             const uint64_t a0 = desc_advance(a_base, static_cast<uint32_t>(s) * STAGE_BYTES);
             const uint64_t b0 = desc_advance(b_base, static_cast<uint32_t>(s) * STAGE_BYTES);
             // a conv tap whose channel count is not a multiple of 128 ends in a partial block:
@@ -271,16 +287,16 @@ __device__ __forceinline__ void mma_role(uint8_t* smem, uint64_t* full_bar, uint
             }
 #pragma unroll
             for (int k = 0; k < 4; ++k)
-                if (k < nmma) {
+                if (k < nmma && issuer) {
                     if (TWO) umma_i8_pair(d_tmem, desc_advance(a0, k * a_step), desc_advance(b0, k * b_step), idesc,
                                           static_cast<uint32_t>(kb != kb_lo || k != 0));
                     else     umma_i8(d_tmem, desc_advance(a0, k * a_step), desc_advance(b0, k * b_step), idesc,
                                      static_cast<uint32_t>(kb != kb_lo || k != 0));
                 }
-            if (TWO) umma_commit_pair(smem_u32(&empty_bar[s])); else umma_commit(smem_u32(&empty_bar[s]));
+            if (issuer) { if (TWO) umma_commit_pair(smem_u32(&empty_bar[s])); else umma_commit(smem_u32(&empty_bar[s])); }
             if (++s == nst) { s = 0; ph ^= 1u; }
         }
-        if (ok) { if (TWO) umma_commit_pair(smem_u32(&tfull_bar[acc])); else umma_commit(smem_u32(&tfull_bar[acc])); }
+        if (ok && issuer) { if (TWO) umma_commit_pair(smem_u32(&tfull_bar[acc])); else umma_commit(smem_u32(&tfull_bar[acc])); }
     }
     if (PARKED) PARK_STAMP(3);
 }
@@ -482,10 +498,10 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     // Only one lane of warps 0 and 1 works; the others wait at __syncwarp so that each warp reaches the
     // block-wide barrier of the teardown converged (an aligned barrier executed by a diverged warp is undefined).
     if (warp == 0) {
-        if (lane == 0) producer_role<BN, STAGES, Cfg::STAGE_BYTES, TWO>(smem, full_bar, empty_bar, &tmA, &tmB, p, abort_flag);
+        producer_role<BN, STAGES, Cfg::STAGE_BYTES, TWO>(smem, full_bar, empty_bar, &tmA, &tmB, p, abort_flag);
         __syncwarp();
     } else if (warp == 1) {
-        if (lane == 0 && rank == 0)
+        if (rank == 0)
             mma_role<BN, STAGES, Cfg::STAGE_BYTES, false, TWO>(smem, full_bar, empty_bar, tfull_bar, tempty_bar, tmem_base, p, abort_flag);
         __syncwarp();
     } else {
@@ -767,10 +783,10 @@ umma_parked_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
     const int cta_step = TWO ? static_cast<int>(gridDim.x >> 1) : static_cast<int>(gridDim.x);
 
     if (warp == 0) {
-        if (lane == 0) producer_role<BN, STAGES, Cfg::STAGE_BYTES, TWO>(smem, full_bar, empty_bar, &tmA, &tmB, p, abort_flag);
+        producer_role<BN, STAGES, Cfg::STAGE_BYTES, TWO>(smem, full_bar, empty_bar, &tmA, &tmB, p, abort_flag);
         __syncwarp();  // reach the teardown's block-wide barrier as a converged warp
     } else if (warp == 1) {
-        if (lane == 0 && rank == 0)
+        if (rank == 0)
             mma_role<BN, STAGES, Cfg::STAGE_BYTES, true, TWO>(smem, full_bar, empty_bar, tfull_bar, nullptr, tmem_base, p, abort_flag);
         __syncwarp();
     } else {
@@ -982,26 +998,30 @@ umma_wgrad_kernel(const __grid_constant__ CUtensorMap tmErr, const __grid_consta
     const int chunk_lo = static_cast<int>(static_cast<long long>(split) * p.chunks / p.splits);
     const int chunk_hi = static_cast<int>(static_cast<long long>(split + 1) * p.chunks / p.splits);
 
+    // Warps 0 and 1 run their loops whole (uniform control flow keeps TMA / MMA operands in uniform registers);
+    // lane 0 issues.
     if (warp == 0) {
-        if (lane == 0) {
+        {
             int s = 0; uint32_t ph = 0;
-            // tile coordinates as running counters: this single thread's instruction stream paces the pipeline
+            // tile coordinates as running counters: this instruction stream paces the pipeline
             int tw = chunk_lo % p.tiles_w, th = (chunk_lo / p.tiles_w) % p.tiles_h, tn = chunk_lo / (p.tiles_w * p.tiles_h);
             for (int ch = chunk_lo; ch < chunk_hi; ++ch) {
                 if (!mbar_wait(smem_u32(&empty_bar[s]), ph ^ 1u, abort_flag)) { report_abort(p.status, 11, 0); break; }
                 const uint32_t fb = smem_u32(&full_bar[s]);
                 const uint32_t sa = smem_u32(smem + s * WG_STAGE_BYTES);
-                mbar_arrive_expect_tx(fb, static_cast<uint32_t>((1 + p.S) * p.box_bytes));
-                tma_load_4d(sa, &tmErr, fb, kt * 128, tw * p.BW, th * p.BH, tn * p.BI);
-                for (int sx = 0; sx < p.S; ++sx)
-                    tma_load_4d(sa + (1 + sx) * PANEL_BYTES, &tmX, fb, ct * 128, tw * p.BW + sx - p.pad, th * p.BH + r - p.pad, tn * p.BI);
+                if (lane == 0) {
+                    mbar_arrive_expect_tx(fb, static_cast<uint32_t>((1 + p.S) * p.box_bytes));
+                    tma_load_4d(sa, &tmErr, fb, kt * 128, tw * p.BW, th * p.BH, tn * p.BI);
+                    for (int sx = 0; sx < p.S; ++sx)
+                        tma_load_4d(sa + (1 + sx) * PANEL_BYTES, &tmX, fb, ct * 128, tw * p.BW + sx - p.pad, th * p.BH + r - p.pad, tn * p.BI);
+                }
                 if (++s == WG_STAGES) { s = 0; ph ^= 1u; }
                 if (++tw == p.tiles_w) { tw = 0; if (++th == p.tiles_h) { th = 0; ++tn; } }
             }
         }
         __syncwarp();  // reach the teardown's block-wide barrier as a converged warp
     } else if (warp == 1) {
-        if (lane == 0) {
+        {
             const uint32_t idesc = make_idesc_i8(BLOCK_M, 128, 1, 1);
             const uint32_t idesc2 = make_idesc_i8(BLOCK_M, 256, 1, 1);
             int s = 0; uint32_t ph = 0; bool ok = true;
@@ -1019,19 +1039,21 @@ umma_wgrad_kernel(const __grid_constant__ CUtensorMap tmErr, const __grid_consta
                 for (; sx + 1 < p.S; sx += 2) {
                     const uint64_t b0 = make_smem_desc(sa + (1 + sx) * PANEL_BYTES, PANEL_BYTES, 1024, SWIZZLE_128B_CODE);
                     for (int k = 0; k < p.mma_per_chunk; ++k)
-                        umma_i8(tmem_base + sx * 128, desc_advance(a0, k * 32u * ROW_BYTES), desc_advance(b0, k * 32u * ROW_BYTES),
-                                idesc2, static_cast<uint32_t>(ch != chunk_lo || k != 0));
+                        if (lane == 0)
+                            umma_i8(tmem_base + sx * 128, desc_advance(a0, k * 32u * ROW_BYTES), desc_advance(b0, k * 32u * ROW_BYTES),
+                                    idesc2, static_cast<uint32_t>(ch != chunk_lo || k != 0));
                 }
                 for (; sx < p.S; ++sx) {
                     const uint64_t b0 = make_smem_desc(sa + (1 + sx) * PANEL_BYTES, PANEL_BYTES, 1024, SWIZZLE_128B_CODE);
                     for (int k = 0; k < p.mma_per_chunk; ++k)
-                        umma_i8(tmem_base + sx * 128, desc_advance(a0, k * 32u * ROW_BYTES), desc_advance(b0, k * 32u * ROW_BYTES),
-                                idesc, static_cast<uint32_t>(ch != chunk_lo || k != 0));
+                        if (lane == 0)
+                            umma_i8(tmem_base + sx * 128, desc_advance(a0, k * 32u * ROW_BYTES), desc_advance(b0, k * 32u * ROW_BYTES),
+                                    idesc, static_cast<uint32_t>(ch != chunk_lo || k != 0));
                 }
-                umma_commit(smem_u32(&empty_bar[s]));
+                if (lane == 0) umma_commit(smem_u32(&empty_bar[s]));
                 if (++s == WG_STAGES) { s = 0; ph ^= 1u; }
             }
-            if (ok) umma_commit(smem_u32(&tfull_bar[0]));
+            if (ok && lane == 0) umma_commit(smem_u32(&tfull_bar[0]));
             if (blockIdx.y == 0) PARK_STAMP(13);
         }
         __syncwarp();
