@@ -9,8 +9,9 @@ shard of 128 images; the int32 weight gradients are summed with one NCCL all-red
 Prints ONE JSON line (rank 0).  Fields:
   value      images/s with the batch already resident in HBM (CUDA events, max over ranks)
   e2e        images/s through Trainer.step with pinned host buffers in and the logits read back
-  roofline   the tensor-core contraction kernel (conv forward / error-backward), timed per launch
-             with CUDA events in an eager step: algorithmic int8 ops / time vs 2x the measured bf16 peak
+  roofline   the tensor-core contraction kernels (conv forward / error-backward with the requantisation inside),
+             each call timed as ten back-to-back launches replayed from a CUDA graph: algorithmic int8 ops / time
+             vs 2x the measured bf16 peak
   cpu_baseline  the oracle's restatement of the reference's integer path on the host cores (rank 0, N=1)
 """
 import argparse
@@ -30,7 +31,13 @@ sys.path.insert(0, ROOT)
 VGG7 = [128, 128, "M", 256, 256, "M", 512, 512, "M"]
 PER_GPU_BATCH = 128
 METRIC = "int8 VGG-small-7 training throughput"
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the dominant kernel, from the ncu capture summarised in
+# profiles/umma_parked_conv4_b128_ncu.md (the 256->256 @16x16 forward call at batch 128; algorithmic bytes 8.98e6)
+NCU_TRAFFIC_BYTES = 9.04e6
+NCU_TRAFFIC_OF = "fprop 256->256 @16x16, batch 128 (ncu, one launch); algorithmic 8.98e6 bytes"
 UNIT = "images/s"
+WORKLOAD = ("VGG-small-7 integer training step (conv 128-128-P-256-256-P-512-512-P, FC 8192->10), "
+            "3x32x32 synthetic images, 10 classes, dropout on, grad bit-width 5")
 
 
 def synth_batch(rng, B):
@@ -81,13 +88,49 @@ def step_ops_per_image(cfg):
 # clocks
 # ------------------------------------------------------------------------------------------------
 class ClockSampler:
+    """SM clock and throttle reasons while the timed regions run: NVML polled every 5 ms from a thread (read-only
+    queries); falls back to `nvidia-smi -lms` when the NVML module is missing."""
     FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
               "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    REASON_BITS = {0x4: "sw_power_cap", 0x8: "hw_slowdown", 0x20: "sw_thermal_slowdown", 0x40: "hw_thermal_slowdown"}
 
     def __init__(self, gpu_index):
         self.samples, self.proc, self.idx = [], None, gpu_index
+        self.sm, self.mx, self.reasons, self._stop, self._thread = [], 0, set(), False, None
+
+    def _nvml_loop(self, nv, handle):
+        while not self._stop:
+            try:
+                self.sm.append(float(nv.nvmlDeviceGetClockInfo(handle, nv.NVML_CLOCK_SM)))
+                try:
+                    mask = nv.nvmlDeviceGetCurrentClocksEventReasons(handle)
+                except AttributeError:
+                    mask = nv.nvmlDeviceGetCurrentClocksThrottleReasons(handle)
+                for bit, name in self.REASON_BITS.items():
+                    if mask & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            time.sleep(0.005)
 
     def start(self):
+        try:
+            import pynvml as nv
+            nv.nvmlInit()
+            idx = self.idx
+            vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+            if vis:
+                try:
+                    idx = int(vis.split(",")[self.idx])
+                except (ValueError, IndexError):
+                    idx = self.idx
+            handle = nv.nvmlDeviceGetHandleByIndex(idx)
+            self.mx = float(nv.nvmlDeviceGetMaxClockInfo(handle, nv.NVML_CLOCK_SM))
+            self._thread = threading.Thread(target=self._nvml_loop, args=(nv, handle), daemon=True)
+            self._thread.start()
+            return
+        except Exception:
+            self._thread = None
         try:
             self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.idx), f"--query-gpu={self.FIELDS}",
                                           "--format=csv,noheader,nounits", "-lms", "100"],
@@ -101,6 +144,9 @@ class ClockSampler:
             self.samples.append(line.strip())
 
     def stop(self):
+        self._stop = True
+        if self._thread is not None:
+            self._thread.join(timeout=2)
         if self.proc is not None:
             self.proc.terminate()
             try:
@@ -109,7 +155,7 @@ class ClockSampler:
                 self.proc.kill()
 
     def summary(self):
-        sm, mx, reasons = [], 0, set()
+        sm, mx, reasons = list(self.sm), self.mx, set(self.reasons)
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
         for s in self.samples:
             f = [t.strip() for t in s.split(",")]
@@ -126,7 +172,8 @@ class ClockSampler:
         if not sm:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
         busy = [v for v in sm if v >= 0.5 * max(sm)]
-        return {"sm_mhz": statistics.median(busy), "sm_max_mhz": mx, "reasons": sorted(reasons), "samples": len(sm)}
+        return {"sm_mhz": statistics.median(busy), "sm_max_mhz": mx, "reasons": sorted(reasons), "samples": len(sm),
+                "source": "nvml, 5 ms period" if self._thread is not None else "nvidia-smi -lms 100"}
 
 
 # ------------------------------------------------------------------------------------------------
@@ -168,7 +215,7 @@ def run_reference(args):
     line = {"impl": "reference", "metric": METRIC, "value": v, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": sec * 1e3, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "int8", "data": "synthetic",
-            "config": {"workload": "VGG-small-7 integer training step, 3x32x32 inputs, 10 classes", "batch_per_step": batch},
+            "config": {"workload": WORKLOAD, "per_gpu_batch": PER_GPU_BATCH, "batch_per_step": batch},
             "cpu_baseline": {"value": v, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
             "e2e": {"value": v, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     print(json.dumps(line), flush=True)
@@ -347,8 +394,7 @@ def run_ours(args):
             "metric": METRIC, "value": images / dev_s, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": dev_s / args.steps * 1e3, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "int8", "data": "synthetic",
-            "config": {"workload": "VGG-small-7 integer training step (conv 128-128-P-256-256-P-512-512-P, FC 8192->10), "
-                                   "3x32x32 synthetic images, 10 classes, dropout on, grad bit-width 5",
+            "config": {"workload": WORKLOAD,
                        "per_gpu_batch": B, "global_batch": B * world, "parallelism": f"dp{world}",
                        "l2": "256 MB buffer written between timed steps (L2 flush); per-step CUDA events",
                        "graph": "step replayed from CUDA graphs", "replicas_bit_identical": replicas_equal,
@@ -357,12 +403,12 @@ def run_ours(args):
             "e2e": {"value": images / e2e_s, "unit": UNIT, "h2d_bytes_per_step": trainer.h2d_bytes,
                     "d2h_bytes_per_step": trainer.d2h_bytes, "ms_per_step": e2e_s / args.steps * 1e3},
             "gpu_launches": launches_per_step * args.steps,
-            "roofline": {"bound": "tensor", "kernel": "umma_gemm_kernel<BN, fused> (conv forward + error-backward with fused "
-                                                       "requantisation, tcgen05 kind::i8), all 10 conv calls of a step",
+            "roofline": {"bound": "tensor", "kernel": "umma_parked_kernel / umma_gemm_kernel<fused> (conv forward + error-backward, "
+                                                       "requantisation in the kernel, tcgen05 kind::i8), all 10 such calls of a step",
                          "achieved": achieved, "peak": peak_tops, "unit": "TOP/s", "frac": achieved / peak_tops,
-                         "traffic": None, "launches_timed": tc_launches * 10, "avg_launch_us": tc_time / max(tc_launches, 1) * 1e6,
+                         "traffic": NCU_TRAFFIC_BYTES, "traffic_of": NCU_TRAFFIC_OF, "launches_timed": tc_launches * 10, "avg_launch_us": tc_time / max(tc_launches, 1) * 1e6,
                          "per_layer": per_layer,
-                         "timing": "each call (kernel + 1-thread verify kernel + no-op redo launch) x10 in a CUDA graph, CUDA events around the replay",
+                         "timing": "each call (one launch; two for the layers whose tiles do not fit in tensor memory) x10 in a CUDA graph, CUDA events around the replay",
                          "peak_source": f"2 x bf16_tflops_sustained ({src}); dense int8 rate is twice bf16 on this part"},
             "kernels_eager_step": {k: {"launches": v[0], "ms": v[1] * 1e3,
                                        "tops": (v[2] / v[1] / 1e12 if v[1] > 0 and v[2] else None),
@@ -483,7 +529,7 @@ def run_sweep(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
