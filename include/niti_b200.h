@@ -189,7 +189,11 @@ NITI_API int niti_conv_dgrad_requant_i8(const int8_t* err, const int8_t* w, int8
                        int N, int H, int W, int C, int K, int R, int S, int pad,
                        int round_mode, const uint64_t* seed, uint32_t rng_stream, uint64_t rng_offset,
                        const int32_t* exp_a, const int32_t* exp_b, int32_t* exp_out, int32_t* shift_out,
-                       int32_t* status, void* stream);
+                       const int8_t* relu_mask, int32_t* status, void* stream);
+/* relu_mask (may be null): the int8 tensor [N][H][W][C] this layer received in the forward pass, i.e. the output of
+ * the ReLU in front of it.  Where it is <= 0 the error is zeroed: TiReLU.backward (ti_torch.py:279-290) folded into
+ * the kernel.  The mask is applied after the requantisation, so the shift is that of the unmasked error, exactly as
+ * when the two run one after the other. */
 
 /* int8mm_cuda.int8_mm (int8mm.cpp:9-18, int8mm_kernel.cu:8-34) as used by TiLinear
  * (ti_torch.py:241-266), without the padding / .contiguous() copies around it:

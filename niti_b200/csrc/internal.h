@@ -22,6 +22,7 @@ struct FusedArgs {
     unsigned long long rng_offset;
     int kind, target_bits;
     const int32_t* exp_a; const int32_t* exp_b; int32_t* exp_out; int32_t* shift_out;
+    const int8_t* relu_mask;  // optional, same shape as the output: zero the output where this tensor is <= 0
 };
 
 extern int g_two_cta;    // CTA pairs (cta_group::2) where the shape allows: bit 0 for GEMMs, bit 1 for convolutions

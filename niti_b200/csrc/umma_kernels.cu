@@ -85,6 +85,7 @@ struct GemmParams {
     int kind, target_bits;
     const int32_t* exp_a; const int32_t* exp_b; int32_t* exp_out; int32_t* shift_out;
     int mode, relu;
+    const int8_t* mask;    // fused kernels: optional ReLU-backward mask, same shape as the output (zero where mask <= 0)
     const unsigned long long* seed;
     unsigned rng_stream;
     unsigned long long rng_offset;
@@ -405,6 +406,18 @@ __device__ __forceinline__ void narrow32(const uint32_t (&v)[32], uint32_t (&pac
         }
     }
 }
+// ReLU backward folded into an error-backward epilogue: zero the packed int8 outputs where the layer's forward input
+// (the ReLU's output) was not positive.  `m` points at this row's mask bytes for the same columns; `cols` of them exist.
+template <int WORDS>
+__device__ __forceinline__ void apply_relu_mask(uint32_t (&packed)[WORDS], const int8_t* m, int cols) {
+#pragma unroll
+    for (int q = 0; q < WORDS / 4; ++q)
+        if (16 * q + 16 <= cols) {
+            const uint4 x = __ldg(reinterpret_cast<const uint4*>(m) + q);
+            packed[4 * q + 0] &= __vcmpgts4(x.x, 0); packed[4 * q + 1] &= __vcmpgts4(x.y, 0);
+            packed[4 * q + 2] &= __vcmpgts4(x.z, 0); packed[4 * q + 3] &= __vcmpgts4(x.w, 0);
+        }
+}
 // a 32-byte piece (chunk j of the row's 128 bytes) at its 128-byte-swizzled place in the staging tile
 __device__ __forceinline__ void stage_piece(uint32_t buf, int row, int j, const uint32_t (&w)[8]) {
     const uint32_t base = buf + static_cast<uint32_t>(row) * 128u;
@@ -631,6 +644,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                                 packed[j * 8 + (i >> 2)] = narrow4(&v[j][i], shift, p.mode, p.relu, rnd);
                             }
                     }
+                    if (p.mask != nullptr && valid) apply_relu_mask<32>(packed, p.mask + row_lin * p.N + col0 + g0, lim);
                     if (leader) bulk_wait_read<0>();  // the previous store has read the staging tile
                     named_barrier(bar_id, 128);
                     stage_row(buf, row_in_tile, packed);
@@ -884,6 +898,7 @@ umma_parked_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
                     tmem_ld_32x32(taddr + j * 32, v);
                     tmem_ld_wait();
                     narrow32(v, packed, shift, p.mode, p.relu, seed, p.rng_stream, e0 + 32 * j);
+                    if (p.mask != nullptr && ri.valid) apply_relu_mask<8>(packed, p.mask + ri.row_lin * p.N + col + 32 * j, p.N - col - 32 * j);
                     stage_piece(buf, row_in_tile, j, packed);
                 }
                 fence_proxy_async();
@@ -1248,6 +1263,7 @@ static void set_fused(GemmParams* p, const FusedArgs* f) {
     p->seed = f->seed; p->rng_stream = f->rng_stream; p->rng_offset = f->rng_offset;
     p->kind = f->kind; p->target_bits = f->target_bits;
     p->exp_a = f->exp_a; p->exp_b = f->exp_b; p->exp_out = f->exp_out; p->shift_out = f->shift_out;
+    p->mask = f->relu_mask;
     // max|acc| lives in state[1]; a redo launch must leave it alone (the last CTA of the first launch zeroed it)
     p->maxabs = f->only_if_redo ? nullptr : reinterpret_cast<unsigned*>(f->state + 1);
 }

@@ -155,9 +155,11 @@ def conv_fprop_fused(x, w, state, pad=1, mode=ROUND_NEAREST, seed=None, rng_stre
     return y8, exp_out, shift_out
 
 
-def conv_dgrad_fused(err, w, state, pad=1, mode=ROUND_NEAREST, seed=None, rng_stream=0, rng_offset=0, exp_a=None, exp_b=None):
-    """Error-backward convolution + err_calc in one pass.  Returns (int8 [N,H,W,C], exp_out, shift)."""
-    _need_cuda(err, w, state)
+def conv_dgrad_fused(err, w, state, pad=1, mode=ROUND_NEAREST, seed=None, rng_stream=0, rng_offset=0, exp_a=None, exp_b=None,
+                     relu_mask=None):
+    """Error-backward convolution + err_calc in one pass (+ the backward of the ReLU in front of the layer when
+    relu_mask, the layer's forward input, is given).  Returns (int8 [N,H,W,C], exp_out, shift)."""
+    _need_cuda(err, w, state, relu_mask)
     N, H, W, K = err.shape
     K2, R, S, C = w.shape
     e8 = torch.empty((N, H, W, C), dtype=torch.int8, device=err.device)
@@ -165,7 +167,8 @@ def conv_dgrad_fused(err, w, state, pad=1, mode=ROUND_NEAREST, seed=None, rng_st
     shift_out = torch.empty((), dtype=torch.int32, device=err.device)
     _call("niti_conv_dgrad_requant_i8", 2, 2 * N * H * W * K * R * S * C, err.numel() + w.numel() + e8.numel(),
           lib.niti_conv_dgrad_requant_i8, _p(err), _p(w), _p(e8), _p(state), N, H, W, C, K, R, S, pad, mode, _p(seed),
-          rng_stream, rng_offset, _p(exp_a), _p(exp_b), _p(exp_out), _p(shift_out), _p(status_word(err.device)), _st())
+          rng_stream, rng_offset, _p(exp_a), _p(exp_b), _p(exp_out), _p(shift_out), _p(relu_mask),
+          _p(status_word(err.device)), _st())
     return e8, exp_out, shift_out
 
 

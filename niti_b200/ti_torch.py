@@ -214,8 +214,8 @@ class TiReLU(Module):
     def __init__(self, fused=False):
         super(TiReLU, self).__init__()
         self.fused = fused
-        # set by a model builder when the next layer (a TiMaxpool2d with relu_backward_fused) applies this
-        # ReLU's backward mask itself
+        # set by a model builder when the next layer (a TiMaxpool2d or TiConv2d with relu_backward_fused) applies
+        # this ReLU's backward mask itself
         self.backward_in_next_layer = False
 
     def forward(self, input):
@@ -307,6 +307,9 @@ class TiConv2d(UpdateWeight):
         self.stride = stride
         self.padding = padding
         self.fuse_relu = fuse_relu
+        # True when this layer's input is the output of a TiReLU whose backward mask this layer's error-backward
+        # kernel applies (set by a model builder together with that TiReLU's backward_in_next_layer)
+        self.relu_backward_fused = False
         # shift predictions of the fused conv + requantisation kernels (forward, error-backward)
         self._fwd_state = None
         self._bwd_state = None
@@ -344,12 +347,15 @@ class TiConv2d(UpdateWeight):
                 err_out, self.err_exp, _ = ops.conv_dgrad_fused(err_in, self.weight, self._bwd_state, self.padding,
                                                                 _mode(ERROR_ROUND_METHOD), RNG_SEED(err_in.device),
                                                                 16 * self.layer_id + 1, SAMPLE_OFFSET * per,
-                                                                exp_tensor(self.err_exp, err_in.device), self.weight_exp)
+                                                                exp_tensor(self.err_exp, err_in.device), self.weight_exp,
+                                                                relu_mask=self.act if self.relu_backward_fused else None)
             else:
                 acc, mx = ops.conv_dgrad_acc(err_in, self.weight, self.padding)
                 err_out, self.err_exp, _ = _calc(acc, ops.CALC_ERR, BITWIDTH, ERROR_ROUND_METHOD, 16 * self.layer_id + 1,
                                                  exp_tensor(self.err_exp, acc.device), self.weight_exp, mx, False,
                                                  SAMPLE_OFFSET * per)
+                if self.relu_backward_fused:
+                    err_out = ops.relu_bwd(self.act, err_out)
         K, R, S, C = self.weight.shape
         if (self.grad_accumulate and self.defer_update and self.grad_buffer is not None
                 and ops.conv_wgrad_accumulate_supported(C, K, R, S, self.padding)):

@@ -43,8 +43,12 @@ class TiVGG_cifar(TiNet):
                 layers += [pool]
                 image_size = image_size // 2
             else:
-                layers += [TiConv2d(in_channels, x, first_layer=(idx == 0), fuse_relu=fuse_relu),
-                           TiReLU(fused=fuse_relu)]
+                conv = TiConv2d(in_channels, x, first_layer=(idx == 0), fuse_relu=fuse_relu)
+                if fuse_relu and layers and isinstance(layers[-1], TiReLU):
+                    # conv -> ReLU -> conv: the second convolution's error-backward kernel applies the ReLU's mask
+                    layers[-1].backward_in_next_layer = True
+                    conv.relu_backward_fused = True
+                layers += [conv, TiReLU(fused=fuse_relu)]
                 in_channels = x
         layers += [TiFlat()]
         if dropout:

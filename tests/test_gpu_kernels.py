@@ -407,3 +407,26 @@ def test_conv_wgrad_accumulates_into_the_gradient(N, H, W, C, K):
     ops.conv_wgrad_accumulate(cu(x), cu(e), g)
     want = O.conv_wgrad(x, e, 3, 3, 1)
     assert_same(g, (base.astype(np.int64) + 2 * want).astype(np.int32), "accumulating weight gradient")
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("N,H,W,C,K,parking", [(8, 16, 16, 128, 256, True), (4, 8, 8, 256, 128, True), (16, 32, 32, 128, 128, False),
+                                               (3, 10, 6, 144, 64, True)])
+def test_conv_dgrad_fused_applies_relu_mask(N, H, W, C, K, parking):
+    """Error-backward + requantisation + the backward of the ReLU in front of the layer in one kernel: the shift is
+    that of the UNMASKED error, the mask zeroes where the layer's forward input was not positive."""
+    rng = np.random.default_rng(N * H + C)
+    err, w = rnd8(rng, (N, H, W, K)), rnd8(rng, (K, 3, 3, C))
+    x = np.maximum(rnd8(rng, (N, H, W, C)), 0)  # a ReLU output: about half zeros
+    old = ops.set_accumulator_parking(parking)
+    try:
+        ea = torch.zeros((), dtype=torch.int32, device=DEV)
+        st = ops.new_requant_state(DEV)
+        for _ in range(2):  # second call: the shift prediction of the streaming kernel is right
+            got, _, shift = ops.conv_dgrad_fused(cu(err), cu(w), st, 1, 0, None, 0, 0, ea, ea, relu_mask=cu(x))
+    finally:
+        ops.set_accumulator_parking(old)
+    acc = O.conv_dgrad(err, w, 1)
+    want, s = O.err_calc(acc)
+    assert int(shift) == s
+    assert_same(got, np.where(x > 0, want, 0).astype(np.int8), "dgrad + requant + relu mask")
