@@ -16,6 +16,21 @@ from . import ops, ti_torch
 from .dp import GradBucket
 
 
+class StepResult:
+    """What ``Trainer.step`` returns: unpacks as ``(logits, exponent)`` (pinned host tensors) and carries the
+    event after which they are valid, so a caller can read step i's logits while step i+1 is already running."""
+
+    def __init__(self, out, exp, done):
+        self.out, self.exp, self.done = out, exp, done
+
+    def __iter__(self):
+        return iter((self.out, self.exp))
+
+    def wait(self):
+        self.done.synchronize()
+        return self.out, self.exp
+
+
 class Trainer:
     def __init__(self, model, local_batch, device, group=None, rank=0, world=1, use_graph=True, seed=0,
                  in_shape=(3, 32, 32), warmup_steps=2, overlap_comm=False, keep_gradients=False, wgrad_side_stream=True):
@@ -49,12 +64,25 @@ class Trainer:
                     l.grad_ready = (lambda layer, span=first_of[i]: self._start_allreduce(span))
         self.x = torch.zeros((local_batch,) + tuple(in_shape), dtype=torch.float32, device=self.device)
         self.t = torch.zeros((local_batch,), dtype=torch.int64, device=self.device)
-        self.out_host = torch.zeros((local_batch, self.layers[-1].weight.shape[0]), dtype=torch.int8).pin_memory()
-        self.exp_host = torch.zeros((), dtype=torch.int32).pin_memory()
+        # two result slots, used alternately: step i's logits stay readable while step i+1 writes the other slot
+        self._out_hosts = [torch.zeros((local_batch, self.layers[-1].weight.shape[0]), dtype=torch.int8).pin_memory() for _ in range(2)]
+        self._exp_hosts = [torch.zeros((), dtype=torch.int32).pin_memory() for _ in range(2)]
+        self._done = [torch.cuda.Event() for _ in range(2)]
+        self._res_slot = 0
+        self.out_host, self.exp_host = self._out_hosts[0], self._exp_hosts[0]
         self.h2d_bytes = self.x.numel() * 4 + self.t.numel() * 8
         self.d2h_bytes = self.out_host.numel() + 4
         ti_torch.set_seed(seed, self.device)
         ti_torch.SAMPLE_OFFSET = rank * local_batch
+        # input prefetch: two staging slots filled from pinned host memory on a copy stream while the previous step computes
+        self.copy_stream = torch.cuda.Stream(device=self.device)
+        self._stage_x = [torch.zeros_like(self.x) for _ in range(2)]
+        self._stage_t = [torch.zeros_like(self.t) for _ in range(2)]
+        self._slot_ready = [torch.cuda.Event() for _ in range(2)]
+        self._slot_free = [torch.cuda.Event() for _ in range(2)]
+        for e in self._slot_free:
+            e.record(torch.cuda.current_stream(self.device))
+        self._pf_slot, self._pf_key = 0, None
         self._graphs = None
         self._eager_steps = 0
         self._warmup_steps = warmup_steps
@@ -118,16 +146,42 @@ class Trainer:
             self._eager_steps += 1
 
     # ------------------------------------------------------------------ public call
-    def step(self, x_host, target_host):
+    def prefetch(self, x_host, target_host):
+        """Start the host-to-device copy of a LATER batch now (on a copy stream, into a staging slot), so that it
+        overlaps the step in flight; ``step`` recognises the batch by its host buffers and takes it from the slot."""
+        slot = self._pf_slot = 1 - self._pf_slot
+        self.copy_stream.wait_event(self._slot_free[slot])  # the step that used this slot has copied it out
+        with torch.cuda.stream(self.copy_stream):
+            self._stage_x[slot].copy_(x_host, non_blocking=True)
+            self._stage_t[slot].copy_(target_host, non_blocking=True)
+            self._slot_ready[slot].record(self.copy_stream)
+        self._pf_key = (x_host.data_ptr(), target_host.data_ptr(), slot)
+
+    def step(self, x_host, target_host, prefetch_next=None):
         """x_host float32 [B,3,32,32] and target_host int64 [B] in (pinned) host memory.
         Returns (pinned int8 logits [B, classes], pinned int32 exponent); valid after the
-        stream is synchronised (``Trainer.sync``)."""
-        self.x.copy_(x_host, non_blocking=True)
-        self.t.copy_(target_host, non_blocking=True)
+        stream is synchronised (``Trainer.sync``).  ``prefetch_next=(x, t)``: the next batch, whose copy
+        then runs beside this step's kernels."""
+        main = torch.cuda.current_stream(self.device)
+        if self._pf_key is not None and self._pf_key[:2] == (x_host.data_ptr(), target_host.data_ptr()):
+            slot = self._pf_key[2]
+            self._pf_key = None
+            main.wait_event(self._slot_ready[slot])
+            self.x.copy_(self._stage_x[slot], non_blocking=True)
+            self.t.copy_(self._stage_t[slot], non_blocking=True)
+            self._slot_free[slot].record(main)
+        else:
+            self.x.copy_(x_host, non_blocking=True)
+            self.t.copy_(target_host, non_blocking=True)
+        if prefetch_next is not None:
+            self.prefetch(*prefetch_next)
         self.run_device_step()
+        k = self._res_slot = 1 - self._res_slot
+        self.out_host, self.exp_host = self._out_hosts[k], self._exp_hosts[k]
         self.out_host.copy_(self.model.out, non_blocking=True)
         self.exp_host.copy_(self.model.out_exp, non_blocking=True)
-        return self.out_host, self.exp_host
+        self._done[k].record(main)
+        return StepResult(self.out_host, self.exp_host, self._done[k])
 
     def sync(self):
         torch.cuda.synchronize(self.device)

@@ -45,14 +45,22 @@ def build(cfg, seed, dropout, fuse_relu, mu):
     return model, oracle, rng
 
 
-def run_steps(cfg, B, seed, dropout, steps, mu, fuse_relu, use_graph, rec=None, keep_gradients=True):
-    """keep_gradients: compare every layer's int32 gradient too (the default trainer zeroes them in its update launch)."""
+def run_steps(cfg, B, seed, dropout, steps, mu, fuse_relu, use_graph, rec=None, keep_gradients=True, prefetch=False):
+    """keep_gradients: compare every layer's int32 gradient too (the default trainer zeroes them in its update launch).
+    prefetch: hand every step the next batch, whose host-to-device copy then overlaps the step."""
     model, oracle, rng = build(cfg, seed, dropout, fuse_relu, mu)
     tr = Trainer(model, B, DEV, use_graph=use_graph, seed=seed, warmup_steps=1, keep_gradients=keep_gradients)
+    data = []
     for step in range(steps):
         x = synth_images(rng, B)
         tgt = rng.integers(0, 10, size=B)
-        out_h, exp_h = tr.step(torch.from_numpy(x).pin_memory(), torch.from_numpy(tgt).pin_memory())
+        data.append((x, tgt, torch.from_numpy(x).pin_memory(), torch.from_numpy(tgt).pin_memory()))
+    if prefetch:
+        tr.prefetch(data[0][2], data[0][3])
+    for step in range(steps):
+        x, tgt, xh, th = data[step]
+        nxt = (data[step + 1][2], data[step + 1][3]) if prefetch and step + 1 < steps else None
+        out_h, exp_h = tr.step(xh, th, prefetch_next=nxt)
         tr.sync()
         x8, xe = O.float_to_int8(x)
         want, want_e = oracle.forward(np.ascontiguousarray(x8.transpose(0, 2, 3, 1)), xe, step=step)
@@ -90,7 +98,8 @@ def test_vgg7_three_steps_graph_replay(keep_gradients):
     """Eager warm-up step, capture, then replays: the captured step must keep matching the oracle, with the
     gradients kept for comparison and in the default mode (accumulating weight-gradient kernels, bucket cleared
     by the update launch)."""
-    run_steps([128, 128, "M", 256, 256, "M", 512, 512, "M"], 8, 4321, True, 3, 5, True, True, keep_gradients=keep_gradients)
+    run_steps([128, 128, "M", 256, 256, "M", 512, 512, "M"], 8, 4321, True, 3, 5, True, True, keep_gradients=keep_gradients,
+              prefetch=not keep_gradients)
 
 
 def test_golden_net_default_trainer_mode(golden_dir):
