@@ -315,6 +315,13 @@ NITI_API int niti_fc_head_train_i8(const niti_fc_head_args* args, void* stream);
 NITI_API int niti_quantize_input_f32(const float* x, int8_t* x8, int32_t* exp_out, uint32_t* scratch,
                             int N, int C, int H, int W, void* stream);
 
+/* The two halves of niti_quantize_input_f32, for callers that put something between them: *maxbits = the IEEE bit
+ * pattern of max |x| (non-negative floats order like their bit patterns, so a MAX reduction over ranks on the
+ * uint32 word gives the global maximum: what the global-exact data-parallel mode does). */
+NITI_API int niti_absmax_f32(const float* x, int64_t n, uint32_t* maxbits, void* stream);
+NITI_API int niti_quantize_input_with_max_f32(const float* x, int8_t* x8, int32_t* exp_out, const uint32_t* maxbits,
+                                     int N, int C, int H, int W, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1003,6 +1003,23 @@ extern "C" int niti_update_multi_i8(const niti_update_item* items, int count, in
     return NITI_OK;
 }
 
+extern "C" int niti_absmax_f32(const float* x, int64_t n, uint32_t* maxbits, void* stream) {
+    NITI_REQUIRE(x && maxbits && n > 0);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (int e = set_cuda_error(cudaMemsetAsync(maxbits, 0, 4, st))) return e;
+    absmax_f32_kernel<<<blocks_for(n, 256, sm_count_simt() * 4), 256, 0, st>>>(x, n, maxbits);
+    return set_cuda_error(cudaGetLastError());
+}
+
+extern "C" int niti_quantize_input_with_max_f32(const float* x, int8_t* x8, int32_t* exp_out, const uint32_t* maxbits, int N,
+                                                int C, int H, int W, void* stream) {
+    NITI_REQUIRE(x && x8 && exp_out && maxbits && N > 0 && C > 0 && H > 0 && W > 0);
+    const long long n = static_cast<long long>(N) * C * H * W;
+    quantize_input_kernel<<<blocks_for(n, 256, sm_count_simt() * 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        x, x8, exp_out, maxbits, N, C, H, W);
+    return set_cuda_error(cudaGetLastError());
+}
+
 extern "C" int niti_quantize_input_f32(const float* x, int8_t* x8, int32_t* exp_out, uint32_t* scratch, int N, int C,
                                        int H, int W, void* stream) {
     NITI_REQUIRE(x && x8 && exp_out && scratch && N > 0 && C > 0 && H > 0 && W > 0);

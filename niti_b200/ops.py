@@ -359,13 +359,20 @@ def update_multi(ws, g32s, streams, mu, mode=ROUND_PSEUDO_STOCHASTIC, seed=None,
     return mx
 
 
-def quantize_input(x):
-    """float32 NCHW -> (int8 NHWC, exponent)."""
+def quantize_input(x, reduce_max=None):
+    """float32 NCHW -> (int8 NHWC, exponent).  ``reduce_max(t)``: optional hook that replaces the int32[1] word
+    holding the bit pattern of max|x| by its maximum over a process group, in place."""
     _need_cuda(x)
     assert x.dtype == torch.float32
     N, C, H, W = x.shape
     x8 = torch.empty((N, H, W, C), dtype=torch.int8, device=x.device)
     e = torch.empty((), dtype=torch.int32, device=x.device)
     tmp = torch.empty(1, dtype=torch.int32, device=x.device)
+    if reduce_max is not None:
+        _call("niti_absmax_f32", 1, 0, 4 * x.numel(), lib.niti_absmax_f32, _p(x), x.numel(), _p(tmp), _st())
+        reduce_max(tmp)
+        _call("niti_quantize_input_with_max_f32", 1, 0, 5 * x.numel(), lib.niti_quantize_input_with_max_f32, _p(x), _p(x8), _p(e),
+              _p(tmp), N, C, H, W, _st())
+        return x8, e
     _call("niti_quantize_input_f32", 2, 0, 9 * x.numel(), lib.niti_quantize_input_f32, _p(x), _p(x8), _p(e), _p(tmp), N, C, H, W, _st())
     return x8, e

@@ -52,7 +52,8 @@ class TiNet(Module):
         """(number of head layers, has dropout) if the network ends in [TiDropout,] TiLinear of a size the
         one-kernel classifier head takes, else None."""
         layers = list(self.forward_layers)
-        if not (ti_torch.FUSE_HEAD and ti_torch.TRAINING and layers and isinstance(layers[-1], TiLinear)):
+        if not (ti_torch.FUSE_HEAD and ti_torch.TRAINING and ti_torch.GLOBAL_MAX_GROUP is None and layers
+                and isinstance(layers[-1], TiLinear)):
             return None
         drop = len(layers) >= 2 and isinstance(layers[-2], TiDropout)
         J, F = layers[-1].weight.shape

@@ -128,10 +128,18 @@ def weight_quant(input):
     return round_val, exp_tensor(act_exp)
 
 
+def _global_max(word):
+    """Global-exact data-parallel mode: replace a max word by its maximum over GLOBAL_MAX_GROUP, in place."""
+    import torch.distributed as dist
+    dist.all_reduce(word, op=dist.ReduceOp.MAX, group=None if GLOBAL_MAX_GROUP is True else GLOBAL_MAX_GROUP)
+
+
 def _calc(int32_acc, kind, target_bits, method, stream, exp_a=None, exp_b=None, maxabs=None, relu=False, offset=0):
     acc = int32_acc.contiguous()
     if maxabs is None:
         maxabs = ops.absmax(acc)
+    if GLOBAL_MAX_GROUP is not None and kind != ops.CALC_GRAD:
+        _global_max(maxabs)  # activations / errors of the whole (sharded) batch share one shift
     return ops.requant(acc, maxabs, kind, target_bits, _mode(method), RNG_SEED(acc.device), stream, offset,
                        relu=relu, exp_a=exp_a, exp_b=exp_b, want_shift=True)
 
@@ -275,9 +283,10 @@ def TiFloatToInt8(input):
     """float tensor -> (int8, exponent) with exponent = ceil(log2(max|x|)) - 7 (:341-356).
     4-D inputs are taken as NCHW and returned NHWC (the permute of ti_net.py:19 is fused in)."""
     x = input.to(GPU, dtype=torch.float32).contiguous()
+    hook = _global_max if GLOBAL_MAX_GROUP is not None else None
     if x.dim() == 4:
-        return ops.quantize_input(x)
-    q, e = ops.quantize_input(x.reshape(1, 1, 1, -1))
+        return ops.quantize_input(x, hook)
+    q, e = ops.quantize_input(x.reshape(1, 1, 1, -1), hook)
     return q.reshape(x.shape), e
 
 
@@ -318,7 +327,7 @@ class TiConv2d(UpdateWeight):
         self.act, self.act_in_exp = input
         K, R, S, C = self.weight.shape
         per = self.act.shape[1] * self.act.shape[2] * K
-        if FUSE_REQUANT and self.stride == 1 and ops.conv_fprop_fused_supported(C, K, R, S, self.padding):
+        if FUSE_REQUANT and GLOBAL_MAX_GROUP is None and self.stride == 1 and ops.conv_fprop_fused_supported(C, K, R, S, self.padding):
             # conv2d_int8 + act_calc (:393-395) in one kernel; see ops.conv_fprop_fused
             if self._fwd_state is None:
                 self._fwd_state = ops.new_requant_state(self.act.device)
@@ -341,7 +350,7 @@ class TiConv2d(UpdateWeight):
             # the reference builds flip(w).transpose(0,3) here (:404); the kernels read w in place
             K, R, S, C = self.weight.shape
             per = self.act[0].numel()
-            if FUSE_REQUANT and ops.conv_dgrad_fused_supported(C, K, R, S, self.padding):
+            if FUSE_REQUANT and GLOBAL_MAX_GROUP is None and ops.conv_dgrad_fused_supported(C, K, R, S, self.padding):
                 if self._bwd_state is None:
                     self._bwd_state = ops.new_requant_state(err_in.device)
                 err_out, self.err_exp, _ = ops.conv_dgrad_fused(err_in, self.weight, self._bwd_state, self.padding,
@@ -411,6 +420,11 @@ FUSE_HEAD = True       # TiNet.train_step runs [dropout,] FC, loss, FC backward 
 GRAD_BITWIDTH = 5      # the reference's training loop injects this per epoch (main.py:73-77)
 TRAINING = True        # likewise (main.py:147-149)
 SAMPLE_OFFSET = 0      # global index of this process's first sample (data-parallel shards)
+# Global-exact data-parallel mode: a torch.distributed group (or True for the default group).  Every tensor-wide
+# maximum behind an activation / error shift (and the input quantisation) is MAX-reduced over the group, so k ranks on
+# shards of a batch compute exactly what one rank computes on the whole batch.  The convolutions then take the
+# two-pass route (int32 accumulators, all-reduce of one word, requantise) and the classifier head runs layer by layer.
+GLOBAL_MAX_GROUP = None
 
 _seed_words = {}
 

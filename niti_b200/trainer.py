@@ -33,11 +33,18 @@ class StepResult:
 
 class Trainer:
     def __init__(self, model, local_batch, device, group=None, rank=0, world=1, use_graph=True, seed=0,
-                 in_shape=(3, 32, 32), warmup_steps=2, overlap_comm=False, keep_gradients=False, wgrad_side_stream=True):
+                 in_shape=(3, 32, 32), warmup_steps=2, overlap_comm=False, keep_gradients=False, wgrad_side_stream=True,
+                 global_exact=False):
         self.model, self.device, self.group = model, torch.device(device), group
         self.rank, self.world, self.use_graph = rank, world, use_graph
         self.local_batch = local_batch
         self.keep_gradients = keep_gradients
+        # global-exact mode: every activation / error maximum is MAX-reduced over the ranks, so the ranks together
+        # compute bit for bit what one process computes on the whole batch (eager execution, two-pass requantisation)
+        self.global_exact = bool(global_exact) and world > 1
+        if self.global_exact:
+            ti_torch.GLOBAL_MAX_GROUP = group if group is not None else True
+            self.use_graph = use_graph = False
         # weight-gradient kernels run beside the error-backward kernels on a second stream (joined before the update)
         self.side = torch.cuda.Stream(device=self.device) if (wgrad_side_stream and not keep_gradients and not overlap_comm) else None
         self.layers = model.weighted_layers()

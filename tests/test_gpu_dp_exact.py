@@ -1,0 +1,89 @@
+"""Global-exact data-parallel mode on a GPU: two processes, each with half of a batch, compute bit for bit what one
+process (the oracle) computes on the whole batch.  Both ranks share cuda:0 and talk over gloo (host-side collectives
+only; no kernel of one rank waits for a kernel of the other)."""
+import os
+import socket
+
+import numpy as np
+import pytest
+import torch
+import torch.multiprocessing as mp
+
+from oracle import niti_oracle as O
+from tests.golden.make_golden import synth_images, xavier_exp
+
+pytestmark = pytest.mark.gpu
+
+CFG = [128, "M", 128, "M", 512, "M"]
+GLOBAL_BATCH, STEPS, SEED = 8, 2, 31
+
+
+def _data():
+    rng = np.random.default_rng(SEED)
+    shapes, cin = [], 3
+    for c in CFG:
+        if c != "M":
+            shapes.append((c, 3, 3, cin))
+            cin = c
+    shapes.append((10, 8192))
+    weights = [rng.integers(-127, 128, size=s).astype(np.int8) for s in shapes]
+    batches = [(synth_images(rng, GLOBAL_BATCH), rng.integers(0, 10, size=GLOBAL_BATCH)) for _ in range(STEPS)]
+    return shapes, weights, [xavier_exp(s) for s in shapes], batches
+
+
+def _worker(rank, world, port, q):
+    import torch.distributed as dist
+    from niti_b200 import ti_torch, ti_vgg
+    from niti_b200.dp import shard_range
+    from niti_b200.trainer import Trainer
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        shapes, weights, wexps, batches = _data()
+        ti_torch.GRAD_BITWIDTH, ti_torch.TRAINING = 5, True
+        model = ti_vgg.TiVGG_cifar(list(CFG), dropout=True, fuse_relu=True)
+        for l, w, e in zip(model.weighted_layers(), weights, wexps):
+            l.weight = torch.from_numpy(w).to("cuda:0")
+            l.weight_exp = ti_torch.exp_tensor(e, "cuda:0")
+        lo, hi = shard_range(GLOBAL_BATCH, rank, world)
+        tr = Trainer(model, hi - lo, "cuda:0", rank=rank, world=world, use_graph=False, seed=SEED, global_exact=True)
+        ti_torch.SAMPLE_OFFSET = lo
+        logits = []
+        for x, t in batches:
+            out, exp = tr.step(torch.from_numpy(x[lo:hi].copy()).pin_memory(), torch.from_numpy(t[lo:hi].copy()).pin_memory())
+            tr.sync()
+            logits.append((out.numpy().copy(), int(exp)))
+        q.put((rank, lo, hi, logits, [l.weight.cpu().numpy().tobytes() for l in model.weighted_layers()]))
+    finally:
+        ti_torch.GLOBAL_MAX_GROUP = None
+        dist.destroy_process_group()
+
+
+def test_two_ranks_equal_one_process_on_the_whole_batch():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    results = [q.get(timeout=240) for _ in procs]
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    shapes, weights, wexps, batches = _data()
+    net = O.Net(CFG, weights, wexps, dropout=True, mu=5, seed=SEED)
+    want = []
+    for step, (x, t) in enumerate(batches):
+        x8, xe = O.float_to_int8(x)
+        out, e = net.forward(np.ascontiguousarray(x8.transpose(0, 2, 3, 1)), xe, step=step)
+        net.backward(t, step=step)
+        want.append((out, e))
+    for rank, lo, hi, logits, wbytes in results:
+        for step in range(STEPS):
+            assert np.array_equal(logits[step][0], want[step][0][lo:hi]), f"rank {rank} step {step}: logits"
+            assert logits[step][1] == want[step][1]
+        for i, b in enumerate(wbytes):
+            assert b == net.w[i].tobytes(), f"rank {rank}: weights of layer {i}"

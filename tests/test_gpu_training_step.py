@@ -171,3 +171,31 @@ def test_state_dict_roundtrip_reference_format():
     model2.load_state_dict(ref_style)
     for a, b in zip(model.weighted_layers(), model2.weighted_layers()):
         assert torch.equal(a.weight, b.weight) and int(a.weight_exp) == int(b.weight_exp)
+
+
+def test_eval_mode_forward_and_topk_accuracy():
+    """Forward-only use (main.py:82-83 with TRAINING False): TiDropout is the identity and adds nothing to the
+    exponent (ti_torch.py:449-450); logits equal the oracle's network without dropout; top-k as meters.accuracy."""
+    from niti_b200.meters import accuracy
+    cfg = [128, "M", 128, "M", 512, "M"]
+    model, _, rng = build(cfg, 5, True, True, 5)
+    weights = [l.weight.cpu().numpy() for l in model.weighted_layers()]
+    wexps = [int(l.weight_exp) for l in model.weighted_layers()]
+    oracle = O.Net(cfg, weights, wexps, dropout=False, mu=5, seed=5)
+    x = synth_images(rng, 6)
+    tgt = rng.integers(0, 10, size=6)
+    try:
+        ti_torch.TRAINING = False
+        out, out_exp = model(torch.from_numpy(x).to(DEV))
+    finally:
+        ti_torch.TRAINING = True
+    x8, xe = O.float_to_int8(x)
+    want, want_e = oracle.forward(np.ascontiguousarray(x8.transpose(0, 2, 3, 1)), xe, step=0)
+    assert np.array_equal(out.cpu().numpy(), want) and int(out_exp) == want_e
+    top1, top3 = accuracy(out, torch.from_numpy(tgt).to(DEV), (1, 3))
+    w32 = want.astype(np.int32)
+    own = w32[np.arange(6), tgt][:, None]
+    for k, got in ((1, float(top1)), (3, float(top3))):
+        sure = 100.0 * np.mean(((w32 >= own).sum(1) - 1) < k)        # hits whatever the order among equal logits
+        maybe = 100.0 * np.mean((w32 > own).sum(1) < k)              # hits under the most favourable order
+        assert sure - 1e-4 <= got <= maybe + 1e-4, (k, got, sure, maybe)
