@@ -113,23 +113,32 @@ __device__ __forceinline__ void report_abort(int32_t* status, int code, int role
 }
 
 // Four accumulators of one row -> four int8 packed in a word (NITI's shift, see requant.cuh).
-// Round-to-nearest (the default of activations and errors) gets a short branch-free form:
-// round half away from zero on |x|, clamp to 127, restore the sign (ReLU: negatives become 0).
+// Round-to-nearest (the default of activations and errors) gets a short branch-free form, below.
+// Two int32 -> two saturated bytes in the low half of the result, `upper` moved into the high half
+// (cvt.pack: d = upper << 16 | sat(hi) << 8 | sat(lo)).
+__device__ __forceinline__ uint32_t pack2_sat_s8(int hi, int lo, uint32_t upper) {
+    uint32_t d;
+    asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(hi), "r"(lo), "r"(upper));
+    return d;
+}
+__device__ __forceinline__ uint32_t pack2_sat_u8(int hi, int lo, uint32_t upper) {
+    uint32_t d;
+    asm("cvt.pack.sat.u8.s32.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(hi), "r"(lo), "r"(upper));
+    return d;
+}
+// Round half away from zero is (x + half + (x >> 31)) >> shift with an arithmetic shift (for x < 0 that is
+// -((|x| + half) >> shift)); the saturating pack clamps to a byte and one packed min / max finishes the clamp to
+// +-127 (ReLU: the unsigned pack turns negatives into 0).  About 3 instructions per value.
 template <bool RELU>
 __device__ __forceinline__ uint32_t narrow4_nearest(const uint32_t* v, int shift, int half) {
     int y[4];
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
         const int x = static_cast<int>(v[j]);
-        if (RELU) {
-            y[j] = min((max(x, 0) + half) >> shift, 127);
-        } else {
-            const int sgn = x >> 31;
-            const int t = min(((x ^ sgn) - sgn + half) >> shift, 127);
-            y[j] = (t ^ sgn) - sgn;
-        }
+        y[j] = RELU ? (x + half) >> shift : (x + half + (x >> 31)) >> shift;
     }
-    return __byte_perm(__byte_perm(y[0], y[1], 0x0040), __byte_perm(y[2], y[3], 0x0040), 0x5410);
+    if (RELU) return __vminu4(pack2_sat_u8(y[1], y[0], pack2_sat_u8(y[3], y[2], 0u)), 0x7F7F7F7Fu);
+    return __vmaxs4(pack2_sat_s8(y[1], y[0], pack2_sat_s8(y[3], y[2], 0u)), 0x81818181u);
 }
 __device__ __forceinline__ uint32_t narrow4(const uint32_t* v, int shift, int mode, int relu, const uint32_t* rnd) {
     uint32_t w = 0;
