@@ -18,6 +18,7 @@ Items 3-5 are a ``TorchFunctionMode`` active only inside ``with harness.active(.
 """
 import contextlib
 import importlib
+import os
 import sys
 import types
 
@@ -126,8 +127,12 @@ class Harness:
             yield m
 
 
-def load(ref_dir="/root/reference"):
-    """Import the reference modules from ``ref_dir`` under the stand-ins; returns a Harness."""
+def load(ref_dir=None):
+    """Import the reference modules from ``ref_dir`` (a checkout of wangmaolin/niti; default: the directory named by
+    the NITI_REFERENCE_DIR environment variable) under the stand-ins; returns a Harness."""
+    ref_dir = ref_dir or os.environ.get("NITI_REFERENCE_DIR")
+    if not ref_dir or not os.path.isdir(ref_dir):
+        raise FileNotFoundError("the reference checkout is needed: pass its directory or set NITI_REFERENCE_DIR")
     for name, mod in _stub_modules().items():
         sys.modules[name] = mod
     saved_argv = sys.argv

@@ -210,7 +210,7 @@ def gen_nets(H, out):
 
 
 if __name__ == "__main__":
-    ref = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    ref = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("NITI_REFERENCE_DIR")  # a checkout of wangmaolin/niti
     H = ref_harness.load(ref)
     gen_requant(H, HERE)
     gen_layers(H, HERE)
