@@ -826,29 +826,50 @@ umma_parked_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
         for (int tile = cta_first; tile < total_tiles; tile += cta_step) ++my_tiles;
         const int units = my_tiles * CG;
 
-        // ---- pass 1: max|acc| of this CTA's tiles
+        // Everything about this warpgroup's (at most two) units that does not depend on the accumulators is worked out
+        // now, while the main loop runs: tile coordinates, the row this thread owns, tensor-memory address.
+        constexpr int MAX_UNITS = 2;  // tiles per CTA <= 512 / BN, 128-column groups per tile = BN / 128, two warpgroups
+        RowInfo u_ri[MAX_UNITS]; int u_col[MAX_UNITS], u_it[MAX_UNITS]; uint32_t u_taddr[MAX_UNITS]; bool u_live[MAX_UNITS];
+#pragma unroll
+        for (int k = 0; k < MAX_UNITS; ++k) {
+            const int u = grp + 2 * k;
+            u_live[k] = u < units;
+            u_it[k] = 0; u_col[k] = 0; u_taddr[k] = 0; u_ri[k] = RowInfo{false, 0, 0, 0, 0};
+            if (u_live[k]) {
+                const int it = u / CG, g0 = (u % CG) * 128;
+                const int tile = cta_first + it * cta_step;
+                const int mn = tile % mn_tiles, n_t = mn % p.n_tiles;
+                const int m_t = TWO ? 2 * (mn / p.n_tiles) + static_cast<int>(rank) : mn / p.n_tiles;
+                u_ri[k] = row_info(p, m_t, tile / mn_tiles, row_in_tile);
+                u_it[k] = it;
+                u_col[k] = n_t * BN + g0;
+                u_taddr[k] = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + it * BN + g0;
+            }
+        }
+
+        // ---- pass 1: max|acc| of this CTA's tiles (the load of the next 32-column chunk is in flight while this one is reduced)
         int vmax[4] = {0, 0, 0, 0}, vmin[4] = {0, 0, 0, 0};
         bool ok = true;
-        for (int u = grp; u < units; u += 2) {
-            const int it = u / CG, g0 = (u % CG) * 128;
-            const int tile = cta_first + it * cta_step;
-            const uint32_t failed = mbar_wait(smem_u32(&tfull_bar[it]), 0, abort_flag) ? 0u : 1u;
-            if (barrier_or(bar_id, 128, failed)) { if (failed) report_abort(p.status, 4, 2); ok = false; break; }
-            if (threadIdx.x == 64 && u == 0) PARK_STAMP(4);
+#pragma unroll
+        for (int k = 0; k < MAX_UNITS; ++k) {
+            if (!u_live[k] || !ok) continue;
+            const uint32_t failed = mbar_wait(smem_u32(&tfull_bar[u_it[k]]), 0, abort_flag) ? 0u : 1u;
+            if (barrier_or(bar_id, 128, failed)) { if (failed) report_abort(p.status, 4, 2); ok = false; continue; }
+            if (threadIdx.x == 64 && k == 0) PARK_STAMP(4);
             tc_fence_after();
-            const int mn = tile % mn_tiles, n_t = mn % p.n_tiles;
-            const int m_t = TWO ? 2 * (mn / p.n_tiles) + static_cast<int>(rank) : mn / p.n_tiles;
-            const RowInfo ri = row_info(p, m_t, tile / mn_tiles, row_in_tile);
-            const int col = n_t * BN + g0;
-            if (col >= p.N) continue;
-            const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + it * BN + g0;
+            const int cols = p.N - u_col[k];
+            if (cols <= 0) continue;
+            const int nch = cols >= 128 ? 4 : (cols + 31) >> 5;
+            uint32_t va[32], vb[32];
+            tmem_ld_32x32(u_taddr[k], va);
 #pragma unroll 1
-            for (int j = 0; j < 4; ++j) {
-                if (col + 32 * j >= p.N) break;
-                uint32_t v[32];
-                tmem_ld_32x32(taddr + j * 32, v);
+            for (int j = 0; j < nch; j += 2) {
                 tmem_ld_wait();
-                if (ri.valid) minmax32(v, p.N - col - 32 * j, vmax, vmin);
+                if (j + 1 < nch) tmem_ld_32x32(u_taddr[k] + (j + 1) * 32, vb);
+                if (u_ri[k].valid) minmax32(va, cols - 32 * j, vmax, vmin);
+                tmem_ld_wait();
+                if (j + 2 < nch) tmem_ld_32x32(u_taddr[k] + (j + 2) * 32, va);
+                if (j + 1 < nch && u_ri[k].valid) minmax32(vb, cols - 32 * (j + 1), vmax, vmin);
             }
         }
         unsigned local_max = __reduce_max_sync(0xFFFFFFFFu, fold_minmax(vmax, vmin));
@@ -888,27 +909,36 @@ umma_parked_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
         if (ok && shift >= 0) {
             unsigned long long seed = 0;
             if (p.mode == ROUND_STOCHASTIC && shift > 0) seed = *p.seed;
-            for (int u = grp; u < units; u += 2) {
-                const int it = u / CG, g0 = (u % CG) * 128;
-                const int tile = cta_first + it * cta_step;
-                const int mn = tile % mn_tiles, n_t = mn % p.n_tiles;
-            const int m_t = TWO ? 2 * (mn / p.n_tiles) + static_cast<int>(rank) : mn / p.n_tiles;
-                const RowInfo ri = row_info(p, m_t, tile / mn_tiles, row_in_tile);
-                const int col = n_t * BN + g0;
-                if (col >= p.N) continue;
-                const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + it * BN + g0;
+#pragma unroll
+            for (int k = 0; k < MAX_UNITS; ++k) {
+                const int cols = p.N - u_col[k];
+                if (!u_live[k] || cols <= 0) continue;
+                const RowInfo ri = u_ri[k];
+                const int col = u_col[k];
+                const uint32_t taddr = u_taddr[k];
+                const int nch = cols >= 128 ? 4 : (cols + 31) >> 5;  // the store clips the columns beyond
                 const unsigned long long e0 = p.rng_offset + static_cast<unsigned long long>(ri.row_lin) * p.N + col;
-                if (leader) bulk_wait_read<0>();  // the previous store has read the staging tile
-                named_barrier(bar_id, 128);
+                const int8_t* mrow = (p.mask != nullptr && ri.valid) ? p.mask + ri.row_lin * p.N + col : nullptr;
+                uint32_t va[32], vb[32], packed[8];
+                tmem_ld_32x32(taddr, va);
+                if (k > 0) {
+                    if (leader) bulk_wait_read<0>();  // the previous store has read the staging tile
+                    named_barrier(bar_id, 128);
+                }
 #pragma unroll 1
-                for (int j = 0; j < 4; ++j) {
-                    if (col + 32 * j >= p.N) break;  // the store clips these columns
-                    uint32_t v[32], packed[8];
-                    tmem_ld_32x32(taddr + j * 32, v);
+                for (int j = 0; j < nch; j += 2) {
                     tmem_ld_wait();
-                    narrow32(v, packed, shift, p.mode, p.relu, seed, p.rng_stream, e0 + 32 * j);
-                    if (p.mask != nullptr && ri.valid) apply_relu_mask<8>(packed, p.mask + ri.row_lin * p.N + col + 32 * j, p.N - col - 32 * j);
+                    if (j + 1 < nch) tmem_ld_32x32(taddr + (j + 1) * 32, vb);
+                    narrow32(va, packed, shift, p.mode, p.relu, seed, p.rng_stream, e0 + 32 * j);
+                    if (mrow != nullptr) apply_relu_mask<8>(packed, mrow + 32 * j, cols - 32 * j);
                     stage_piece(buf, row_in_tile, j, packed);
+                    tmem_ld_wait();
+                    if (j + 2 < nch) tmem_ld_32x32(taddr + (j + 2) * 32, va);
+                    if (j + 1 < nch) {
+                        narrow32(vb, packed, shift, p.mode, p.relu, seed, p.rng_stream, e0 + 32 * (j + 1));
+                        if (mrow != nullptr) apply_relu_mask<8>(packed, mrow + 32 * (j + 1), cols - 32 * (j + 1));
+                        stage_piece(buf, row_in_tile, j + 1, packed);
+                    }
                 }
                 fence_proxy_async();
                 named_barrier(bar_id, 128);
