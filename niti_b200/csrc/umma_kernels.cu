@@ -85,6 +85,7 @@ struct GemmParams {
     int kind, target_bits;
     const int32_t* exp_a; const int32_t* exp_b; int32_t* exp_out; int32_t* shift_out;
     int mode, relu;
+    int8_t* out8;          // fused kernels: the int8 output as a plain pointer (rows = row_lin, pitch N bytes)
     const int8_t* mask;    // fused kernels: optional ReLU-backward mask, same shape as the output (zero where mask <= 0)
     const unsigned long long* seed;
     unsigned rng_stream;
@@ -426,6 +427,13 @@ __device__ __forceinline__ void apply_relu_mask(uint32_t (&packed)[WORDS], const
             packed[4 * q + 0] &= __vcmpgts4(x.x, 0); packed[4 * q + 1] &= __vcmpgts4(x.y, 0);
             packed[4 * q + 2] &= __vcmpgts4(x.z, 0); packed[4 * q + 3] &= __vcmpgts4(x.w, 0);
         }
+}
+// 32 packed int8 of one output row to global memory, as two 16-byte stores; `row` is null for rows outside the tensor,
+// `off` the byte offset within the unit's columns of which `cols` exist (a multiple of 16)
+__device__ __forceinline__ void store_piece(int8_t* row, int off, int cols, const uint32_t (&w)[8]) {
+    if (row == nullptr) return;
+    if (off + 16 <= cols) *reinterpret_cast<uint4*>(row + off) = make_uint4(w[0], w[1], w[2], w[3]);
+    if (off + 32 <= cols) *reinterpret_cast<uint4*>(row + off + 16) = make_uint4(w[4], w[5], w[6], w[7]);
 }
 // a 32-byte piece (chunk j of the row's 128 bytes) at its 128-byte-swizzled place in the staging tile
 __device__ __forceinline__ void stage_piece(uint32_t buf, int row, int j, const uint32_t (&w)[8]) {
@@ -819,8 +827,6 @@ umma_parked_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
         const int q = warp & 3;
         const int row_in_tile = q * 32 + lane;
         const int bar_id = EPI_BARRIER + grp;
-        const bool leader = (threadIdx.x == 64 + grp * 128);
-        const uint32_t buf = smem_u32(epi_smem) + grp * Cfg::EPI_GROUP_BYTES;
         constexpr int CG = BN / 128;
         int my_tiles = 0;
         for (int tile = cta_first; tile < total_tiles; tile += cta_step) ++my_tiles;
@@ -919,32 +925,28 @@ umma_parked_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
                 const int nch = cols >= 128 ? 4 : (cols + 31) >> 5;  // the store clips the columns beyond
                 const unsigned long long e0 = p.rng_offset + static_cast<unsigned long long>(ri.row_lin) * p.N + col;
                 const int8_t* mrow = (p.mask != nullptr && ri.valid) ? p.mask + ri.row_lin * p.N + col : nullptr;
+                // Each thread writes its own row straight from registers (32-byte pieces = whole L2 sectors): with one
+                // or two units per warpgroup there is nothing for a staged TMA store to overlap with, and its fence,
+                // barriers and the wait for the store engine at the end of the kernel cost more than the stores.
+                int8_t* orow = ri.valid ? p.out8 + ri.row_lin * p.N + col : nullptr;
                 uint32_t va[32], vb[32], packed[8];
                 tmem_ld_32x32(taddr, va);
-                if (k > 0) {
-                    if (leader) bulk_wait_read<0>();  // the previous store has read the staging tile
-                    named_barrier(bar_id, 128);
-                }
 #pragma unroll 1
                 for (int j = 0; j < nch; j += 2) {
                     tmem_ld_wait();
                     if (j + 1 < nch) tmem_ld_32x32(taddr + (j + 1) * 32, vb);
                     narrow32(va, packed, shift, p.mode, p.relu, seed, p.rng_stream, e0 + 32 * j);
                     if (mrow != nullptr) apply_relu_mask<8>(packed, mrow + 32 * j, cols - 32 * j);
-                    stage_piece(buf, row_in_tile, j, packed);
+                    store_piece(orow, 32 * j, cols, packed);
                     tmem_ld_wait();
                     if (j + 2 < nch) tmem_ld_32x32(taddr + (j + 2) * 32, va);
                     if (j + 1 < nch) {
                         narrow32(vb, packed, shift, p.mode, p.relu, seed, p.rng_stream, e0 + 32 * (j + 1));
                         if (mrow != nullptr) apply_relu_mask<8>(packed, mrow + 32 * (j + 1), cols - 32 * (j + 1));
-                        stage_piece(buf, row_in_tile, j + 1, packed);
+                        store_piece(orow, 32 * (j + 1), cols, packed);
                     }
                 }
-                fence_proxy_async();
-                named_barrier(bar_id, 128);
-                if (leader) { tma_store_4d(&tmC, buf, col, ri.cy, ri.cz, ri.cw); bulk_commit(); }
             }
-            if (leader) bulk_wait_read<0>();
         }
         if (threadIdx.x == 64) PARK_STAMP(7);
         // ---- the CTA that leaves last publishes the shift and clears the words for the next call
@@ -1303,6 +1305,7 @@ static void set_fused(GemmParams* p, const FusedArgs* f) {
     p->kind = f->kind; p->target_bits = f->target_bits;
     p->exp_a = f->exp_a; p->exp_b = f->exp_b; p->exp_out = f->exp_out; p->shift_out = f->shift_out;
     p->mask = f->relu_mask;
+    p->out8 = nullptr;
     // max|acc| lives in state[1]; a redo launch must leave it alone (the last CTA of the first launch zeroed it)
     p->maxabs = f->only_if_redo ? nullptr : reinterpret_cast<unsigned*>(f->state + 1);
 }
@@ -1399,6 +1402,7 @@ int umma_conv(const int8_t* x, const int8_t* w, void* out, unsigned* maxabs, int
     p.maxabs = maxabs; p.status = status;
     p.split_cols = (bn == 256 && p.m_tiles * p.n_tiles <= 2 * (pair ? sm_count() / 2 : sm_count())) ? 1 : 0;
     set_fused(&p, fused);
+    if (fused) p.out8 = static_cast<int8_t*>(out);
     if (parked) {
         if (!fits_parked(bn, p.m_tiles * p.n_tiles, pair)) return NITI_ERR_UNSUPPORTED;
         if (pair) return bn == 256 ? launch_parked_inst<256, true>(ma, mb, mc, p, st) : launch_parked_inst<128, true>(ma, mb, mc, p, st);
