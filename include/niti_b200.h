@@ -169,9 +169,10 @@ NITI_API int niti_conv_wgrad_builtin_scratch_i8(const int8_t* x, const int8_t* e
  * 148 x (512 / tile width) tiles, all accumulators fit in tensor memory at once and a single
  * cooperative launch does it without any prediction: reduce max, grid barrier, narrow (state[0]
  * still receives the shift; state[2] stays 0).
- *   state: device int32[8] owned by the caller, one per layer and direction, zeroed once:
+ *   state: device int32[8], 8-byte aligned, owned by the caller, one per layer and direction, zeroed once:
  *          [0] shift (in: prediction, out: true value), [1] max|acc| (zero between calls), [2] 1 if
- *          the last call had to redo, [3] number of redos so far, [4] block ticket (zero between calls).
+ *          the last call had to redo, [3] number of redos so far, [4] block ticket, [5..7] grid-barrier
+ *          words of the single-launch kernel (all zero between calls).
  *   kind is ACT for fprop (exp_out = shift + *exp_a + *exp_b) and ERR for dgrad; target 7 bits.
  * Shapes: niti_conv_*_requant_supported() != 0 (the tensor-core shapes of the entry points above
  * with 16-byte-multiple output channels); otherwise NITI_ERR_UNSUPPORTED and the caller uses

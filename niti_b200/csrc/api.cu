@@ -242,7 +242,7 @@ extern "C" int niti_conv_fprop_requant_i8(const int8_t* x, const int8_t* w, int8
                                           int32_t* shift_out, int32_t* status, void* stream) {
     NITI_REQUIRE(x && w && y8 && state && N > 0 && H > 0 && W > 0 && C > 0 && K > 0 && R > 0 && S > 0 && pad >= 0);
     NITI_REQUIRE(round_mode >= 0 && round_mode <= 2 && (seed || round_mode != NITI_ROUND_STOCHASTIC));
-    NITI_REQUIRE(aligned16(x) && aligned16(w) && aligned16(y8));
+    NITI_REQUIRE(aligned16(x) && aligned16(w) && aligned16(y8) && reinterpret_cast<uintptr_t>(state) % 8 == 0);
     if (!niti_conv_fprop_requant_supported(C, K, R, S, pad)) return NITI_ERR_UNSUPPORTED;
     return fused_conv(x, w, y8, state, scratch, scratch_bytes, N, H, W, C, K, R, S, pad, 0, NITI_CALC_ACT, round_mode, seed,
                       rng_stream, rng_offset, relu, exp_a, exp_b, exp_out, shift_out, status, static_cast<cudaStream_t>(stream));
@@ -255,7 +255,7 @@ extern "C" int niti_conv_dgrad_requant_i8(const int8_t* err, const int8_t* w, in
                                           void* stream) {
     NITI_REQUIRE(err && w && e8 && state && N > 0 && H > 0 && W > 0 && C > 0 && K > 0 && R > 0 && S > 0 && pad >= 0);
     NITI_REQUIRE(round_mode >= 0 && round_mode <= 2 && (seed || round_mode != NITI_ROUND_STOCHASTIC));
-    NITI_REQUIRE(aligned16(err) && aligned16(w) && aligned16(e8) && aligned16(relu_mask));
+    NITI_REQUIRE(aligned16(err) && aligned16(w) && aligned16(e8) && aligned16(relu_mask) && reinterpret_cast<uintptr_t>(state) % 8 == 0);
     if (!niti_conv_dgrad_requant_supported(C, K, R, S, pad)) return NITI_ERR_UNSUPPORTED;
     return fused_conv(err, w, e8, state, nullptr, 0, N, H, W, C, K, R, S, pad, 1, NITI_CALC_ERR, round_mode, seed, rng_stream,
                       rng_offset, 0, exp_a, exp_b, exp_out, shift_out, status, static_cast<cudaStream_t>(stream), relu_mask);

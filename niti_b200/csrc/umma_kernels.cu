@@ -751,7 +751,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 // barrier (cooperative launch: all resident; bounded spin), read the now final max, derive the true
 // shift and only then narrow their parked accumulators to int8.  No prediction, no second launch,
 // no int32 in memory.  state = {shift out, max|acc|, redo flag (cleared), redo count, exit ticket,
-// barrier arrivals}; words 1, 4 and 5 are zero between calls.
+// -, max|acc| and barrier arrivals (adjacent: read with one 64-bit load)}; words 1, 4, 5, 6 and 7 are zero between calls.
 // ------------------------------------------------------------------------------------------------
 template <int BN, bool TWO = false>
 struct ParkedCfg {
@@ -890,20 +890,22 @@ umma_parked_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
             unsigned cta_max = 0;
 #pragma unroll
             for (int i = 0; i < 8; ++i) cta_max = max(cta_max, warp_max[i]);
-            if (cta_max != 0) atomicMax(reinterpret_cast<unsigned*>(&st[1]), cta_max);
-            __threadfence();
-            atomicAdd(&st[5], 1);
+            // The maximum and the arrival count sit side by side (st[6], st[7]): two fire-and-forget reductions on the
+            // way in (the count's release orders the maximum before it), ONE 64-bit acquire load per poll that returns
+            // both -- a fence + atomicAdd + atomicMax read-back would add three round trips to the L2.
+            if (cta_max != 0) red_relaxed_max(reinterpret_cast<unsigned*>(&st[6]), cta_max);
+            red_release_add(&st[7], 1);
             const unsigned long long t0 = global_timer_ns();
             bool arrived = false;
+            unsigned m = 0;
             for (unsigned spin = 0;; ++spin) {
-                if (ld_acquire_gpu(&st[5]) >= static_cast<int>(gridDim.x)) { arrived = true; break; }
+                const unsigned long long both = ld_acquire_gpu_u64(&st[6]);
+                if (static_cast<int>(both >> 32) >= static_cast<int>(gridDim.x)) { arrived = true; m = static_cast<unsigned>(both); break; }
                 if ((spin & 63) == 63) {
                     if (*abort_flag || global_timer_ns() - t0 > GRID_BARRIER_LIMIT_NS) break;
                 }
             }
-            __threadfence();
             bool zero_out;
-            const unsigned m = atomicMax(reinterpret_cast<unsigned*>(&st[1]), 0u);
             *shift_slot = arrived ? shift_for(m, p.kind, p.target_bits, &zero_out) : -1;
             if (!arrived) { *abort_flag = 1; report_abort(p.status, 5, 2); }
         }
@@ -955,7 +957,7 @@ umma_parked_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
             if (atomicAdd(&st[4], 1) == static_cast<int>(gridDim.x) - 1) {
                 __threadfence();
                 const int s_out = shift < 0 ? 0 : shift;
-                st[0] = s_out; st[2] = 0; st[1] = 0; st[5] = 0; st[4] = 0;
+                st[0] = s_out; st[2] = 0; st[1] = 0; st[5] = 0; st[4] = 0; st[6] = 0; st[7] = 0;
                 if (p.exp_out) *p.exp_out = s_out + (p.exp_a ? *p.exp_a : 0) + (p.exp_b ? *p.exp_b : 0);
                 if (p.shift_out) *p.shift_out = s_out;
             }
