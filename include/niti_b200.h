@@ -316,6 +316,11 @@ NITI_API int niti_fc_head_train_i8(const niti_fc_head_args* args, void* stream);
 NITI_API int niti_quantize_input_f32(const float* x, int8_t* x8, int32_t* exp_out, uint32_t* scratch,
                             int N, int C, int H, int W, void* stream);
 
+/* Self-test of the bounded waits: launches one thread block that waits at a grid barrier expecting two blocks.  The
+ * wait gives up after its 0.5 s limit, writes {8, block index, expected arrivals} to status[0..2] (int32[4], zeroed by
+ * the caller) and the kernel returns normally: the context stays usable.  scratch: one int32 word. */
+NITI_API int niti_selftest_barrier_timeout(int32_t* scratch, int32_t* status, void* stream);
+
 /* The two halves of niti_quantize_input_f32, for callers that put something between them: *maxbits = the IEEE bit
  * pattern of max |x| (non-negative floats order like their bit patterns, so a MAX reduction over ranks on the
  * uint32 word gives the global maximum: what the global-exact data-parallel mode does). */

@@ -45,6 +45,7 @@ SIGNATURES = {
     "niti_loss_i8": (_i, [_p, _p, _p, _p, _i, _i, _p, _u32, _u64, _p]),
     "niti_update_i8": (_i, [_p, _p, _p, _i64, _i, _i, _p, _u32, _p]),
     "niti_quantize_input_f32": (_i, [_p, _p, _p, _p, _i, _i, _i, _i, _p]),
+    "niti_selftest_barrier_timeout": (_i, [_p, _p, _p]),
     "niti_absmax_f32": (_i, [_p, _i64, _p, _p]),
     "niti_quantize_input_with_max_f32": (_i, [_p, _p, _p, _p, _i, _i, _i, _i, _p]),
     "niti_update_multi_scratch_bytes": (_sz, []),

@@ -1003,6 +1003,20 @@ extern "C" int niti_update_multi_i8(const niti_update_item* items, int count, in
     return NITI_OK;
 }
 
+// Self-test of the bounded grid barrier: ONE block waits at a barrier that expects two.  Nothing else will ever arrive,
+// so the wait runs into its 0.5 s limit, the block writes {code 8, block, target} to `status` and the kernel returns.
+__global__ void barrier_timeout_selftest_kernel(int32_t* counter, int32_t* status) {
+    __shared__ int flag;
+    if (bounded_grid_barrier(counter, 2, status, 8, &flag)) status[3] = 1;  // cannot happen: one arrival, target two
+}
+extern "C" int niti_selftest_barrier_timeout(int32_t* scratch, int32_t* status, void* stream) {
+    NITI_REQUIRE(scratch && status);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (int e = set_cuda_error(cudaMemsetAsync(scratch, 0, 4, st))) return e;
+    barrier_timeout_selftest_kernel<<<1, 32, 0, st>>>(scratch, status);
+    return set_cuda_error(cudaGetLastError());
+}
+
 extern "C" int niti_absmax_f32(const float* x, int64_t n, uint32_t* maxbits, void* stream) {
     NITI_REQUIRE(x && maxbits && n > 0);
     cudaStream_t st = static_cast<cudaStream_t>(stream);

@@ -1,5 +1,6 @@
-"""Global-exact data-parallel mode on a GPU: two processes, each with half of a batch, compute bit for bit what one
-process (the oracle) computes on the whole batch.  Both ranks share cuda:0 and talk over gloo (host-side collectives
+"""Data-parallel training on a GPU with two processes, each with half of a batch.  Default mode: the ranks equal two
+independent oracle replicas on the shards whose int32 gradients are summed before ONE update.  Global-exact mode: they
+equal one oracle on the whole batch, bit for bit.  Both ranks share cuda:0 and talk over gloo (host-side collectives
 only; no kernel of one rank waits for a kernel of the other)."""
 import os
 import socket
@@ -31,7 +32,7 @@ def _data():
     return shapes, weights, [xavier_exp(s) for s in shapes], batches
 
 
-def _worker(rank, world, port, q):
+def _worker(rank, world, port, q, exact):
     import torch.distributed as dist
     from niti_b200 import ti_torch, ti_vgg
     from niti_b200.dp import shard_range
@@ -46,7 +47,8 @@ def _worker(rank, world, port, q):
             l.weight = torch.from_numpy(w).to("cuda:0")
             l.weight_exp = ti_torch.exp_tensor(e, "cuda:0")
         lo, hi = shard_range(GLOBAL_BATCH, rank, world)
-        tr = Trainer(model, hi - lo, "cuda:0", rank=rank, world=world, use_graph=False, seed=SEED, global_exact=True)
+        tr = Trainer(model, hi - lo, "cuda:0", rank=rank, world=world, use_graph=not exact, seed=SEED, global_exact=exact,
+                     warmup_steps=1)
         ti_torch.SAMPLE_OFFSET = lo
         logits = []
         for x, t in batches:
@@ -59,20 +61,25 @@ def _worker(rank, world, port, q):
         dist.destroy_process_group()
 
 
-def test_two_ranks_equal_one_process_on_the_whole_batch():
+def _run_ranks(exact):
     s = socket.socket()
     s.bind(("127.0.0.1", 0))
     port = s.getsockname()[1]
     s.close()
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
-    procs = [ctx.Process(target=_worker, args=(r, 2, port, q)) for r in range(2)]
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, q, exact)) for r in range(2)]
     for p in procs:
         p.start()
     results = [q.get(timeout=240) for _ in procs]
     for p in procs:
         p.join(timeout=60)
         assert p.exitcode == 0
+    return results
+
+
+def test_two_ranks_equal_one_process_on_the_whole_batch():
+    results = _run_ranks(True)
     shapes, weights, wexps, batches = _data()
     net = O.Net(CFG, weights, wexps, dropout=True, mu=5, seed=SEED)
     want = []
@@ -87,3 +94,28 @@ def test_two_ranks_equal_one_process_on_the_whole_batch():
             assert logits[step][1] == want[step][1]
         for i, b in enumerate(wbytes):
             assert b == net.w[i].tobytes(), f"rank {rank}: weights of layer {i}"
+
+
+def test_two_ranks_equal_independent_replicas_with_summed_gradients():
+    """The default data-parallel step (graph replay included): rank-local shifts, one exact int32 sum, one update."""
+    results = _run_ranks(False)
+    shapes, weights, wexps, batches = _data()
+    spans = sorted((lo, hi) for _, lo, hi, _, _ in results)
+    nets = [O.Net(CFG, weights, wexps, dropout=True, mu=5, seed=SEED) for _ in spans]
+    want = {}
+    for step, (x, t) in enumerate(batches):
+        grads = []
+        for net, (lo, hi) in zip(nets, spans):
+            x8, xe = O.float_to_int8(x[lo:hi])
+            out, e = net.forward(np.ascontiguousarray(x8.transpose(0, 2, 3, 1)), xe, step=step, sample_offset=lo)
+            want[(step, lo)] = (out, e)
+            grads.append(net.backward(t[lo:hi], step=step, sample_offset=lo, update=False))
+        summed = {i: sum(np.asarray(g[i], dtype=np.int64) for g in grads) for i in range(len(shapes))}
+        for net in nets:
+            net.apply_grads(summed, step=step)
+    for rank, lo, hi, logits, wbytes in results:
+        for step in range(STEPS):
+            assert np.array_equal(logits[step][0], want[(step, lo)][0]), f"rank {rank} step {step}: logits"
+            assert logits[step][1] == want[(step, lo)][1]
+        for i, b in enumerate(wbytes):
+            assert b == nets[0].w[i].tobytes(), f"rank {rank}: weights of layer {i}"

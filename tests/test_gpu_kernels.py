@@ -430,3 +430,23 @@ def test_conv_dgrad_fused_applies_relu_mask(N, H, W, C, K, parking):
     want, s = O.err_calc(acc)
     assert int(shift) == s
     assert_same(got, np.where(x > 0, want, 0).astype(np.int8), "dgrad + requant + relu mask")
+
+
+@pytest.mark.gpu
+def test_bounded_grid_barrier_gives_up_and_reports():
+    """A grid barrier that cannot be met (one block, two expected) returns after its 0.5 s limit with a status code;
+    nothing traps or hangs and the device keeps working afterwards."""
+    import time
+    from niti_b200._lib import lib, check
+    scratch = torch.zeros(1, dtype=torch.int32, device=DEV)
+    status = torch.zeros(4, dtype=torch.int32, device=DEV)
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    check(lib.niti_selftest_barrier_timeout(scratch.data_ptr(), status.data_ptr(), torch.cuda.current_stream().cuda_stream), "selftest")
+    torch.cuda.synchronize()
+    dt = time.perf_counter() - t0
+    s = status.tolist()
+    assert s[0] == 8 and s[1] == 0 and s[2] == 2 and s[3] == 0, s
+    assert 0.3 < dt < 5.0, dt
+    x = cu(np.arange(64, dtype=np.int32) - 32)            # the context is alive
+    assert int(ops.absmax(x)) == 32
