@@ -450,3 +450,31 @@ def test_bounded_grid_barrier_gives_up_and_reports():
     assert 0.3 < dt < 5.0, dt
     x = cu(np.arange(64, dtype=np.int32) - 32)            # the context is alive
     assert int(ops.absmax(x)) == 32
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("N,H,W,C,K", [(128, 32, 32, 128, 128), (128, 8, 8, 512, 512), (256, 16, 16, 256, 256)])
+def test_conv_passes_are_adjoint_at_full_size(N, H, W, C, K):
+    """At the benchmark's full sizes, where the oracle is out of reach: the three passes must satisfy, exactly in
+    integers, <conv(x, w), e> = <x, dgrad(e, w)> = <w, wgrad(x, e)> (the oracle satisfies the same identity, see
+    tests/test_oracle_properties.py), and max|acc| reported by each pass must be the tensor's."""
+    g = torch.Generator().manual_seed(N + C)
+    x = torch.randint(-127, 128, (N, H, W, C), dtype=torch.int8, generator=g).to(DEV)
+    w = torch.randint(-127, 128, (K, 3, 3, C), dtype=torch.int8, generator=g).to(DEV)
+    e = torch.randint(-127, 128, (N, H, W, K), dtype=torch.int8, generator=g).to(DEV)
+    y32, my = ops.conv_fprop_acc(x, w)
+    d32, md = ops.conv_dgrad_acc(e, w)
+    g32, mg = ops.conv_wgrad_acc(x, e)
+    lhs = int((y32.to(torch.int64) * e.to(torch.int64)).sum())
+    assert lhs == int((d32.to(torch.int64) * x.to(torch.int64)).sum()), "forward vs error-backward"
+    assert lhs == int((g32.to(torch.int64) * w.to(torch.int64)).sum()), "forward vs weight gradient"
+    for acc, m in ((y32, my), (d32, md), (g32, mg)):
+        assert int(m) == int(acc.abs().max())
+    ops.check_status(DEV)
+    # the fused forms agree with narrowing the int32 tensors by the same shift
+    st = ops.new_requant_state(DEV)
+    ea = torch.zeros((), dtype=torch.int32, device=DEV)
+    for _ in range(2):
+        y8, _, shift = ops.conv_fprop_fused(x, w, st, 1, 0, None, 0, 0, True, ea, ea)
+    want8, _, _ = ops.requant(y32, my, ops.CALC_ACT, 7, 0, None, 0, 0, relu=True)
+    assert torch.equal(y8, want8)
