@@ -199,3 +199,14 @@ def test_eval_mode_forward_and_topk_accuracy():
         sure = 100.0 * np.mean(((w32 >= own).sum(1) - 1) < k)        # hits whatever the order among equal logits
         maybe = 100.0 * np.mean((w32 > own).sum(1) < k)              # hits under the most favourable order
         assert sure - 1e-4 <= got <= maybe + 1e-4, (k, got, sure, maybe)
+
+
+def test_vgg7_batch128_full_size_step():
+    """The benchmark's own configuration (VGG-small-7, batch 128, dropout, grad bit-width 5): one graph-replayed
+    step pair against the oracle (exact int8 x int8 -> int32 products through torch._int_mm on the host)."""
+    O.set_backend("int_mm")
+    try:
+        run_steps([128, 128, "M", 256, 256, "M", 512, 512, "M"], 128, 2024, True, 2, 5, True, True, keep_gradients=False,
+                  prefetch=True)
+    finally:
+        O.set_backend("int64")
