@@ -478,3 +478,43 @@ def test_conv_passes_are_adjoint_at_full_size(N, H, W, C, K):
         y8, _, shift = ops.conv_fprop_fused(x, w, st, 1, 0, None, 0, 0, True, ea, ea)
     want8, _, _ = ops.requant(y32, my, ops.CALC_ACT, 7, 0, None, 0, 0, relu=True)
     assert torch.equal(y8, want8)
+
+
+@pytest.mark.gpu
+def test_single_conv_layer_step_full_size_stochastic():
+    """The single-layer benchmark configuration at full size (N=128, 32x32, C=K=128, 3x3, pad 1): forward, error-backward,
+    weight gradient and update with stochastic rounding from the seeded stream, against the oracle (torch._int_mm
+    products on the host)."""
+    O.set_backend("int_mm")
+    try:
+        rng = np.random.default_rng(1234)
+        N, H, W, C, K = 128, 32, 32, 128, 128
+        x, w, e = rnd8(rng, (N, H, W, C)), rnd8(rng, (K, 3, 3, C)), rnd8(rng, (N, H, W, K))
+        seed = ops.seed_tensor(42, DEV)
+        ea = torch.zeros((), dtype=torch.int32, device=DEV)
+        xt, wt, et = cu(x), cu(w), cu(e)
+        # forward + act_calc (StoShift), stream 32
+        st = ops.new_requant_state(DEV)
+        for _ in range(2):
+            y8, _, s_y = ops.conv_fprop_fused(xt, wt, st, 1, ops.ROUND_STOCHASTIC, seed, 32, 0, False, ea, ea)
+        acc = O.conv_fprop(x, w, 1)
+        want, _, s = O.act_calc(acc, 0, O.STOCHASTIC, philox.random_u32_tensor(42, 32, acc.shape))
+        assert int(s_y) == s
+        assert_same(y8, want, "forward, stochastic")
+        # error-backward + err_calc (StoShift), stream 33
+        st = ops.new_requant_state(DEV)
+        for _ in range(2):
+            e8, _, s_e = ops.conv_dgrad_fused(et, wt, st, 1, ops.ROUND_STOCHASTIC, seed, 33, 0, ea, ea)
+        acc = O.conv_dgrad(e, w, 1)
+        want, s = O.err_calc(acc, O.STOCHASTIC, philox.random_u32_tensor(42, 33, acc.shape))
+        assert int(s_e) == s
+        assert_same(e8, want, "error-backward, stochastic")
+        # weight gradient (exact int32) + update with StoShift, stream 34
+        g32, mg = ops.conv_wgrad_acc(xt, et)
+        gacc = O.conv_wgrad(x, e, 3, 3, 1)
+        assert_same(g32, gacc.astype(np.int32), "weight gradient")
+        w2 = wt.clone()
+        ops.update(w2, g32, mg, 5, ops.ROUND_STOCHASTIC, seed, 34)
+        assert_same(w2, O.weight_update(w, gacc, 5, O.STOCHASTIC, philox.random_u32_tensor(42, 34, gacc.shape))[0], "update")
+    finally:
+        O.set_backend("int64")
