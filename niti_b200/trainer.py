@@ -33,7 +33,7 @@ class StepResult:
 
 class Trainer:
     def __init__(self, model, local_batch, device, group=None, rank=0, world=1, use_graph=True, seed=0,
-                 in_shape=(3, 32, 32), warmup_steps=2, overlap_comm=False, keep_gradients=False, wgrad_side_stream=True,
+                 in_shape=(3, 32, 32), warmup_steps=2, keep_gradients=False, wgrad_side_stream=True,
                  global_exact=False):
         self.model, self.device, self.group = model, torch.device(device), group
         self.rank, self.world, self.use_graph = rank, world, use_graph
@@ -46,7 +46,7 @@ class Trainer:
             ti_torch.GLOBAL_MAX_GROUP = group if group is not None else True
             self.use_graph = use_graph = False
         # weight-gradient kernels run beside the error-backward kernels on a second stream (joined before the update)
-        self.side = torch.cuda.Stream(device=self.device) if (wgrad_side_stream and not keep_gradients and not overlap_comm) else None
+        self.side = torch.cuda.Stream(device=self.device) if (wgrad_side_stream and not keep_gradients) else None
         self.layers = model.weighted_layers()
         self.bucket = GradBucket([l.weight.shape for l in self.layers], self.device)
         for l, v in zip(self.layers, self.bucket.views):
@@ -56,19 +56,9 @@ class Trainer:
             # keep_gradients leaves each step's int32 gradients readable in the bucket instead (one memset per layer)
             l.grad_accumulate = not keep_gradients
             l.wgrad_stream = self.side
-        # Optional overlap (off by default): as soon as the last gradient of a bucket segment has been enqueued,
-        # that segment's all-reduce starts on NCCL's stream while the backward pass goes on (segments of ~4 MB
-        # or more).  Measured on 2 B200s it LOSES 9 % against the plain "backward graph, one all-reduce, update
-        # graph" sequence: the NCCL kernels take SMs away from the persistent one-CTA-per-SM contraction kernels
-        # and delay the cooperative ones, which need every SM free.
-        self.overlap_comm = overlap_comm and world > 1
-        self._works = []
-        if self.overlap_comm:
-            self._segments = self.bucket.comm_groups()
-            first_of = {lo: (start, end) for lo, hi, start, end in self._segments}
-            for i, l in enumerate(self.layers):
-                if i in first_of:
-                    l.grad_ready = (lambda layer, span=first_of[i]: self._start_allreduce(span))
+        # The all-reduce is NOT overlapped with the backward pass: starting each bucket segment's all-reduce as soon as its
+        # gradients were enqueued was built and measured 9 % slower on 2 B200s (NCCL's kernels take SMs away from the
+        # one-CTA-per-SM contraction kernels and delay the cooperative ones, which need every SM free).
         self.x = torch.zeros((local_batch,) + tuple(in_shape), dtype=torch.float32, device=self.device)
         self.t = torch.zeros((local_batch,), dtype=torch.int64, device=self.device)
         # two result slots, used alternately: step i's logits stay readable while step i+1 writes the other slot
@@ -95,15 +85,6 @@ class Trainer:
         self._warmup_steps = warmup_steps
         self.kernels_per_step = None
 
-    def _start_allreduce(self, span):
-        work = dist.all_reduce(self.bucket.flat[span[0]:span[1]], op=dist.ReduceOp.SUM, group=self.group, async_op=True)
-        self._works.append(work)
-
-    def _finish_allreduce(self):
-        for w in self._works:
-            w.wait()  # the compute stream waits for NCCL's stream; the host does not block
-        self._works = []
-
     # ------------------------------------------------------------------ pieces of one step
     def _forward_backward(self):
         self.model.train_step(self.x, self.t)
@@ -116,9 +97,7 @@ class Trainer:
 
     def _run_eager(self):
         self._forward_backward()
-        if self.overlap_comm:
-            self._finish_allreduce()
-        elif self.world > 1:
+        if self.world > 1:
             self.bucket.allreduce_(self.group)
         self._update()
 
@@ -127,12 +106,10 @@ class Trainer:
         g1 = torch.cuda.CUDAGraph()
         with torch.cuda.graph(g1):
             self._forward_backward()
-            if self.overlap_comm:
-                self._finish_allreduce()  # the all-reduces are nodes of the same graph, on a forked branch
-            if self.world == 1 or self.overlap_comm:
+            if self.world == 1:
                 self._update()
         g2 = None
-        if self.world > 1 and not self.overlap_comm:
+        if self.world > 1:
             g2 = torch.cuda.CUDAGraph()
             with torch.cuda.graph(g2, pool=g1.pool()):
                 self._update()
