@@ -16,6 +16,7 @@ CALC_ACT, CALC_ERR, CALC_GRAD = 0, 1, 2
 
 _status = {}
 _scratch = {}
+_scratch_retired = []
 
 # Launch accounting.  LAUNCHES counts kernels of this library enqueued through this module.
 # PROFILE, when set to a list (eager execution only, never under graph capture), makes every
@@ -68,10 +69,13 @@ def check_status(device):
 
 
 def scratch(device, nbytes):
-    """Grow-only per-device scratch arena (stream-ordered reuse on the current stream)."""
+    """Grow-only per-device scratch arena (stream-ordered reuse on the current stream).  An arena that is outgrown is
+    kept alive, not freed: a captured CUDA graph may still hold its address."""
     key = torch.device(device).index
     cur = _scratch.get(key)
     if cur is None or cur.numel() < nbytes:
+        if cur is not None:
+            _scratch_retired.append(cur)
         cur = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
         _scratch[key] = cur
     return cur
