@@ -42,8 +42,8 @@ class Trainer:
         # global-exact mode: every activation / error maximum is MAX-reduced over the ranks, so the ranks together
         # compute bit for bit what one process computes on the whole batch (eager execution, two-pass requantisation)
         self.global_exact = bool(global_exact) and world > 1
+        ti_torch.GLOBAL_MAX_GROUP = (group if group is not None else True) if self.global_exact else None
         if self.global_exact:
-            ti_torch.GLOBAL_MAX_GROUP = group if group is not None else True
             self.use_graph = use_graph = False
         # weight-gradient kernels run beside the error-backward kernels on a second stream (joined before the update)
         self.side = torch.cuda.Stream(device=self.device) if (wgrad_side_stream and not keep_gradients) else None
