@@ -274,7 +274,9 @@ def run_ours(args):
     for l, w, s in zip(model.weighted_layers(), weights, shapes):
         l.weight = torch.from_numpy(w).to(dev)
         l.weight_exp = ti_torch.exp_tensor(xavier_exp(s), dev)
-    trainer = Trainer(model, B, dev, rank=rank, world=world, use_graph=True, seed=1235)
+    trainer = Trainer(model, B, dev, rank=rank, world=world, use_graph=True, seed=1235,
+                      peer_update="auto" if args.exchange == "auto" else False)
+    peer_exchange = trainer.peer is not None
     data_rng = np.random.default_rng(5000 + rank)
     batches = []
     for _ in range(4):
@@ -407,6 +409,8 @@ def run_ours(args):
                        "per_gpu_batch": B, "global_batch": B * world, "parallelism": f"dp{world}",
                        "l2": "256 MB buffer written between timed steps (L2 flush); per-step CUDA events",
                        "graph": "step replayed from CUDA graphs", "replicas_bit_identical": replicas_equal,
+                       "exchange": ("none" if world == 1 else "reduce-scatter + update + weight broadcast in one kernel over peer memory"
+                                    if peer_exchange else "NCCL all-reduce of the int32 gradients, then the update launch"),
                        "shift_mispredictions_per_layer_since_start": redos,
                        "effective_int8_tops": step_ops_per_image(VGG7) * images / dev_s / 1e12},
             "e2e": {"value": images / e2e_s, "unit": UNIT, "h2d_bytes_per_step": trainer.h2d_bytes,
@@ -431,6 +435,7 @@ def run_ours(args):
                                               f"({sec:.2f} s per step), oracle port with torch._int_mm, {cores} threads"}
         os.write(real_stdout, (json.dumps(line) + "\n").encode())
     if world > 1:
+        trainer.close()
         dist.destroy_process_group()
 
 
@@ -542,6 +547,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--exchange", default="auto", choices=["auto", "nccl"],
+                    help="N>1: 'auto' = the peer-memory update kernel when the ranks share a node, else NCCL; 'nccl' = all-reduce")
     ap.add_argument("--case", help="time one kernel case instead of the training step (see make_case)")
     ap.add_argument("--shape", default="128,16,16,256,256")
     ap.add_argument("--plain-launches", type=int, default=0, help="with --case: just launch it this many times (for ncu)")

@@ -271,6 +271,52 @@ NITI_API size_t niti_update_multi_scratch_bytes(void);
 NITI_API int niti_update_multi_i8(const niti_update_item* items, int count, int mu, int round_mode, int clear_gradients,
                          const uint64_t* seed, void* scratch, size_t scratch_bytes, int32_t* status, void* stream);
 
+/* The update of a data-parallel step as ONE (cooperative) kernel per rank over peer memory, in place of an
+ * all-reduce of the gradients followed by niti_update_multi_i8.  Every rank (one process per GPU, all GPUs of one
+ * node with peer access) calls it once per step, on buffers that hold the same layout on every rank:
+ *   weights[r]  rank r's weight arena: layer i's int8 weights start w_offset bytes in (a multiple of 4);
+ *   grads[r]    rank r's int32 gradient bucket: layer i's accumulators start g_offset ELEMENTS in (a multiple of 4);
+ *   exchange[r] niti_dp_exchange_bytes() bytes of rank r, zeroed ONCE by its owner before any rank's first call.
+ * weights / grads / exchange are host arrays of `world` device pointers valid in the calling process (the caller's
+ * own allocation at index `rank`, the peers' through CUDA IPC or any other peer mapping).  The kernel
+ *   1. waits until every rank's earlier work on the stream has finished (flags in the exchange areas),
+ *   2. sums slice `rank` of every layer (word groups [G rank / world, G (rank + 1) / world) of its G = n / 4 groups)
+ *      over all ranks' buckets with plain peer loads, and sends the slice's max |sum| per layer to every rank,
+ *   3. takes each layer's maximum over the ranks, updates ITS slice of the weights exactly as niti_update_i8 would
+ *      (same shift, same random words: they are indexed by the element's position in the layer) and stores the new
+ *      bytes into every rank's arena; zeroes its own bucket,
+ *   4. waits until every rank's stores have landed.
+ * Afterwards all replicas hold the weights one process would hold after niti_update_multi_i8 on the summed
+ * gradients (integer addition is associative), and every bucket is zero.  maxabs (nullable): uint32[count], each
+ * layer's max |summed g32|.  n must be a multiple of 4, count <= 16, world <= 8.  Every wait is bounded (0.5 s for
+ * the blocks of the own GPU, 4 s for a peer): on expiry status receives {9, rank it waited for or -1, barrier
+ * number}, the kernel returns, and the replicas must be considered out of step.  The ranks must therefore reach the
+ * call within 4 s of each other.  Never run two ranks on ONE GPU: their kernels would wait for each other without
+ * being co-resident.  No counterpart in the reference (single GPU). */
+/* Peer-visible device memory for niti_dp_update_i8, owned by the library.  niti_peer_arena_create allocates `bytes`
+ * of zeroed device memory on the current device and fills `handle` (NITI_PEER_HANDLE_BYTES bytes, to be sent to the
+ * other processes of the node by any host channel); niti_peer_arena_open maps another process's arena into the
+ * calling process for kernels of the CURRENT device (peer access to the owner's GPU is switched on by the mapping);
+ * niti_peer_arena_close unmaps it, niti_peer_arena_destroy frees an own arena (after every peer has closed it).
+ * Plain CUDA IPC mappings: the memory is not bound to a multicast object. */
+#define NITI_PEER_HANDLE_BYTES 64
+NITI_API int niti_peer_arena_create(size_t bytes, void** ptr, void* handle);
+NITI_API int niti_peer_arena_open(const void* handle, void** ptr);
+NITI_API int niti_peer_arena_close(void* ptr);
+NITI_API int niti_peer_arena_destroy(void* ptr);
+typedef struct niti_dp_item { int64_t w_offset; int64_t g_offset; int64_t n; uint32_t rng_stream; } niti_dp_item;
+typedef struct niti_dp_update_args {
+    const niti_dp_item* items; int32_t count;
+    int32_t rank, world;
+    void* const* weights; void* const* grads; void* const* exchange;
+    int32_t mu, round_mode;
+    const uint64_t* seed;
+    uint32_t* maxabs;
+    int32_t* status;
+} niti_dp_update_args;
+NITI_API size_t niti_dp_exchange_bytes(void);
+NITI_API int niti_dp_update_i8(const niti_dp_update_args* args, void* stream);
+
 /* The classifier head of a training step in one (cooperative) kernel: TiDropout.forward
  * (ti_torch.py:439-455), TiLinear.forward (:241-253), TiLoss.forward (ti_loss.py:6-36), TiLinear.backward
  * (:255-266) with UpdateWeight.weight_update (:16-21), and TiDropout.backward.  Same integers as the calls

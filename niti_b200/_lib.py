@@ -55,12 +55,30 @@ SIGNATURES = {
     "niti_fc_head_supported": (_i, [_i, _i, _i]),
     "niti_fc_head_scratch_bytes": (_sz, [_i, _i, _i]),
     "niti_fc_head_train_i8": (_i, [_p, _p]),
+    "niti_dp_exchange_bytes": (_sz, []),
+    "niti_peer_arena_create": (_i, [_sz, _p, _p]),
+    "niti_peer_arena_open": (_i, [_p, _p]),
+    "niti_peer_arena_close": (_i, [_p]),
+    "niti_peer_arena_destroy": (_i, [_p]),
+    "niti_dp_update_i8": (_i, [_p, _p]),
 }
 
 
 class UpdateItem(C.Structure):
     """niti_update_item of include/niti_b200.h"""
     _fields_ = [("w", _p), ("g32", _p), ("maxabs", _p), ("n", _i64), ("rng_stream", _u32)]
+
+
+class DpItem(C.Structure):
+    """niti_dp_item of include/niti_b200.h"""
+    _fields_ = [("w_offset", _i64), ("g_offset", _i64), ("n", _i64), ("rng_stream", _u32)]
+
+
+class DpUpdateArgs(C.Structure):
+    """niti_dp_update_args of include/niti_b200.h"""
+    _fields_ = [("items", _p), ("count", C.c_int32), ("rank", C.c_int32), ("world", C.c_int32),
+                ("weights", _p), ("grads", _p), ("exchange", _p), ("mu", C.c_int32), ("round_mode", C.c_int32),
+                ("seed", _p), ("maxabs", _p), ("status", _p)]
 
 
 class FcHeadArgs(C.Structure):

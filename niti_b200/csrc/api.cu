@@ -58,6 +58,39 @@ extern "C" int niti_set_option(int option, int value) {
     return NITI_ERR_BAD_ARG;
 }
 
+// ---- peer-visible arenas (CUDA IPC) for the data-parallel update kernel
+static_assert(sizeof(cudaIpcMemHandle_t) <= NITI_PEER_HANDLE_BYTES, "handle size");
+extern "C" int niti_peer_arena_create(size_t bytes, void** ptr, void* handle) {
+    NITI_REQUIRE(bytes > 0 && ptr && handle);
+    void* p = nullptr;
+    if (int e = set_cuda_error(cudaMalloc(&p, bytes))) return e;
+    if (int e = set_cuda_error(cudaMemset(p, 0, bytes))) { cudaFree(p); return e; }
+    if (int e = set_cuda_error(cudaDeviceSynchronize())) { cudaFree(p); return e; }
+    cudaIpcMemHandle_t h;
+    if (int e = set_cuda_error(cudaIpcGetMemHandle(&h, p))) { cudaFree(p); return e; }
+    memset(handle, 0, NITI_PEER_HANDLE_BYTES);
+    memcpy(handle, &h, sizeof(h));
+    *ptr = p;
+    return NITI_OK;
+}
+extern "C" int niti_peer_arena_open(const void* handle, void** ptr) {
+    NITI_REQUIRE(handle && ptr);
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handle, sizeof(h));
+    void* p = nullptr;
+    if (int e = set_cuda_error(cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess))) return e;
+    *ptr = p;
+    return NITI_OK;
+}
+extern "C" int niti_peer_arena_close(void* ptr) {
+    NITI_REQUIRE(ptr);
+    return set_cuda_error(cudaIpcCloseMemHandle(ptr));
+}
+extern "C" int niti_peer_arena_destroy(void* ptr) {
+    NITI_REQUIRE(ptr);
+    return set_cuda_error(cudaFree(ptr));
+}
+
 static int clear_word(uint32_t* p, cudaStream_t st) { return set_cuda_error(cudaMemsetAsync(p, 0, 4, st)); }
 
 static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }

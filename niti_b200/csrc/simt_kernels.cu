@@ -608,6 +608,173 @@ update_multi_kernel(const UpdateMultiParams p) {
 }
 
 // ------------------------------------------------------------------------------------------------
+// the update of a data-parallel step over peer memory: every rank sums ITS slice of the gradient buckets of all
+// ranks, the slices' maxima are exchanged, every rank updates its slice of the weights and stores the new bytes
+// into every replica.  Against all-reduce + update this moves the int32 sums once instead of twice (the way back
+// carries int8 weights) and needs no second launch.
+// ------------------------------------------------------------------------------------------------
+constexpr int DP_MAX_RANKS = 8;
+constexpr unsigned long long PEER_WAIT_LIMIT_NS = 4000000000ull;  // 4 s
+// exchange area of one rank, in 32-bit words
+constexpr int DPX_EPOCH = 0, DPX_ARRIVALS = 1, DPX_GO = 2 /* and DPX_GO + 1 = failed; one 8-byte word */,
+              DPX_OWN_MAX = 16 /* [UPDATE_MULTI_MAX] */, DPX_FLAGS = 32 /* [DP_MAX_RANKS], written by the peers */,
+              DPX_MAXIMA = 64 /* [DP_MAX_RANKS][UPDATE_MULTI_MAX], written by the peers */,
+              DPX_WORDS = DPX_MAXIMA + DP_MAX_RANKS * UPDATE_MULTI_MAX;
+struct DpItem { long long w_off, g_off, n; unsigned rng_stream; };
+struct DpUpdateParams {
+    DpItem item[UPDATE_MULTI_MAX];
+    int first_block[UPDATE_MULTI_MAX + 1];
+    int count, mu, mode, rank, world;
+    int8_t* weights[DP_MAX_RANKS];
+    int32_t* grads[DP_MAX_RANKS];
+    int32_t* exchange[DP_MAX_RANKS];
+    const unsigned long long* seed;
+    unsigned* maxabs;
+    int32_t* status;
+};
+__device__ __forceinline__ void st_release_sys(int32_t* p, int v) {
+    asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ void st_relaxed_sys(unsigned* p, unsigned v) {
+    asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ int ld_acquire_sys(const int32_t* p) {
+    int v;
+    asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void st_release_gpu_u64(void* p, unsigned long long v) {
+    asm volatile("st.release.gpu.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+// a peer's memory is read with system scope, so that no cache of THIS GPU can answer with an older step's value
+__device__ __forceinline__ int4 ld_relaxed_sys_v4(const int4* p) {
+    int4 v;
+    asm volatile("ld.relaxed.sys.global.v4.s32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ int4 add4(const int4 a, const int4 b) { return make_int4(a.x + b.x, a.y + b.y, a.z + b.z, a.w + b.w); }
+
+// Barrier number `seq` (grows by one per barrier, over all launches) across all blocks of all ranks.  Block 0 collects
+// the arrivals of its own grid, tells every rank (thread r talks to rank r) and waits for every rank's word; the other
+// blocks wait for block 0's verdict.  send_maxima: the layer maxima of this rank's slices travel with the arrival.
+__device__ bool dp_barrier(const DpUpdateParams& p, int seq, int number, bool send_maxima, int* flag) {
+    int32_t* L = p.exchange[p.rank];
+    __syncthreads();
+    if (blockIdx.x == 0) {
+        if (threadIdx.x == 0) {
+            const unsigned long long t0 = grid_timer_ns();
+            bool ok = true;
+            for (unsigned spin = 0; ld_acquire_gpu(&L[DPX_ARRIVALS]) < static_cast<int>(gridDim.x) - 1; ++spin)
+                if ((spin & 63) == 63 && grid_timer_ns() - t0 > GRID_WAIT_LIMIT_NS) { ok = false; break; }
+            L[DPX_ARRIVALS] = 0;  // nobody arrives again before this barrier's verdict, which is stored after this
+            *flag = ok ? 1 : 0;
+        }
+        __syncthreads();
+        int ok = *flag, waited_for = -1;
+        if (ok && static_cast<int>(threadIdx.x) < p.world) {
+            const int peer = static_cast<int>(threadIdx.x);
+            int32_t* X = p.exchange[peer];
+            if (send_maxima) {
+                unsigned* dst = reinterpret_cast<unsigned*>(X + DPX_MAXIMA + p.rank * UPDATE_MULTI_MAX);
+                for (int l = 0; l < p.count; ++l) st_relaxed_sys(dst + l, static_cast<unsigned>(__ldcg(&L[DPX_OWN_MAX + l])));
+            }
+            st_release_sys(&X[DPX_FLAGS + p.rank], seq);  // release: everything this grid wrote before is visible to who sees it
+            const unsigned long long t0 = grid_timer_ns();
+            for (unsigned spin = 0; ld_acquire_sys(&L[DPX_FLAGS + peer]) - seq < 0; ++spin)
+                if ((spin & 63) == 63 && grid_timer_ns() - t0 > PEER_WAIT_LIMIT_NS) { ok = 0; waited_for = peer; break; }
+        }
+        const int all_ok = __syncthreads_and(ok);
+        if (!ok && p.status != nullptr && atomicCAS(p.status, 0, 9) == 0) { p.status[1] = waited_for; p.status[2] = number; }
+        if (threadIdx.x == 0) {
+            if (send_maxima) for (int l = 0; l < p.count; ++l) L[DPX_OWN_MAX + l] = 0;  // for the next launch
+            const unsigned long long verdict = all_ok ? static_cast<unsigned long long>(static_cast<unsigned>(seq))
+                                                      : (static_cast<unsigned long long>(static_cast<unsigned>(seq)) << 32);
+            st_release_gpu_u64(&L[DPX_GO], verdict);
+            *flag = all_ok;
+        }
+    } else if (threadIdx.x == 0) {
+        red_release_add(&L[DPX_ARRIVALS], 1);
+        const unsigned long long t0 = grid_timer_ns();
+        int ok = 0;
+        for (unsigned spin = 0;; ++spin) {
+            const unsigned long long v = ld_acquire_gpu_u64(&L[DPX_GO]);
+            if (static_cast<int>(v & 0xFFFFFFFFu) == seq) { ok = 1; break; }
+            if (static_cast<int>(v >> 32) == seq) break;
+            if ((spin & 63) == 63 && grid_timer_ns() - t0 > PEER_WAIT_LIMIT_NS + 2 * GRID_WAIT_LIMIT_NS) break;
+        }
+        *flag = ok;
+    }
+    __syncthreads();
+    return *flag != 0;
+}
+
+__global__ void __launch_bounds__(256)
+dp_update_kernel(const DpUpdateParams p) {
+    __shared__ int flag;
+    int32_t* L = p.exchange[p.rank];
+    int l = 0;
+    while (l + 1 < p.count && static_cast<int>(blockIdx.x) >= p.first_block[l + 1]) ++l;
+    const DpItem& it = p.item[l];
+    const long long nthreads = static_cast<long long>(p.first_block[l + 1] - p.first_block[l]) * blockDim.x;
+    const long long tid = static_cast<long long>(static_cast<int>(blockIdx.x) - p.first_block[l]) * blockDim.x + threadIdx.x;
+    const long long groups = it.n >> 2;
+    const long long lo = groups * p.rank / p.world, hi = groups * (p.rank + 1) / p.world;
+    int4* mine = reinterpret_cast<int4*>(p.grads[p.rank] + it.g_off);
+    const int seq0 = 3 * __ldcg(&L[DPX_EPOCH]);  // the same in every block: the word changes after the last barrier only
+
+    // ---- 1: every rank's gradients are complete
+    if (!dp_barrier(p, seq0 + 1, 1, false, &flag)) return;
+    {   // ---- 2: sum this rank's slice over the ranks (in place in the own bucket), its maximum
+        unsigned m = 0;
+        for (long long g = lo + tid; g < hi; g += nthreads) {
+            int4 v[DP_MAX_RANKS];
+#pragma unroll
+            for (int r = 1; r < DP_MAX_RANKS; ++r) {
+                if (r < p.world) {
+                    int pr = p.rank + r;
+                    if (pr >= p.world) pr -= p.world;
+                    v[r] = ld_relaxed_sys_v4(reinterpret_cast<const int4*>(p.grads[pr] + it.g_off) + g);
+                }
+            }
+            int4 s = __ldcg(mine + g);
+#pragma unroll
+            for (int r = 1; r < DP_MAX_RANKS; ++r)
+                if (r < p.world) s = add4(s, v[r]);
+            mine[g] = s;
+            m = max(m, absmax4(s));
+        }
+        block_atomic_max(reinterpret_cast<unsigned*>(&L[DPX_OWN_MAX + l]), m);
+    }
+    // ---- 3: the slices' maxima reach every rank; every rank has finished reading the others' buckets
+    if (!dp_barrier(p, seq0 + 2, 2, true, &flag)) return;
+    {
+        unsigned mx = 0;
+        for (int r = 0; r < p.world; ++r) mx = max(mx, static_cast<unsigned>(__ldcg(&L[DPX_MAXIMA + r * UPDATE_MULTI_MAX + l])));
+        if (tid == 0 && p.maxabs != nullptr) p.maxabs[l] = mx;
+        bool zero_out;
+        const int shift = shift_for(mx, CALC_GRAD, p.mu, &zero_out);
+        const bool stochastic = (p.mode == ROUND_STOCHASTIC) && shift > 0;
+        const unsigned long long seed = stochastic ? *p.seed : 0ull;
+        const uint32_t* w_own = reinterpret_cast<const uint32_t*>(p.weights[p.rank] + it.w_off);
+        for (long long g = tid; g < groups; g += nthreads) {
+            if (g >= lo && g < hi) {
+                uint32_t rnd[4] = {0, 0, 0, 0};
+                if (stochastic) random_block(seed, it.rng_stream, static_cast<unsigned long long>(g), rnd);
+                const uint32_t o = update_word(__ldcg(mine + g), w_own[g], rnd, shift, p.mode, zero_out);
+#pragma unroll
+                for (int r = 0; r < DP_MAX_RANKS; ++r)
+                    if (r < p.world) reinterpret_cast<uint32_t*>(p.weights[r] + it.w_off)[g] = o;
+            }
+            mine[g] = make_int4(0, 0, 0, 0);  // the weight-gradient kernels of the next step add into a zeroed bucket
+        }
+        __threadfence_system();
+    }
+    // ---- 4: every rank's weight stores have landed
+    if (!dp_barrier(p, seq0 + 3, 3, false, &flag)) return;
+    if (blockIdx.x == 0 && threadIdx.x == 0) L[DPX_EPOCH] = L[DPX_EPOCH] + 1;
+}
+
+// ------------------------------------------------------------------------------------------------
 // input quantisation (ti_torch.py:341-356 + the permute of ti_net.py:19)
 // ------------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(256) absmax_f32_kernel(const float* __restrict__ x, long long n, unsigned* bits) {
@@ -1001,6 +1168,60 @@ extern "C" int niti_update_multi_i8(const niti_update_item* items, int count, in
         if (int e = set_cuda_error(cudaLaunchKernelEx(&cfg, update_multi_kernel, p))) return e;
     }
     return NITI_OK;
+}
+
+extern "C" size_t niti_dp_exchange_bytes(void) { return DPX_WORDS * sizeof(int32_t); }
+
+extern "C" int niti_dp_update_i8(const niti_dp_update_args* a, void* stream) {
+    NITI_REQUIRE(a && a->items && a->count > 0 && a->count <= UPDATE_MULTI_MAX);
+    NITI_REQUIRE(a->world >= 1 && a->world <= DP_MAX_RANKS && a->rank >= 0 && a->rank < a->world);
+    NITI_REQUIRE(a->weights && a->grads && a->exchange && a->round_mode >= 0 && a->round_mode <= 2);
+    NITI_REQUIRE(a->seed || a->round_mode != NITI_ROUND_STOCHASTIC);
+    DpUpdateParams p;
+    long long total = 0;
+    for (int i = 0; i < a->count; ++i) {
+        const niti_dp_item& it = a->items[i];
+        NITI_REQUIRE(it.n > 0 && it.n % 4 == 0 && it.w_offset % 4 == 0 && it.g_offset % 4 == 0);
+        p.item[i] = DpItem{it.w_offset, it.g_offset, it.n, it.rng_stream};
+        total += it.n;
+    }
+    for (int r = 0; r < DP_MAX_RANKS; ++r) {
+        const int s = r < a->world ? r : a->rank;  // unused slots repeat the own pointers
+        NITI_REQUIRE(a->weights[s] && a->grads[s] && a->exchange[s]);
+        NITI_REQUIRE(reinterpret_cast<uintptr_t>(a->weights[s]) % 4 == 0 && reinterpret_cast<uintptr_t>(a->grads[s]) % 16 == 0 &&
+                     reinterpret_cast<uintptr_t>(a->exchange[s]) % 8 == 0);
+        p.weights[r] = static_cast<int8_t*>(a->weights[s]);
+        p.grads[r] = static_cast<int32_t*>(a->grads[s]);
+        p.exchange[r] = static_cast<int32_t*>(a->exchange[s]);
+    }
+    p.count = a->count; p.mu = a->mu; p.mode = a->round_mode; p.rank = a->rank; p.world = a->world;
+    p.seed = reinterpret_cast<const unsigned long long*>(a->seed);
+    p.maxabs = a->maxabs; p.status = a->status;
+    static int blocks_per_sm = 0;
+    if (blocks_per_sm == 0) {
+        int n = 0;
+        if (int e = set_cuda_error(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, dp_update_kernel, 256, 0))) return e;
+        blocks_per_sm = n < 1 ? 1 : (n > 8 ? 8 : n);
+    }
+    // one resident wave, dealt to the layers in proportion to their sizes; a block per 256 word groups of the WHOLE
+    // layer is as fine as it gets (the clearing pass walks the whole layer, the slice is 1 / world of it)
+    const int wave = sm_count_simt() * blocks_per_sm;
+    int grid = 0;
+    for (int i = 0; i < p.count; ++i) {
+        long long share = (static_cast<long long>(wave - p.count) * p.item[i].n) / (total > 0 ? total : 1);
+        const long long useful = (p.item[i].n / 4 + 255) / 256;
+        if (share > useful - 1) share = useful - 1;
+        if (share < 0) share = 0;
+        p.first_block[i] = grid;
+        grid += 1 + static_cast<int>(share);
+    }
+    p.first_block[p.count] = grid;
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(grid); cfg.blockDim = dim3(256); cfg.dynamicSmemBytes = 0; cfg.stream = static_cast<cudaStream_t>(stream);
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeCooperative; attr[0].val.cooperative = g_cooperative;  // the grid fits in one wave
+    cfg.attrs = attr; cfg.numAttrs = 1;
+    return set_cuda_error(cudaLaunchKernelEx(&cfg, dp_update_kernel, p));
 }
 
 // Self-test of the bounded grid barrier: ONE block waits at a barrier that expects two.  Nothing else will ever arrive,

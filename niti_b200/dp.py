@@ -21,7 +21,8 @@ def shard_range(global_batch, rank, world):
 class GradBucket:
     """One flat int32 buffer with a 16-byte-aligned view per weight tensor."""
 
-    def __init__(self, shapes, device):
+    def __init__(self, shapes, device, flat=None):
+        """``flat``: an int32 tensor to adopt as the bucket (a region of peer-visible memory, say) instead of a new one."""
         self.shapes = [tuple(s) for s in shapes]
         self.offsets = []
         off = 0
@@ -31,13 +32,27 @@ class GradBucket:
             for d in s:
                 n *= d
             off += (n + 3) // 4 * 4
-        self.flat = torch.zeros(off, dtype=torch.int32, device=device)
+        if flat is None:
+            flat = torch.zeros(off, dtype=torch.int32, device=device)
+        assert flat.dtype == torch.int32 and flat.numel() == off and flat.is_contiguous()
+        self.flat = flat
         self.views = []
         for s, o in zip(self.shapes, self.offsets):
             n = 1
             for d in s:
                 n *= d
             self.views.append(self.flat[o:o + n].view(s))
+
+    @staticmethod
+    def numel_for(shapes):
+        """Length of the flat buffer that __init__ lays out for `shapes`."""
+        off = 0
+        for s in shapes:
+            n = 1
+            for d in s:
+                n *= d
+            off += (n + 3) // 4 * 4
+        return off
 
     def nbytes(self):
         return self.flat.numel() * 4

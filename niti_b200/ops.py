@@ -9,7 +9,7 @@ import torch
 
 import ctypes
 
-from ._lib import lib, check, FcHeadArgs, UpdateItem
+from ._lib import lib, check, FcHeadArgs, UpdateItem, DpItem, DpUpdateArgs
 
 ROUND_NEAREST, ROUND_STOCHASTIC, ROUND_PSEUDO_STOCHASTIC = 0, 1, 2
 CALC_ACT, CALC_ERR, CALC_GRAD = 0, 1, 2
@@ -361,6 +361,25 @@ def update_multi(ws, g32s, streams, mu, mode=ROUND_PSEUDO_STOCHASTIC, seed=None,
     _call("niti_update_multi_i8", (n + 15) // 16, 0, 10 * total, lib.niti_update_multi_i8, items, n, mu, mode, int(clear), _p(seed),
           _p(sc), nbytes, _p(status_word(dev)), _st())
     return mx
+
+
+def dp_exchange_bytes():
+    return int(lib.niti_dp_exchange_bytes())
+
+
+def dp_update(items, rank, world, weight_ptrs, grad_ptrs, exchange_ptrs, mu, mode, seed, device, maxabs=None):
+    """One rank's part of the data-parallel update over peer memory (niti_dp_update_i8): `items` is a list of
+    (w_offset bytes, g_offset elements, n, rng_stream); the three pointer lists hold one device address per rank."""
+    _need_cuda(seed, maxabs)
+    n = len(items)
+    arr = (DpItem * n)(*[DpItem(int(a), int(b), int(c), int(d)) for a, b, c, d in items])
+    vp = ctypes.c_void_p * world
+    w, g, x = vp(*weight_ptrs), vp(*grad_ptrs), vp(*exchange_ptrs)
+    args = DpUpdateArgs(ctypes.cast(arr, ctypes.c_void_p), n, rank, world, ctypes.cast(w, ctypes.c_void_p),
+                        ctypes.cast(g, ctypes.c_void_p), ctypes.cast(x, ctypes.c_void_p), mu, mode, _p(seed), _p(maxabs),
+                        _p(status_word(device)))
+    total = sum(it[2] for it in items)
+    _call("niti_dp_update_i8", 1, 0, 9 * total, lib.niti_dp_update_i8, ctypes.byref(args), _st())
 
 
 def quantize_input(x, reduce_max=None):

@@ -5,15 +5,20 @@ labels from pinned host memory, runs TiNet.forward + TiNet.backward (loss, error
 back-propagation, weight gradients, integer update) and copies the int8 logits and their
 exponent back.  After two eager steps the device work is captured in CUDA graphs and replayed,
 because a step is ~100 short kernels and would otherwise be bound by launch overhead.
-With a process group of more than one rank the batch is sharded (one process per GPU), the
-int32 gradient bucket is all-reduced between the backward graph and the update graph, and every
-rank applies the same update.
+With a process group of more than one rank the batch is sharded (one process per GPU).  Ranks on
+different GPUs of one node exchange through one kernel over peer memory that sums the gradients
+slice by slice, updates and stores the new weights into every replica (all in the same graph);
+otherwise the int32 gradient bucket is all-reduced by NCCL between the backward graph and the
+update graph, and every rank applies the same update.
 """
+import warnings
+
 import torch
 import torch.distributed as dist
 
 from . import ops, ti_torch
 from .dp import GradBucket
+from .peer import PeerArena, peers_on_one_node
 
 
 class StepResult:
@@ -34,7 +39,7 @@ class StepResult:
 class Trainer:
     def __init__(self, model, local_batch, device, group=None, rank=0, world=1, use_graph=True, seed=0,
                  in_shape=(3, 32, 32), warmup_steps=2, keep_gradients=False, wgrad_side_stream=True,
-                 global_exact=False):
+                 global_exact=False, peer_update="auto"):
         self.model, self.device, self.group = model, torch.device(device), group
         self.rank, self.world, self.use_graph = rank, world, use_graph
         self.local_batch = local_batch
@@ -48,7 +53,15 @@ class Trainer:
         # weight-gradient kernels run beside the error-backward kernels on a second stream (joined before the update)
         self.side = torch.cuda.Stream(device=self.device) if (wgrad_side_stream and not keep_gradients) else None
         self.layers = model.weighted_layers()
-        self.bucket = GradBucket([l.weight.shape for l in self.layers], self.device)
+        # With more than one rank the exchange is either ONE kernel per rank over peer memory (reduce-scatter of the
+        # gradients, update of the own slice, new weights stored into every replica: ops.dp_update) when the ranks sit
+        # on different GPUs of one node, or an NCCL all-reduce of the bucket followed by the update launch.
+        self.peer = None
+        shapes = [l.weight.shape for l in self.layers]
+        if self._peer_update_possible(peer_update):
+            self._setup_peer(shapes)
+        if self.peer is None:
+            self.bucket = GradBucket(shapes, self.device)
         for l, v in zip(self.layers, self.bucket.views):
             l.grad_buffer = v
             l.defer_update = True  # one launch updates every layer at the end of the step (after the all-reduce, if any)
@@ -85,6 +98,52 @@ class Trainer:
         self._warmup_steps = warmup_steps
         self.kernels_per_step = None
 
+    # ------------------------------------------------------------------ peer-memory update
+    def _peer_update_possible(self, wanted):
+        if not wanted or self.world < 2 or self.world > 8 or self.keep_gradients or self.global_exact:
+            return False
+        if self.device.type != "cuda" or len(self.layers) > 16 or any(l.weight.numel() % 4 for l in self.layers):
+            return False
+        if dist.get_backend(self.group) != "nccl" or not peers_on_one_node(self.device, self.group):
+            if wanted is True:
+                raise RuntimeError("peer_update needs an NCCL group whose ranks sit on different GPUs of one node")
+            return False
+        return True
+
+    def _setup_peer(self, shapes):
+        w_offs, off = [], 0
+        for l in self.layers:
+            w_offs.append(off)
+            off += (l.weight.numel() + 255) // 256 * 256
+        g_off, g_numel = off, GradBucket.numel_for(shapes)
+        x_off = (g_off + 4 * g_numel + 255) // 256 * 256
+        arena = PeerArena(x_off + ops.dp_exchange_bytes(), self.device, self.group)
+        if not arena.ok:
+            warnings.warn(f"peer mapping failed ({arena.error or 'on another rank'}): falling back to the NCCL all-reduce")
+            return
+        for l, o in zip(self.layers, w_offs):  # the weights move into the arena, where the peers' kernels store updates
+            v = arena.view(o, l.weight.numel(), torch.int8, l.weight.shape)
+            v.copy_(l.weight)
+            l.weight = v
+        self.bucket = GradBucket(shapes, self.device, flat=arena.view(g_off, 4 * g_numel, torch.int32))
+        self._dp_items = [(w_offs[i], self.bucket.offsets[i], l.weight.numel(), 16 * l.layer_id + 2)
+                          for i, l in enumerate(self.layers)]
+        self._dp_ptrs = (list(arena.ptrs), [p + g_off for p in arena.ptrs], [p + x_off for p in arena.ptrs])
+        self.peer = arena
+        torch.cuda.synchronize(self.device)
+        dist.barrier(self.group)
+
+    def close(self):
+        """Collective: unmaps the peers' memory (call on every rank before the process group goes away)."""
+        if self.peer is not None:
+            torch.cuda.synchronize(self.device)
+            for l in self.layers:  # the arena is about to be freed: the model keeps its weights in memory of its own
+                l.weight = l.weight.clone()
+                l.grad_buffer = None
+            self.peer.close()
+            self.peer = None
+            self._graphs = None
+
     # ------------------------------------------------------------------ pieces of one step
     def _forward_backward(self):
         self.model.train_step(self.x, self.t)
@@ -92,12 +151,16 @@ class Trainer:
             torch.cuda.current_stream(self.device).wait_stream(self.side)
 
     def _update(self):
-        ti_torch.weight_update_all(self.layers, clear=not self.keep_gradients)
+        if self.peer is not None:
+            ops.dp_update(self._dp_items, self.rank, self.world, *self._dp_ptrs, ti_torch.GRAD_BITWIDTH,
+                          ti_torch._mode(ti_torch.GRAD_ROUND_METHOD), ti_torch.RNG_SEED(self.device), self.device)
+        else:
+            ti_torch.weight_update_all(self.layers, clear=not self.keep_gradients)
         ti_torch.advance_seed(self.device)
 
     def _run_eager(self):
         self._forward_backward()
-        if self.world > 1:
+        if self.world > 1 and self.peer is None:
             self.bucket.allreduce_(self.group)
         self._update()
 
@@ -106,10 +169,10 @@ class Trainer:
         g1 = torch.cuda.CUDAGraph()
         with torch.cuda.graph(g1):
             self._forward_backward()
-            if self.world == 1:
+            if self.world == 1 or self.peer is not None:
                 self._update()
         g2 = None
-        if self.world > 1:
+        if self.world > 1 and self.peer is None:
             g2 = torch.cuda.CUDAGraph()
             with torch.cuda.graph(g2, pool=g1.pool()):
                 self._update()
