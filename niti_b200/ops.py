@@ -62,10 +62,14 @@ def status_word(device):
 
 
 def check_status(device):
-    """Synchronises and raises if a tensor-core kernel reported a timed-out wait."""
+    """Synchronises and raises if a kernel reported a timed-out wait."""
     s = status_word(device).tolist()
+    if s[0] == 9:
+        who = f"rank {s[1]}" if s[1] >= 0 else "the blocks of its own grid"
+        raise RuntimeError(f"niti_b200 data-parallel update gave up waiting for {who} at barrier {s[2]}: "
+                           "the replicas are out of step")
     if s[0] != 0:
-        raise RuntimeError(f"niti_b200 tensor-core kernel gave up waiting: code={s[0]} block={s[1]} role={s[2]}")
+        raise RuntimeError(f"niti_b200 kernel gave up waiting: code={s[0]} block={s[1]} role={s[2]}")
 
 
 def scratch(device, nbytes):

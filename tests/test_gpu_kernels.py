@@ -395,6 +395,49 @@ def test_update_multi_can_clear_the_accumulators():
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("mode", [0, 1, 2])
+def test_dp_update_with_one_rank_equals_update_multi(mode):
+    """niti_dp_update_i8 with world = 1 (all three barriers, slice = whole layer) against niti_update_multi_i8 with
+    clearing; three launches in a row, so the barrier sequence numbers carry over.  The multi-rank arithmetic is
+    checked on two GPUs in test_gpu_dp_peer.py."""
+    rng = np.random.default_rng(40 + mode)
+    sizes = [128 * 3 * 3 * 3, 128 * 3 * 3 * 128, 4 * 1001, 10 * 8192]
+    seed = ops.seed_tensor(99, DEV)
+    w_offs, off = [], 0
+    for n in sizes:
+        w_offs.append(off)
+        off += (n + 255) // 256 * 256
+    g_off = off
+    g_offs, goff = [], 0
+    for n in sizes:
+        g_offs.append(goff)
+        goff += n
+    x_off = (g_off + 4 * goff + 255) // 256 * 256
+    arena = torch.zeros(x_off + ops.dp_exchange_bytes(), dtype=torch.uint8, device=DEV)
+    ws = [arena[o:o + n].view(torch.int8) for o, n in zip(w_offs, sizes)]
+    bucket = arena[g_off:g_off + 4 * goff].view(torch.int32)
+    gs = [bucket[o:o + n] for o, n in zip(g_offs, sizes)]
+    items = [(w_offs[i], g_offs[i], sizes[i], 16 * i + 2) for i in range(len(sizes))]
+    base = arena.data_ptr()
+    for w in ws:
+        w.copy_(cu(rnd8(rng, (w.numel(),))))
+    for step in range(3):
+        for i, g in enumerate(gs):
+            scale = [3, 700, 90000, 0][(i + step) % 4]
+            g.copy_(cu(rng.integers(-scale, scale + 1, size=g.numel()).astype(np.int32)))
+        ref_w = [w.clone() for w in ws]
+        ref_g = [g.clone() for g in gs]
+        want_mx = ops.update_multi(ref_w, ref_g, [it[3] for it in items], 5, mode, seed, want_max=True, clear=True)
+        got_mx = torch.zeros(len(sizes), dtype=torch.int32, device=DEV)
+        ops.dp_update(items, 0, 1, [base], [base + g_off], [base + x_off], 5, mode, seed, DEV, maxabs=got_mx)
+        ops.check_status(DEV)
+        for i in range(len(sizes)):
+            assert_same(ws[i], ref_w[i].cpu().numpy(), f"dp_update step {step} layer {i}")
+            assert int(got_mx[i]) == int(want_mx[i])
+        assert int(bucket.abs().max()) == 0
+
+
+@pytest.mark.gpu
 @pytest.mark.parametrize("N,H,W,C,K", [(8, 16, 16, 128, 128), (4, 8, 8, 256, 128), (3, 10, 6, 64, 144)])
 def test_conv_wgrad_accumulates_into_the_gradient(N, H, W, C, K):
     """g32 += weight gradient: twice the same call gives base + 2 * gradient (gradient accumulation over micro-batches)."""
