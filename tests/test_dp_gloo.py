@@ -112,3 +112,14 @@ def test_comm_groups_cover_bucket_in_backward_order():
     assert all(a[2] == b_[3] for a, b_ in zip(groups, groups[1:]))
     assert all((g[3] - g[2]) * 4 >= 4 << 20 for g in groups[:-1])
     assert GradBucket([(4, 4)], "cpu").comm_groups() == [(0, 0, 0, 16)]
+
+
+def test_bucket_adopts_external_memory():
+    """The peer-memory exchange keeps the bucket inside an arena the other ranks can address."""
+    shapes = [(128, 3, 3, 3), (10, 8192), (5, 7)]
+    n = GradBucket.numel_for(shapes)
+    arena = torch.zeros(n + 8, dtype=torch.int32)
+    b = GradBucket(shapes, "cpu", flat=arena[4:4 + n])
+    assert b.flat.data_ptr() == arena.data_ptr() + 16 and b.flat.numel() == n
+    b.views[2].fill_(3)
+    assert int(arena.sum()) == 3 * 35 and all(o % 4 == 0 for o in b.offsets)
