@@ -638,11 +638,12 @@ __device__ __forceinline__ void st_release_sys(int32_t* p, int v) {
 __device__ __forceinline__ void st_relaxed_sys(unsigned* p, unsigned v) {
     asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
-__device__ __forceinline__ int ld_acquire_sys(const int32_t* p) {
+__device__ __forceinline__ int ld_relaxed_sys(const int32_t* p) {
     int v;
-    asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    asm volatile("ld.relaxed.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
     return v;
 }
+__device__ __forceinline__ void fence_acq_rel_sys() { asm volatile("fence.acq_rel.sys;" ::: "memory"); }
 __device__ __forceinline__ void st_release_gpu_u64(void* p, unsigned long long v) {
     asm volatile("st.release.gpu.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
 }
@@ -667,6 +668,9 @@ __device__ bool dp_barrier(const DpUpdateParams& p, int seq, int number, bool se
             for (unsigned spin = 0; ld_acquire_gpu(&L[DPX_ARRIVALS]) < static_cast<int>(gridDim.x) - 1; ++spin)
                 if ((spin & 63) == 63 && grid_timer_ns() - t0 > GRID_WAIT_LIMIT_NS) { ok = false; break; }
             L[DPX_ARRIVALS] = 0;  // nobody arrives again before this barrier's verdict, which is stored after this
+#ifdef NITI_DP_TIMING
+            reinterpret_cast<unsigned long long*>(L + 40)[5 + number] = grid_timer_ns();
+#endif
             *flag = ok ? 1 : 0;
         }
         __syncthreads();
@@ -680,8 +684,10 @@ __device__ bool dp_barrier(const DpUpdateParams& p, int seq, int number, bool se
             }
             st_release_sys(&X[DPX_FLAGS + p.rank], seq);  // release: everything this grid wrote before is visible to who sees it
             const unsigned long long t0 = grid_timer_ns();
-            for (unsigned spin = 0; ld_acquire_sys(&L[DPX_FLAGS + peer]) - seq < 0; ++spin)
+            // relaxed polls (the word is in this GPU's memory), ONE acquire fence once the peer's number is there
+            for (unsigned spin = 0; ld_relaxed_sys(&L[DPX_FLAGS + peer]) - seq < 0; ++spin)
                 if ((spin & 63) == 63 && grid_timer_ns() - t0 > PEER_WAIT_LIMIT_NS) { ok = 0; waited_for = peer; break; }
+            fence_acq_rel_sys();
         }
         const int all_ok = __syncthreads_and(ok);
         if (!ok && p.status != nullptr && atomicCAS(p.status, 0, 9) == 0) { p.status[1] = waited_for; p.status[2] = number; }
@@ -708,6 +714,54 @@ __device__ bool dp_barrier(const DpUpdateParams& p, int seq, int number, bool se
     return *flag != 0;
 }
 
+// Sum of word groups [lo, hi) of one layer over all ranks, stored in place in the own bucket; returns max |sum| of
+// this thread's groups.  A thread has U groups x (world - 1) peer loads in flight (about eight 16-byte loads): the
+// loop is bound by the round trip to the peers, not by bandwidth.  U = 4 serves world <= 2, U = 2 world <= 4.
+template <int U>
+__device__ __forceinline__ unsigned reduce_slice(const DpUpdateParams& p, const DpItem& it, int4* mine, long long lo, long long hi,
+                                                 long long tid, long long nthreads) {
+    constexpr int SLOTS = DP_MAX_RANKS / U;  // own + peers
+    unsigned m = 0;
+    for (long long g0 = lo + tid; g0 < hi; g0 += U * nthreads) {
+        int4 v[U][SLOTS];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const long long g = g0 + u * nthreads;
+            if (g < hi) {
+                v[u][0] = __ldcg(mine + g);
+#pragma unroll
+                for (int r = 1; r < SLOTS; ++r) {
+                    if (r < p.world) {
+                        int pr = p.rank + r;
+                        if (pr >= p.world) pr -= p.world;
+                        v[u][r] = ld_relaxed_sys_v4(reinterpret_cast<const int4*>(p.grads[pr] + it.g_off) + g);
+                    }
+                }
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const long long g = g0 + u * nthreads;
+            if (g < hi) {
+                int4 s = v[u][0];
+#pragma unroll
+                for (int r = 1; r < SLOTS; ++r)
+                    if (r < p.world) s = add4(s, v[u][r]);
+                mine[g] = s;
+                m = max(m, absmax4(s));
+            }
+        }
+    }
+    return m;
+}
+
+// -DNITI_DP_TIMING: block 0 leaves %globaltimer stamps in the unused words 40..63 of the exchange area: 0..5 = start,
+// after each barrier and each phase; 6..8 = inside barrier 1..3, when the own grid had arrived
+#ifdef NITI_DP_TIMING
+#define DP_STAMP(i) do { if (blockIdx.x == 0 && threadIdx.x == 0) reinterpret_cast<unsigned long long*>(L + 40)[i] = grid_timer_ns(); } while (0)
+#else
+#define DP_STAMP(i) do { } while (0)
+#endif
 __global__ void __launch_bounds__(256)
 dp_update_kernel(const DpUpdateParams p) {
     __shared__ int flag;
@@ -722,31 +776,20 @@ dp_update_kernel(const DpUpdateParams p) {
     int4* mine = reinterpret_cast<int4*>(p.grads[p.rank] + it.g_off);
     const int seq0 = 3 * __ldcg(&L[DPX_EPOCH]);  // the same in every block: the word changes after the last barrier only
 
+    DP_STAMP(0);
     // ---- 1: every rank's gradients are complete
     if (!dp_barrier(p, seq0 + 1, 1, false, &flag)) return;
+    DP_STAMP(1);
     {   // ---- 2: sum this rank's slice over the ranks (in place in the own bucket), its maximum
-        unsigned m = 0;
-        for (long long g = lo + tid; g < hi; g += nthreads) {
-            int4 v[DP_MAX_RANKS];
-#pragma unroll
-            for (int r = 1; r < DP_MAX_RANKS; ++r) {
-                if (r < p.world) {
-                    int pr = p.rank + r;
-                    if (pr >= p.world) pr -= p.world;
-                    v[r] = ld_relaxed_sys_v4(reinterpret_cast<const int4*>(p.grads[pr] + it.g_off) + g);
-                }
-            }
-            int4 s = __ldcg(mine + g);
-#pragma unroll
-            for (int r = 1; r < DP_MAX_RANKS; ++r)
-                if (r < p.world) s = add4(s, v[r]);
-            mine[g] = s;
-            m = max(m, absmax4(s));
-        }
+        const unsigned m = p.world <= 2 ? reduce_slice<4>(p, it, mine, lo, hi, tid, nthreads)
+                         : p.world <= 4 ? reduce_slice<2>(p, it, mine, lo, hi, tid, nthreads)
+                                        : reduce_slice<1>(p, it, mine, lo, hi, tid, nthreads);
         block_atomic_max(reinterpret_cast<unsigned*>(&L[DPX_OWN_MAX + l]), m);
     }
+    DP_STAMP(2);
     // ---- 3: the slices' maxima reach every rank; every rank has finished reading the others' buckets
     if (!dp_barrier(p, seq0 + 2, 2, true, &flag)) return;
+    DP_STAMP(3);
     {
         unsigned mx = 0;
         for (int r = 0; r < p.world; ++r) mx = max(mx, static_cast<unsigned>(__ldcg(&L[DPX_MAXIMA + r * UPDATE_MULTI_MAX + l])));
@@ -756,21 +799,37 @@ dp_update_kernel(const DpUpdateParams p) {
         const bool stochastic = (p.mode == ROUND_STOCHASTIC) && shift > 0;
         const unsigned long long seed = stochastic ? *p.seed : 0ull;
         const uint32_t* w_own = reinterpret_cast<const uint32_t*>(p.weights[p.rank] + it.w_off);
-        for (long long g = tid; g < groups; g += nthreads) {
-            if (g >= lo && g < hi) {
-                uint32_t rnd[4] = {0, 0, 0, 0};
-                if (stochastic) random_block(seed, it.rng_stream, static_cast<unsigned long long>(g), rnd);
-                const uint32_t o = update_word(__ldcg(mine + g), w_own[g], rnd, shift, p.mode, zero_out);
+        for (long long g0 = lo + tid; g0 < hi; g0 += 4 * nthreads) {  // the own slice: four groups' loads go out together
+            int4 sv[4];
+            uint32_t wv[4];
 #pragma unroll
-                for (int r = 0; r < DP_MAX_RANKS; ++r)
-                    if (r < p.world) reinterpret_cast<uint32_t*>(p.weights[r] + it.w_off)[g] = o;
+            for (int u = 0; u < 4; ++u) {
+                const long long g = g0 + u * nthreads;
+                if (g < hi) { sv[u] = __ldcg(mine + g); wv[u] = w_own[g]; }
             }
-            mine[g] = make_int4(0, 0, 0, 0);  // the weight-gradient kernels of the next step add into a zeroed bucket
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const long long g = g0 + u * nthreads;
+                if (g < hi) {
+                    uint32_t rnd[4] = {0, 0, 0, 0};
+                    if (stochastic) random_block(seed, it.rng_stream, static_cast<unsigned long long>(g), rnd);
+                    const uint32_t o = update_word(sv[u], wv[u], rnd, shift, p.mode, zero_out);
+#pragma unroll
+                    for (int r = 0; r < DP_MAX_RANKS; ++r)
+                        if (r < p.world) reinterpret_cast<uint32_t*>(p.weights[r] + it.w_off)[g] = o;
+                    mine[g] = make_int4(0, 0, 0, 0);
+                }
+            }
         }
+        // the rest of the own bucket: the weight-gradient kernels of the next step add into a zeroed bucket
+        for (long long g = tid; g < lo; g += nthreads) mine[g] = make_int4(0, 0, 0, 0);
+        for (long long g = hi + tid; g < groups; g += nthreads) mine[g] = make_int4(0, 0, 0, 0);
         __threadfence_system();
     }
+    DP_STAMP(4);
     // ---- 4: every rank's weight stores have landed
     if (!dp_barrier(p, seq0 + 3, 3, false, &flag)) return;
+    DP_STAMP(5);
     if (blockIdx.x == 0 && threadIdx.x == 0) L[DPX_EPOCH] = L[DPX_EPOCH] + 1;
 }
 
