@@ -148,7 +148,10 @@ NITI_API int niti_conv_wgrad_accumulate_i8(const int8_t* x, const int8_t* err, i
  *    first-layer patch matrix N*H*W*32 bytes above it) is refused with NITI_ERR_TOO_LARGE before
  *    anything is launched.
  *  - The first call on each device looks up the buffer's device address (cudaGetSymbolAddress, with that
- *    device current); make that first call during set-up, before any stream capture is begun.
+ *    device current); make that first call during set-up, before any stream capture is begun.  `stream` must
+ *    belong to the current device.  The address is remembered per device ordinal: a process that resets a
+ *    device (cudaDeviceReset) must not use this entry point on it afterwards.  Concurrent first calls from
+ *    several host threads are safe.  maxabs may be null, as in niti_conv_wgrad_i8.
  *  - All calls on a device share the one buffer and it keeps the previous call's contents; this entry
  *    point needs none of it zeroed, but two calls whose kernels overlap on the GPU (different streams
  *    without ordering) race on it: keep calls stream-ordered.
@@ -227,6 +230,17 @@ NITI_API int niti_requant_i8(const int32_t* acc, int8_t* out, const uint32_t* ma
 /* max |acc| over n int32 values, reduced into *maxabs (cleared first).  RangeEstimate for
  * tensors that did not come out of a contraction kernel (e.g. all-reduced gradients). */
 NITI_API int niti_absmax_i32(const int32_t* acc, int64_t n, uint32_t* maxabs, void* stream);
+
+/* int8conv_cuda.group_conv (int8conv.cpp:35-45, int8conv_kernel.cu:248-334) in the one form the reference
+ * calls it: conv2d_weight_int8 (ti_torch.py:194-233) folds batch and input channels into G = N*C groups of one
+ * channel each and turns the error maps into G*Kg filters as large as the image, so that the "convolution"
+ * yields every sample's own weight gradient.  in [H][W][G], wt [G*Kg][R][S] (one channel), stride 1, dilation 1:
+ * out32[p][q][g*Kg+k] = sum_{r,s} in[p+r-pad][q+s-pad][g] * wt[g*Kg+k][r][s], P = H+2*pad-R+1, exact int32
+ * (the reference accumulates in float32).  Batch and channels cannot be told apart from G alone, which is why this
+ * form cannot be handed to niti_conv_wgrad_i8; code written against this library calls that entry point directly.
+ */
+NITI_API int niti_group_conv1_i8(const int8_t* in, const int8_t* wt, int32_t* out32, int H, int W, int G, int Kg,
+                        int R, int S, int pad, void* stream);
 
 /* ---------------------------------------------------------------- memory-bound layers
  * int8pool_cuda.int8_pool / int8_pool_backward (int8pool.cpp, int8pool_kernel.cu:28-138) as

@@ -37,6 +37,7 @@ SIGNATURES = {
     "niti_gemm_i8": (_i, [_p, _p, _p, _p] + [_i] * 5 + [_p, _p]),
     "niti_requant_i8": (_i, [_p, _p, _p, _i64, _i, _i, _i, _p, _u32, _u64, _i, _p, _p, _p, _p, _p]),
     "niti_absmax_i32": (_i, [_p, _i64, _p, _p]),
+    "niti_group_conv1_i8": (_i, [_p, _p, _p] + [_i] * 7 + [_p]),
     "niti_maxpool_fwd_i8": (_i, [_p, _p] + [_i] * 6 + [_p]),
     "niti_maxpool_bwd_i8": (_i, [_p, _p, _p] + [_i] * 7 + [_p]),
     "niti_relu_fwd_i8": (_i, [_p, _p, _i64, _p]),

@@ -1,6 +1,7 @@
 // C ABI: error reporting and the contraction entry points, which choose between the tensor-core
 // (tcgen05) kernels and the CUDA-core kernels by shape.  Declarations: include/niti_b200.h.
 #include <cuda_runtime.h>
+#include <atomic>
 #include <cstdint>
 #include <cstdio>
 #include <cstring>
@@ -301,26 +302,30 @@ static __device__ __align__(256) unsigned char g_builtin_scratch[NITI_BUILTIN_SC
 
 // `g_builtin_scratch` names the buffer only in device code.  Host code must ask the runtime for the
 // device address (per device: each device has its own copy of the array); it is looked up the first
-// time a device uses the entry point, with that device current, and remembered.
-static void* g_builtin_scratch_addr[64] = {nullptr};
+// time a device uses the entry point, with that device current, and remembered.  The table is keyed by
+// the CURRENT device (the stream passed in must belong to it); its slots are atomics because two host
+// threads may make their first call on a device at the same time (both would store the same address).
+// After cudaDeviceReset the remembered address is stale: a process that resets a device must not call
+// the entry point on it again.
+static std::atomic<void*> g_builtin_scratch_addr[64];
 
 static int builtin_scratch(void** out) {
     int dev = -1;
     if (int e = set_cuda_error(cudaGetDevice(&dev))) return e;
     if (dev < 0 || dev >= 64) return set_cuda_error_text("device ordinal outside the range the built-in scratch table covers");
-    if (g_builtin_scratch_addr[dev] == nullptr) {
-        void* p = nullptr;
+    void* p = g_builtin_scratch_addr[dev].load(std::memory_order_acquire);
+    if (p == nullptr) {
         if (int e = set_cuda_error(cudaGetSymbolAddress(&p, g_builtin_scratch))) return e;
-        g_builtin_scratch_addr[dev] = p;
+        g_builtin_scratch_addr[dev].store(p, std::memory_order_release);
     }
-    *out = g_builtin_scratch_addr[dev];
+    *out = p;
     return NITI_OK;
 }
 
 extern "C" int niti_conv_wgrad_builtin_scratch_i8(const int8_t* x, const int8_t* err, int32_t* g32, uint32_t* maxabs, int N,
                                                   int H, int W, int C, int K, int R, int S, int pad, int32_t* status,
                                                   void* stream) {
-    NITI_REQUIRE(x && err && g32 && maxabs && N > 0 && H > 0 && W > 0 && C > 0 && K > 0 && R > 0 && S > 0 && pad >= 0);
+    NITI_REQUIRE(x && err && g32 && N > 0 && H > 0 && W > 0 && C > 0 && K > 0 && R > 0 && S > 0 && pad >= 0);
     NITI_REQUIRE(aligned16(g32));
     if (H + 2 * pad - R + 1 <= 0 || W + 2 * pad - S + 1 <= 0) return NITI_ERR_BAD_ARG;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
@@ -340,7 +345,8 @@ extern "C" int niti_conv_wgrad_builtin_scratch_i8(const int8_t* x, const int8_t*
         if (fixed + per_split > cap) return NITI_ERR_TOO_LARGE;
         max_splits = static_cast<int>((cap - fixed) / per_split);
     }
-    if (int e = clear_word(maxabs, st)) return e;
+    if (maxabs != nullptr)  // null, as in niti_conv_wgrad_i8: the caller finds max|g32| later
+        if (int e = clear_word(maxabs, st)) return e;
     if (path == CONV_SIMT) return simt_conv_wgrad(x, err, g32, maxabs, N, H, W, C, K, R, S, pad, st);
     void* scratch = nullptr;
     if (int e = builtin_scratch(&scratch)) return e;

@@ -91,6 +91,40 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     }
 }
 
+// The same bounded wait for loops whose control flow must stay warp-uniform (the TMA producer and the MMA issuer:
+// their TMA / MMA instructions take operands from uniform registers, and the compiler keeps loop counters,
+// addresses and descriptors there only while it can prove that every lane follows the same path).  The spin is
+// inside ONE asm block, so no C++ branch depends on a per-lane value; the verdict is made warp-uniform with a
+// vote.  All 32 lanes must call it.  Returns false when the limit ran out or another role raised the abort flag.
+__device__ __forceinline__ bool mbar_wait_uniform(uint32_t bar, uint32_t parity, uint32_t abort_flag_smem) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t"
+        ".reg .pred P, Q;\n\t"
+        ".reg .u64 t0, t1;\n\t"
+        ".reg .u32 a;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 P, [%1], %2;\n\t"
+        "@P bra WAIT_DONE;\n\t"
+        "mov.u64 t0, %%globaltimer;\n\t"
+        "WAIT_SPIN:\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 P, [%1], %2;\n\t"
+        "@P bra WAIT_DONE;\n\t"
+        "ld.volatile.shared.u32 a, [%3];\n\t"
+        "setp.ne.u32 Q, a, 0;\n\t"
+        "@Q bra WAIT_DONE;\n\t"
+        "mov.u64 t1, %%globaltimer;\n\t"
+        "sub.u64 t1, t1, t0;\n\t"
+        "setp.lt.u64 Q, t1, %4;\n\t"
+        "@Q bra WAIT_SPIN;\n\t"
+        "WAIT_DONE:\n\t"
+        "selp.u32 %0, 1, 0, P;\n\t"
+        "}"
+        : "=r"(done)
+        : "r"(bar), "r"(parity), "r"(abort_flag_smem), "l"(WAIT_LIMIT_NS)
+        : "memory");
+    return __all_sync(0xFFFFFFFFu, done != 0);
+}
+
 // ----------------------------------------------------------------------------- TMA
 __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* m) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(m)) : "memory");
@@ -170,6 +204,73 @@ __device__ __forceinline__ void umma_i8(uint32_t d_tmem, uint64_t a_desc, uint64
         "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, P;\n\t}"
         ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
         : "memory");
+}
+// One reduction block of the main loop as ONE asm statement, run by the whole (converged) warp: a non-blocking probe of
+// the NEXT stage's "full" barrier is started, an elected lane issues the block's four MMAs (K = 32 each, operand
+// descriptors a, a + a_step, ... ; the first one accumulates only if `accumulate`) and the commit that hands the stage
+// back, and only then is the probe's answer read -- its shared-memory round trip runs under the MMA issue instead of
+// in front of the next block.  Returns the probe's answer (per lane; make it uniform with a vote).
+template <bool PAIR>
+__device__ __forceinline__ uint32_t umma_block4(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint64_t a_step, uint64_t b_step,
+                                                uint32_t idesc, uint32_t accumulate, uint32_t commit_bar, uint32_t next_full_bar,
+                                                uint32_t next_parity) {
+    uint32_t ready;
+    if (PAIR) {
+        asm volatile(
+            "{\n\t"
+            ".reg .pred P, Q, E, T;\n\t"
+            ".reg .b32 r;\n\t"
+            ".reg .b64 a1, a2, a3, b1, b2, b3;\n\t"
+            "mbarrier.test_wait.parity.shared::cta.b64 Q, [%9], %10;\n\t"
+            "elect.sync r|E, 0xFFFFFFFF;\n\t"
+            "setp.ne.b32 P, %7, 0;\n\t"
+            "setp.eq.b32 T, 0, 0;\n\t"
+            "add.u64 a1, %2, %4;\n\t"
+            "add.u64 b1, %3, %5;\n\t"
+            "add.u64 a2, a1, %4;\n\t"
+            "add.u64 b2, b1, %5;\n\t"
+            "add.u64 a3, a2, %4;\n\t"
+            "add.u64 b3, b2, %5;\n\t"
+            "@E tcgen05.mma.cta_group::2.kind::i8 [%1], %2, %3, %6, P;\n\t"
+            "@E tcgen05.mma.cta_group::2.kind::i8 [%1], a1, b1, %6, T;\n\t"
+            "@E tcgen05.mma.cta_group::2.kind::i8 [%1], a2, b2, %6, T;\n\t"
+            "@E tcgen05.mma.cta_group::2.kind::i8 [%1], a3, b3, %6, T;\n\t"
+            "@E tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%8], %11;\n\t"
+            "selp.u32 %0, 1, 0, Q;\n\t"
+            "}"
+            : "=r"(ready)
+            : "r"(d_tmem), "l"(a_desc), "l"(b_desc), "l"(a_step), "l"(b_step), "r"(idesc), "r"(accumulate), "r"(commit_bar),
+              "r"(next_full_bar), "r"(next_parity), "h"(static_cast<uint16_t>(3))
+            : "memory");
+    } else {
+        asm volatile(
+            "{\n\t"
+            ".reg .pred P, Q, E, T;\n\t"
+            ".reg .b32 r;\n\t"
+            ".reg .b64 a1, a2, a3, b1, b2, b3;\n\t"
+            "mbarrier.test_wait.parity.shared::cta.b64 Q, [%9], %10;\n\t"
+            "elect.sync r|E, 0xFFFFFFFF;\n\t"
+            "setp.ne.b32 P, %7, 0;\n\t"
+            "setp.eq.b32 T, 0, 0;\n\t"
+            "add.u64 a1, %2, %4;\n\t"
+            "add.u64 b1, %3, %5;\n\t"
+            "add.u64 a2, a1, %4;\n\t"
+            "add.u64 b2, b1, %5;\n\t"
+            "add.u64 a3, a2, %4;\n\t"
+            "add.u64 b3, b2, %5;\n\t"
+            "@E tcgen05.mma.cta_group::1.kind::i8 [%1], %2, %3, %6, P;\n\t"
+            "@E tcgen05.mma.cta_group::1.kind::i8 [%1], a1, b1, %6, T;\n\t"
+            "@E tcgen05.mma.cta_group::1.kind::i8 [%1], a2, b2, %6, T;\n\t"
+            "@E tcgen05.mma.cta_group::1.kind::i8 [%1], a3, b3, %6, T;\n\t"
+            "@E tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%8];\n\t"
+            "selp.u32 %0, 1, 0, Q;\n\t"
+            "}"
+            : "=r"(ready)
+            : "r"(d_tmem), "l"(a_desc), "l"(b_desc), "l"(a_step), "l"(b_step), "r"(idesc), "r"(accumulate), "r"(commit_bar),
+              "r"(next_full_bar), "r"(next_parity)
+            : "memory");
+    }
+    return ready;
 }
 // mbarrier arrives once all tcgen05 operations issued so far by this thread have completed.
 __device__ __forceinline__ void umma_commit(uint32_t bar) {

@@ -1097,6 +1097,46 @@ extern "C" int niti_absmax_i32(const int32_t* acc, int64_t n, uint32_t* maxabs, 
     return set_cuda_error(cudaGetLastError());
 }
 
+// Grouped cross-correlation with ONE input channel per group and a batch of one: the only form in which the
+// reference calls int8conv_cuda.group_conv (conv2d_weight_int8 folds batch and channels into groups and the error
+// maps into filters as large as the image).  out[p][q][g*Kg + k] = sum_{r,s} in[p+r-pad][q+s-pad][g] * wt[g*Kg+k][r][s].
+// One warp per output channel: the lanes split the filter window, a shuffle tree adds up, exact int32.
+__global__ void __launch_bounds__(256)
+group_conv1_kernel(const int8_t* __restrict__ in, const int8_t* __restrict__ wt, int32_t* __restrict__ out, int H, int W,
+                   int G, int Kg, int R, int S, int pad, int P, int Q) {
+    const int lane = threadIdx.x & 31;
+    const long long warps = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
+    const long long chans = static_cast<long long>(G) * Kg;
+    for (long long oc = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5; oc < chans; oc += warps) {
+        const int g = static_cast<int>(oc / Kg);
+        const int8_t* f = wt + oc * R * S;
+        for (int p = 0; p < P; ++p)
+            for (int q = 0; q < Q; ++q) {
+                int acc = 0;
+                for (int i = lane; i < R * S; i += 32) {
+                    const int r = i / S, sx = i - r * S;
+                    const int hh = p + r - pad, ww = q + sx - pad;
+                    if (hh >= 0 && hh < H && ww >= 0 && ww < W)
+                        acc += static_cast<int>(in[(static_cast<long long>(hh) * W + ww) * G + g]) * static_cast<int>(f[i]);
+                }
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xFFFFFFFFu, acc, o);
+                if (lane == 0) out[(static_cast<long long>(p) * Q + q) * chans + oc] = acc;
+            }
+    }
+}
+
+extern "C" int niti_group_conv1_i8(const int8_t* in, const int8_t* wt, int32_t* out32, int H, int W, int G, int Kg, int R, int S,
+                                   int pad, void* stream) {
+    NITI_REQUIRE(in && wt && out32 && H > 0 && W > 0 && G > 0 && Kg > 0 && R > 0 && S > 0 && pad >= 0);
+    const int P = H + 2 * pad - R + 1, Q = W + 2 * pad - S + 1;
+    if (P <= 0 || Q <= 0) return NITI_ERR_BAD_ARG;
+    const long long chans = static_cast<long long>(G) * Kg;
+    group_conv1_kernel<<<blocks_for(chans * 32, 256, sm_count_simt() * 16), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        in, wt, out32, H, W, G, Kg, R, S, pad, P, Q);
+    return set_cuda_error(cudaGetLastError());
+}
+
 extern "C" int niti_maxpool_fwd_i8(const int8_t* x, int8_t* y, int N, int H, int W, int C, int k, int stride, void* stream) {
     NITI_REQUIRE(x && y && N > 0 && H >= k && W >= k && C > 0 && k > 0 && stride > 0);
     cudaStream_t st = static_cast<cudaStream_t>(stream);

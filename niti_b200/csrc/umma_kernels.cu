@@ -31,9 +31,21 @@ namespace niti {
 #ifdef NITI_PARKED_TIMING
 __device__ unsigned long long g_dbg_stamps[32];
 #define PARK_STAMP(i) do { if (blockIdx.x == 0) g_dbg_stamps[i] = global_timer_ns(); } while (0)
+#define DBG_CLK(v) const long long v = clock64()
+#define DBG_DECL long long dbg_acc[4] = {0, 0, 0, 0}
+#define DBG_ACC(i, d) dbg_acc[(i) & 3] += (d)
+#define DBG_OUT(base) do { if (blockIdx.x == 0 && (threadIdx.x & 31) == 0) for (int q_ = 0; q_ < 4; ++q_) g_dbg_stamps[(base) + q_] = dbg_acc[q_]; } while (0)
 #else
+#define DBG_CLK(v) do { } while (0)
+#define DBG_DECL do { } while (0)
+#define DBG_ACC(i, d) do { } while (0)
+#define DBG_OUT(base) do { } while (0)
 #define PARK_STAMP(i) do { } while (0)
 #endif
+
+// Pin a value in a register: kernel parameters live in the constant bank, and under register pressure the compiler
+// re-reads them at every use; in the producer / MMA loops each such load sits on one warp's serial critical path.
+__device__ __forceinline__ int keep_reg(int v) { asm volatile("" : "+r"(v)); return v; }
 
 constexpr int BLOCK_M = 128;
 constexpr int ROW_BYTES = 128;               // bytes per shared-memory row of an operand tile
@@ -171,9 +183,13 @@ __device__ __forceinline__ void tile_coords(const GemmParams& p, int mn, int* m_
 
 // ---- warp roles shared by the streaming kernel and the accumulator-parking kernel -------------
 // TMA producer: fills the stage ring for every tile of this CTA, in tile order.  The WHOLE warp runs the loop and
-// one lane issues: with warp-uniform control flow the compiler keeps addresses, coordinates and descriptors in
-// uniform registers, which is where the TMA and MMA instructions take their operands from; a loop entered by a
-// single lane pays a register-to-uniform-register move per operand instead (measured: ~100 cycles per MMA issue).
+// an elected lane issues.  TMA and MMA instructions take their operands from uniform registers, and the compiler keeps
+// addresses, coordinates and descriptors there only while every branch around them is provably warp-uniform: waits
+// therefore spin INSIDE one asm statement and hand back a voted verdict (mbar_wait_uniform), values read from shared
+// memory or special registers pass through a shuffle, and the issuing lane comes from elect.sync.  Measured on B200
+// (clock64 around the instructions): 50 cycles per tcgen05.mma and ~20 per TMA instruction this way; 85-90 and ~50 when
+// a loop-carried value depends on a per-lane asm result or the issuer is chosen by `lane == 0`; a loop entered by a
+// single lane sits in between.  Per-tile integer divisions are skipped when the reduction is not split.
 // TWO: this CTA is half of a CTA pair (cluster ranks 0/1).  Tiles are 256 rows high: rank r owns rows
 // [128 r, 128 r + 128) of the pair's tile (m tile 2*pair_m + r) and columns [r BN/2, (r+1) BN/2) of the B
 // operand; all byte counts are reported to rank 0's "full" barrier, which its MMA thread waits on.
@@ -182,153 +198,193 @@ __device__ __forceinline__ void producer_role(uint8_t* smem, uint64_t* full_bar,
                                               const CUtensorMap* tmB, const GemmParams& p, volatile int* abort_flag) {
     const int mn_tiles = p.m_tiles * p.n_tiles;
     const int total_tiles = mn_tiles * p.splits;
-    const uint32_t rank = TWO ? cluster_ctarank() : 0u;
+    const uint32_t rank = TWO ? __shfl_sync(0xFFFFFFFFu, cluster_ctarank(), 0) : 0u;  // a special register: make it provably uniform
     const int first = TWO ? static_cast<int>(blockIdx.x >> 1) : static_cast<int>(blockIdx.x);
     const int step = TWO ? static_cast<int>(gridDim.x >> 1) : static_cast<int>(gridDim.x);
     constexpr int BNH = TWO ? BN / 2 : BN;  // B columns this CTA loads
     const int nst = (p.nstages > 0 && p.nstages < STAGES) ? p.nstages : STAGES;
-    const bool issuer = (threadIdx.x & 31) == 0;
+    const uint32_t abort_addr = smem_u32(const_cast<int*>(abort_flag));
+    const uint32_t smem0 = smem_u32(smem), full0 = smem_u32(full_bar), empty0 = smem_u32(empty_bar);
+    const int conv = keep_reg(p.conv), flip = keep_reg(p.flip), pad = keep_reg(p.pad), S = keep_reg(p.S), cblocks = keep_reg(p.cblocks);
+    const int tapstride = keep_reg(p.tapstride), b_mn = keep_reg(p.b_mn), a_mn = keep_reg(p.a_mn);
+    const uint32_t tx_bytes = static_cast<uint32_t>(keep_reg(TWO ? 2 * (p.a_bytes + BNH * ROW_BYTES) : p.a_bytes + BN * ROW_BYTES));
     int s = 0; uint32_t ph = 0; bool ok = true;
-    bool ready = false;  // the current stage's "empty" phase was already seen complete by the previous iteration's probe
+    DBG_DECL;
+    DBG_CLK(c_begin);
     for (int tile = first; ok && tile < total_tiles; tile += step) {
-        const int split = tile / mn_tiles, mn = tile % mn_tiles;
+        int mn = tile, kb_lo = 0, kb_hi = p.num_kb;
+        if (p.splits > 1) {
+            const int split = tile / mn_tiles;
+            mn = tile % mn_tiles;
+            kb_lo = static_cast<int>(static_cast<long long>(split) * p.num_kb / p.splits);
+            kb_hi = static_cast<int>(static_cast<long long>(split + 1) * p.num_kb / p.splits);
+        }
         int m_pair, n_t;
         tile_coords(p, mn, &m_pair, &n_t);
         const int m_t = TWO ? 2 * m_pair + static_cast<int>(rank) : m_pair;
-        const int kb_lo = static_cast<int>(static_cast<long long>(split) * p.num_kb / p.splits);
-        const int kb_hi = static_cast<int>(static_cast<long long>(split + 1) * p.num_kb / p.splits);
         int tw = 0, th = 0, tn = 0;
-        if (p.conv) { tw = m_t % p.tiles_w; th = (m_t / p.tiles_w) % p.tiles_h; tn = m_t / (p.tiles_w * p.tiles_h); }
+        if (conv) { tw = m_t % p.tiles_w; th = (m_t / p.tiles_w) % p.tiles_h; tn = m_t / (p.tiles_w * p.tiles_h); }
         const int ncol = n_t * BN + static_cast<int>(rank) * BNH;  // first B column of this CTA
-        // This loop is one thread's serial instruction stream and sets the pace of the whole pipeline: the tap
+        const int px = tw * p.BW, py = th * p.BH, pn = tn * p.BI;
+        // This loop is one warp's serial instruction stream and sets the pace of the whole pipeline: the tap
         // (r, sx) and channel block cb of a reduction block are kept as running counters, because four integer
         // divisions per block cost more than the block's MMAs.
         int cb = 0, sx = 0, r = 0;
-        if (p.conv) { const int tap0 = kb_lo / p.cblocks; cb = kb_lo % p.cblocks; r = tap0 / p.S; sx = tap0 % p.S; }
+        if (conv && kb_lo != 0) { const int tap0 = kb_lo / cblocks; cb = kb_lo % cblocks; r = tap0 / S; sx = tap0 % S; }
         for (int kb = kb_lo; kb < kb_hi; ++kb) {
-            if (!ready && !mbar_wait(smem_u32(&empty_bar[s]), ph ^ 1u, abort_flag)) { ok = false; report_abort(p.status, 1, 0); break; }
-            {   // probe the next stage's "empty" phase while this stage's loads are being issued
-                const int sn = (s + 1 == nst) ? 0 : s + 1;
-                ready = mbar_test_wait(smem_u32(&empty_bar[sn]), (sn == 0 ? ph ^ 1u : ph) ^ 1u) != 0;
-            }
-            const uint32_t sa = smem_u32(smem + s * STAGE_BYTES);
+            ok = mbar_wait_uniform(empty0 + 8u * s, ph ^ 1u, abort_addr);
+            if (!ok) { *abort_flag = 1; report_abort(p.status, 1, 0); break; }
+            DBG_ACC(22, 1);
+            const uint32_t sa = smem0 + static_cast<uint32_t>(s) * STAGE_BYTES;
             const uint32_t sb = sa + PANEL_BYTES;
-            uint32_t fb = smem_u32(&full_bar[s]);
-            if (TWO) {
-                if (rank == 0 && issuer) mbar_arrive_expect_tx(fb, 2u * static_cast<uint32_t>(p.a_bytes + BNH * ROW_BYTES));
-                fb = mapa_u32(fb, 0);
-            } else {
-                if (issuer) mbar_arrive_expect_tx(fb, static_cast<uint32_t>(p.a_bytes + BN * ROW_BYTES));
-            }
-            if (!issuer) {
-                // the other lanes only follow the counters
-            } else if (p.conv) {
-                const int tap = r * p.S + sx;
-                const int dx = p.flip ? p.pad - sx : sx - p.pad, dy = p.flip ? p.pad - r : r - p.pad;
-                if (TWO) tma_load_4d_pair(sa, tmA, fb, cb * ROW_BYTES, tw * p.BW + dx, th * p.BH + dy, tn * p.BI);
-                else     tma_load_4d(sa, tmA, fb, cb * ROW_BYTES, tw * p.BW + dx, th * p.BH + dy, tn * p.BI);
-                if (p.b_mn) {
-#pragma unroll
-                    for (int pn = 0; pn < BNH / 128; ++pn) {
-                        if (TWO) tma_load_2d_pair(sb + pn * PANEL_BYTES, tmB, fb, tap * p.tapstride + ncol + pn * 128, cb * 128);
-                        else     tma_load_2d(sb + pn * PANEL_BYTES, tmB, fb, tap * p.tapstride + ncol + pn * 128, cb * 128);
-                    }
-                } else {
-                    if (TWO) tma_load_2d_pair(sb, tmB, fb, tap * p.tapstride + cb * ROW_BYTES, ncol);
-                    else     tma_load_2d(sb, tmB, fb, tap * p.tapstride + cb * ROW_BYTES, ncol);
-                }
-            } else {
+            uint32_t fb = full0 + 8u * s;
+            if (elect_one()) {
                 if (TWO) {
-                    if (p.a_mn) tma_load_2d_pair(sa, tmA, fb, m_t * BLOCK_M, kb * 128);
-                    else        tma_load_2d_pair(sa, tmA, fb, kb * ROW_BYTES, m_t * BLOCK_M);
+                    if (rank == 0) mbar_arrive_expect_tx(fb, tx_bytes);
+                    fb = mapa_u32(fb, 0);
                 } else {
-                    if (p.a_mn) tma_load_2d(sa, tmA, fb, m_t * BLOCK_M, kb * 128);
-                    else        tma_load_2d(sa, tmA, fb, kb * ROW_BYTES, m_t * BLOCK_M);
+                    mbar_arrive_expect_tx(fb, tx_bytes);
                 }
-                if (p.b_mn) {
+                if (conv) {
+                    const int tap = r * S + sx;
+                    const int dx = flip ? pad - sx : sx - pad, dy = flip ? pad - r : r - pad;
+                    if (TWO) tma_load_4d_pair(sa, tmA, fb, cb * ROW_BYTES, px + dx, py + dy, pn);
+                    else     tma_load_4d(sa, tmA, fb, cb * ROW_BYTES, px + dx, py + dy, pn);
+                    if (b_mn) {
 #pragma unroll
-                    for (int pn = 0; pn < BNH / 128; ++pn) {
-                        if (TWO) tma_load_2d_pair(sb + pn * PANEL_BYTES, tmB, fb, ncol + pn * 128, kb * 128);
-                        else     tma_load_2d(sb + pn * PANEL_BYTES, tmB, fb, ncol + pn * 128, kb * 128);
+                        for (int q = 0; q < BNH / 128; ++q) {
+                            if (TWO) tma_load_2d_pair(sb + q * PANEL_BYTES, tmB, fb, tap * tapstride + ncol + q * 128, cb * 128);
+                            else     tma_load_2d(sb + q * PANEL_BYTES, tmB, fb, tap * tapstride + ncol + q * 128, cb * 128);
+                        }
+                    } else {
+                        if (TWO) tma_load_2d_pair(sb, tmB, fb, tap * tapstride + cb * ROW_BYTES, ncol);
+                        else     tma_load_2d(sb, tmB, fb, tap * tapstride + cb * ROW_BYTES, ncol);
                     }
                 } else {
-                    if (TWO) tma_load_2d_pair(sb, tmB, fb, kb * ROW_BYTES, ncol);
-                    else     tma_load_2d(sb, tmB, fb, kb * ROW_BYTES, ncol);
+                    if (TWO) {
+                        if (a_mn) tma_load_2d_pair(sa, tmA, fb, m_t * BLOCK_M, kb * 128);
+                        else      tma_load_2d_pair(sa, tmA, fb, kb * ROW_BYTES, m_t * BLOCK_M);
+                    } else {
+                        if (a_mn) tma_load_2d(sa, tmA, fb, m_t * BLOCK_M, kb * 128);
+                        else      tma_load_2d(sa, tmA, fb, kb * ROW_BYTES, m_t * BLOCK_M);
+                    }
+                    if (b_mn) {
+#pragma unroll
+                        for (int q = 0; q < BNH / 128; ++q) {
+                            if (TWO) tma_load_2d_pair(sb + q * PANEL_BYTES, tmB, fb, ncol + q * 128, kb * 128);
+                            else     tma_load_2d(sb + q * PANEL_BYTES, tmB, fb, ncol + q * 128, kb * 128);
+                        }
+                    } else {
+                        if (TWO) tma_load_2d_pair(sb, tmB, fb, kb * ROW_BYTES, ncol);
+                        else     tma_load_2d(sb, tmB, fb, kb * ROW_BYTES, ncol);
+                    }
                 }
             }
-            if (p.conv && ++cb == p.cblocks) { cb = 0; if (++sx == p.S) { sx = 0; ++r; } }
+            if (conv && ++cb == cblocks) { cb = 0; if (++sx == S) { sx = 0; ++r; } }
             if (++s == nst) { s = 0; ph ^= 1u; }
         }
     }
+    DBG_CLK(c_end); DBG_ACC(20, c_end - c_begin);
+    DBG_OUT(20);
 }
 
-// MMA issuer: the whole warp runs the loop (uniform control flow, see the producer), lane 0 issues MMAs and commits.  Streaming: two accumulators used alternately, each handed back by the
+// MMA issuer: the whole warp runs the loop with warp-uniform control flow (see the producer), one elected lane issues
+// the MMAs and the commits.  Streaming: two accumulators used alternately, each handed back by the
 // epilogue (tempty).  PARKED: tile i of this CTA accumulates into TMEM columns [i*BN, (i+1)*BN) and
 // stays there until the kernel ends, so no accumulator is ever waited for.
 // TWO: run by rank 0 of a CTA pair only; M = 256 MMAs over both CTAs' shared and tensor memory, and every
 // completion (stage free, accumulator full) is signalled to both CTAs.
+template <bool TWO>
+__device__ __forceinline__ void umma_issue(uint32_t d_tmem, uint64_t a, uint64_t b, uint32_t idesc, uint32_t accumulate) {
+    if (TWO) umma_i8_pair(d_tmem, a, b, idesc, accumulate); else umma_i8(d_tmem, a, b, idesc, accumulate);
+}
 template <int BN, int STAGES, int STAGE_BYTES, bool PARKED, bool TWO>
 __device__ __forceinline__ void mma_role(uint8_t* smem, uint64_t* full_bar, uint64_t* empty_bar, uint64_t* tfull_bar,
-                                         uint64_t* tempty_bar, uint32_t tmem_base, const GemmParams& p, volatile int* abort_flag) {
+                                         uint64_t* tempty_bar, uint32_t tmem_base_in, const GemmParams& p, volatile int* abort_flag) {
     const int mn_tiles = p.m_tiles * p.n_tiles;
     const int total_tiles = mn_tiles * p.splits;
     const uint32_t idesc = make_idesc_i8(TWO ? 2 * BLOCK_M : BLOCK_M, BN, p.a_mn, p.b_mn);
     const int nst = (p.nstages > 0 && p.nstages < STAGES) ? p.nstages : STAGES;
     const int first = TWO ? static_cast<int>(blockIdx.x >> 1) : static_cast<int>(blockIdx.x);
     const int step = TWO ? static_cast<int>(gridDim.x >> 1) : static_cast<int>(gridDim.x);
+    const uint32_t tmem_base = __shfl_sync(0xFFFFFFFFu, tmem_base_in, 0);  // read from shared memory: make it provably uniform
+    const uint32_t abort_addr = smem_u32(const_cast<int*>(abort_flag));
+    const uint32_t full0 = smem_u32(full_bar), empty0 = smem_u32(empty_bar);
     // operand descriptors of stage 0 (a stage's are these advanced by the stage offset) and the K = 32 steps
     const uint32_t s0 = smem_u32(smem);
     const uint64_t a_base = p.a_mn ? make_smem_desc(s0, PANEL_BYTES, 1024, SWIZZLE_128B_CODE) : make_smem_desc(s0, 16, 1024, SWIZZLE_128B_CODE);
     const uint64_t b_base = p.b_mn ? make_smem_desc(s0 + PANEL_BYTES, PANEL_BYTES, 1024, SWIZZLE_128B_CODE)
                                    : make_smem_desc(s0 + PANEL_BYTES, 16, 1024, SWIZZLE_128B_CODE);
-    const uint32_t a_step = p.a_mn ? 32u * ROW_BYTES : 32u;
-    const uint32_t b_step = p.b_mn ? 32u * ROW_BYTES : 32u;
-    const bool issuer = (threadIdx.x & 31) == 0;
+    const uint32_t a_step = static_cast<uint32_t>(keep_reg((p.a_mn ? 32 * ROW_BYTES : 32) >> 4));  // in descriptor units of 16 bytes
+    const uint32_t b_step = static_cast<uint32_t>(keep_reg((p.b_mn ? 32 * ROW_BYTES : 32) >> 4));
+    const int conv = keep_reg(p.conv), red = keep_reg(p.red), cblocks = keep_reg(p.cblocks), num_kb = keep_reg(p.num_kb), splits = keep_reg(p.splits);
     int s = 0; uint32_t ph = 0; bool ok = true; int it = 0;
-    bool ready = false;  // the current stage's "full" phase was already seen complete by the previous iteration's probe
+    bool ready = false;  // the current stage's "full" phase was already seen complete by the previous block's probe
+    DBG_DECL;
+#ifdef NITI_PARKED_TIMING
+    long long c_first = 0;
+#endif
     for (int tile = first; ok && tile < total_tiles; tile += step, ++it) {
         const int acc = PARKED ? it : (it & 1);
         if (!PARKED) {
             const uint32_t aph = (it >> 1) & 1u;
-            if (!mbar_wait(smem_u32(&tempty_bar[acc]), aph ^ 1u, abort_flag)) { report_abort(p.status, 2, 1); break; }
+            ok = mbar_wait_uniform(smem_u32(&tempty_bar[acc]), aph ^ 1u, abort_addr);
+            if (!ok) { *abort_flag = 1; report_abort(p.status, 2, 1); break; }
             tc_fence_after();
         }
         const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BN);
-        const int split = tile / mn_tiles;
-        const int kb_lo = static_cast<int>(static_cast<long long>(split) * p.num_kb / p.splits);
-        const int kb_hi = static_cast<int>(static_cast<long long>(split + 1) * p.num_kb / p.splits);
-        int cb = p.conv ? kb_lo % p.cblocks : 0;  // channel block within the tap: a running counter, no division per block
+        int kb_lo = 0, kb_hi = num_kb;
+        if (splits > 1) {
+            const int split = tile / mn_tiles;
+            kb_lo = static_cast<int>(static_cast<long long>(split) * num_kb / splits);
+            kb_hi = static_cast<int>(static_cast<long long>(split + 1) * num_kb / splits);
+        }
+        int cb = (conv && kb_lo != 0) ? kb_lo % cblocks : 0;  // channel block within the tap: a running counter, no division per block
         for (int kb = kb_lo; kb < kb_hi; ++kb) {
-            if (!ready && !mbar_wait(smem_u32(&full_bar[s]), ph, abort_flag)) { ok = false; report_abort(p.status, 3, 1); break; }
-            if (PARKED && it == 0 && kb == kb_lo) PARK_STAMP(2);
-            {   // ask about the next stage now; the answer is needed only after this stage's MMAs have been issued
-                const int sn = (s + 1 == nst) ? 0 : s + 1;
-                ready = mbar_test_wait(smem_u32(&full_bar[sn]), sn == 0 ? ph ^ 1u : ph) != 0;
+            if (!ready) {
+                ok = mbar_wait_uniform(full0 + 8u * s, ph, abort_addr);
+                if (!ok) { *abort_flag = 1; report_abort(p.status, 3, 1); break; }
             }
-            const uint64_t a0 = desc_advance(a_base, static_cast<uint32_t>(s) * STAGE_BYTES);
-            const uint64_t b0 = desc_advance(b_base, static_cast<uint32_t>(s) * STAGE_BYTES);
+            DBG_ACC(19, 1);
+#ifdef NITI_PARKED_TIMING
+            if (it == 0 && kb == kb_lo) { c_first = clock64(); if (PARKED) PARK_STAMP(2); }
+#endif
+            const uint64_t a0 = a_base + ((static_cast<uint32_t>(s) * STAGE_BYTES) >> 4);
+            const uint64_t b0 = b_base + ((static_cast<uint32_t>(s) * STAGE_BYTES) >> 4);
             // a conv tap whose channel count is not a multiple of 128 ends in a partial block:
             // issue only the MMAs (K = 32 each) that cover real channels (the rest is TMA zero fill)
             int nmma = 4;
-            if (p.conv) {
-                const int left = p.red - cb * 128;
+            if (conv) {
+                const int left = red - cb * 128;
                 nmma = left >= 128 ? 4 : (left + 31) >> 5;
-                if (++cb == p.cblocks) cb = 0;
+                if (++cb == cblocks) cb = 0;
             }
-#pragma unroll
-            for (int k = 0; k < 4; ++k)
-                if (k < nmma && issuer) {
-                    if (TWO) umma_i8_pair(d_tmem, desc_advance(a0, k * a_step), desc_advance(b0, k * b_step), idesc,
-                                          static_cast<uint32_t>(kb != kb_lo || k != 0));
-                    else     umma_i8(d_tmem, desc_advance(a0, k * a_step), desc_advance(b0, k * b_step), idesc,
-                                     static_cast<uint32_t>(kb != kb_lo || k != 0));
+            const uint32_t eb = empty0 + 8u * s;
+            // the next stage's "full" barrier is probed while this block's MMAs are issued
+            const int sn = (s + 1 == nst) ? 0 : s + 1;
+            const uint32_t phn = (sn == 0) ? ph ^ 1u : ph;
+            uint32_t probe;
+            if (nmma == 4) {
+                probe = umma_block4<TWO>(d_tmem, a0, b0, a_step, b_step, idesc, static_cast<uint32_t>(kb != kb_lo), eb,
+                                         full0 + 8u * sn, phn);
+            } else {
+                if (elect_one()) {
+                    for (int k = 0; k < nmma; ++k)
+                        umma_issue<TWO>(d_tmem, a0 + k * a_step, b0 + k * b_step, idesc, static_cast<uint32_t>(kb != kb_lo || k != 0));
+                    if (TWO) umma_commit_pair(eb); else umma_commit(eb);
                 }
-            if (issuer) { if (TWO) umma_commit_pair(smem_u32(&empty_bar[s])); else umma_commit(smem_u32(&empty_bar[s])); }
-            if (++s == nst) { s = 0; ph ^= 1u; }
+                probe = mbar_test_wait(full0 + 8u * sn, phn);
+            }
+            ready = __all_sync(0xFFFFFFFFu, probe != 0);
+            s = sn; ph = phn;
         }
-        if (ok && issuer) { if (TWO) umma_commit_pair(smem_u32(&tfull_bar[acc])); else umma_commit(smem_u32(&tfull_bar[acc])); }
+        if (ok && elect_one()) { if (TWO) umma_commit_pair(smem_u32(&tfull_bar[acc])); else umma_commit(smem_u32(&tfull_bar[acc])); }
     }
     if (PARKED) PARK_STAMP(3);
+#ifdef NITI_PARKED_TIMING
+    DBG_ACC(16, clock64() - c_first);
+#endif
+    DBG_OUT(16);
 }
 
 // Output row of an epilogue thread: validity, TMA store coordinates of its tile, linear row index.

@@ -61,15 +61,20 @@ def status_word(device):
     return _status[key]
 
 
+def status_message(s):
+    """Text for a non-zero status word (a list of its four values)."""
+    if s[0] == 9:
+        who = f"rank {s[1]}" if s[1] >= 0 else "the blocks of its own grid"
+        return (f"niti_b200 data-parallel update gave up waiting for {who} at barrier {s[2]}: "
+                "the replicas are out of step")
+    return f"niti_b200 kernel gave up waiting: code={s[0]} block={s[1]} role={s[2]}"
+
+
 def check_status(device):
     """Synchronises and raises if a kernel reported a timed-out wait."""
     s = status_word(device).tolist()
-    if s[0] == 9:
-        who = f"rank {s[1]}" if s[1] >= 0 else "the blocks of its own grid"
-        raise RuntimeError(f"niti_b200 data-parallel update gave up waiting for {who} at barrier {s[2]}: "
-                           "the replicas are out of step")
     if s[0] != 0:
-        raise RuntimeError(f"niti_b200 kernel gave up waiting: code={s[0]} block={s[1]} role={s[2]}")
+        raise RuntimeError(status_message(s))
 
 
 def scratch(device, nbytes):
@@ -237,6 +242,20 @@ def gemm_acc(a, b, trans_a=False, trans_b=False, out=None):
           lib.niti_gemm_i8, _p(a), _p(b), _p(c32), _p(mx), M, N, K, int(trans_a), int(trans_b),
           _p(status_word(a.device)), _st())
     return c32, mx
+
+
+def group_conv1(inp, wt, pad):
+    """Grouped cross-correlation, one input channel per group, batch 1: inp [1,H,W,G] int8, wt [G*Kg,R,S,1] int8
+    -> int32 [1,P,Q,G*Kg] (what the reference's conv2d_weight_int8 asks of int8conv_cuda.group_conv)."""
+    _need_cuda(inp, wt)
+    _, H, W, G = inp.shape
+    GK, R, S, one = wt.shape
+    assert inp.shape[0] == 1 and one == 1 and GK % G == 0 and inp.dtype == torch.int8 and wt.dtype == torch.int8
+    P, Q = H + 2 * pad - R + 1, W + 2 * pad - S + 1
+    out = torch.empty((1, P, Q, GK), dtype=torch.int32, device=inp.device)
+    _call("niti_group_conv1_i8", 1, 2 * GK * P * Q * R * S, inp.numel() + wt.numel() + 4 * out.numel(),
+          lib.niti_group_conv1_i8, _p(inp), _p(wt), _p(out), H, W, G, GK // G, R, S, pad, _st())
+    return out
 
 
 # ------------------------------------------------------------------ requantisation

@@ -107,10 +107,20 @@ class TiNet(Module):
         return state_dict
 
     def load_state_dict(self, state_dict):
-        """Accepts a reference checkpoint (float 0-dim ``weight_exp`` on the host) or one of ours."""
+        """Accepts a reference checkpoint (float 0-dim ``weight_exp`` on the host) or one of ours.  The values are
+        copied INTO the existing weight tensors (same shape): captured CUDA graphs and a data-parallel trainer's
+        peer-visible arena keep pointing at that memory, so a checkpoint may be loaded at any time between steps."""
         for idx, l in enumerate(self.forward_layers):
             if hasattr(l, 'weight'):
                 layer_prefix = 'layers.' + str(idx) + '.'
                 dev = l.weight.device
-                l.weight = state_dict[layer_prefix + 'weight'].to(device=dev, dtype=torch.int8).contiguous()
-                l.weight_exp = exp_tensor(state_dict[layer_prefix + 'weight_exp'], dev)
+                w = state_dict[layer_prefix + 'weight']
+                e = exp_tensor(state_dict[layer_prefix + 'weight_exp'], dev)
+                if tuple(w.shape) == tuple(l.weight.shape) and l.weight.dtype == torch.int8:
+                    l.weight.copy_(w.to(device=dev, dtype=torch.int8))
+                else:
+                    l.weight = w.to(device=dev, dtype=torch.int8).contiguous()
+                if isinstance(l.weight_exp, torch.Tensor) and l.weight_exp.device == e.device and l.weight_exp.dtype == e.dtype:
+                    l.weight_exp.copy_(e)
+                else:
+                    l.weight_exp = e

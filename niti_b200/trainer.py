@@ -23,23 +23,43 @@ from .peer import PeerArena, peers_on_one_node
 
 class StepResult:
     """What ``Trainer.step`` returns: unpacks as ``(logits, exponent)`` (pinned host tensors) and carries the
-    event after which they are valid, so a caller can read step i's logits while step i+1 is already running."""
+    event after which they are valid, so a caller can read step i's logits while step i+1 is already running.
+    ``wait`` also looks at the kernels' status word as it stood after this step and raises if one of their bounded
+    waits had run out (the trainer then refuses further steps, see ``Trainer.reset_exchange``)."""
 
-    def __init__(self, out, exp, done):
-        self.out, self.exp, self.done = out, exp, done
+    def __init__(self, out, exp, done, status=None, owner=None):
+        self.out, self.exp, self.done, self.status, self.owner = out, exp, done, status, owner
 
     def __iter__(self):
         return iter((self.out, self.exp))
 
     def wait(self):
         self.done.synchronize()
+        if self.status is not None and int(self.status[0]) != 0:
+            msg = ops.status_message(self.status.tolist())
+            if self.owner is not None:
+                self.owner._failed = msg
+            raise RuntimeError(msg)
         return self.out, self.exp
 
 
 class Trainer:
+    """One integer training step per ``step`` call; see the module docstring.
+
+    Data parallel over peer memory: the ranks' update kernels wait for one another, with a limit of 4 s per
+    barrier.  Ranks must therefore enter their steps within 4 s of each other: after anything that may hold one
+    rank back longer (evaluation, a checkpoint, a long host pause) call ``resync()`` on every rank before the
+    next step.  A wait that does run out is reported by ``StepResult.wait`` / ``sync``; from then on ``step``
+    raises, because the replicas may no longer agree: restore the weights on every rank (``load_state_dict``)
+    and call ``reset_exchange()`` (collective) to continue.
+
+    ``sample_offset``: global index of this rank's first sample (``dp.shard_range(global_batch, rank, world)[0]``);
+    default ``rank * local_batch``, which is right for equal shards.  It keys the per-sample random bits.
+    """
+
     def __init__(self, model, local_batch, device, group=None, rank=0, world=1, use_graph=True, seed=0,
                  in_shape=(3, 32, 32), warmup_steps=2, keep_gradients=False, wgrad_side_stream=True,
-                 global_exact=False, peer_update="auto"):
+                 global_exact=False, peer_update="auto", sample_offset=None):
         self.model, self.device, self.group = model, torch.device(device), group
         self.rank, self.world, self.use_graph = rank, world, use_graph
         self.local_batch = local_batch
@@ -83,7 +103,10 @@ class Trainer:
         self.h2d_bytes = self.x.numel() * 4 + self.t.numel() * 8
         self.d2h_bytes = self.out_host.numel() + 4
         ti_torch.set_seed(seed, self.device)
-        ti_torch.SAMPLE_OFFSET = rank * local_batch
+        self.sample_offset = rank * local_batch if sample_offset is None else int(sample_offset)
+        ti_torch.SAMPLE_OFFSET = self.sample_offset
+        self._status_hosts = [torch.zeros(4, dtype=torch.int32).pin_memory() for _ in range(2)]
+        self._failed = None  # message of a kernel wait that ran out: no further steps until reset_exchange()
         # input prefetch: two staging slots filled from pinned host memory on a copy stream while the previous step computes
         self.copy_stream = torch.cuda.Stream(device=self.device)
         self._stage_x = [torch.zeros_like(self.x) for _ in range(2)]
@@ -133,6 +156,31 @@ class Trainer:
         torch.cuda.synchronize(self.device)
         dist.barrier(self.group)
 
+    def resync(self):
+        """Collective: brings the ranks back in step on the host (call on every rank after a pause that may have
+        held one of them back for more than a second or so, before the next ``step``)."""
+        if self.world > 1:
+            torch.cuda.synchronize(self.device)
+            dist.barrier(self.group)
+            torch.cuda.synchronize(self.device)
+
+    def reset_exchange(self):
+        """Collective: after a reported wait expiry, clear the exchange area, the gradient bucket and the status word on
+        every rank so that steps may resume.  The weights are NOT repaired: a step that gave up may have updated some
+        slices and not others, so load the same checkpoint on every rank first."""
+        torch.cuda.synchronize(self.device)
+        if self.world > 1:
+            dist.barrier(self.group)
+        if self.peer is not None:
+            x_off = self._dp_ptrs[2][self.rank] - self.peer.ptrs[self.rank]
+            self.peer.view(x_off, ops.dp_exchange_bytes(), torch.uint8).zero_()
+        self.bucket.flat.zero_()
+        ops.status_word(self.device).zero_()
+        torch.cuda.synchronize(self.device)
+        if self.world > 1:
+            dist.barrier(self.group)
+        self._failed = None
+
     def close(self):
         """Collective: unmaps the peers' memory (call on every rank before the process group goes away)."""
         if self.peer is not None:
@@ -166,6 +214,8 @@ class Trainer:
 
     def _capture(self):
         torch.cuda.synchronize(self.device)
+        if self.peer is not None:
+            dist.barrier(self.group)  # capture takes each rank a different time: start the replays together
         g1 = torch.cuda.CUDAGraph()
         with torch.cuda.graph(g1):
             self._forward_backward()
@@ -177,6 +227,9 @@ class Trainer:
             with torch.cuda.graph(g2, pool=g1.pool()):
                 self._update()
         self._graphs = (g1, g2)
+        if self.peer is not None:
+            torch.cuda.synchronize(self.device)
+            dist.barrier(self.group)
 
     def run_device_step(self):
         """The device part of a step on inputs already resident in self.x / self.t."""
@@ -209,6 +262,8 @@ class Trainer:
         Returns (pinned int8 logits [B, classes], pinned int32 exponent); valid after the
         stream is synchronised (``Trainer.sync``).  ``prefetch_next=(x, t)``: the next batch, whose copy
         then runs beside this step's kernels."""
+        if self._failed is not None:
+            raise RuntimeError(f"{self._failed}; the trainer takes no further steps until reset_exchange()")
         main = torch.cuda.current_stream(self.device)
         if self._pf_key is not None and self._pf_key[:2] == (x_host.data_ptr(), target_host.data_ptr()):
             slot = self._pf_key[2]
@@ -227,12 +282,17 @@ class Trainer:
         self.out_host, self.exp_host = self._out_hosts[k], self._exp_hosts[k]
         self.out_host.copy_(self.model.out, non_blocking=True)
         self.exp_host.copy_(self.model.out_exp, non_blocking=True)
+        self._status_hosts[k].copy_(ops.status_word(self.device), non_blocking=True)
         self._done[k].record(main)
-        return StepResult(self.out_host, self.exp_host, self._done[k])
+        return StepResult(self.out_host, self.exp_host, self._done[k], self._status_hosts[k], self)
 
     def sync(self):
         torch.cuda.synchronize(self.device)
-        ops.check_status(self.device)
+        try:
+            ops.check_status(self.device)
+        except RuntimeError as e:
+            self._failed = str(e)
+            raise
 
     def replica_checksum(self):
         """Digest of all weights; equal on every rank of a healthy data-parallel run."""

@@ -9,7 +9,7 @@ import pytest
 import torch
 import torch.multiprocessing as mp
 
-from oracle import niti_oracle as O
+from oracle import dp_oracle
 from tests.test_gpu_dp_exact import CFG, GLOBAL_BATCH, SEED, STEPS, _data
 
 pytestmark = pytest.mark.gpu
@@ -33,9 +33,9 @@ def _worker(rank, world, port, q):
             l.weight = torch.from_numpy(w).to(dev)
             l.weight_exp = ti_torch.exp_tensor(e, dev)
         lo, hi = shard_range(GLOBAL_BATCH, rank, world)
-        tr = Trainer(model, hi - lo, dev, rank=rank, world=world, use_graph=True, seed=SEED, warmup_steps=1, peer_update=True)
+        tr = Trainer(model, hi - lo, dev, rank=rank, world=world, use_graph=True, seed=SEED, warmup_steps=1, peer_update=True,
+                     sample_offset=lo)
         assert tr.peer is not None
-        ti_torch.SAMPLE_OFFSET = lo
         logits = []
         for x, t in batches:
             out, exp = tr.step(torch.from_numpy(x[lo:hi].copy()).pin_memory(), torch.from_numpy(t[lo:hi].copy()).pin_memory())
@@ -66,22 +66,11 @@ def test_peer_memory_update_equals_summed_gradient_update():
         assert p.exitcode == 0
     shapes, weights, wexps, batches = _data()
     spans = sorted((lo, hi) for _, lo, hi, _, _, _ in results)
-    nets = [O.Net(CFG, weights, wexps, dropout=True, mu=5, seed=SEED) for _ in spans]
-    want = {}
-    for step, (x, t) in enumerate(batches):
-        grads = []
-        for net, (lo, hi) in zip(nets, spans):
-            x8, xe = O.float_to_int8(x[lo:hi])
-            out, e = net.forward(np.ascontiguousarray(x8.transpose(0, 2, 3, 1)), xe, step=step, sample_offset=lo)
-            want[(step, lo)] = (out, e)
-            grads.append(net.backward(t[lo:hi], step=step, sample_offset=lo, update=False))
-        summed = {i: sum(np.asarray(g[i], dtype=np.int64) for g in grads) for i in range(len(shapes))}
-        for net in nets:
-            net.apply_grads(summed, step=step)
+    want, want_w = dp_oracle.expected(CFG, weights, wexps, batches, spans, SEED)
     for rank, lo, hi, logits, wbytes, bucket_clear in results:
         assert bucket_clear, f"rank {rank}: the gradient bucket is not zero after the update"
         for step in range(STEPS):
             assert np.array_equal(logits[step][0], want[(step, lo)][0]), f"rank {rank} step {step}: logits"
             assert logits[step][1] == want[(step, lo)][1]
         for i, b in enumerate(wbytes):
-            assert b == nets[0].w[i].tobytes(), f"rank {rank}: weights of layer {i}"
+            assert b == want_w[i].tobytes(), f"rank {rank}: weights of layer {i}"

@@ -496,6 +496,53 @@ def test_bounded_grid_barrier_gives_up_and_reports():
 
 
 @pytest.mark.gpu
+def test_dp_update_peer_wait_gives_up_and_reports():
+    """niti_dp_update_i8 told that there are two ranks, the second one a zeroed local area that nobody signals: the first
+    cross-rank barrier runs into its 4 s limit, the kernel returns with status {9, rank waited for, barrier number}, updates
+    nothing and the context keeps working.  One process, one GPU, one kernel: nothing waits for another launch."""
+    import time
+    sizes = [128 * 3 * 3 * 16, 4 * 1000]
+    w_offs, off = [], 0
+    for n in sizes:
+        w_offs.append(off)
+        off += (n + 255) // 256 * 256
+    g_off = off
+    g_offs, goff = [], 0
+    for n in sizes:
+        g_offs.append(goff)
+        goff += n
+    x_off = (g_off + 4 * goff + 255) // 256 * 256
+    nbytes = x_off + ops.dp_exchange_bytes()
+    arenas = [torch.zeros(nbytes, dtype=torch.uint8, device=DEV) for _ in range(2)]
+    rng = np.random.default_rng(3)
+    w0 = cu(rnd8(rng, (g_off,)))
+    arenas[0][:g_off].view(torch.int8).copy_(w0)
+    arenas[0][g_off:g_off + 4 * goff].view(torch.int32).copy_(cu(rng.integers(-500, 500, size=goff).astype(np.int32)))
+    items = [(w_offs[i], g_offs[i], sizes[i], 16 * i + 2) for i in range(len(sizes))]
+    seed = ops.seed_tensor(5, DEV)
+    status = ops.status_word(DEV)
+    status.zero_()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    ops.dp_update(items, 0, 2, [a.data_ptr() for a in arenas], [a.data_ptr() + g_off for a in arenas],
+                  [a.data_ptr() + x_off for a in arenas], 5, 2, seed, DEV)
+    torch.cuda.synchronize()
+    dt = time.perf_counter() - t0
+    s = status.tolist()
+    try:
+        assert s[0] == 9 and s[1] == 1 and s[2] == 1, s
+        assert 3.0 < dt < 12.0, dt
+        with pytest.raises(RuntimeError, match="gave up waiting for rank 1 at barrier 1"):
+            ops.check_status(DEV)
+        assert torch.equal(arenas[0][:g_off].view(torch.int8), w0), "no weight may change when the exchange did not happen"
+    finally:
+        status.zero_()
+    del arenas  # the exchange areas are discarded: their barrier numbers are meaningless now
+    x = cu(np.arange(64, dtype=np.int32) - 32)            # the context is alive
+    assert int(ops.absmax(x)) == 32
+
+
+@pytest.mark.gpu
 @pytest.mark.parametrize("N,H,W,C,K", [(128, 32, 32, 128, 128), (128, 8, 8, 512, 512), (256, 16, 16, 256, 256)])
 def test_conv_passes_are_adjoint_at_full_size(N, H, W, C, K):
     """At the benchmark's full sizes, where the oracle is out of reach: the three passes must satisfy, exactly in

@@ -210,3 +210,65 @@ def test_vgg7_batch128_full_size_step():
                   prefetch=True)
     finally:
         O.set_backend("int64")
+
+
+@pytest.mark.parametrize("name,B", [("vgg9_wide", 32), ("vgg13", 128)])
+def test_benchmark_configs_at_their_per_gpu_shard_size(name, B):
+    """VGG-small-9 at 32 images (its global batch of 256 over 8 GPUs) and VGG-13 at 128 images (1024 over 8): one
+    graph-replayed step pair each against the oracle, as for VGG-small-7 above."""
+    O.set_backend("int_mm")
+    try:
+        run_steps(list(ti_vgg.cifar_cfg[name]), B, 2025, True, 2, 5, True, True, keep_gradients=False, prefetch=True)
+    finally:
+        O.set_backend("int64")
+
+
+def test_checkpoint_loaded_after_graph_capture_takes_effect():
+    """load_state_dict copies INTO the weight tensors, so the captured graphs (which hold their addresses) train on the
+    loaded values: three steps (capture happens on the second), reload the initial weights, and the next step must equal
+    the oracle's step from those initial weights with that step's random bits."""
+    cfg, B, seed = [128, "M", 128, "M", 512, "M"], 4, 4242
+    model, oracle, rng = build(cfg, seed, True, True, 5)
+    initial = {k: v.clone() for k, v in model.state_dict().items()}
+    w0 = [np.array(w) for w in oracle.w]
+    tr = Trainer(model, B, DEV, use_graph=True, seed=seed, warmup_steps=1)
+    for step in range(3):
+        x, tgt = synth_images(rng, B), rng.integers(0, 10, size=B)
+        tr.step(torch.from_numpy(x).pin_memory(), torch.from_numpy(tgt).pin_memory())
+    tr.sync()
+    assert tr._graphs is not None
+    ptrs = [l.weight.data_ptr() for l in model.weighted_layers()]
+    model.load_state_dict(initial)
+    assert ptrs == [l.weight.data_ptr() for l in model.weighted_layers()], "weights must be loaded in place"
+    x, tgt = synth_images(rng, B), rng.integers(0, 10, size=B)
+    out_h, exp_h = tr.step(torch.from_numpy(x).pin_memory(), torch.from_numpy(tgt).pin_memory())
+    tr.sync()
+    fresh = O.Net(cfg, w0, oracle.w_exp, dropout=True, mu=5, seed=seed)
+    x8, xe = O.float_to_int8(x)
+    want, want_e = fresh.forward(np.ascontiguousarray(x8.transpose(0, 2, 3, 1)), xe, step=3)
+    fresh.backward(tgt, step=3)
+    assert np.array_equal(out_h.numpy(), want) and int(exp_h) == want_e
+    for i, l in enumerate(model.weighted_layers()):
+        assert np.array_equal(l.weight.cpu().numpy(), fresh.w[i]), f"weights {i}"
+
+
+def test_a_reported_wait_expiry_is_sticky():
+    """A non-zero status word after a step surfaces in StepResult.wait and the trainer then refuses further steps until
+    reset_exchange() (here the word is set by hand: no kernel is made to give up)."""
+    from niti_b200 import ops
+    model, _, rng = build([128, "M", 128, "M", 512, "M"], 7, True, True, 5)
+    tr = Trainer(model, 4, DEV, use_graph=False, seed=7)
+    x, tgt = synth_images(rng, 4), rng.integers(0, 10, size=4)
+    xh, th = torch.from_numpy(x).pin_memory(), torch.from_numpy(tgt).pin_memory()
+    tr.step(xh, th).wait()
+    ops.status_word(DEV).copy_(torch.tensor([9, 1, 1, 0], dtype=torch.int32))
+    try:
+        res = tr.step(xh, th)
+        with pytest.raises(RuntimeError, match="gave up waiting for rank 1"):
+            res.wait()
+        with pytest.raises(RuntimeError, match="no further steps"):
+            tr.step(xh, th)
+        tr.reset_exchange()
+        tr.step(xh, th).wait()
+    finally:
+        ops.status_word(DEV).zero_()

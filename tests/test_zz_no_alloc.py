@@ -15,6 +15,7 @@ if not torch.cuda.is_available():
     pytest.skip("needs a CUDA device", allow_module_level=True)
 
 from niti_b200._lib import lib  # noqa: E402
+from oracle import niti_oracle as O  # noqa: E402
 
 DEV = "cuda:0"
 LIMIT = 16 << 20
@@ -53,6 +54,8 @@ def wgrad_both(x, err, pad=1):
 @pytest.mark.parametrize("N,H,W,C,K", [
     (16, 16, 16, 256, 256),   # tensor-core path; the usual 12 splits (28 MB) do not fit: runs with 7
     (8, 8, 8, 128, 128),      # tensor-core path, fits as planned
+    (8, 8, 8, 144, 144),      # channel counts that are multiples of 16 but not of 128: the tail tiles are clipped by TMA
+    (8, 8, 8, 16, 48),        # a single, mostly clipped tile per tap
     (32, 32, 32, 3, 128),     # first-layer path: patch matrix + split-K partials in the buffer
     (2, 6, 10, 5, 7),         # CUDA-core path: needs no scratch at all
 ])
@@ -60,11 +63,27 @@ def test_matches_caller_scratch_variant_twice_in_a_row(N, H, W, C, K):
     torch.cuda.set_device(0)
     rng = np.random.default_rng(N * 3 + C + K)
     for call in range(2):  # the second call finds the first call's partial sums in the buffer
-        x = torch.from_numpy(rng.integers(-127, 128, size=(N, H, W, C)).astype(np.int8)).to(DEV)
-        err = torch.from_numpy(rng.integers(-127, 128, size=(N, H, W, K)).astype(np.int8)).to(DEV)
+        xh = rng.integers(-127, 128, size=(N, H, W, C)).astype(np.int8)
+        eh = rng.integers(-127, 128, size=(N, H, W, K)).astype(np.int8)
+        x, err = torch.from_numpy(xh).to(DEV), torch.from_numpy(eh).to(DEV)
         (g_ref, m_ref), (g_new, m_new) = wgrad_both(x, err)
         assert np.array_equal(g_new, g_ref), f"call {call}: gradients differ"
         assert m_new == m_ref == int(np.abs(g_ref).max())
+        if call == 0:  # and against the oracle itself, not only against the sibling entry point
+            assert np.array_equal(g_new, O.conv_wgrad(xh, eh, 3, 3, 1).astype(np.int32))
+
+
+def test_maximum_is_optional_as_in_the_caller_scratch_variant():
+    torch.cuda.set_device(0)
+    rng = np.random.default_rng(5)
+    xh = rng.integers(-127, 128, size=(4, 8, 8, 128)).astype(np.int8)
+    eh = rng.integers(-127, 128, size=(4, 8, 8, 128)).astype(np.int8)
+    x, err = torch.from_numpy(xh).to(DEV), torch.from_numpy(eh).to(DEV)
+    g32 = torch.zeros((128, 3, 3, 128), dtype=torch.int32, device=DEV)
+    rc = lib.niti_conv_wgrad_builtin_scratch_i8(_ptr(x), _ptr(err), _ptr(g32), None, 4, 8, 8, 128, 128, 3, 3, 1, None, _stream())
+    assert rc == 0, lib.niti_strerror(rc)
+    torch.cuda.synchronize()
+    assert np.array_equal(g32.cpu().numpy(), O.conv_wgrad(xh, eh, 3, 3, 1).astype(np.int32))
 
 
 def test_refuses_what_does_not_fit_and_allocates_nothing():
