@@ -199,6 +199,19 @@ NITI_API int niti_conv_dgrad_requant_i8(const int8_t* err, const int8_t* w, int8
  * the kernel.  The mask is applied after the requantisation, so the shift is that of the unmasked error, exactly as
  * when the two run one after the other. */
 
+/* niti_conv_fprop_requant_i8 that ALSO writes the 2x2 / stride-2 max-pooled output, y8_pooled [N][H/2][W/2][K]:
+ * TiConv2d.forward + TiReLU.forward + TiMaxpool2d.forward (ti_torch.py:391-397, 268-277, 302-307;
+ * int8pool_cuda.int8_pool, int8pool_kernel.cu:28-80) in one launch.  The unpooled y8 is still written: the pool's
+ * backward routes by it.  Only where the single-launch (accumulator-parking) kernel takes the layer and every
+ * pooling window lies within one warp's rows of an output tile: niti_conv_fprop_requant_pool_supported() != 0
+ * (H, W even; images at most 16 pixels wide); elsewhere NITI_ERR_UNSUPPORTED and the caller runs niti_maxpool_fwd_i8. */
+NITI_API int niti_conv_fprop_requant_pool_supported(int N, int H, int W, int C, int K, int R, int S, int pad);
+NITI_API int niti_conv_fprop_requant_pool_i8(const int8_t* x, const int8_t* w, int8_t* y8, int8_t* y8_pooled, int32_t* state,
+                       int N, int H, int W, int C, int K, int R, int S, int pad,
+                       int round_mode, const uint64_t* seed, uint32_t rng_stream, uint64_t rng_offset, int relu,
+                       const int32_t* exp_a, const int32_t* exp_b, int32_t* exp_out, int32_t* shift_out,
+                       int32_t* status, void* stream);
+
 /* int8mm_cuda.int8_mm (int8mm.cpp:9-18, int8mm_kernel.cu:8-34) as used by TiLinear
  * (ti_torch.py:241-266), without the padding / .contiguous() copies around it:
  * C32[M][N] = op(A) * op(B); trans_a == 0: A is [M][K], else [K][M];

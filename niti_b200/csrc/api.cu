@@ -234,9 +234,9 @@ static int fused_conv(const int8_t* in, const int8_t* w, int8_t* out8, int32_t* 
                       int N, int H, int W, int C, int K, int R, int S, int pad, int flip, int kind, int round_mode,
                       const uint64_t* seed, uint32_t rng_stream, uint64_t rng_offset, int relu, const int32_t* exp_a,
                       const int32_t* exp_b, int32_t* exp_out, int32_t* shift_out, int32_t* status, cudaStream_t st,
-                      const int8_t* relu_mask = nullptr) {
+                      const int8_t* relu_mask = nullptr, int8_t* pool_out = nullptr) {
     FusedArgs f{state, 0, 0, round_mode, relu, reinterpret_cast<const unsigned long long*>(seed), rng_stream, rng_offset,
-                kind, 7, exp_a, exp_b, exp_out, shift_out, relu_mask};
+                kind, 7, exp_a, exp_b, exp_out, shift_out, relu_mask, pool_out};
     const bool thin = !flip && fprop_path(C, K, R, S, pad) == CONV_THIN;
     const size_t m = static_cast<size_t>(N) * H * W;
     int8_t* xcol = static_cast<int8_t*>(scratch);
@@ -246,6 +246,7 @@ static int fused_conv(const int8_t* in, const int8_t* w, int8_t* out8, int32_t* 
         if (int e = im2col32(in, xcol, N, H, W, C, R, S, pad, st)) return e;
         if (int e = pad_rows32(w, wp, K, R * S * C, st)) return e;
     }
+    if (pool_out != nullptr && !(g_opt_parking && !thin && !flip && umma_conv_pool_fusable(N, H, W, K))) return NITI_ERR_UNSUPPORTED;
     // Few enough output tiles for every accumulator to stay in tensor memory: one exact launch.
     if (g_opt_parking && !thin && umma_conv_fits_parked(N, H, W, flip ? C : K, flip)) {
         f.parked = 1;
@@ -280,6 +281,24 @@ extern "C" int niti_conv_fprop_requant_i8(const int8_t* x, const int8_t* w, int8
     if (!niti_conv_fprop_requant_supported(C, K, R, S, pad)) return NITI_ERR_UNSUPPORTED;
     return fused_conv(x, w, y8, state, scratch, scratch_bytes, N, H, W, C, K, R, S, pad, 0, NITI_CALC_ACT, round_mode, seed,
                       rng_stream, rng_offset, relu, exp_a, exp_b, exp_out, shift_out, status, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int niti_conv_fprop_requant_pool_supported(int N, int H, int W, int C, int K, int R, int S, int pad) {
+    if (N <= 0 || H <= 0 || W <= 0 || !niti_conv_fprop_requant_supported(C, K, R, S, pad)) return 0;
+    return g_opt_parking && fprop_path(C, K, R, S, pad) == CONV_TC && umma_conv_pool_fusable(N, H, W, K) ? 1 : 0;
+}
+
+extern "C" int niti_conv_fprop_requant_pool_i8(const int8_t* x, const int8_t* w, int8_t* y8, int8_t* y8_pooled, int32_t* state, int N,
+                                               int H, int W, int C, int K, int R, int S, int pad, int round_mode,
+                                               const uint64_t* seed, uint32_t rng_stream, uint64_t rng_offset, int relu,
+                                               const int32_t* exp_a, const int32_t* exp_b, int32_t* exp_out, int32_t* shift_out,
+                                               int32_t* status, void* stream) {
+    NITI_REQUIRE(x && w && y8 && y8_pooled && state && N > 0 && H > 0 && W > 0 && C > 0 && K > 0 && R > 0 && S > 0 && pad >= 0);
+    NITI_REQUIRE(round_mode >= 0 && round_mode <= 2 && (seed || round_mode != NITI_ROUND_STOCHASTIC));
+    NITI_REQUIRE(aligned16(x) && aligned16(w) && aligned16(y8) && aligned16(y8_pooled) && reinterpret_cast<uintptr_t>(state) % 8 == 0);
+    if (!niti_conv_fprop_requant_pool_supported(N, H, W, C, K, R, S, pad)) return NITI_ERR_UNSUPPORTED;
+    return fused_conv(x, w, y8, state, nullptr, 0, N, H, W, C, K, R, S, pad, 0, NITI_CALC_ACT, round_mode, seed, rng_stream,
+                      rng_offset, relu, exp_a, exp_b, exp_out, shift_out, status, static_cast<cudaStream_t>(stream), nullptr, y8_pooled);
 }
 
 extern "C" int niti_conv_dgrad_requant_i8(const int8_t* err, const int8_t* w, int8_t* e8, int32_t* state, int N, int H, int W,

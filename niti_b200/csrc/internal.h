@@ -23,6 +23,7 @@ struct FusedArgs {
     int kind, target_bits;
     const int32_t* exp_a; const int32_t* exp_b; int32_t* exp_out; int32_t* shift_out;
     const int8_t* relu_mask;  // optional, same shape as the output: zero the output where this tensor is <= 0
+    int8_t* pool_out;         // optional (forward, parked kernel): 2x2 / stride-2 max-pooled copy of the output
 };
 
 extern int g_two_cta;    // CTA pairs (cta_group::2) where the shape allows: bit 0 for GEMMs, bit 1 for convolutions
@@ -36,6 +37,7 @@ int umma_gemm(const int8_t* A, const int8_t* B, void* out, unsigned* maxabs, int
 int umma_conv(const int8_t* x, const int8_t* w, void* out, unsigned* maxabs, int Nimg, int H, int W, int C, int K,
               int R, int S, int pad, int flip, const FusedArgs* fused, int32_t* status, cudaStream_t st);
 bool umma_conv_fits_parked(int Nimg, int H, int W, int outc, int flip);
+bool umma_conv_pool_fusable(int Nimg, int H, int W, int outc);  // the fused forward kernel can also emit the 2x2-pooled output
 size_t umma_wgrad_scratch_bytes(int Nimg, int H, int W, int C, int K, int R, int S);
 // max_splits > 0 caps the number of pixel-range splits (and with it the size of `partial`)
 // direct == 1: `partial` is the zeroed gradient and the CTAs add into it (TMA reduction) instead of storing partials

@@ -272,6 +272,33 @@ __device__ __forceinline__ uint32_t umma_block4(uint32_t d_tmem, uint64_t a_desc
     }
     return ready;
 }
+// Four MMAs (K = 32 each, descriptors a, a + a_step, ...) issued by an elected lane of the converged warp, in one asm
+// statement; no commit (more MMAs on the same stage follow).
+__device__ __forceinline__ void umma_seq4(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint64_t a_step, uint64_t b_step,
+                                          uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred P, E, T;\n\t"
+        ".reg .b32 r;\n\t"
+        ".reg .b64 a1, a2, a3, b1, b2, b3;\n\t"
+        "elect.sync r|E, 0xFFFFFFFF;\n\t"
+        "setp.ne.b32 P, %6, 0;\n\t"
+        "setp.eq.b32 T, 0, 0;\n\t"
+        "add.u64 a1, %1, %3;\n\t"
+        "add.u64 b1, %2, %4;\n\t"
+        "add.u64 a2, a1, %3;\n\t"
+        "add.u64 b2, b1, %4;\n\t"
+        "add.u64 a3, a2, %3;\n\t"
+        "add.u64 b3, b2, %4;\n\t"
+        "@E tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %5, P;\n\t"
+        "@E tcgen05.mma.cta_group::1.kind::i8 [%0], a1, b1, %5, T;\n\t"
+        "@E tcgen05.mma.cta_group::1.kind::i8 [%0], a2, b2, %5, T;\n\t"
+        "@E tcgen05.mma.cta_group::1.kind::i8 [%0], a3, b3, %5, T;\n\t"
+        "}"
+        :
+        : "r"(d_tmem), "l"(a_desc), "l"(b_desc), "l"(a_step), "l"(b_step), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
 // mbarrier arrives once all tcgen05 operations issued so far by this thread have completed.
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");

@@ -100,6 +100,7 @@ struct GemmParams {
     int mode, relu;
     int8_t* out8;          // fused kernels: the int8 output as a plain pointer (rows = row_lin, pitch N bytes)
     const int8_t* mask;    // fused kernels: optional ReLU-backward mask, same shape as the output (zero where mask <= 0)
+    int8_t* pool_out;      // parked kernel, forward convolutions: optional 2x2 / stride-2 max-pooled copy of the output [N][H/2][W/2][K]
     const unsigned long long* seed;
     unsigned rng_stream;
     unsigned long long rng_offset;
@@ -388,7 +389,7 @@ __device__ __forceinline__ void mma_role(uint8_t* smem, uint64_t* full_bar, uint
 }
 
 // Output row of an epilogue thread: validity, TMA store coordinates of its tile, linear row index.
-struct RowInfo { bool valid; int cy, cz, cw; long long row_lin; };
+struct RowInfo { bool valid; int cy, cz, cw; long long row_lin; long long pool_row; };
 __device__ __forceinline__ RowInfo row_info(const GemmParams& p, int m_t, int split, int row_in_tile) {
     RowInfo r;
     if (p.conv) {
@@ -399,10 +400,13 @@ __device__ __forceinline__ RowInfo row_info(const GemmParams& p, int m_t, int sp
         r.valid = row_in_tile < p.BW * p.BH * p.BI && w < p.W && h < p.H && n < p.Nimg;
         r.cy = tw * p.BW; r.cz = th * p.BH; r.cw = tn * p.BI;
         r.row_lin = (static_cast<long long>(n) * p.H + h) * p.W + w;
+        // row of the 2x2-pooled tensor this pixel's window goes to; only the window's top-left pixel writes it
+        r.pool_row = ((w | h) & 1) == 0 ? (static_cast<long long>(n) * (p.H >> 1) + (h >> 1)) * (p.W >> 1) + (w >> 1) : -1;
     } else {
         r.row_lin = static_cast<long long>(m_t) * BLOCK_M + row_in_tile;
         r.valid = r.row_lin < p.M;
         r.cy = m_t * BLOCK_M; r.cz = split; r.cw = 0;
+        r.pool_row = -1;
     }
     return r;
 }
@@ -502,6 +506,15 @@ __device__ __forceinline__ void apply_relu_mask(uint32_t (&packed)[WORDS], const
             packed[4 * q + 0] &= __vcmpgts4(x.x, 0); packed[4 * q + 1] &= __vcmpgts4(x.y, 0);
             packed[4 * q + 2] &= __vcmpgts4(x.z, 0); packed[4 * q + 3] &= __vcmpgts4(x.w, 0);
         }
+}
+// Byte-wise maximum over a 2x2 pixel window whose four pixels are the rows of lanes l, l^1, l^bw, l^bw^1 of this warp
+// (all 32 lanes call it): afterwards every lane of a window holds the window's maxima.
+__device__ __forceinline__ void pool_window(uint32_t (&w)[8], int bw) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        uint32_t m = __vmaxs4(w[i], __shfl_xor_sync(0xFFFFFFFFu, w[i], 1));
+        w[i] = __vmaxs4(m, __shfl_xor_sync(0xFFFFFFFFu, m, bw));
+    }
 }
 // 32 packed int8 of one output row to global memory, as two 16-byte stores; `row` is null for rows outside the tensor,
 // `off` the byte offset within the unit's columns of which `cols` exist (a multiple of 16)
@@ -917,7 +930,7 @@ umma_parked_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
         for (int k = 0; k < MAX_UNITS; ++k) {
             const int u = grp + 2 * k;
             u_live[k] = u < units;
-            u_it[k] = 0; u_col[k] = 0; u_taddr[k] = 0; u_ri[k] = RowInfo{false, 0, 0, 0, 0};
+            u_it[k] = 0; u_col[k] = 0; u_taddr[k] = 0; u_ri[k] = RowInfo{false, 0, 0, 0, 0, -1};
             if (u_live[k]) {
                 const int it = u / CG, g0 = (u % CG) * 128;
                 const int tile = cta_first + it * cta_step;
@@ -1008,6 +1021,11 @@ umma_parked_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
                 // or two units per warpgroup there is nothing for a staged TMA store to overlap with, and its fence,
                 // barriers and the wait for the store engine at the end of the kernel cost more than the stores.
                 int8_t* orow = ri.valid ? p.out8 + ri.row_lin * p.N + col : nullptr;
+                // Max pooling in the same pass (TiMaxpool2d.forward): a warp's 32 rows are whole image rows of the tile
+                // (BW is a power of two <= 16, BH even), so the 2x2 window of lane l is lanes l, l^1, l^BW, l^BW^1:
+                // two shuffles and two byte-wise maxima per word, and the window's top-left lane stores the pooled piece.
+                const bool pooling = p.pool_out != nullptr;  // the same for the whole grid
+                int8_t* prow = (pooling && ri.valid && ri.pool_row >= 0) ? p.pool_out + ri.pool_row * p.N + col : nullptr;
                 uint32_t va[32], vb[32], packed[8];
                 tmem_ld_32x32(taddr, va);
 #pragma unroll 1
@@ -1017,12 +1035,14 @@ umma_parked_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
                     narrow32(va, packed, shift, p.mode, p.relu, seed, p.rng_stream, e0 + 32 * j);
                     if (mrow != nullptr) apply_relu_mask<8>(packed, mrow + 32 * j, cols - 32 * j);
                     store_piece(orow, 32 * j, cols, packed);
+                    if (pooling) { pool_window(packed, p.BW); store_piece(prow, 32 * j, cols, packed); }
                     tmem_ld_wait();
                     if (j + 2 < nch) tmem_ld_32x32(taddr + (j + 2) * 32, va);
                     if (j + 1 < nch) {
                         narrow32(vb, packed, shift, p.mode, p.relu, seed, p.rng_stream, e0 + 32 * (j + 1));
                         if (mrow != nullptr) apply_relu_mask<8>(packed, mrow + 32 * (j + 1), cols - 32 * (j + 1));
                         store_piece(orow, 32 * (j + 1), cols, packed);
+                        if (pooling) { pool_window(packed, p.BW); store_piece(prow, 32 * (j + 1), cols, packed); }
                     }
                 }
             }
@@ -1133,25 +1153,30 @@ umma_wgrad_kernel(const __grid_constant__ CUtensorMap tmErr, const __grid_consta
     const int chunk_lo = static_cast<int>(static_cast<long long>(split) * p.chunks / p.splits);
     const int chunk_hi = static_cast<int>(static_cast<long long>(split + 1) * p.chunks / p.splits);
 
-    // Warps 0 and 1 run their loops whole (uniform control flow keeps TMA / MMA operands in uniform registers);
-    // lane 0 issues.
+    // Warps 0 and 1 run their loops whole, with warp-uniform control flow (see producer_role); an elected lane issues.
+    const uint32_t abort_addr = smem_u32(const_cast<int*>(abort_flag));
+    const uint32_t smem0 = smem_u32(smem), full0 = smem_u32(full_bar), empty0 = smem_u32(empty_bar);
+    const int S = keep_reg(p.S);
     if (warp == 0) {
         {
+            const int pad = keep_reg(p.pad), BW = keep_reg(p.BW), BH = keep_reg(p.BH), BI = keep_reg(p.BI);
+            const int tiles_w = keep_reg(p.tiles_w), tiles_h = keep_reg(p.tiles_h);
+            const uint32_t tx_bytes = static_cast<uint32_t>(keep_reg((1 + p.S) * p.box_bytes));
             int s = 0; uint32_t ph = 0;
             // tile coordinates as running counters: this instruction stream paces the pipeline
             int tw = chunk_lo % p.tiles_w, th = (chunk_lo / p.tiles_w) % p.tiles_h, tn = chunk_lo / (p.tiles_w * p.tiles_h);
             for (int ch = chunk_lo; ch < chunk_hi; ++ch) {
-                if (!mbar_wait(smem_u32(&empty_bar[s]), ph ^ 1u, abort_flag)) { report_abort(p.status, 11, 0); break; }
-                const uint32_t fb = smem_u32(&full_bar[s]);
-                const uint32_t sa = smem_u32(smem + s * WG_STAGE_BYTES);
-                if (lane == 0) {
-                    mbar_arrive_expect_tx(fb, static_cast<uint32_t>((1 + p.S) * p.box_bytes));
-                    tma_load_4d(sa, &tmErr, fb, kt * 128, tw * p.BW, th * p.BH, tn * p.BI);
-                    for (int sx = 0; sx < p.S; ++sx)
-                        tma_load_4d(sa + (1 + sx) * PANEL_BYTES, &tmX, fb, ct * 128, tw * p.BW + sx - p.pad, th * p.BH + r - p.pad, tn * p.BI);
+                if (!mbar_wait_uniform(empty0 + 8u * s, ph ^ 1u, abort_addr)) { *abort_flag = 1; report_abort(p.status, 11, 0); break; }
+                const uint32_t fb = full0 + 8u * s;
+                const uint32_t sa = smem0 + static_cast<uint32_t>(s) * WG_STAGE_BYTES;
+                if (elect_one()) {
+                    mbar_arrive_expect_tx(fb, tx_bytes);
+                    tma_load_4d(sa, &tmErr, fb, kt * 128, tw * BW, th * BH, tn * BI);
+                    for (int sx = 0; sx < S; ++sx)
+                        tma_load_4d(sa + (1 + sx) * PANEL_BYTES, &tmX, fb, ct * 128, tw * BW + sx - pad, th * BH + r - pad, tn * BI);
                 }
                 if (++s == WG_STAGES) { s = 0; ph ^= 1u; }
-                if (++tw == p.tiles_w) { tw = 0; if (++th == p.tiles_h) { th = 0; ++tn; } }
+                if (++tw == tiles_w) { tw = 0; if (++th == tiles_h) { th = 0; ++tn; } }
             }
         }
         __syncwarp();  // reach the teardown's block-wide barrier as a converged warp
@@ -1159,36 +1184,46 @@ umma_wgrad_kernel(const __grid_constant__ CUtensorMap tmErr, const __grid_consta
         {
             const uint32_t idesc = make_idesc_i8(BLOCK_M, 128, 1, 1);
             const uint32_t idesc2 = make_idesc_i8(BLOCK_M, 256, 1, 1);
+            const uint32_t tm = __shfl_sync(0xFFFFFFFFu, tmem_base, 0);
+            const int nmma = keep_reg(p.mma_per_chunk);
+            const uint64_t kstep = (32u * ROW_BYTES) >> 4;  // 32 reduction rows per MMA, in descriptor units
+            const uint64_t d0 = make_smem_desc(smem0, PANEL_BYTES, 1024, SWIZZLE_128B_CODE);
             int s = 0; uint32_t ph = 0; bool ok = true;
+            bool ready = false;  // the stage's "full" phase was seen complete by the previous chunk's probe
             for (int ch = chunk_lo; ch < chunk_hi; ++ch) {
-                if (!mbar_wait(smem_u32(&full_bar[s]), ph, abort_flag)) { ok = false; report_abort(p.status, 13, 1); break; }
+                if (!ready && !mbar_wait_uniform(full0 + 8u * s, ph, abort_addr)) { ok = false; *abort_flag = 1; report_abort(p.status, 13, 1); break; }
                 if (ch == chunk_lo && blockIdx.y == 0) PARK_STAMP(12);
-                tc_fence_after();
-                const uint32_t sa = smem_u32(smem + s * WG_STAGE_BYTES);
-                const uint64_t a0 = make_smem_desc(sa, PANEL_BYTES, 1024, SWIZZLE_128B_CODE);
+                const uint64_t a0 = d0 + ((static_cast<uint32_t>(s) * WG_STAGE_BYTES) >> 4);
+                const uint32_t first = static_cast<uint32_t>(ch != chunk_lo);
+                const int sn = (s + 1 == WG_STAGES) ? 0 : s + 1;
+                const uint32_t phn = (sn == 0) ? ph ^ 1u : ph;
+                const uint32_t eb = empty0 + 8u * s;
                 // The taps' x tiles lie one panel apart, which is exactly the layout of an MN-major B operand of
-                // two 128-column panels: two taps go through ONE 256-column MMA (wide MMAs use the tensor pipe
-                // better: measured ~217 cycles for N = 256 against ~146 for N = 128), accumulating into the
-                // adjacent TMEM column blocks of the two taps.
-                int sx = 0;
-                for (; sx + 1 < p.S; sx += 2) {
-                    const uint64_t b0 = make_smem_desc(sa + (1 + sx) * PANEL_BYTES, PANEL_BYTES, 1024, SWIZZLE_128B_CODE);
-                    for (int k = 0; k < p.mma_per_chunk; ++k)
-                        if (lane == 0)
-                            umma_i8(tmem_base + sx * 128, desc_advance(a0, k * 32u * ROW_BYTES), desc_advance(b0, k * 32u * ROW_BYTES),
-                                    idesc2, static_cast<uint32_t>(ch != chunk_lo || k != 0));
+                // two 128-column panels: two taps go through ONE 256-column MMA (half as many instructions to issue),
+                // accumulating into the adjacent TMEM column blocks of the two taps.
+                uint32_t probe;
+                if (nmma == 4 && S == 3) {
+                    umma_seq4(tm, a0, a0 + (PANEL_BYTES >> 4), kstep, kstep, idesc2, first);
+                    probe = umma_block4<false>(tm + 256, a0, a0 + ((3 * PANEL_BYTES) >> 4), kstep, kstep, idesc, first, eb, full0 + 8u * sn, phn);
+                } else {
+                    if (elect_one()) {
+                        int sx = 0;
+                        for (; sx + 1 < S; sx += 2)
+                            for (int k = 0; k < nmma; ++k)
+                                umma_i8(tm + sx * 128, a0 + k * kstep, a0 + (((1 + sx) * PANEL_BYTES) >> 4) + k * kstep, idesc2,
+                                        static_cast<uint32_t>(ch != chunk_lo || k != 0));
+                        for (; sx < S; ++sx)
+                            for (int k = 0; k < nmma; ++k)
+                                umma_i8(tm + sx * 128, a0 + k * kstep, a0 + (((1 + sx) * PANEL_BYTES) >> 4) + k * kstep, idesc,
+                                        static_cast<uint32_t>(ch != chunk_lo || k != 0));
+                        umma_commit(eb);
+                    }
+                    probe = mbar_test_wait(full0 + 8u * sn, phn);
                 }
-                for (; sx < p.S; ++sx) {
-                    const uint64_t b0 = make_smem_desc(sa + (1 + sx) * PANEL_BYTES, PANEL_BYTES, 1024, SWIZZLE_128B_CODE);
-                    for (int k = 0; k < p.mma_per_chunk; ++k)
-                        if (lane == 0)
-                            umma_i8(tmem_base + sx * 128, desc_advance(a0, k * 32u * ROW_BYTES), desc_advance(b0, k * 32u * ROW_BYTES),
-                                    idesc, static_cast<uint32_t>(ch != chunk_lo || k != 0));
-                }
-                if (lane == 0) umma_commit(smem_u32(&empty_bar[s]));
-                if (++s == WG_STAGES) { s = 0; ph ^= 1u; }
+                ready = __all_sync(0xFFFFFFFFu, probe != 0);
+                s = sn; ph = phn;
             }
-            if (ok && lane == 0) umma_commit(smem_u32(&tfull_bar[0]));
+            if (ok && elect_one()) umma_commit(smem_u32(&tfull_bar[0]));
             if (blockIdx.y == 0) PARK_STAMP(13);
         }
         __syncwarp();
@@ -1384,6 +1419,7 @@ static void set_fused(GemmParams* p, const FusedArgs* f) {
     p->kind = f->kind; p->target_bits = f->target_bits;
     p->exp_a = f->exp_a; p->exp_b = f->exp_b; p->exp_out = f->exp_out; p->shift_out = f->shift_out;
     p->mask = f->relu_mask;
+    p->pool_out = nullptr;
     p->out8 = nullptr;
     // max|acc| lives in state[1]; a redo launch must leave it alone (the last CTA of the first launch zeroed it)
     p->maxabs = f->only_if_redo ? nullptr : reinterpret_cast<unsigned*>(f->state + 1);
@@ -1397,6 +1433,8 @@ static void pick_pixel_box(int Nimg, int H, int W, int* BW, int* BH, int* BI) {
     int bi = 128 / (*BW * *BH); if (bi > Nimg) bi = Nimg; if (bi < 1) bi = 1;
     *BI = bi;
 }
+
+static bool pool_box_ok(int H, int W, int bw, int bh);
 
 int umma_gemm_splits(int M, int N, int K) {
     const int bn = (N > 128) ? 256 : 128;
@@ -1484,12 +1522,26 @@ int umma_conv(const int8_t* x, const int8_t* w, void* out, unsigned* maxabs, int
     p.split_cols = (bn == 256 && p.m_tiles * p.n_tiles <= 2 * (pair ? sm_count() / 2 : sm_count())) ? 1 : 0;
     set_fused(&p, fused);
     if (fused) p.out8 = static_cast<int8_t*>(out);
+    if (fused && fused->pool_out != nullptr) {
+        if (!parked || flip || !pool_box_ok(H, W, p.BW, p.BH)) return NITI_ERR_UNSUPPORTED;
+        p.pool_out = fused->pool_out;
+    }
     if (parked) {
         if (!fits_parked(bn, p.m_tiles * p.n_tiles, pair)) return NITI_ERR_UNSUPPORTED;
         if (pair) return bn == 256 ? launch_parked_inst<256, true>(ma, mb, mc, p, st) : launch_parked_inst<128, true>(ma, mb, mc, p, st);
         return bn == 256 ? launch_parked_inst<256, false>(ma, mb, mc, p, st) : launch_parked_inst<128, false>(ma, mb, mc, p, st);
     }
     return launch_gemm(bn, fused != nullptr, pair, ma, mb, mc, p, st);
+}
+
+// the parked kernel can pool 2x2 / stride 2 in its epilogue when every window lies inside one warp's 32 rows of a tile
+static bool pool_box_ok(int H, int W, int bw, int bh) {
+    return H % 2 == 0 && W % 2 == 0 && bh % 2 == 0 && (bw == 2 || bw == 4 || bw == 8 || bw == 16);
+}
+bool umma_conv_pool_fusable(int Nimg, int H, int W, int outc) {
+    int bw, bh, bi;
+    pick_pixel_box(Nimg, H, W, &bw, &bh, &bi);
+    return pool_box_ok(H, W, bw, bh) && umma_conv_fits_parked(Nimg, H, W, outc, 0);
 }
 
 bool umma_conv_fits_parked(int Nimg, int H, int W, int outc, int flip) {

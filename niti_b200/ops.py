@@ -168,6 +168,28 @@ def conv_fprop_fused(x, w, state, pad=1, mode=ROUND_NEAREST, seed=None, rng_stre
     return y8, exp_out, shift_out
 
 
+def conv_fprop_pool_fused_supported(N, H, W, C, K, R, S, pad):
+    return bool(lib.niti_conv_fprop_requant_pool_supported(N, H, W, C, K, R, S, pad))
+
+
+def conv_fprop_pool_fused(x, w, state, pad=1, mode=ROUND_NEAREST, seed=None, rng_stream=0, rng_offset=0, relu=False,
+                          exp_a=None, exp_b=None):
+    """Convolution + act_calc (+ ReLU) + 2x2 max pooling in one launch.  Returns (int8 [N,H,W,K], int8 [N,H/2,W/2,K],
+    exp_out, shift)."""
+    _need_cuda(x, w, state)
+    N, H, W, C = x.shape
+    K, R, S, _ = w.shape
+    y8 = torch.empty((N, H, W, K), dtype=torch.int8, device=x.device)
+    yp = torch.empty((N, H // 2, W // 2, K), dtype=torch.int8, device=x.device)
+    exp_out = torch.empty((), dtype=torch.int32, device=x.device)
+    shift_out = torch.empty((), dtype=torch.int32, device=x.device)
+    _call("niti_conv_fprop_requant_pool_i8", 1, 2 * N * H * W * K * R * S * C, x.numel() + w.numel() + y8.numel() + yp.numel(),
+          lib.niti_conv_fprop_requant_pool_i8, _p(x), _p(w), _p(y8), _p(yp), _p(state),
+          N, H, W, C, K, R, S, pad, mode, _p(seed), rng_stream, rng_offset, int(relu), _p(exp_a), _p(exp_b),
+          _p(exp_out), _p(shift_out), _p(status_word(x.device)), _st())
+    return y8, yp, exp_out, shift_out
+
+
 def conv_dgrad_fused(err, w, state, pad=1, mode=ROUND_NEAREST, seed=None, rng_stream=0, rng_offset=0, exp_a=None, exp_b=None,
                      relu_mask=None):
     """Error-backward convolution + err_calc in one pass (+ the backward of the ReLU in front of the layer when

@@ -253,10 +253,16 @@ class TiMaxpool2d(Module):
         # True when this layer's input is the output of a TiReLU whose backward mask is applied here
         # (x > 0 on the ReLU's output exactly where its input was > 0): one pass instead of two
         self.relu_backward_fused = False
+        # (input tensor, pooled tensor) left by a convolution whose kernel already pooled its output
+        self.precomputed = None
 
     def forward(self, input):
         self.act_in, exp_in = input
-        self.act_out = ops.maxpool_fwd(self.act_in, self.kernel_size, self.stride)
+        pre, self.precomputed = self.precomputed, None
+        if pre is not None and pre[0] is self.act_in:
+            self.act_out = pre[1]
+        else:
+            self.act_out = ops.maxpool_fwd(self.act_in, self.kernel_size, self.stride)
         return self.act_out, exp_in
 
     def backward(self, input):
@@ -319,6 +325,9 @@ class TiConv2d(UpdateWeight):
         # True when this layer's input is the output of a TiReLU whose backward mask this layer's error-backward
         # kernel applies (set by a model builder together with that TiReLU's backward_in_next_layer)
         self.relu_backward_fused = False
+        # the TiMaxpool2d that follows this layer's (fused) ReLU, when a model builder found one: where the kernel
+        # can, the forward launch also writes the pooled tensor and hands it to that layer
+        self.pool_layer = None
         # shift predictions of the fused conv + requantisation kernels (forward, error-backward)
         self._fwd_state = None
         self._bwd_state = None
@@ -331,6 +340,16 @@ class TiConv2d(UpdateWeight):
             # conv2d_int8 + act_calc (:393-395) in one kernel; see ops.conv_fprop_fused
             if self._fwd_state is None:
                 self._fwd_state = ops.new_requant_state(self.act.device)
+            pool = self.pool_layer
+            if (pool is not None and FUSE_POOL and self.fuse_relu and pool.kernel_size == 2 and pool.stride == 2
+                    and ops.conv_fprop_pool_fused_supported(*self.act.shape, K, R, S, self.padding)):
+                # conv2d_int8 + act_calc + ReLU (:393-395, :268-277) and the pool's forward (:302-307) in one kernel
+                out, pooled, exp_out, _ = ops.conv_fprop_pool_fused(self.act, self.weight, self._fwd_state, self.padding,
+                                                                    _mode(ACT_ROUND_METHOD), RNG_SEED(self.act.device),
+                                                                    16 * self.layer_id, SAMPLE_OFFSET * per, True,
+                                                                    exp_tensor(self.act_in_exp, self.act.device), self.weight_exp)
+                pool.precomputed = (out, pooled)
+                return out, exp_out
             out, exp_out, _ = ops.conv_fprop_fused(self.act, self.weight, self._fwd_state, self.padding, _mode(ACT_ROUND_METHOD),
                                                    RNG_SEED(self.act.device), 16 * self.layer_id, SAMPLE_OFFSET * per,
                                                    self.fuse_relu, exp_tensor(self.act_in_exp, self.act.device), self.weight_exp)
@@ -416,6 +435,7 @@ GRAD_ROUND_METHOD = PstoShift
 WEIGHT_INIT_METHOD = UniformWeights
 
 FUSE_REQUANT = True    # convolutions narrow to int8 inside their own kernel (predicted shift, verified, redone if wrong)
+FUSE_POOL = True       # conv -> ReLU -> 2x2 pool: the convolution's kernel also writes the pooled tensor where it can
 FUSE_HEAD = True       # TiNet.train_step runs [dropout,] FC, loss, FC backward and update as one kernel
 GRAD_BITWIDTH = 5      # the reference's training loop injects this per epoch (main.py:73-77)
 TRAINING = True        # likewise (main.py:147-149)

@@ -37,9 +37,12 @@ class TiVGG_cifar(TiNet):
             if x == 'M':
                 pool = TiMaxpool2d(2, 2)
                 if fuse_relu and layers and isinstance(layers[-1], TiReLU):
-                    # conv -> ReLU -> pool: the pool's backward also applies the ReLU's mask
+                    # conv -> ReLU -> pool: the pool's backward also applies the ReLU's mask, and the convolution's
+                    # kernel writes the pooled tensor too where it can
                     layers[-1].backward_in_next_layer = True
                     pool.relu_backward_fused = True
+                    if len(layers) >= 2 and isinstance(layers[-2], TiConv2d):
+                        layers[-2].pool_layer = pool
                 layers += [pool]
                 image_size = image_size // 2
             else:

@@ -496,6 +496,38 @@ def test_bounded_grid_barrier_gives_up_and_reports():
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("N,H,W,C,K,mode", [
+    (128, 16, 16, 256, 256, 0), (128, 8, 8, 512, 512, 0), (32, 16, 16, 128, 256, 0),   # VGG shapes that park at these batches
+    (3, 16, 16, 32, 48, 0), (5, 8, 8, 144, 16, 0), (7, 4, 4, 64, 272, 0), (2, 2, 2, 16, 32, 0), (6, 8, 16, 128, 128, 1)])
+def test_conv_fprop_fused_with_pool_in_the_same_launch(N, H, W, C, K, mode):
+    """conv + act_calc + ReLU + 2x2 max pooling in one kernel against the oracle's four separate steps; the unpooled
+    tensor is written too (the pool's backward routes by it)."""
+    assert ops.conv_fprop_pool_fused_supported(N, H, W, C, K, 3, 3, 1)
+    rng = np.random.default_rng(N * 7 + H + C + K)
+    x, w = rnd8(rng, (N, H, W, C)), rnd8(rng, (K, 3, 3, C))
+    seed = ops.seed_tensor(77, DEV)
+    ea = torch.full((), -3, dtype=torch.int32, device=DEV)
+    st = ops.new_requant_state(DEV)
+    for _ in range(2):
+        y8, yp, exp_out, shift = ops.conv_fprop_pool_fused(cu(x), cu(w), st, 1, mode, seed, 5, 0, True, ea, ea)
+    acc = O.conv_fprop(x, w)
+    words = philox.random_u32_tensor(77, 5, acc.shape) if mode == 1 else None
+    want, want_e, _ = O.act_calc(acc, -6, mode, words)
+    want = O.relu_fwd(want)
+    assert int(exp_out) == want_e
+    assert_same(y8, want, "fused conv + relu")
+    assert_same(yp, O.maxpool_fwd(want), "pooled output of the same launch")
+
+
+@pytest.mark.gpu
+def test_conv_fprop_pool_fusion_is_refused_where_it_cannot_run():
+    # 32-pixel-wide images: a pooling window spans two warps' rows of a tile; odd sizes; layers that do not fit in tensor memory
+    assert not ops.conv_fprop_pool_fused_supported(8, 32, 32, 128, 128, 3, 3, 1)
+    assert not ops.conv_fprop_pool_fused_supported(8, 6, 5, 128, 128, 3, 3, 1)
+    assert not ops.conv_fprop_pool_fused_supported(1024, 16, 16, 128, 128, 3, 3, 1)
+
+
+@pytest.mark.gpu
 def test_dp_update_peer_wait_gives_up_and_reports():
     """niti_dp_update_i8 told that there are two ranks, the second one a zeroed local area that nobody signals: the first
     cross-rank barrier runs into its 4 s limit, the kernel returns with status {9, rank waited for, barrier number}, updates
