@@ -205,6 +205,104 @@ __device__ __forceinline__ void umma_i8(uint32_t d_tmem, uint64_t a_desc, uint64
         ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
         : "memory");
 }
+// Bounded wait without a verdict: spins inside the asm until the phase completes, the CTA's abort flag is up, or the
+// limit runs out -- in which case it raises the abort flag itself -- and then simply returns.  Nothing of the caller's
+// control flow depends on it, which keeps the loops of the TMA producer and the MMA issuer straight-line uniform code;
+// once the flag is up every later wait falls through at its first poll, so a role that runs on after a failed wait
+// finishes in microseconds (its loads and MMAs are harmless: the kernel's results are discarded with the status).
+// All 32 lanes of the (converged) warp call it.
+#define NITI_QUIET_WAIT_ASM(LBL, BAR, PAR, ABRT, LIM)                           \
+    "mbarrier.try_wait.parity.shared::cta.b64 Q, [" BAR "], " PAR ";\n\t"       \
+    "@Q bra " LBL "_GO;\n\t"                                                    \
+    "mov.u64 t0, %%globaltimer;\n\t"                                            \
+    LBL "_SPIN:\n\t"                                                            \
+    "mbarrier.try_wait.parity.shared::cta.b64 Q, [" BAR "], " PAR ";\n\t"       \
+    "@Q bra " LBL "_GO;\n\t"                                                    \
+    "ld.volatile.shared.u32 ab, [" ABRT "];\n\t"                                \
+    "setp.ne.u32 P, ab, 0;\n\t"                                                 \
+    "@P bra " LBL "_GO;\n\t"                                                    \
+    "mov.u64 t1, %%globaltimer;\n\t"                                            \
+    "sub.u64 t1, t1, t0;\n\t"                                                   \
+    "setp.lt.u64 P, t1, " LIM ";\n\t"                                           \
+    "@P bra " LBL "_SPIN;\n\t"                                                  \
+    "mov.u32 ab, 1;\n\t"                                                        \
+    "st.volatile.shared.u32 [" ABRT "], ab;\n\t"                                \
+    LBL "_GO:\n\t"
+
+__device__ __forceinline__ void mbar_wait_quiet(uint32_t bar, uint32_t parity, uint32_t abort_flag_smem) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred P, Q;\n\t"
+        ".reg .u64 t0, t1;\n\t"
+        ".reg .u32 ab;\n\t"
+        NITI_QUIET_WAIT_ASM("QW", "%0", "%1", "%2", "%3")
+        "}"
+        :: "r"(bar), "r"(parity), "r"(abort_flag_smem), "l"(WAIT_LIMIT_NS)
+        : "memory");
+}
+
+// One reduction block of the MMA issuer's main loop as ONE asm statement with no outputs: wait (quietly, see above) for
+// the stage's "full" barrier, then an elected lane issues the block's four MMAs (K = 32 each, operand descriptors a,
+// a + a_step, ...; the first one accumulates only if `accumulate`) and the commit that hands the stage back.
+template <bool PAIR>
+__device__ __forceinline__ void umma_block4_wait(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint64_t a_step, uint64_t b_step,
+                                                 uint32_t idesc, uint32_t accumulate, uint32_t commit_bar, uint32_t full_bar,
+                                                 uint32_t parity, uint32_t abort_flag_smem) {
+    if (PAIR) {
+        asm volatile(
+            "{\n\t"
+            ".reg .pred P, Q, E, T;\n\t"
+            ".reg .b32 r, ab;\n\t"
+            ".reg .u64 t0, t1;\n\t"
+            ".reg .b64 a1, a2, a3, b1, b2, b3;\n\t"
+            NITI_QUIET_WAIT_ASM("BWP", "%8", "%9", "%10", "%11")
+            "elect.sync r|E, 0xFFFFFFFF;\n\t"
+            "setp.ne.b32 P, %6, 0;\n\t"
+            "setp.eq.b32 T, 0, 0;\n\t"
+            "add.u64 a1, %1, %3;\n\t"
+            "add.u64 b1, %2, %4;\n\t"
+            "add.u64 a2, a1, %3;\n\t"
+            "add.u64 b2, b1, %4;\n\t"
+            "add.u64 a3, a2, %3;\n\t"
+            "add.u64 b3, b2, %4;\n\t"
+            "@E tcgen05.mma.cta_group::2.kind::i8 [%0], %1, %2, %5, P;\n\t"
+            "@E tcgen05.mma.cta_group::2.kind::i8 [%0], a1, b1, %5, T;\n\t"
+            "@E tcgen05.mma.cta_group::2.kind::i8 [%0], a2, b2, %5, T;\n\t"
+            "@E tcgen05.mma.cta_group::2.kind::i8 [%0], a3, b3, %5, T;\n\t"
+            "@E tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%7], %12;\n\t"
+            "}"
+            :: "r"(d_tmem), "l"(a_desc), "l"(b_desc), "l"(a_step), "l"(b_step), "r"(idesc), "r"(accumulate), "r"(commit_bar),
+               "r"(full_bar), "r"(parity), "r"(abort_flag_smem), "l"(WAIT_LIMIT_NS), "h"(static_cast<uint16_t>(3))
+            : "memory");
+    } else {
+        asm volatile(
+            "{\n\t"
+            ".reg .pred P, Q, E, T;\n\t"
+            ".reg .b32 r, ab;\n\t"
+            ".reg .u64 t0, t1;\n\t"
+            ".reg .b64 a1, a2, a3, b1, b2, b3;\n\t"
+            NITI_QUIET_WAIT_ASM("BW", "%8", "%9", "%10", "%11")
+            "elect.sync r|E, 0xFFFFFFFF;\n\t"
+            "setp.ne.b32 P, %6, 0;\n\t"
+            "setp.eq.b32 T, 0, 0;\n\t"
+            "add.u64 a1, %1, %3;\n\t"
+            "add.u64 b1, %2, %4;\n\t"
+            "add.u64 a2, a1, %3;\n\t"
+            "add.u64 b2, b1, %4;\n\t"
+            "add.u64 a3, a2, %3;\n\t"
+            "add.u64 b3, b2, %4;\n\t"
+            "@E tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %5, P;\n\t"
+            "@E tcgen05.mma.cta_group::1.kind::i8 [%0], a1, b1, %5, T;\n\t"
+            "@E tcgen05.mma.cta_group::1.kind::i8 [%0], a2, b2, %5, T;\n\t"
+            "@E tcgen05.mma.cta_group::1.kind::i8 [%0], a3, b3, %5, T;\n\t"
+            "@E tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%7];\n\t"
+            "}"
+            :: "r"(d_tmem), "l"(a_desc), "l"(b_desc), "l"(a_step), "l"(b_step), "r"(idesc), "r"(accumulate), "r"(commit_bar),
+               "r"(full_bar), "r"(parity), "r"(abort_flag_smem), "l"(WAIT_LIMIT_NS)
+            : "memory");
+    }
+}
+
 // One reduction block of the main loop as ONE asm statement, run by the whole (converged) warp: a non-blocking probe of
 // the NEXT stage's "full" barrier is started, an elected lane issues the block's four MMAs (K = 32 each, operand
 // descriptors a, a + a_step, ... ; the first one accumulates only if `accumulate`) and the commit that hands the stage

@@ -209,10 +209,11 @@ __device__ __forceinline__ void producer_role(uint8_t* smem, uint64_t* full_bar,
     const int conv = keep_reg(p.conv), flip = keep_reg(p.flip), pad = keep_reg(p.pad), S = keep_reg(p.S), cblocks = keep_reg(p.cblocks);
     const int tapstride = keep_reg(p.tapstride), b_mn = keep_reg(p.b_mn), a_mn = keep_reg(p.a_mn);
     const uint32_t tx_bytes = static_cast<uint32_t>(keep_reg(TWO ? 2 * (p.a_bytes + BNH * ROW_BYTES) : p.a_bytes + BN * ROW_BYTES));
-    int s = 0; uint32_t ph = 0; bool ok = true;
+    int s = 0; uint32_t ph = 0;
+    uint32_t sa = smem0, fb_cur = full0, eb_cur = empty0;  // running stage pointers, wrapping with the ring
     DBG_DECL;
     DBG_CLK(c_begin);
-    for (int tile = first; ok && tile < total_tiles; tile += step) {
+    for (int tile = first; tile < total_tiles; tile += step) {
         int mn = tile, kb_lo = 0, kb_hi = p.num_kb;
         if (p.splits > 1) {
             const int split = tile / mn_tiles;
@@ -228,17 +229,15 @@ __device__ __forceinline__ void producer_role(uint8_t* smem, uint64_t* full_bar,
         const int ncol = n_t * BN + static_cast<int>(rank) * BNH;  // first B column of this CTA
         const int px = tw * p.BW, py = th * p.BH, pn = tn * p.BI;
         // This loop is one warp's serial instruction stream and sets the pace of the whole pipeline: the tap
-        // (r, sx) and channel block cb of a reduction block are kept as running counters, because four integer
-        // divisions per block cost more than the block's MMAs.
+        // (r, sx) and channel block cb of a reduction block are kept as running counters (four integer divisions per
+        // block cost more than the block's MMAs), waits return nothing to branch on, pointers advance by addition.
         int cb = 0, sx = 0, r = 0;
         if (conv && kb_lo != 0) { const int tap0 = kb_lo / cblocks; cb = kb_lo % cblocks; r = tap0 / S; sx = tap0 % S; }
         for (int kb = kb_lo; kb < kb_hi; ++kb) {
-            ok = mbar_wait_uniform(empty0 + 8u * s, ph ^ 1u, abort_addr);
-            if (!ok) { *abort_flag = 1; report_abort(p.status, 1, 0); break; }
+            mbar_wait_quiet(eb_cur, ph ^ 1u, abort_addr);
             DBG_ACC(22, 1);
-            const uint32_t sa = smem0 + static_cast<uint32_t>(s) * STAGE_BYTES;
             const uint32_t sb = sa + PANEL_BYTES;
-            uint32_t fb = full0 + 8u * s;
+            uint32_t fb = fb_cur;
             if (elect_one()) {
                 if (TWO) {
                     if (rank == 0) mbar_arrive_expect_tx(fb, tx_bytes);
@@ -282,9 +281,11 @@ __device__ __forceinline__ void producer_role(uint8_t* smem, uint64_t* full_bar,
                 }
             }
             if (conv && ++cb == cblocks) { cb = 0; if (++sx == S) { sx = 0; ++r; } }
-            if (++s == nst) { s = 0; ph ^= 1u; }
+            sa += STAGE_BYTES; fb_cur += 8u; eb_cur += 8u;
+            if (++s == nst) { s = 0; ph ^= 1u; sa = smem0; fb_cur = full0; eb_cur = empty0; }
         }
     }
+    if (*abort_flag) report_abort(p.status, 1, 0);  // a quiet wait of this role (or another role) gave up
     DBG_CLK(c_end); DBG_ACC(20, c_end - c_begin);
     DBG_OUT(20);
 }
@@ -320,7 +321,12 @@ __device__ __forceinline__ void mma_role(uint8_t* smem, uint64_t* full_bar, uint
     const uint32_t b_step = static_cast<uint32_t>(keep_reg((p.b_mn ? 32 * ROW_BYTES : 32) >> 4));
     const int conv = keep_reg(p.conv), red = keep_reg(p.red), cblocks = keep_reg(p.cblocks), num_kb = keep_reg(p.num_kb), splits = keep_reg(p.splits);
     int s = 0; uint32_t ph = 0; bool ok = true; int it = 0;
-    bool ready = false;  // the current stage's "full" phase was already seen complete by the previous block's probe
+    // every reduction block has four MMAs unless a conv tap's channel count ends in a partial 128-byte block
+    const bool all4 = !conv || (red & 127) == 0;
+    // running stage pointers: descriptors and barrier addresses advance by one stage per block and wrap with the ring
+    const uint64_t stage_step = STAGE_BYTES >> 4;
+    uint64_t a_cur = a_base, b_cur = b_base;
+    uint32_t full_cur = full0, empty_cur = empty0;
     DBG_DECL;
 #ifdef NITI_PARKED_TIMING
     long long c_first = 0;
@@ -342,45 +348,32 @@ __device__ __forceinline__ void mma_role(uint8_t* smem, uint64_t* full_bar, uint
         }
         int cb = (conv && kb_lo != 0) ? kb_lo % cblocks : 0;  // channel block within the tap: a running counter, no division per block
         for (int kb = kb_lo; kb < kb_hi; ++kb) {
-            if (!ready) {
-                ok = mbar_wait_uniform(full0 + 8u * s, ph, abort_addr);
-                if (!ok) { *abort_flag = 1; report_abort(p.status, 3, 1); break; }
-            }
             DBG_ACC(19, 1);
 #ifdef NITI_PARKED_TIMING
             if (it == 0 && kb == kb_lo) { c_first = clock64(); if (PARKED) PARK_STAMP(2); }
 #endif
-            const uint64_t a0 = a_base + ((static_cast<uint32_t>(s) * STAGE_BYTES) >> 4);
-            const uint64_t b0 = b_base + ((static_cast<uint32_t>(s) * STAGE_BYTES) >> 4);
-            // a conv tap whose channel count is not a multiple of 128 ends in a partial block:
-            // issue only the MMAs (K = 32 each) that cover real channels (the rest is TMA zero fill)
-            int nmma = 4;
-            if (conv) {
-                const int left = red - cb * 128;
-                nmma = left >= 128 ? 4 : (left + 31) >> 5;
-                if (++cb == cblocks) cb = 0;
-            }
-            const uint32_t eb = empty0 + 8u * s;
-            // the next stage's "full" barrier is probed while this block's MMAs are issued
-            const int sn = (s + 1 == nst) ? 0 : s + 1;
-            const uint32_t phn = (sn == 0) ? ph ^ 1u : ph;
-            uint32_t probe;
-            if (nmma == 4) {
-                probe = umma_block4<TWO>(d_tmem, a0, b0, a_step, b_step, idesc, static_cast<uint32_t>(kb != kb_lo), eb,
-                                         full0 + 8u * sn, phn);
+            if (all4) {
+                // wait for the stage, four MMAs, commit: one asm statement, nothing for the loop to branch on
+                umma_block4_wait<TWO>(d_tmem, a_cur, b_cur, a_step, b_step, idesc, static_cast<uint32_t>(kb != kb_lo), empty_cur,
+                                      full_cur, ph, abort_addr);
             } else {
+                // a partial block: issue only the MMAs (K = 32 each) that cover real channels (the rest is TMA zero fill)
+                const int left = red - cb * 128;
+                const int nmma = left >= 128 ? 4 : (left + 31) >> 5;
+                if (++cb == cblocks) cb = 0;
+                mbar_wait_quiet(full_cur, ph, abort_addr);
                 if (elect_one()) {
                     for (int k = 0; k < nmma; ++k)
-                        umma_issue<TWO>(d_tmem, a0 + k * a_step, b0 + k * b_step, idesc, static_cast<uint32_t>(kb != kb_lo || k != 0));
-                    if (TWO) umma_commit_pair(eb); else umma_commit(eb);
+                        umma_issue<TWO>(d_tmem, a_cur + k * a_step, b_cur + k * b_step, idesc, static_cast<uint32_t>(kb != kb_lo || k != 0));
+                    if (TWO) umma_commit_pair(empty_cur); else umma_commit(empty_cur);
                 }
-                probe = mbar_test_wait(full0 + 8u * sn, phn);
             }
-            ready = __all_sync(0xFFFFFFFFu, probe != 0);
-            s = sn; ph = phn;
+            a_cur += stage_step; b_cur += stage_step; full_cur += 8u; empty_cur += 8u;
+            if (++s == nst) { s = 0; ph ^= 1u; a_cur = a_base; b_cur = b_base; full_cur = full0; empty_cur = empty0; }
         }
         if (ok && elect_one()) { if (TWO) umma_commit_pair(smem_u32(&tfull_bar[acc])); else umma_commit(smem_u32(&tfull_bar[acc])); }
     }
+    if (*abort_flag) report_abort(p.status, 3, 1);  // a quiet wait of this role (or another role) gave up
     if (PARKED) PARK_STAMP(3);
 #ifdef NITI_PARKED_TIMING
     DBG_ACC(16, clock64() - c_first);
