@@ -665,6 +665,23 @@ def make_case(name, shape):
     def r8(*s):
         return torch.randint(-127, 128, s, dtype=torch.int8, generator=g).to(dev)
 
+    if name == "train_step":
+        # one whole training step of the default workload (VGG-small-7), eager launches: shape = (batch,)
+        from niti_b200 import ti_torch, ti_vgg
+        from niti_b200.trainer import Trainer
+        B = shape[0]
+        cfg = CONFIGS["vgg7"][0]
+        shapes_, weights, wexps, rng = synth_weights(cfg, 1235)
+        ti_torch.GRAD_BITWIDTH, ti_torch.TRAINING = 5, True
+        model = ti_vgg.TiVGG_cifar(list(cfg), dropout=True, fuse_relu=True)
+        for l, w, e in zip(model.weighted_layers(), weights, wexps):
+            l.weight = torch.from_numpy(w).to(dev)
+            l.weight_exp = ti_torch.exp_tensor(e, dev)
+        trainer = Trainer(model, B, dev, use_graph=False, seed=1235)
+        x, t = synth_batch(rng, B)
+        trainer.x.copy_(torch.from_numpy(x))
+        trainer.t.copy_(torch.from_numpy(t))
+        return trainer.run_device_step, step_ops_per_image(cfg) * B, 0
     if name.startswith("gemm"):
         M, N, K = shape
         ta, tb = {"gemm_tn": (False, True), "gemm_nn": (False, False), "gemm_tn_a": (True, False)}[name]
@@ -747,7 +764,8 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--exchange", default="auto", choices=["auto", "nccl"],
                     help="N>1: 'auto' = the peer-memory update kernel when the ranks share a node, else NCCL; 'nccl' = all-reduce")
-    ap.add_argument("--case", help="time one kernel case instead of the training step (see make_case)")
+    ap.add_argument("--case", help="time one kernel case instead of the training step (see make_case; 'train_step' with "
+                                   "--shape BATCH runs whole eager steps of the default workload)")
     ap.add_argument("--shape", default="128,16,16,256,256")
     ap.add_argument("--plain-launches", type=int, default=0, help="with --case: just launch it this many times (for ncu)")
     ap.add_argument("--sweep", action="store_true", help="GEMM and conv roofline sweep, one JSON line per case")

@@ -103,6 +103,19 @@ NITI_API int niti_conv_fprop_i8(const int8_t* x, const int8_t* w, int32_t* y32, 
                        int N, int H, int W, int C, int K, int R, int S, int pad, int stride,
                        int32_t* status, void* stream);
 
+/* cutlassconv_cuda.int4_conv / int4_conv_optimized (cutlassconv.cpp:83-97, cutlassconv_kernel.cu:602-884), which the
+ * reference exports but never calls from ti_torch.py: a 3x3 (RxS) convolution of int4 operands packed two per byte along
+ * the channels, element 2i in the low nibble (CUTLASS' int4b_t arrays, include/cutlass/array_subbyte.h:116-124), signed.
+ * x4 [N][H][W][C2] bytes = 2*C2 channels, w4 [K][R][S][C2] -> y32 [N][P][Q][K] exact int32 (the reference's epilogue
+ * saturates, which cannot trigger: |sum| <= 64*R*S*2*C2), stride 1.  The tensor cores of this part have no int4 integer
+ * MMA (tcgen05 kind::i8 takes 8-bit integers): the operands are widened to int8 in `scratch` and go through
+ * niti_conv_fprop_i8's kernels.  Parity unpinned at the nibble order: the reference has no caller and no test for it. */
+NITI_API size_t niti_conv_fprop_i4_scratch_bytes(int N, int H, int W, int C2, int K, int R, int S);
+NITI_API int niti_conv_fprop_i4(const uint8_t* x4, const uint8_t* w4, int32_t* y32, uint32_t* maxabs,
+                       void* scratch, size_t scratch_bytes,
+                       int N, int H, int W, int C2, int K, int R, int S, int pad,
+                       int32_t* status, void* stream);
+
 /* Error back-propagation of a convolution: TiConv2d.backward's
  * conv2d_int8(err, flip(w,[1,2]).transpose(0,3)) (ti_torch.py:403-405) WITHOUT the flipped,
  * transposed copy of the weights: the kernel reads w [K][R][S][C] in place (as the reduction

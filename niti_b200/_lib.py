@@ -26,6 +26,8 @@ SIGNATURES = {
     "niti_last_cuda_error": (C.c_char_p, []),
     "niti_conv_fprop_scratch_bytes": (_sz, [_i] * 7),
     "niti_conv_fprop_i8": (_i, [_p, _p, _p, _p, _p, _sz] + [_i] * 9 + [_p, _p]),
+    "niti_conv_fprop_i4_scratch_bytes": (_sz, [_i] * 7),
+    "niti_conv_fprop_i4": (_i, [_p, _p, _p, _p, _p, _sz] + [_i] * 8 + [_p, _p]),
     "niti_conv_fprop_requant_supported": (_i, [_i] * 5),
     "niti_conv_dgrad_requant_supported": (_i, [_i] * 5),
     "niti_conv_fprop_requant_i8": (_i, [_p, _p, _p, _p, _p, _sz] + [_i] * 8 + [_i, _p, _u32, _u64, _i, _p, _p, _p, _p, _p, _p]),

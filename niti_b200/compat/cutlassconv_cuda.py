@@ -39,3 +39,19 @@ def sp_conv(input, weight, stride, padding):
 
 def sp_conv_optimized(input, weight, stride, padding):
     return _conv(input, weight, stride, padding)
+
+
+def _conv4(input, weight):
+    check_input(input, weight)
+    if input.dim() != 4 or weight.dim() != 4 or input.shape[3] != weight.shape[3]:
+        raise RuntimeError("int4_conv: [N,H,W,C/2] input and [K,R,S,C/2] filters expected (two int4 per byte)")
+    return ops.conv_fprop_i4(input.view(torch.uint8), weight.view(torch.uint8), 1)[0]
+
+
+def int4_conv(input, weight):
+    """cutlassconv.cpp:83-89: 3x3, pad 1, stride 1; int4 pairs packed in the bytes of int8 / uint8 tensors."""
+    return _conv4(input, weight)
+
+
+def int4_conv_optimized(input, weight):
+    return _conv4(input, weight)

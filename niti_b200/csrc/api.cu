@@ -145,6 +145,30 @@ extern "C" int niti_conv_fprop_i8(const int8_t* x, const int8_t* w, int32_t* y32
     return simt_conv_fprop(x, w, y32, maxabs, N, H, W, C, K, R, S, pad, st);
 }
 
+// ---------------------------------------------------------------- int4 operands
+extern "C" size_t niti_conv_fprop_i4_scratch_bytes(int N, int H, int W, int C2, int K, int R, int S) {
+    if (N <= 0 || H <= 0 || W <= 0 || C2 <= 0 || K <= 0 || R <= 0 || S <= 0) return 0;
+    const size_t xb = align_up(static_cast<size_t>(N) * H * W * C2 * 2, 1024), wb = align_up(static_cast<size_t>(K) * R * S * C2 * 2, 1024);
+    return xb + wb + niti_conv_fprop_scratch_bytes(N, H, W, 2 * C2, K, R, S);
+}
+
+extern "C" int niti_conv_fprop_i4(const uint8_t* x4, const uint8_t* w4, int32_t* y32, uint32_t* maxabs, void* scratch,
+                                  size_t scratch_bytes, int N, int H, int W, int C2, int K, int R, int S, int pad,
+                                  int32_t* status, void* stream) {
+    NITI_REQUIRE(x4 && w4 && y32 && maxabs && scratch && N > 0 && H > 0 && W > 0 && C2 > 0 && K > 0 && R > 0 && S > 0 && pad >= 0);
+    NITI_REQUIRE(aligned16(scratch) && reinterpret_cast<uintptr_t>(x4) % 2 == 0);
+    if (scratch_bytes < niti_conv_fprop_i4_scratch_bytes(N, H, W, C2, K, R, S)) return NITI_ERR_SCRATCH;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const size_t xn = static_cast<size_t>(N) * H * W * C2, wn = static_cast<size_t>(K) * R * S * C2;
+    int8_t* x8 = static_cast<int8_t*>(scratch);
+    int8_t* w8 = x8 + align_up(2 * xn, 1024);
+    int8_t* rest = w8 + align_up(2 * wn, 1024);
+    if (int e = unpack_i4(x4, x8, static_cast<long long>(xn), st)) return e;
+    if (int e = unpack_i4(w4, w8, static_cast<long long>(wn), st)) return e;
+    const size_t used = static_cast<size_t>(rest - static_cast<int8_t*>(scratch));
+    return niti_conv_fprop_i8(x8, w8, y32, maxabs, rest, scratch_bytes - used, N, H, W, 2 * C2, K, R, S, pad, 1, status, stream);
+}
+
 extern "C" int niti_conv_dgrad_i8(const int8_t* err, const int8_t* w, int32_t* e32, uint32_t* maxabs, int N, int H,
                                   int W, int C, int K, int R, int S, int pad, int32_t* status, void* stream) {
     NITI_REQUIRE(err && w && e32 && maxabs && N > 0 && H > 0 && W > 0 && C > 0 && K > 0 && R > 0 && S > 0 && pad >= 0);

@@ -59,5 +59,6 @@ int reduce_partials(const int32_t* partial, int splits, long long n, int32_t* ou
 int reduce_rows32(const int32_t* partial, int splits, int rows, int cols_out, int32_t* out, unsigned* maxabs, cudaStream_t st);
 int im2col32(const int8_t* x, int8_t* xcol, int Nimg, int H, int W, int C, int R, int S, int pad, cudaStream_t st);
 int pad_rows32(const int8_t* w, int8_t* wp, int K, int rsc, cudaStream_t st);
+int unpack_i4(const uint8_t* in, int8_t* out, long long nbytes, cudaStream_t st);  // two int4 per byte (low nibble first) -> int8
 
 }  // namespace niti

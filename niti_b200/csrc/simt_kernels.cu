@@ -1097,6 +1097,22 @@ extern "C" int niti_absmax_i32(const int32_t* acc, int64_t n, uint32_t* maxabs, 
     return set_cuda_error(cudaGetLastError());
 }
 
+// Two signed 4-bit values per byte, element 2i in the low nibble (the packing of CUTLASS' int4b_t arrays), to int8.
+__global__ void __launch_bounds__(256) unpack_i4_kernel(const uint8_t* __restrict__ in, int8_t* __restrict__ out, long long nbytes) {
+    const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+    for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < nbytes; i += stride) {
+        const unsigned b = in[i];
+        const int lo = static_cast<int>(b << 28) >> 28, hi = static_cast<int>(b << 24) >> 28;  // sign-extend each nibble
+        reinterpret_cast<char2*>(out)[i] = make_char2(static_cast<signed char>(lo), static_cast<signed char>(hi));
+    }
+}
+namespace niti {
+int unpack_i4(const uint8_t* in, int8_t* out, long long nbytes, cudaStream_t st) {
+    unpack_i4_kernel<<<blocks_for(nbytes, 256, sm_count_simt() * 16), 256, 0, st>>>(in, out, nbytes);
+    return set_cuda_error(cudaGetLastError());
+}
+}  // namespace niti
+
 // Grouped cross-correlation with ONE input channel per group and a batch of one: the only form in which the
 // reference calls int8conv_cuda.group_conv (conv2d_weight_int8 folds batch and channels into groups and the error
 // maps into filters as large as the image).  out[p][q][g*Kg + k] = sum_{r,s} in[p+r-pad][q+s-pad][g] * wt[g*Kg+k][r][s].

@@ -112,6 +112,24 @@ def conv_fprop_acc(x, w, pad=1, stride=1):
     return y32, mx
 
 
+def conv_fprop_i4(x4, w4, pad=1):
+    """int4 convolution: x4 uint8 [N,H,W,C/2] and w4 uint8 [K,R,S,C/2] hold two signed 4-bit channels per byte (even channel
+    in the low nibble) -> (int32 [N,P,Q,K], max|y|).  The reference's cutlassconv_cuda.int4_conv."""
+    _need_cuda(x4, w4)
+    assert x4.dtype == torch.uint8 and w4.dtype == torch.uint8
+    N, H, W, C2 = x4.shape
+    K, R, S, _ = w4.shape
+    P, Q = H + 2 * pad - R + 1, W + 2 * pad - S + 1
+    y32 = torch.empty((N, P, Q, K), dtype=torch.int32, device=x4.device)
+    mx = torch.empty(1, dtype=torch.int32, device=x4.device)
+    nbytes = lib.niti_conv_fprop_i4_scratch_bytes(N, H, W, C2, K, R, S)
+    sc = scratch(x4.device, nbytes)
+    _call("niti_conv_fprop_i4", 3, 2 * N * P * Q * K * R * S * 2 * C2, x4.numel() + w4.numel() + 4 * y32.numel(),
+          lib.niti_conv_fprop_i4, _p(x4), _p(w4), _p(y32), _p(mx), _p(sc), sc.numel(), N, H, W, C2, K, R, S, pad,
+          _p(status_word(x4.device)), _st())
+    return y32, mx
+
+
 def set_accumulator_parking(enabled):
     """Switch the single-launch (accumulators parked in tensor memory) fused kernels on or off; returns the old setting."""
     return bool(lib.niti_set_option(1, int(bool(enabled))))

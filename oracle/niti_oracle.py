@@ -205,6 +205,22 @@ def conv_fprop(x, w, pad=1, stride=1):
     return check_acc(acc)
 
 
+def unpack_int4(a):
+    """Bytes holding two signed 4-bit values each, even element in the low nibble (cutlass int4b_t arrays,
+    include/cutlass/array_subbyte.h:116-124) -> int8 with twice as many entries along the last axis."""
+    b = np.asarray(a).view(np.uint8)
+    lo = (b & 15).astype(np.int8)
+    hi = (b >> 4).astype(np.int8)
+    lo = np.where(lo > 7, lo - 16, lo).astype(np.int8)
+    hi = np.where(hi > 7, hi - 16, hi).astype(np.int8)
+    return np.stack([lo, hi], axis=-1).reshape(b.shape[:-1] + (2 * b.shape[-1],))
+
+
+def conv_fprop_int4(x4, w4, pad=1):
+    """cutlassconv_cuda.int4_conv (cutlassconv_kernel.cu:602-884): the int8 convolution of the unpacked operands."""
+    return conv_fprop(unpack_int4(x4), unpack_int4(w4), pad=pad)
+
+
 def flip_transpose(w):
     """ti_torch.py:404: torch.flip(w,[1,2]).transpose(0,3) -> [C,R,S,K]."""
     return np.ascontiguousarray(np.flip(w, axis=(1, 2)).transpose(3, 1, 2, 0))

@@ -528,6 +528,19 @@ def test_conv_fprop_pool_fusion_is_refused_where_it_cannot_run():
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("N,H,W,C2,K", [(4, 8, 8, 64, 32), (2, 5, 7, 8, 12), (3, 6, 6, 1, 16), (16, 16, 16, 128, 128)])
+def test_conv_int4_operands(N, H, W, C2, K):
+    """int4 pairs packed per byte (every nibble pattern occurs, -8 included), against the oracle's unpack + convolution."""
+    rng = np.random.default_rng(N + C2 + K)
+    x4 = rng.integers(0, 256, size=(N, H, W, C2), dtype=np.uint8)
+    w4 = rng.integers(0, 256, size=(K, 3, 3, C2), dtype=np.uint8)
+    y32, mx = ops.conv_fprop_i4(cu(x4), cu(w4), 1)
+    want = O.conv_fprop_int4(x4, w4)
+    assert_same(y32, want.astype(np.int32), "int4 convolution")
+    assert int(mx) == int(np.abs(want).max())
+
+
+@pytest.mark.gpu
 def test_dp_update_peer_wait_gives_up_and_reports():
     """niti_dp_update_i8 told that there are two ranks, the second one a zeroed local area that nobody signals: the first
     cross-rank barrier runs into its 4 s limit, the kernel returns with status {9, rank waited for, barrier number}, updates

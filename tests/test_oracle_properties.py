@@ -73,3 +73,8 @@ def test_exact_backends_agree():
         assert np.array_equal(O.int8_mm(a, b), r64)
     finally:
         O.set_backend("int64")
+
+
+def test_int4_unpacking_order_and_sign():
+    a = np.array([[0x10, 0x8F, 0x7A]], dtype=np.uint8)      # (lo, hi) = (0, 1), (-1, -8), (-6, 7)
+    assert O.unpack_int4(a).tolist() == [[0, 1, -1, -8, -6, 7]]
