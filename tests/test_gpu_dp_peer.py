@@ -9,7 +9,7 @@ import pytest
 import torch
 import torch.multiprocessing as mp
 
-from oracle import dp_oracle
+from oracle import dp_oracle, niti_oracle as O
 from tests.test_gpu_dp_exact import CFG, GLOBAL_BATCH, SEED, STEPS, _data
 
 pytestmark = pytest.mark.gpu
@@ -42,7 +42,22 @@ def _worker(rank, world, port, q):
             tr.sync()
             logits.append((out.numpy().copy(), int(exp)))
         bucket_clear = int(tr.bucket.flat.abs().max().item()) == 0
-        q.put((rank, lo, hi, logits, [l.weight.cpu().numpy().tobytes() for l in model.weighted_layers()], bucket_clear))
+        final_w = [l.weight.cpu().numpy().tobytes() for l in model.weighted_layers()]
+        # a checkpoint loaded AFTER graph capture and after the weights moved into the peer-visible arena: the values
+        # are copied into that memory, so the next step trains on them on every rank
+        sd, wi = {}, 0
+        for idx, l in enumerate(model.forward_layers):
+            if hasattr(l, "weight"):
+                sd[f"layers.{idx}.weight"] = torch.from_numpy(weights[wi])
+                sd[f"layers.{idx}.weight_exp"] = torch.tensor(float(wexps[wi]))  # the reference's checkpoints hold floats
+                wi += 1
+        model.load_state_dict(sd)
+        tr.resync()
+        x, t = batches[0]
+        out, exp = tr.step(torch.from_numpy(x[lo:hi].copy()).pin_memory(), torch.from_numpy(t[lo:hi].copy()).pin_memory())
+        tr.sync()
+        reloaded = (out.numpy().copy(), int(exp), [l.weight.cpu().numpy().tobytes() for l in model.weighted_layers()])
+        q.put((rank, lo, hi, logits, final_w, bucket_clear, reloaded))
     finally:
         if tr is not None:
             tr.close()
@@ -65,9 +80,21 @@ def test_peer_memory_update_equals_summed_gradient_update():
         p.join(timeout=60)
         assert p.exitcode == 0
     shapes, weights, wexps, batches = _data()
-    spans = sorted((lo, hi) for _, lo, hi, _, _, _ in results)
+    spans = sorted((lo, hi) for _, lo, hi, _, _, _, _ in results)
     want, want_w = dp_oracle.expected(CFG, weights, wexps, batches, spans, SEED)
-    for rank, lo, hi, logits, wbytes, bucket_clear in results:
+    # the step after the reload: the initial weights again, batch 0, but the random bits of step STEPS
+    nets = [O.Net(CFG, weights, wexps, dropout=True, mu=5, seed=SEED) for _ in spans]
+    grads, again = [], {}
+    for net, (lo, hi) in zip(nets, spans):
+        x8, xe = O.float_to_int8(batches[0][0][lo:hi])
+        again[lo] = net.forward(np.ascontiguousarray(x8.transpose(0, 2, 3, 1)), xe, step=STEPS, sample_offset=lo)
+        grads.append(net.backward(batches[0][1][lo:hi], step=STEPS, sample_offset=lo, update=False))
+    summed = {i: sum(np.asarray(g[i], dtype=np.int64) for g in grads) for i in range(len(shapes))}
+    nets[0].apply_grads(summed, step=STEPS)
+    for rank, lo, hi, logits, wbytes, bucket_clear, reloaded in results:
+        assert np.array_equal(reloaded[0], again[lo][0]) and reloaded[1] == again[lo][1], f"rank {rank}: logits after the reload"
+        for i, b in enumerate(reloaded[2]):
+            assert b == nets[0].w[i].tobytes(), f"rank {rank}: weights of layer {i} after the reload"
         assert bucket_clear, f"rank {rank}: the gradient bucket is not zero after the update"
         for step in range(STEPS):
             assert np.array_equal(logits[step][0], want[(step, lo)][0]), f"rank {rank} step {step}: logits"
