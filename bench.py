@@ -538,12 +538,14 @@ def run_ours(args):
                    "how": "graph-replayed device steps back to back, no L2 flush; mean of the second half of the chunks",
                    "clocks": cs, "ms_x_mhz": (sus_ms * cs["sm_mhz"] if cs.get("sm_mhz") else None)}
 
-    redos = {}
+    redos, downs = {}, {}
     for i, l in enumerate(model.weighted_layers()):
         for name in ("_fwd_state", "_bwd_state"):
             stt = getattr(l, name, None)
             if stt is not None:
                 redos[f"conv{i + 1}{name[:4]}"] = int(stt[3].item())
+                if int(stt[2].item()) >> 8:
+                    downs[f"conv{i + 1}{name[:4]}"] = int(stt[2].item()) >> 8
     checksum = trainer.replica_checksum()
     if world > 1:
         cs = torch.tensor([checksum], dtype=torch.int64, device=dev)
@@ -593,6 +595,7 @@ def run_ours(args):
                                         f"sharded over {world} ranks, through the {parity_route}: logits and final weights of every rank "
                                         "equal oracle replicas with summed int32 gradients and one update"),
                        "shift_mispredictions_per_layer_since_start": redos,
+                       "shift_step_downs_per_layer_since_start": downs,
                        "effective_int8_tops": step_ops_per_image(cfg) * images / dev_s / 1e12},
             "e2e": {"value": images / e2e_s, "unit": UNIT, "h2d_bytes_per_step": trainer.h2d_bytes,
                     "d2h_bytes_per_step": trainer.d2h_bytes, "ms_per_step": e2e_s / args.steps * 1e3},

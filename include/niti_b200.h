@@ -187,7 +187,7 @@ NITI_API int niti_conv_wgrad_builtin_scratch_i8(const int8_t* x, const int8_t* e
  * still receives the shift; state[2] stays 0).
  *   state: device int32[8], 8-byte aligned, owned by the caller, one per layer and direction, zeroed once:
  *          [0] shift (in: prediction, out: true value), [1] max|acc| (zero between calls), [2] 1 if
- *          the last call had to redo, [3] number of redos so far, [4] block ticket, [5..7] grid-barrier
+ *          the last call had to redo (bits 0-1; see niti_conv_dgrad_requant_side_i8), [3] number of redos so far, [4] block ticket, [5..7] grid-barrier
  *          words of the single-launch kernel (all zero between calls).
  *   kind is ACT for fprop (exp_out = shift + *exp_a + *exp_b) and ERR for dgrad; target 7 bits.
  * Shapes: niti_conv_*_requant_supported() != 0 (the tensor-core shapes of the entry points above
@@ -211,6 +211,25 @@ NITI_API int niti_conv_dgrad_requant_i8(const int8_t* err, const int8_t* w, int8
  * the ReLU in front of it.  Where it is <= 0 the error is zeroed: TiReLU.backward (ti_torch.py:279-290) folded into
  * the kernel.  The mask is applied after the requantisation, so the shift is that of the unmasked error, exactly as
  * when the two run one after the other. */
+
+/* niti_conv_dgrad_requant_i8 with `side`, niti_conv_dgrad_requant_side_bytes() bytes of caller-owned device memory
+ * (16-byte aligned, contents irrelevant) that belongs to the layer like `state`.  A layer whose max |error| hovers
+ * around a power of two needs shift S in some steps and S - 1 in others, and every wrong guess costs a second
+ * contraction.  With `side` the first launch (round-to-nearest only) also stores bits S-1 and S-2 of every rounded
+ * sum, 2 bits per output; when the true shift turns out to be S - 1 the second launch rewrites the int8 output from
+ * them (exactly: sign(x) * ((|x| + 2^(S-2)) >> (S-1)) follows from x's value at shift S and those two bits) instead of
+ * contracting again, and the guess stays S until the lower shift has applied 12 times in a row.  state[2] then
+ * reads: bits 0-1 = 0 right / 1 contracted again / 2 stepped down, bits 4-7 = step-downs in a row, bits 8-31 = step-downs so
+ * far; state[3] counts second contractions only.  niti_conv_dgrad_requant_side_bytes returns 0 when the single-launch
+ * kernel serves the shape (nothing is predicted there); side may be null (= niti_conv_dgrad_requant_i8).  No counterpart in
+ * the reference. */
+NITI_API size_t niti_conv_dgrad_requant_side_bytes(int N, int H, int W, int C, int K, int R, int S, int pad);
+NITI_API int niti_conv_dgrad_requant_side_i8(const int8_t* err, const int8_t* w, int8_t* e8, int32_t* state,
+                       void* side, size_t side_bytes,
+                       int N, int H, int W, int C, int K, int R, int S, int pad,
+                       int round_mode, const uint64_t* seed, uint32_t rng_stream, uint64_t rng_offset,
+                       const int32_t* exp_a, const int32_t* exp_b, int32_t* exp_out, int32_t* shift_out,
+                       const int8_t* relu_mask, int32_t* status, void* stream);
 
 /* niti_conv_fprop_requant_i8 that ALSO writes the 2x2 / stride-2 max-pooled output, y8_pooled [N][H/2][W/2][K]:
  * TiConv2d.forward + TiReLU.forward + TiMaxpool2d.forward (ti_torch.py:391-397, 268-277, 302-307;

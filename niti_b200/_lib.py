@@ -34,6 +34,8 @@ SIGNATURES = {
     "niti_conv_fprop_requant_pool_supported": (_i, [_i] * 8),
     "niti_conv_fprop_requant_pool_i8": (_i, [_p, _p, _p, _p, _p] + [_i] * 8 + [_i, _p, _u32, _u64, _i, _p, _p, _p, _p, _p, _p]),
     "niti_conv_dgrad_requant_i8": (_i, [_p, _p, _p, _p] + [_i] * 8 + [_i, _p, _u32, _u64, _p, _p, _p, _p, _p, _p, _p]),
+    "niti_conv_dgrad_requant_side_bytes": (_sz, [_i] * 8),
+    "niti_conv_dgrad_requant_side_i8": (_i, [_p, _p, _p, _p, _p, _sz] + [_i] * 8 + [_i, _p, _u32, _u64, _p, _p, _p, _p, _p, _p, _p]),
     "niti_conv_dgrad_i8": (_i, [_p, _p, _p, _p] + [_i] * 8 + [_p, _p]),
     "niti_conv_wgrad_scratch_bytes": (_sz, [_i] * 7),
     "niti_conv_wgrad_i8": (_i, [_p, _p, _p, _p, _p, _sz] + [_i] * 8 + [_p, _p]),

@@ -258,9 +258,9 @@ static int fused_conv(const int8_t* in, const int8_t* w, int8_t* out8, int32_t* 
                       int N, int H, int W, int C, int K, int R, int S, int pad, int flip, int kind, int round_mode,
                       const uint64_t* seed, uint32_t rng_stream, uint64_t rng_offset, int relu, const int32_t* exp_a,
                       const int32_t* exp_b, int32_t* exp_out, int32_t* shift_out, int32_t* status, cudaStream_t st,
-                      const int8_t* relu_mask = nullptr, int8_t* pool_out = nullptr) {
+                      const int8_t* relu_mask = nullptr, int8_t* pool_out = nullptr, void* side = nullptr) {
     FusedArgs f{state, 0, 0, round_mode, relu, reinterpret_cast<const unsigned long long*>(seed), rng_stream, rng_offset,
-                kind, 7, exp_a, exp_b, exp_out, shift_out, relu_mask, pool_out};
+                kind, 7, exp_a, exp_b, exp_out, shift_out, relu_mask, pool_out, side};
     const bool thin = !flip && fprop_path(C, K, R, S, pad) == CONV_THIN;
     const size_t m = static_cast<size_t>(N) * H * W;
     int8_t* xcol = static_cast<int8_t*>(scratch);
@@ -336,6 +336,27 @@ extern "C" int niti_conv_dgrad_requant_i8(const int8_t* err, const int8_t* w, in
     if (!niti_conv_dgrad_requant_supported(C, K, R, S, pad)) return NITI_ERR_UNSUPPORTED;
     return fused_conv(err, w, e8, state, nullptr, 0, N, H, W, C, K, R, S, pad, 1, NITI_CALC_ERR, round_mode, seed, rng_stream,
                       rng_offset, 0, exp_a, exp_b, exp_out, shift_out, status, static_cast<cudaStream_t>(stream), relu_mask);
+}
+
+extern "C" size_t niti_conv_dgrad_requant_side_bytes(int N, int H, int W, int C, int K, int R, int S, int pad) {
+    if (N <= 0 || H <= 0 || W <= 0 || !niti_conv_dgrad_requant_supported(C, K, R, S, pad)) return 0;
+    if (g_opt_parking && umma_conv_fits_parked(N, H, W, C, 1)) return 0;  // exact in one launch: nothing to predict
+    return static_cast<size_t>(N) * H * W * C / 4;
+}
+
+extern "C" int niti_conv_dgrad_requant_side_i8(const int8_t* err, const int8_t* w, int8_t* e8, int32_t* state, void* side,
+                                               size_t side_bytes, int N, int H, int W, int C, int K, int R, int S, int pad,
+                                               int round_mode, const uint64_t* seed, uint32_t rng_stream, uint64_t rng_offset,
+                                               const int32_t* exp_a, const int32_t* exp_b, int32_t* exp_out, int32_t* shift_out,
+                                               const int8_t* relu_mask, int32_t* status, void* stream) {
+    NITI_REQUIRE(err && w && e8 && state && N > 0 && H > 0 && W > 0 && C > 0 && K > 0 && R > 0 && S > 0 && pad >= 0);
+    NITI_REQUIRE(round_mode >= 0 && round_mode <= 2 && (seed || round_mode != NITI_ROUND_STOCHASTIC));
+    NITI_REQUIRE(aligned16(err) && aligned16(w) && aligned16(e8) && aligned16(relu_mask) && reinterpret_cast<uintptr_t>(state) % 8 == 0);
+    if (!niti_conv_dgrad_requant_supported(C, K, R, S, pad)) return NITI_ERR_UNSUPPORTED;
+    if (side != nullptr && (!aligned16(side) || side_bytes < static_cast<size_t>(N) * H * W * C / 4)) return NITI_ERR_SCRATCH;
+    return fused_conv(err, w, e8, state, nullptr, 0, N, H, W, C, K, R, S, pad, 1, NITI_CALC_ERR, round_mode, seed, rng_stream,
+                      rng_offset, 0, exp_a, exp_b, exp_out, shift_out, status, static_cast<cudaStream_t>(stream), relu_mask,
+                      nullptr, side);
 }
 
 // ---------------------------------------------------------------- weight gradient without caller scratch

@@ -24,6 +24,7 @@ struct FusedArgs {
     const int32_t* exp_a; const int32_t* exp_b; int32_t* exp_out; int32_t* shift_out;
     const int8_t* relu_mask;  // optional, same shape as the output: zero the output where this tensor is <= 0
     int8_t* pool_out;         // optional (forward, parked kernel): 2x2 / stride-2 max-pooled copy of the output
+    void* side;               // optional (streaming kernel, round-to-nearest, no ReLU): outputs / 4 bytes of side codes
 };
 
 extern int g_two_cta;    // CTA pairs (cta_group::2) where the shape allows: bit 0 for GEMMs, bit 1 for convolutions

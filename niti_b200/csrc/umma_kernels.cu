@@ -101,12 +101,15 @@ struct GemmParams {
     int8_t* out8;          // fused kernels: the int8 output as a plain pointer (rows = row_lin, pitch N bytes)
     const int8_t* mask;    // fused kernels: optional ReLU-backward mask, same shape as the output (zero where mask <= 0)
     int8_t* pool_out;      // parked kernel, forward convolutions: optional 2x2 / stride-2 max-pooled copy of the output [N][H/2][W/2][K]
+    uint32_t* side;        // streaming fused kernel, round-to-nearest without ReLU: two more bits per output (16 per word, rows of
+                           // N / 4 bytes) from which the output for the next LOWER shift follows exactly (requant_step_down)
     const unsigned long long* seed;
     unsigned rng_stream;
     unsigned long long rng_offset;
 };
 
 constexpr int GEMM_THREADS = 320;  // producer warp, MMA warp, two epilogue warpgroups of 4 warps
+constexpr unsigned STEP_DOWN_RUN = 12;  // step-downs in a row after which the predicted shift is lowered (< 16)
 
 template <int BN, bool FUSED, bool TWO = false>
 struct GemmCfg {
@@ -164,6 +167,79 @@ __device__ __forceinline__ uint32_t narrow4(const uint32_t* v, int shift, int mo
         w |= static_cast<uint32_t>(static_cast<uint8_t>(y)) << (8 * j);
     }
     return w;
+}
+
+// Round-to-nearest narrowing of 16 values (one 16-byte piece of an output row) with shift S >= 2 that also keeps bits
+// S-1 and S-2 of the rounded-up sum: with u = x + 2^(S-1) - (x < 0), T = u >> (S-2) = 4 * (u >> S) + code, and the value
+// for shift S - 1, sign(x) * ((|x| + 2^(S-2)) >> (S-1)), is 2 * (u >> S) + (code == 3) - (code == 0) for either sign.
+// The code of byte j of word q sits at bit 8 j + 2 q of the piece's code word.
+__device__ __forceinline__ uint32_t narrow16_nearest_codes(const uint32_t* v, int shift2, int half, uint32_t* packed) {
+    uint32_t codes = 0;
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+        int y[4], t[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int x = static_cast<int>(v[4 * q + j]);
+            t[j] = (x + half + (x >> 31)) >> shift2;
+            y[j] = t[j] >> 2;
+        }
+        packed[q] = __vmaxs4(pack2_sat_s8(y[1], y[0], pack2_sat_s8(y[3], y[2], 0u)), 0x81818181u);
+        // the low bytes of the four t side by side, their two low bits moved to this word's place in every byte
+        const uint32_t low = __byte_perm(__byte_perm(t[0], t[1], 0x0040), __byte_perm(t[2], t[3], 0x0040), 0x5410);
+        codes |= (low & 0x03030303u) << (2 * q);
+    }
+    return codes;
+}
+// Four outputs narrowed with shift S (one word) and their codes (bits 0-1 of each byte of e) -> the four outputs for
+// shift S - 1, clamped to +-127.  Two 16-bit lanes per register, biased by 128 so that plain 32-bit arithmetic cannot
+// borrow between lanes; the lane-wise add + min / max are single instructions.
+__device__ __forceinline__ uint32_t step_down4(uint32_t y4, uint32_t e) {
+    const uint32_t e1 = e >> 1;
+    const uint32_t eq3 = e & e1;                       // bit 0 of a byte: code == 3
+    const uint32_t eq0 = ~(e | e1) & 0x01010101u;      // code == 0
+    const uint32_t dd = eq3 + 0x01010101u - eq0;       // d + 1 in {0, 1, 2} per byte
+    const uint32_t yb = y4 ^ 0x80808080u;              // y + 128 per byte
+    uint32_t la = (yb & 0x00FF00FFu) * 2u + (dd & 0x00FF00FFu);                // bytes 0, 2: 2 y + d + 257
+    uint32_t lb = ((yb >> 8) & 0x00FF00FFu) * 2u + ((dd >> 8) & 0x00FF00FFu);  // bytes 1, 3
+    la = __viaddmax_s16x2(__viaddmin_s16x2(la, 0xFFFFFFFFu, 0x017F017Fu), 0u, 0x00810081u);  // clamp(2 y + d, +-127) + 256
+    lb = __viaddmax_s16x2(__viaddmin_s16x2(lb, 0xFFFFFFFFu, 0x017F017Fu), 0u, 0x00810081u);
+    return __byte_perm(la, lb, 0x6240);                // the low byte of a lane is the value modulo 256
+}
+// The whole int8 output, narrowed with shift S by the launch before, rewritten for shift S - 1 from the side codes
+// (every thread of the grid takes 16-byte pieces; the ReLU-backward mask is applied again, the codes ignore it).
+__device__ void requant_step_down(int8_t* out8, const uint32_t* side, const int8_t* mask, long long pieces) {
+    constexpr int U = 8;
+    uint4* o = reinterpret_cast<uint4*>(out8);
+    const uint4* m = reinterpret_cast<const uint4*>(mask);
+    const long long step = static_cast<long long>(gridDim.x) * blockDim.x;
+    for (long long i0 = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i0 < pieces; i0 += U * step) {
+        uint4 y[U], k[U];
+        uint32_t c[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const long long i = i0 + u * step;
+            if (i < pieces) {
+                y[u] = __ldcg(o + i);
+                c[u] = __ldcg(side + i);
+                if (mask != nullptr) k[u] = __ldg(m + i);
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const long long i = i0 + u * step;
+            if (i < pieces) {
+                uint4 r;
+                r.x = step_down4(y[u].x, c[u] & 0x03030303u); r.y = step_down4(y[u].y, (c[u] >> 2) & 0x03030303u);
+                r.z = step_down4(y[u].z, (c[u] >> 4) & 0x03030303u); r.w = step_down4(y[u].w, (c[u] >> 6) & 0x03030303u);
+                if (mask != nullptr) {
+                    r.x &= __vcmpgts4(k[u].x, 0); r.y &= __vcmpgts4(k[u].y, 0);
+                    r.z &= __vcmpgts4(k[u].z, 0); r.w &= __vcmpgts4(k[u].w, 0);
+                }
+                o[i] = r;
+            }
+        }
+    }
 }
 
 // Output tile (row tile, column tile) of the mn-th tile in launch order.  Convolutions: row-major (the few column
@@ -564,7 +640,14 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                  const __grid_constant__ CUtensorMap tmC, const GemmParams p) {
     using Cfg = GemmCfg<BN, FUSED, TWO>;
     constexpr int STAGES = Cfg::STAGES;
-    if (FUSED && p.only_if_redo && p.state[2] == 0) return;  // prediction was right: nothing to redo
+    if (FUSED && p.only_if_redo) {
+        const int verdict = p.state[2] & 3;
+        if (verdict == 0) return;  // the prediction was right: nothing to redo
+        if (verdict == 2) {        // one bit too many was shifted out and the side codes hold what is missing
+            requant_step_down(p.out8, p.side, p.mask, static_cast<long long>(p.M) * p.N / 16);
+            return;
+        }
+    }
 
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -639,6 +722,8 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             if (p.mode == ROUND_STOCHASTIC && shift > 0) seed = *p.seed;
         }
         const bool fast = FUSED && p.mode == ROUND_NEAREST && shift > 0;
+        // a first launch also keeps what the next lower shift would need (see narrow16_nearest_codes)
+        const bool with_codes = fast && shift >= 2 && !p.relu && p.side != nullptr && !p.only_if_redo;
         const int half = shift > 0 ? 1 << (shift - 1) : 0;
         int vmax[4] = {0, 0, 0, 0}, vmin[4] = {0, 0, 0, 0};
         const int tile_step = p.split_cols ? cta_step : 2 * cta_step;
@@ -713,7 +798,26 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                 }
                 if constexpr (FUSED) {
                     uint32_t packed[32];
-                    if (fast) {
+                    if (with_codes) {
+                        uint32_t codes[8];
+#pragma unroll
+                        for (int j = 0; j < 4; ++j)
+#pragma unroll
+                            for (int i = 0; i < 32; i += 16) {
+                                codes[j * 2 + (i >> 4)] = narrow16_nearest_codes(&v[j][i], shift - 2, half, &packed[j * 8 + (i >> 2)]);
+                            }
+                        if (valid) {  // a row's codes are 32 consecutive bytes, the rows of a tile mostly consecutive: plain stores
+                            uint32_t* srow = p.side + ((row_lin * p.N + col0 + g0) >> 4);
+                            if (lim >= 128 && (p.N & 63) == 0) {  // rows of N / 4 bytes: 16-byte aligned when N is a multiple of 64
+                                reinterpret_cast<uint4*>(srow)[0] = make_uint4(codes[0], codes[1], codes[2], codes[3]);
+                                reinterpret_cast<uint4*>(srow)[1] = make_uint4(codes[4], codes[5], codes[6], codes[7]);
+                            } else {
+#pragma unroll
+                                for (int k = 0; k < 8; ++k)
+                                    if (16 * k + 16 <= lim) srow[k] = codes[k];
+                            }
+                        }
+                    } else if (fast) {
                         if (p.relu) {
 #pragma unroll
                             for (int j = 0; j < 4; ++j)
@@ -802,10 +906,28 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                     bool zero_out;
                     const unsigned m = static_cast<unsigned>(atomicMax(reinterpret_cast<unsigned*>(&st[1]), 0u));
                     const int true_shift = shift_for(m, p.kind, p.target_bits, &zero_out);
-                    const int redo = true_shift != st[0];
-                    st[2] = redo;
-                    st[3] += redo;
-                    st[0] = true_shift;
+                    // st[2] = verdict (0 right, 1 launch again, 2 step the output down one shift from the side codes)
+                    //         | run of step-downs << 4 | step-downs so far << 8
+                    const int pred = st[0];
+                    const unsigned old = static_cast<unsigned>(st[2]);
+                    unsigned run = (old >> 4) & 15u, downs = old >> 8;
+                    int verdict = 0;
+                    if (true_shift == pred) {
+                        run = 0;
+                    } else if (p.side != nullptr && p.mode == ROUND_NEAREST && !p.relu && pred >= 2 && true_shift == pred - 1) {
+                        // the prediction stays: a layer whose maximum hovers around a power of two keeps the upper
+                        // shift as its guess and pays the cheap pass when the lower one applies; after
+                        // STEP_DOWN_RUN lower ones in a row the guess follows
+                        verdict = 2;
+                        ++downs;
+                        if (++run >= STEP_DOWN_RUN) { run = 0; st[0] = true_shift; }
+                    } else {
+                        verdict = 1;
+                        run = 0;
+                        st[3] += 1;
+                        st[0] = true_shift;
+                    }
+                    st[2] = static_cast<int>(static_cast<unsigned>(verdict) | (run << 4) | (downs << 8));
                     st[1] = 0;  // ready for the next call
                     st[4] = 0;
                     if (p.exp_out) *p.exp_out = true_shift + (p.exp_a ? *p.exp_a : 0) + (p.exp_b ? *p.exp_b : 0);
@@ -1414,6 +1536,7 @@ static void set_fused(GemmParams* p, const FusedArgs* f) {
     p->mask = f->relu_mask;
     p->pool_out = nullptr;
     p->out8 = nullptr;
+    p->side = static_cast<uint32_t*>(f->side);
     // max|acc| lives in state[1]; a redo launch must leave it alone (the last CTA of the first launch zeroed it)
     p->maxabs = f->only_if_redo ? nullptr : reinterpret_cast<unsigned*>(f->state + 1);
 }

@@ -208,18 +208,26 @@ def conv_fprop_pool_fused(x, w, state, pad=1, mode=ROUND_NEAREST, seed=None, rng
     return y8, yp, exp_out, shift_out
 
 
+def conv_dgrad_side_bytes(N, H, W, C, K, R, S, pad):
+    """Bytes of per-layer side memory conv_dgrad_fused can use for this shape (0: the single-launch kernel serves it)."""
+    return int(lib.niti_conv_dgrad_requant_side_bytes(N, H, W, C, K, R, S, pad))
+
+
 def conv_dgrad_fused(err, w, state, pad=1, mode=ROUND_NEAREST, seed=None, rng_stream=0, rng_offset=0, exp_a=None, exp_b=None,
-                     relu_mask=None):
+                     relu_mask=None, side=None):
     """Error-backward convolution + err_calc in one pass (+ the backward of the ReLU in front of the layer when
-    relu_mask, the layer's forward input, is given).  Returns (int8 [N,H,W,C], exp_out, shift)."""
-    _need_cuda(err, w, state, relu_mask)
+    relu_mask, the layer's forward input, is given).  side: optional uint8 tensor of conv_dgrad_side_bytes() bytes kept
+    with the layer; with it a shift guessed one too high is repaired by a cheap pass instead of a second contraction.
+    Returns (int8 [N,H,W,C], exp_out, shift)."""
+    _need_cuda(err, w, state, relu_mask, side)
     N, H, W, K = err.shape
     K2, R, S, C = w.shape
     e8 = torch.empty((N, H, W, C), dtype=torch.int8, device=err.device)
     exp_out = torch.empty((), dtype=torch.int32, device=err.device)
     shift_out = torch.empty((), dtype=torch.int32, device=err.device)
     _call("niti_conv_dgrad_requant_i8", 2, 2 * N * H * W * K * R * S * C, err.numel() + w.numel() + e8.numel(),
-          lib.niti_conv_dgrad_requant_i8, _p(err), _p(w), _p(e8), _p(state), N, H, W, C, K, R, S, pad, mode, _p(seed),
+          lib.niti_conv_dgrad_requant_side_i8, _p(err), _p(w), _p(e8), _p(state), _p(side), side.numel() if side is not None else 0,
+          N, H, W, C, K, R, S, pad, mode, _p(seed),
           rng_stream, rng_offset, _p(exp_a), _p(exp_b), _p(exp_out), _p(shift_out), _p(relu_mask),
           _p(status_word(err.device)), _st())
     return e8, exp_out, shift_out

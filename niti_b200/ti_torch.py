@@ -331,6 +331,7 @@ class TiConv2d(UpdateWeight):
         # shift predictions of the fused conv + requantisation kernels (forward, error-backward)
         self._fwd_state = None
         self._bwd_state = None
+        self._bwd_side, self._bwd_side_shape = None, None
 
     def forward(self, input):
         self.act, self.act_in_exp = input
@@ -372,11 +373,19 @@ class TiConv2d(UpdateWeight):
             if FUSE_REQUANT and GLOBAL_MAX_GROUP is None and ops.conv_dgrad_fused_supported(C, K, R, S, self.padding):
                 if self._bwd_state is None:
                     self._bwd_state = ops.new_requant_state(err_in.device)
+                n, h, w_ = err_in.shape[:3]
+                if STEP_DOWN_CODES and (self._bwd_side is None or self._bwd_side_shape != (n, h, w_)):
+                    # layers whose output does not fit in tensor memory guess their shift; two more bits per output
+                    # make a guess one too high a cheap repair instead of a second contraction
+                    nbytes = ops.conv_dgrad_side_bytes(n, h, w_, C, K, R, S, self.padding)
+                    self._bwd_side = torch.empty(nbytes, dtype=torch.uint8, device=err_in.device) if nbytes else None
+                    self._bwd_side_shape = (n, h, w_)
                 err_out, self.err_exp, _ = ops.conv_dgrad_fused(err_in, self.weight, self._bwd_state, self.padding,
                                                                 _mode(ERROR_ROUND_METHOD), RNG_SEED(err_in.device),
                                                                 16 * self.layer_id + 1, SAMPLE_OFFSET * per,
                                                                 exp_tensor(self.err_exp, err_in.device), self.weight_exp,
-                                                                relu_mask=self.act if self.relu_backward_fused else None)
+                                                                relu_mask=self.act if self.relu_backward_fused else None,
+                                                                side=self._bwd_side if STEP_DOWN_CODES else None)
             else:
                 acc, mx = ops.conv_dgrad_acc(err_in, self.weight, self.padding)
                 err_out, self.err_exp, _ = _calc(acc, ops.CALC_ERR, BITWIDTH, ERROR_ROUND_METHOD, 16 * self.layer_id + 1,
@@ -435,6 +444,7 @@ GRAD_ROUND_METHOD = PstoShift
 WEIGHT_INIT_METHOD = UniformWeights
 
 FUSE_REQUANT = True    # convolutions narrow to int8 inside their own kernel (predicted shift, verified, redone if wrong)
+STEP_DOWN_CODES = True  # error-backward layers that guess their shift keep two more bits per output (see ops.conv_dgrad_fused)
 FUSE_POOL = True       # conv -> ReLU -> 2x2 pool: the convolution's kernel also writes the pooled tensor where it can
 FUSE_HEAD = True       # TiNet.train_step runs [dropout,] FC, loss, FC backward and update as one kernel
 GRAD_BITWIDTH = 5      # the reference's training loop injects this per epoch (main.py:73-77)

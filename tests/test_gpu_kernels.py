@@ -476,6 +476,55 @@ def test_conv_dgrad_fused_applies_relu_mask(N, H, W, C, K, parking):
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("N,H,W,C,K,masked", [(3, 16, 16, 128, 64, False), (2, 8, 8, 48, 144, True), (5, 32, 32, 16, 32, True),
+                                              (1, 4, 4, 272, 16, False)])
+def test_conv_dgrad_fused_steps_down_one_shift_from_side_codes(N, H, W, C, K, masked):
+    """The streaming kernel narrows with the shift it guessed.  With side memory a guess ONE too high is repaired from
+    two extra bits per output instead of a second contraction: state[2] reads 2 (not 1), state[3] (second contractions)
+    does not grow, the guess stays, and the output is the oracle's for the true shift.  After 12 step-downs in a row the
+    guess follows."""
+    rng = np.random.default_rng(N * 131 + C)
+    w = rnd8(rng, (K, 3, 3, C))
+    big = rnd8(rng, (N, H, W, K))
+    small = (big.astype(np.int32) // 2).astype(np.int8)  # every sum about half as large: one bit less
+    x = np.maximum(rnd8(rng, (N, H, W, C)), 0)
+    mask = cu(x) if masked else None
+    want = {}
+    for name, e in (("big", big), ("small", small)):
+        y, sft = O.err_calc(O.conv_dgrad(e, w, 1))
+        want[name] = (np.where(x > 0, y, 0).astype(np.int8) if masked else y, sft)
+    assert want["small"][1] == want["big"][1] - 1 and want["small"][1] >= 1
+    old = ops.set_accumulator_parking(False)
+    try:
+        nbytes = ops.conv_dgrad_side_bytes(N, H, W, C, K, 3, 3, 1)
+        assert nbytes == N * H * W * C // 4
+        side = torch.full((nbytes,), 0xA5, dtype=torch.uint8, device=DEV)
+        ea = torch.zeros((), dtype=torch.int32, device=DEV)
+        st = ops.new_requant_state(DEV)
+
+        def run(name):
+            got, _, shift = ops.conv_dgrad_fused(cu(big if name == "big" else small), cu(w), st, 1, 0, None, 0, 0, ea, ea,
+                                                 relu_mask=mask, side=side)
+            assert int(shift) == want[name][1]
+            assert_same(got, want[name][0], f"dgrad + requant ({name})")
+            v = st.tolist()
+            return v[0], v[2] & 3, (v[2] >> 4) & 15, v[2] >> 8, v[3]
+
+        S = want["big"][1]
+        assert run("big") == (S, 1, 0, 0, 1)        # guess 0: contracted again
+        assert run("big") == (S, 0, 0, 0, 1)        # right
+        assert run("small") == (S, 2, 1, 1, 1)      # one too high: stepped down, the guess stays
+        assert run("big") == (S, 0, 0, 1, 1)
+        for i in range(11):
+            assert run("small") == (S, 2, i + 1, i + 2, 1)
+        assert run("small") == (S - 1, 2, 0, 13, 1)  # the twelfth in a row: the guess follows
+        assert run("small") == (S - 1, 0, 0, 13, 1)
+        assert run("big") == (S, 1, 0, 13, 2)        # one too LOW cannot be repaired: contracted again
+    finally:
+        ops.set_accumulator_parking(old)
+
+
+@pytest.mark.gpu
 def test_bounded_grid_barrier_gives_up_and_reports():
     """A grid barrier that cannot be met (one block, two expected) returns after its 0.5 s limit with a status code;
     nothing traps or hangs and the device keeps working afterwards."""
