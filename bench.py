@@ -709,11 +709,47 @@ def make_case(name, shape):
     raise SystemExit(f"unknown case {name}")
 
 
+def run_step_down_case(shape):
+    """Error-backward + requantisation of one layer when the shift guess is right, one too high every call, and
+    alternately right / one too high, without and with the per-layer side buffer: microseconds per call (both launches)."""
+    import torch
+    from niti_b200 import ops
+    dev = torch.device("cuda", 0)
+    N, H, W, C, K = shape
+    g = torch.Generator().manual_seed(7)
+    w = torch.randint(-127, 128, (K, 3, 3, C), dtype=torch.int8, generator=g).to(dev)
+    big = torch.randint(-127, 128, (N, H, W, K), dtype=torch.int8, generator=g).to(dev)
+    small = (big.int() // 2).to(torch.int8)          # every sum about half as large: one bit less
+    mask = torch.randint(-127, 128, (N, H, W, C), dtype=torch.int8, generator=g).to(dev).clamp_(min=0)
+    ea = torch.zeros((), dtype=torch.int32, device=dev)
+    out = {"case": "dgrad_step_down", "shape": shape}
+    for use_side in (False, True):
+        st = ops.new_requant_state(dev)
+        nbytes = ops.conv_dgrad_side_bytes(N, H, W, C, K, 3, 3, 1)
+        side = torch.empty(nbytes, dtype=torch.uint8, device=dev) if use_side and nbytes else None
+
+        def f(e):
+            return ops.conv_dgrad_fused(e, w, st, 1, 0, None, 0, 0, ea, ea, relu_mask=mask, side=side)
+        for _ in range(3):
+            f(big)
+        key = "with_side" if use_side else "without_side"
+        out[key] = {"right_us": time_graph(lambda: f(big)) * 1e6}
+        f(big)
+        # every second call is one shift below the guess: repaired with the side buffer, contracted again without it
+        # (there the guess follows the last value, so both calls of a pair miss)
+        out[key]["alternating_us"] = time_graph(lambda: (f(big), f(small))) * 1e6 / 2
+        out[key]["verdict_of_last_call"] = int(st[2].item()) & 3
+    ops.check_status("cuda:0")
+    print(json.dumps(out))
+
+
 def run_case(args):
     import torch
     from niti_b200 import ops
     torch.cuda.set_device(0)
     shape = tuple(int(v) for v in args.shape.split(","))
+    if args.case == "dgrad_step_down":
+        return run_step_down_case(shape)
     fn, aops, abytes = make_case(args.case, shape)
     if args.plain_launches:
         for _ in range(args.plain_launches):  # eager launches only: what a profiler should see
@@ -765,6 +801,8 @@ def main():
     ap.add_argument("--sustained-s", type=float, default=2.0, help="seconds of back-to-back steps after the timed regions (0: skip)")
     ap.add_argument("--no-parity-check", action="store_true", help="N > 1: skip the oracle check of the exchange route")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-step-down-codes", action="store_true",
+                    help="ablation: error-backward layers that guess their shift contract again on every wrong guess")
     ap.add_argument("--exchange", default="auto", choices=["auto", "nccl"],
                     help="N>1: 'auto' = the peer-memory update kernel when the ranks share a node, else NCCL; 'nccl' = all-reduce")
     ap.add_argument("--case", help="time one kernel case instead of the training step (see make_case; 'train_step' with "
@@ -777,6 +815,9 @@ def main():
         return run_case(args)
     if args.sweep:
         return run_sweep(args)
+    if args.no_step_down_codes:
+        from niti_b200 import ti_torch
+        ti_torch.STEP_DOWN_CODES = False
     if args.impl == "reference":
         run_reference(args)
     else:
