@@ -140,6 +140,20 @@ NITI_API int niti_conv_wgrad_i8(const int8_t* x, const int8_t* err, int32_t* g32
                        void* scratch, size_t scratch_bytes,
                        int N, int H, int W, int C, int K, int R, int S, int pad,
                        int32_t* status, void* stream);
+
+/* The weight gradient of a thin layer (R*S*C <= 32: the 3-channel first layer) from the patch matrix that the
+ * layer's forward call already built: niti_conv_fprop_i8 / niti_conv_fprop_requant_i8 leave it in the first
+ * N*H*W*32 bytes of THEIR scratch ([pixel][32]: the R*S*C bytes of the pixel's receptive field, zero padded), so a
+ * caller that gives the forward call a scratch buffer of its own and keeps it until the backward pass saves the
+ * second gather (TiConv2d.backward's first-layer branch, ti_torch.py:412-428, rebuilds its operands from the input
+ * every time).  Same result as niti_conv_wgrad_i8 on the layer's input.  scratch:
+ * niti_conv_wgrad_patches_scratch_bytes() bytes (split-reduction partial sums), nothing to zero.
+ * NITI_ERR_UNSUPPORTED for layers that are not thin. */
+NITI_API size_t niti_conv_wgrad_patches_scratch_bytes(int N, int H, int W, int C, int K, int R, int S);
+NITI_API int niti_conv_wgrad_patches_i8(const int8_t* patches, const int8_t* err, int32_t* g32, uint32_t* maxabs,
+                       void* scratch, size_t scratch_bytes,
+                       int N, int H, int W, int C, int K, int R, int S,
+                       int32_t* status, void* stream);
 /* The same contraction ADDED into g32: g32 += sum err * x, with no clearing pass, no scratch and no maximum.
  * The caller has zeroed g32 (niti_update_multi_i8 with clear_gradients does) or keeps the gradient of earlier
  * micro-batches in it.  Tensor-core shapes only (niti_conv_wgrad_accumulate_supported); x, err, g32 16-byte aligned. */

@@ -39,6 +39,8 @@ SIGNATURES = {
     "niti_conv_dgrad_i8": (_i, [_p, _p, _p, _p] + [_i] * 8 + [_p, _p]),
     "niti_conv_wgrad_scratch_bytes": (_sz, [_i] * 7),
     "niti_conv_wgrad_i8": (_i, [_p, _p, _p, _p, _p, _sz] + [_i] * 8 + [_p, _p]),
+    "niti_conv_wgrad_patches_scratch_bytes": (_sz, [_i] * 7),
+    "niti_conv_wgrad_patches_i8": (_i, [_p, _p, _p, _p, _p, _sz] + [_i] * 7 + [_p, _p]),
     "niti_conv_wgrad_builtin_scratch_i8": (_i, [_p, _p, _p, _p] + [_i] * 8 + [_p, _p]),
     "niti_gemm_i8": (_i, [_p, _p, _p, _p] + [_i] * 5 + [_p, _p]),
     "niti_requant_i8": (_i, [_p, _p, _p, _i64, _i, _i, _i, _p, _u32, _u64, _i, _p, _p, _p, _p, _p]),

@@ -138,8 +138,7 @@ extern "C" int niti_conv_fprop_i8(const int8_t* x, const int8_t* w, int32_t* y32
         if (!scratch || !aligned16(scratch) || scratch_bytes < niti_conv_fprop_scratch_bytes(N, H, W, C, K, R, S)) return NITI_ERR_SCRATCH;
         int8_t* xcol = static_cast<int8_t*>(scratch);
         int8_t* wp = xcol + align_up(m * 32, 1024);
-        if (int e = im2col32(x, xcol, N, H, W, C, R, S, pad, st)) return e;
-        if (int e = pad_rows32(w, wp, K, R * S * C, st)) return e;
+        if (int e = im2col32(x, xcol, N, H, W, C, R, S, pad, st, w, wp, K)) return e;
         return umma_gemm(xcol, wp, y32, maxabs, static_cast<int>(m), K, 32, 0, 1, 1, nullptr, status, st);
     }
     return simt_conv_fprop(x, w, y32, maxabs, N, H, W, C, K, R, S, pad, st);
@@ -227,6 +226,29 @@ extern "C" int niti_conv_wgrad_i8(const int8_t* x, const int8_t* err, int32_t* g
     return reduce_rows32(partial, splits, K, R * S * C, g32, maxabs, st);
 }
 
+extern "C" size_t niti_conv_wgrad_patches_scratch_bytes(int N, int H, int W, int C, int K, int R, int S) {
+    if (N <= 0 || H <= 0 || W <= 0 || C <= 0 || K <= 0 || R <= 0 || S <= 0) return 0;
+    if (wgrad_path(C, K, R, S, (R - 1) / 2) != CONV_THIN) return 0;
+    return static_cast<size_t>(umma_gemm_splits(K, 32, static_cast<int>(static_cast<size_t>(N) * H * W))) * K * 32 * 4;
+}
+
+extern "C" int niti_conv_wgrad_patches_i8(const int8_t* patches, const int8_t* err, int32_t* g32, uint32_t* maxabs, void* scratch,
+                                          size_t scratch_bytes, int N, int H, int W, int C, int K, int R, int S,
+                                          int32_t* status, void* stream) {
+    NITI_REQUIRE(patches && err && g32 && N > 0 && H > 0 && W > 0 && C > 0 && K > 0 && R > 0 && S > 0);
+    NITI_REQUIRE(aligned16(patches) && aligned16(err) && aligned16(g32));
+    if (wgrad_path(C, K, R, S, (R - 1) / 2) != CONV_THIN) return NITI_ERR_UNSUPPORTED;
+    if (!scratch || !aligned16(scratch) || scratch_bytes < niti_conv_wgrad_patches_scratch_bytes(N, H, W, C, K, R, S)) return NITI_ERR_SCRATCH;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (maxabs != nullptr)
+        if (int e = clear_word(maxabs, st)) return e;
+    const size_t m = static_cast<size_t>(N) * H * W;
+    const int splits = umma_gemm_splits(K, 32, static_cast<int>(m));
+    int32_t* partial = static_cast<int32_t*>(scratch);
+    if (int e = umma_gemm(err, patches, partial, nullptr, K, 32, static_cast<int>(m), 1, 0, splits, nullptr, status, st)) return e;
+    return reduce_rows32(partial, splits, K, R * S * C, g32, maxabs, st);
+}
+
 extern "C" int niti_conv_wgrad_accumulate_supported(int C, int K, int R, int S, int pad) {
     return wgrad_path(C, K, R, S, pad) == CONV_TC ? 1 : 0;
 }
@@ -267,8 +289,7 @@ static int fused_conv(const int8_t* in, const int8_t* w, int8_t* out8, int32_t* 
     int8_t* wp = thin ? xcol + align_up(m * 32, 1024) : nullptr;
     if (thin) {
         if (!scratch || !aligned16(scratch) || scratch_bytes < niti_conv_fprop_scratch_bytes(N, H, W, C, K, R, S)) return NITI_ERR_SCRATCH;
-        if (int e = im2col32(in, xcol, N, H, W, C, R, S, pad, st)) return e;
-        if (int e = pad_rows32(w, wp, K, R * S * C, st)) return e;
+        if (int e = im2col32(in, xcol, N, H, W, C, R, S, pad, st, w, wp, K)) return e;
     }
     if (pool_out != nullptr && !(g_opt_parking && !thin && !flip && umma_conv_pool_fusable(N, H, W, K))) return NITI_ERR_UNSUPPORTED;
     // Few enough output tiles for every accumulator to stay in tensor memory: one exact launch.

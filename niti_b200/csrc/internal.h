@@ -58,8 +58,9 @@ int simt_gemm(const int8_t* A, const int8_t* B, int32_t* C32, unsigned* maxabs, 
               int trans_b, cudaStream_t st);
 int reduce_partials(const int32_t* partial, int splits, long long n, int32_t* out, unsigned* maxabs, cudaStream_t st);
 int reduce_rows32(const int32_t* partial, int splits, int rows, int cols_out, int32_t* out, unsigned* maxabs, cudaStream_t st);
-int im2col32(const int8_t* x, int8_t* xcol, int Nimg, int H, int W, int C, int R, int S, int pad, cudaStream_t st);
-int pad_rows32(const int8_t* w, int8_t* wp, int K, int rsc, cudaStream_t st);
+// w / wp / K: optionally the layer's filters w[K][R*S*C] are padded to wp[K][32] by the same launch
+int im2col32(const int8_t* x, int8_t* xcol, int Nimg, int H, int W, int C, int R, int S, int pad, cudaStream_t st,
+             const int8_t* w = nullptr, int8_t* wp = nullptr, int K = 0);
 int unpack_i4(const uint8_t* in, int8_t* out, long long nbytes, cudaStream_t st);  // two int4 per byte (low nibble first) -> int8
 
 }  // namespace niti

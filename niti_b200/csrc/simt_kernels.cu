@@ -204,9 +204,16 @@ int reduce_rows32(const int32_t* partial, int splits, int rows, int cols_out, in
 // One thread per pixel: walks the receptive field in (r, s, c) order, packs the bytes into eight
 // words and writes the 32-byte row with two 16-byte stores.
 __global__ void __launch_bounds__(256)
-im2col32_kernel(const int8_t* __restrict__ x, uint4* __restrict__ xcol, int Nimg, int H, int W, int C, int R, int S, int pad) {
+im2col32_kernel(const int8_t* __restrict__ x, uint4* __restrict__ xcol, int Nimg, int H, int W, int C, int R, int S, int pad,
+                const int8_t* __restrict__ w, int8_t* __restrict__ wp, int K) {
     const int rsc = R * S * C;
     const long long pixels = static_cast<long long>(Nimg) * H * W;
+    // the filters of the same layer, w[K][rsc] -> wp[K][32] zero padded, ride along (wp null: not wanted)
+    if (wp != nullptr)
+        for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < K * 32; i += gridDim.x * blockDim.x) {
+            const int k = i >> 5, e = i & 31;
+            wp[i] = e < rsc ? w[k * rsc + e] : int8_t(0);
+        }
     for (long long pix = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; pix < pixels;
          pix += static_cast<long long>(gridDim.x) * blockDim.x) {
         const int wq = static_cast<int>(pix % W);
@@ -232,18 +239,11 @@ im2col32_kernel(const int8_t* __restrict__ x, uint4* __restrict__ xcol, int Nimg
         xcol[pix * 2 + 1] = make_uint4(word[4], word[5], word[6], word[7]);
     }
 }
-// w[K][rsc] -> wp[K][32], zero padded
-__global__ void pad_rows32_kernel(const int8_t* __restrict__ w, int8_t* __restrict__ wp, int K, int rsc) {
-    const int i = blockIdx.x * blockDim.x + threadIdx.x;
-    if (i < K * 32) { const int k = i >> 5, e = i & 31; wp[i] = e < rsc ? w[k * rsc + e] : int8_t(0); }
-}
-int im2col32(const int8_t* x, int8_t* xcol, int Nimg, int H, int W, int C, int R, int S, int pad, cudaStream_t st) {
+int im2col32(const int8_t* x, int8_t* xcol, int Nimg, int H, int W, int C, int R, int S, int pad, cudaStream_t st,
+             const int8_t* w, int8_t* wp, int K) {
     const long long total = static_cast<long long>(Nimg) * H * W;
-    im2col32_kernel<<<blocks_for(total, 256, sm_count_simt() * 16), 256, 0, st>>>(x, reinterpret_cast<uint4*>(xcol), Nimg, H, W, C, R, S, pad);
-    return set_cuda_error(cudaGetLastError());
-}
-int pad_rows32(const int8_t* w, int8_t* wp, int K, int rsc, cudaStream_t st) {
-    pad_rows32_kernel<<<(K * 32 + 255) / 256, 256, 0, st>>>(w, wp, K, rsc);
+    im2col32_kernel<<<blocks_for(total, 256, sm_count_simt() * 16), 256, 0, st>>>(x, reinterpret_cast<uint4*>(xcol), Nimg, H, W, C, R, S, pad,
+                                                                                 w, wp, K);
     return set_cuda_error(cudaGetLastError());
 }
 

@@ -106,7 +106,7 @@ def conv_fprop_acc(x, w, pad=1, stride=1):
     mx = torch.empty(1, dtype=torch.int32, device=x.device)
     nbytes = lib.niti_conv_fprop_scratch_bytes(N, H, W, C, K, R, S)
     sc = scratch(x.device, nbytes) if nbytes else None
-    _call("niti_conv_fprop_i8", 3 if nbytes else 1, 2 * N * P * Q * K * R * S * C, x.numel() + w.numel() + 4 * y32.numel(),
+    _call("niti_conv_fprop_i8", 2 if nbytes else 1, 2 * N * P * Q * K * R * S * C, x.numel() + w.numel() + 4 * y32.numel(),
           lib.niti_conv_fprop_i8, _p(x), _p(w), _p(y32), _p(mx), _p(sc), sc.numel() if nbytes else 0,
           N, H, W, C, K, R, S, pad, stride, _p(status_word(x.device)), _st())
     return y32, mx
@@ -168,18 +168,25 @@ def conv_dgrad_fused_supported(C, K, R, S, pad):
     return bool(lib.niti_conv_dgrad_requant_supported(C, K, R, S, pad))
 
 
+def conv_fprop_scratch_bytes(N, H, W, C, K, R, S):
+    """Scratch bytes of a forward convolution (non-zero for thin layers: their patch matrix [N*H*W][32] + padded filters)."""
+    return int(lib.niti_conv_fprop_scratch_bytes(N, H, W, C, K, R, S))
+
+
 def conv_fprop_fused(x, w, state, pad=1, mode=ROUND_NEAREST, seed=None, rng_stream=0, rng_offset=0, relu=False,
-                     exp_a=None, exp_b=None):
-    """Convolution + act_calc in one pass.  Returns (int8 [N,H,W,K], exp_out, shift)."""
-    _need_cuda(x, w, state)
+                     exp_a=None, exp_b=None, scratch_buf=None):
+    """Convolution + act_calc in one pass.  Returns (int8 [N,H,W,K], exp_out, shift).  scratch_buf: a uint8 tensor of
+    conv_fprop_scratch_bytes() bytes owned by the caller instead of the shared scratch; a thin layer's patch matrix
+    then survives in its first N*H*W*32 bytes for conv_wgrad_from_patches."""
+    _need_cuda(x, w, state, scratch_buf)
     N, H, W, C = x.shape
     K, R, S, _ = w.shape
     y8 = torch.empty((N, H, W, K), dtype=torch.int8, device=x.device)
     exp_out = torch.empty((), dtype=torch.int32, device=x.device)
     shift_out = torch.empty((), dtype=torch.int32, device=x.device)
     nbytes = lib.niti_conv_fprop_scratch_bytes(N, H, W, C, K, R, S)
-    sc = scratch(x.device, nbytes) if nbytes else None
-    _call("niti_conv_fprop_requant_i8", 4 if nbytes else 2, 2 * N * H * W * K * R * S * C, x.numel() + w.numel() + y8.numel(),
+    sc = (scratch_buf if scratch_buf is not None else scratch(x.device, nbytes)) if nbytes else None
+    _call("niti_conv_fprop_requant_i8", 3 if nbytes else 2, 2 * N * H * W * K * R * S * C, x.numel() + w.numel() + y8.numel(),
           lib.niti_conv_fprop_requant_i8, _p(x), _p(w), _p(y8), _p(state), _p(sc), sc.numel() if nbytes else 0,
           N, H, W, C, K, R, S, pad, mode, _p(seed), rng_stream, rng_offset, int(relu), _p(exp_a), _p(exp_b),
           _p(exp_out), _p(shift_out), _p(status_word(x.device)), _st())
@@ -259,6 +266,21 @@ def conv_wgrad_acc(x, err, R=3, S=3, pad=1, out=None, want_max=True):
     _call("niti_conv_wgrad_i8", 2 if C % 16 == 0 else 3, 2 * N * H * W * K * R * S * C, x.numel() + err.numel() + 4 * g32.numel(),
           lib.niti_conv_wgrad_i8, _p(x), _p(err), _p(g32), _p(mx), _p(sc), sc.numel(), N, H, W, C, K, R, S, pad,
           _p(status_word(x.device)), _st())
+    return g32, mx
+
+
+def conv_wgrad_from_patches(patches, err, C, R=3, S=3, out=None, want_max=True):
+    """Weight gradient of a thin layer (R*S*C <= 32) from the patch matrix its forward call left in `patches` (see
+    conv_fprop_fused(scratch_buf=...)): same result as conv_wgrad_acc on the layer's input, without gathering again."""
+    _need_cuda(patches, err, out)
+    N, H, W, K = err.shape
+    g32 = out if out is not None else torch.empty((K, R, S, C), dtype=torch.int32, device=err.device)
+    mx = torch.empty(1, dtype=torch.int32, device=err.device) if want_max else None
+    nbytes = lib.niti_conv_wgrad_patches_scratch_bytes(N, H, W, C, K, R, S)
+    sc = scratch(err.device, nbytes)
+    _call("niti_conv_wgrad_patches_i8", 2, 2 * N * H * W * K * R * S * C, N * H * W * 32 + err.numel() + 4 * g32.numel(),
+          lib.niti_conv_wgrad_patches_i8, _p(patches), _p(err), _p(g32), _p(mx), _p(sc), sc.numel(), N, H, W, C, K, R, S,
+          _p(status_word(err.device)), _st())
     return g32, mx
 
 

@@ -332,6 +332,7 @@ class TiConv2d(UpdateWeight):
         self._fwd_state = None
         self._bwd_state = None
         self._bwd_side, self._bwd_side_shape = None, None
+        self._patches, self._patches_of = None, None
 
     def forward(self, input):
         self.act, self.act_in_exp = input
@@ -351,9 +352,19 @@ class TiConv2d(UpdateWeight):
                                                                     exp_tensor(self.act_in_exp, self.act.device), self.weight_exp)
                 pool.precomputed = (out, pooled)
                 return out, exp_out
+            self._patches_of = None
+            if TRAINING and KEEP_PATCHES and self.first_layer:
+                # a thin layer runs as a GEMM over a patch matrix; kept in memory of its own it also serves the weight
+                # gradient of this step (the reference gathers its first-layer operands twice, :412-428)
+                nbytes = ops.conv_fprop_scratch_bytes(*self.act.shape, K, R, S)
+                if nbytes:
+                    if self._patches is None or self._patches.numel() < nbytes or self._patches.device != self.act.device:
+                        self._patches = torch.empty(nbytes, dtype=torch.uint8, device=self.act.device)
+                    self._patches_of = self.act
             out, exp_out, _ = ops.conv_fprop_fused(self.act, self.weight, self._fwd_state, self.padding, _mode(ACT_ROUND_METHOD),
                                                    RNG_SEED(self.act.device), 16 * self.layer_id, SAMPLE_OFFSET * per,
-                                                   self.fuse_relu, exp_tensor(self.act_in_exp, self.act.device), self.weight_exp)
+                                                   self.fuse_relu, exp_tensor(self.act_in_exp, self.act.device), self.weight_exp,
+                                                   scratch_buf=self._patches if self._patches_of is not None else None)
             return out, exp_out
         acc, mx = ops.conv_fprop_acc(self.act, self.weight, self.padding, self.stride)
         return act_calc(acc, self.act_in_exp, mx, 16 * self.layer_id, self.fuse_relu, SAMPLE_OFFSET * per, self.weight_exp)
@@ -406,6 +417,11 @@ class TiConv2d(UpdateWeight):
                 self.grad_int32acc, self.grad_maxabs = self.grad_buffer, None
             else:
                 self.grad_int32acc, self.grad_maxabs = ops.conv_wgrad_accumulate(self.act, err_in, self.grad_buffer, R, S, self.padding), None
+        elif getattr(self, "_patches_of", None) is self.act and self._patches is not None:
+            # the patch matrix of this step's forward pass is still there
+            self.grad_int32acc, self.grad_maxabs = ops.conv_wgrad_from_patches(self._patches, err_in, C, R, S, out=self.grad_buffer,
+                                                                               want_max=not self.defer_update)
+            self._patches_of = None
         else:
             # a deferred update finds max|g| itself (weight_update_all)
             self.grad_int32acc, self.grad_maxabs = ops.conv_wgrad_acc(self.act, err_in, R, S, self.padding, out=self.grad_buffer,
@@ -445,6 +461,7 @@ WEIGHT_INIT_METHOD = UniformWeights
 
 FUSE_REQUANT = True    # convolutions narrow to int8 inside their own kernel (predicted shift, verified, redone if wrong)
 STEP_DOWN_CODES = True  # error-backward layers that guess their shift keep two more bits per output (see ops.conv_dgrad_fused)
+KEEP_PATCHES = True    # the first layer's patch matrix is kept from the forward pass for its weight gradient
 FUSE_POOL = True       # conv -> ReLU -> 2x2 pool: the convolution's kernel also writes the pooled tensor where it can
 FUSE_HEAD = True       # TiNet.train_step runs [dropout,] FC, loss, FC backward and update as one kernel
 GRAD_BITWIDTH = 5      # the reference's training loop injects this per epoch (main.py:73-77)

@@ -525,6 +525,29 @@ def test_conv_dgrad_fused_steps_down_one_shift_from_side_codes(N, H, W, C, K, ma
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("N,H,W,C,K", [(4, 32, 32, 3, 128), (3, 8, 8, 3, 64), (130, 32, 32, 3, 128), (2, 6, 10, 2, 32)])
+def test_first_layer_weight_gradient_from_the_forward_patch_matrix(N, H, W, C, K):
+    """A thin layer's forward call leaves its patch matrix in caller-owned scratch; the weight gradient computed from
+    it equals the oracle's (and the one computed from the input)."""
+    rng = np.random.default_rng(N + 7 * K)
+    x, w, err = rnd8(rng, (N, H, W, C)), rnd8(rng, (K, 3, 3, C)), rnd8(rng, (N, H, W, K))
+    nbytes = ops.conv_fprop_scratch_bytes(N, H, W, C, K, 3, 3)
+    assert nbytes >= N * H * W * 32
+    buf = torch.full((nbytes,), 0x5A, dtype=torch.uint8, device=DEV)
+    ea = torch.zeros((), dtype=torch.int32, device=DEV)
+    st = ops.new_requant_state(DEV)
+    y, _, shift = ops.conv_fprop_fused(cu(x), cu(w), st, 1, 0, None, 0, 0, True, ea, ea, scratch_buf=buf)
+    want_y, s = O.act_calc(O.conv_fprop(x, w, 1), 0)[0], None
+    assert_same(y, np.maximum(want_y, 0).astype(np.int8), "thin forward with caller scratch")
+    g, mx = ops.conv_wgrad_from_patches(buf, cu(err), C)
+    want = O.conv_wgrad(x, err, 3, 3, 1)
+    assert_same(g, want, "weight gradient from patches")
+    assert int(mx) == int(np.abs(want).max())
+    g2, _ = ops.conv_wgrad_acc(cu(x), cu(err), 3, 3, 1)
+    assert torch.equal(g, g2)
+
+
+@pytest.mark.gpu
 def test_bounded_grid_barrier_gives_up_and_reports():
     """A grid barrier that cannot be met (one block, two expected) returns after its 0.5 s limit with a status code;
     nothing traps or hangs and the device keeps working afterwards."""
