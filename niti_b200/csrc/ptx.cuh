@@ -126,6 +126,10 @@ __device__ __forceinline__ bool mbar_wait_uniform(uint32_t bar, uint32_t parity,
 }
 
 // ----------------------------------------------------------------------------- TMA
+// start moving the 128-byte line at p towards the L2 (no register, nothing to wait for)
+__device__ __forceinline__ void prefetch_l2(const void* p) {
+    asm volatile("prefetch.global.L2 [%0];" ::"l"(p));
+}
 __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* m) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(m)) : "memory");
 }

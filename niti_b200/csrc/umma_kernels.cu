@@ -68,6 +68,20 @@ __device__ __forceinline__ void stage_row(uint32_t buf, int row, const uint32_t 
 // ------------------------------------------------------------------------------------------------
 // GEMM / convolution forward / error-backward
 // ------------------------------------------------------------------------------------------------
+// Division of a non-negative int by a divisor fixed at launch: q = (umulhi(mul, n) + n) >> shift with
+// shift = ceil(log2 d) and mul = floor(2^32 (2^shift - d) / d) + 1, exact for 0 <= n < 2^31.  The tile loops turn a
+// tile number into coordinates once per tile; eight hardware-less 32-bit divisions there were a quarter of an epilogue.
+struct FastDiv { unsigned mul, shift; int d; };
+static FastDiv make_fastdiv(int d) {
+    FastDiv f{1u, 0u, d < 1 ? 1 : d};
+    while ((1ull << f.shift) < static_cast<unsigned long long>(f.d)) ++f.shift;
+    f.mul = static_cast<unsigned>(((1ull << 32) * ((1ull << f.shift) - static_cast<unsigned long long>(f.d))) / static_cast<unsigned long long>(f.d) + 1ull);
+    return f;
+}
+__device__ __forceinline__ int fdiv(int n, const FastDiv& f) {
+    return static_cast<int>((__umulhi(f.mul, static_cast<unsigned>(n)) + static_cast<unsigned>(n)) >> f.shift);
+}
+
 struct GemmParams {
     int conv;              // 0: plain GEMM, 1: implicit-GEMM convolution (A tile = 4-D box of pixels)
     int M, N;              // output rows (GEMM rows or pixels) and columns
@@ -82,6 +96,7 @@ struct GemmParams {
     int tapstride;         // elements between consecutive taps in a filter row
     int BW, BH, BI;        // pixels of one tile along w, h and images; BW*BH*BI <= 128
     int tiles_w, tiles_h;
+    FastDiv fd_mn, fd_n, fd_tw, fd_th;  // by m_tiles * n_tiles, n_tiles, tiles_w, tiles_h (set by finish_params)
     int cblocks;           // 128-byte blocks per tap: ceil(reduction channels / 128)
     int red;               // reduction channels per tap (conv) -- the last block of a tap may be partial
     unsigned* maxabs;      // max|acc| is reduced into this word; may be null (split-K partials)
@@ -248,7 +263,7 @@ __device__ void requant_step_down(int8_t* out8, const uint32_t* side, const int8
 // of 2-3 whole rows: a wave then re-reads ~36 MB of operands instead of all of B.  Only when the operands do not fit
 // in L2 anyway (group_m is set on the host): 8192^3 406 -> 376 us, 16384^3 3679 -> 2977 us, 4096^3 unchanged.
 __device__ __forceinline__ void tile_coords(const GemmParams& p, int mn, int* m_pair, int* n_t) {
-    if (p.group_m <= 1) { *m_pair = mn / p.n_tiles; *n_t = mn % p.n_tiles; return; }
+    if (p.group_m <= 1) { *m_pair = fdiv(mn, p.fd_n); *n_t = mn - *m_pair * p.n_tiles; return; }
     const int GM = p.group_m;
     const int per_group = GM * p.n_tiles;
     const int group = mn / per_group, in_group = mn % per_group;
@@ -292,8 +307,8 @@ __device__ __forceinline__ void producer_role(uint8_t* smem, uint64_t* full_bar,
     for (int tile = first; tile < total_tiles; tile += step) {
         int mn = tile, kb_lo = 0, kb_hi = p.num_kb;
         if (p.splits > 1) {
-            const int split = tile / mn_tiles;
-            mn = tile % mn_tiles;
+            const int split = fdiv(tile, p.fd_mn);
+            mn = tile - split * mn_tiles;
             kb_lo = static_cast<int>(static_cast<long long>(split) * p.num_kb / p.splits);
             kb_hi = static_cast<int>(static_cast<long long>(split + 1) * p.num_kb / p.splits);
         }
@@ -301,7 +316,7 @@ __device__ __forceinline__ void producer_role(uint8_t* smem, uint64_t* full_bar,
         tile_coords(p, mn, &m_pair, &n_t);
         const int m_t = TWO ? 2 * m_pair + static_cast<int>(rank) : m_pair;
         int tw = 0, th = 0, tn = 0;
-        if (conv) { tw = m_t % p.tiles_w; th = (m_t / p.tiles_w) % p.tiles_h; tn = m_t / (p.tiles_w * p.tiles_h); }
+        if (conv) { const int q1 = fdiv(m_t, p.fd_tw); tw = m_t - q1 * p.tiles_w; tn = fdiv(q1, p.fd_th); th = q1 - tn * p.tiles_h; }
         const int ncol = n_t * BN + static_cast<int>(rank) * BNH;  // first B column of this CTA
         const int px = tw * p.BW, py = th * p.BH, pn = tn * p.BI;
         // This loop is one warp's serial instruction stream and sets the pace of the whole pipeline: the tap
@@ -728,32 +743,41 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         int vmax[4] = {0, 0, 0, 0}, vmin[4] = {0, 0, 0, 0};
         const int tile_step = p.split_cols ? cta_step : 2 * cta_step;
         int it = p.split_cols ? 0 : grp;
+        // this thread's row inside a tile never changes: pixel offsets within the tile's box
+        int row_w = 0, row_h = 0, row_n = 0;
+        bool row_in_box = true;
+        if (p.conv) {
+            const int t_ = row_in_tile / p.BW;
+            row_w = row_in_tile - t_ * p.BW; row_n = t_ / p.BH; row_h = t_ - row_n * p.BH;
+            row_in_box = row_in_tile < p.BW * p.BH * p.BI;
+        }
         for (int tile = cta_first + (p.split_cols ? 0 : grp * cta_step); tile < total_tiles; tile += tile_step, it += (p.split_cols ? 1 : 2)) {
             const int acc = it & 1; const uint32_t aph = (it >> 1) & 1u;
-            const uint32_t failed = mbar_wait(smem_u32(&tfull_bar[acc]), aph, abort_flag) ? 0u : 1u;
-            if (barrier_or(bar_id, 128, failed)) {  // same verdict in all 128 threads of the warpgroup
-                if (failed) report_abort(p.status, 4, 2);
-                break;
-            }
-            tc_fence_after();
-            const int split = tile / mn_tiles, mn = tile % mn_tiles;
+            // where the tile lies, before waiting for its accumulator: the arithmetic and the first touch of the mask hide in the wait
+            int split = 0, mn = tile;
+            if (p.splits > 1) { split = fdiv(tile, p.fd_mn); mn = tile - split * mn_tiles; }
             int m_pair, n_t;
             tile_coords(p, mn, &m_pair, &n_t);
             const int m_t = TWO ? 2 * m_pair + static_cast<int>(rank) : m_pair;
             bool valid; int cy, cz, cw; long long row_lin;
             if (p.conv) {
-                const int tw = m_t % p.tiles_w, th = (m_t / p.tiles_w) % p.tiles_h, tn = m_t / (p.tiles_w * p.tiles_h);
-                const int w = tw * p.BW + row_in_tile % p.BW;
-                const int h = th * p.BH + (row_in_tile / p.BW) % p.BH;
-                const int n = tn * p.BI + row_in_tile / (p.BW * p.BH);
-                valid = row_in_tile < p.BW * p.BH * p.BI && w < p.W && h < p.H && n < p.Nimg;
+                const int q1 = fdiv(m_t, p.fd_tw), tw = m_t - q1 * p.tiles_w, tn = fdiv(q1, p.fd_th), th = q1 - tn * p.tiles_h;
                 cy = tw * p.BW; cz = th * p.BH; cw = tn * p.BI;
+                const int w = cy + row_w, h = cz + row_h, n = cw + row_n;
+                valid = row_in_box && w < p.W && h < p.H && n < p.Nimg;
                 row_lin = (static_cast<long long>(n) * p.H + h) * p.W + w;
             } else {
                 row_lin = static_cast<long long>(m_t) * BLOCK_M + row_in_tile;
                 valid = row_lin < p.M;
                 cy = m_t * BLOCK_M; cz = split; cw = 0;
             }
+            if (FUSED && p.mask != nullptr && valid) prefetch_l2(p.mask + row_lin * p.N + n_t * BN);
+            const uint32_t failed = mbar_wait(smem_u32(&tfull_bar[acc]), aph, abort_flag) ? 0u : 1u;
+            if (barrier_or(bar_id, 128, failed)) {  // same verdict in all 128 threads of the warpgroup
+                if (failed) report_abort(p.status, 4, 2);
+                break;
+            }
+            tc_fence_after();
             const int col0 = n_t * BN;
             const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(acc * BN);
             // column groups of this warpgroup: all of them, or every other one when the tile is shared
@@ -855,6 +879,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                     fence_proxy_async();
                     named_barrier(bar_id, 128);
                     if (leader) { tma_store_4d(&tmC, buf, col0 + g0, cy, cz, cw); bulk_commit(); }
+
                 } else {
 #pragma unroll
                     for (int half_i = 0; half_i < 2; ++half_i) {
@@ -1526,6 +1551,11 @@ int g_stage_cap = 0;  // 0: use every compiled stage
 // nothing else occupying the SMs, and a barrier that is not met ends in the bounded wait's error status.
 int g_cooperative = 1;
 
+static void finish_params(GemmParams* p) {
+    p->fd_mn = make_fastdiv(p->m_tiles * p->n_tiles); p->fd_n = make_fastdiv(p->n_tiles);
+    p->fd_tw = make_fastdiv(p->tiles_w); p->fd_th = make_fastdiv(p->tiles_h);
+}
+
 static void set_fused(GemmParams* p, const FusedArgs* f) {
     p->nstages = g_stage_cap;
     if (!f) return;
@@ -1592,6 +1622,7 @@ int umma_gemm(const int8_t* A, const int8_t* B, void* out, unsigned* maxabs, int
     // operands beyond ~half of the 126 MB L2: order the tiles in compact groups
     p.group_m = (static_cast<long long>(M) + N) * K > (48ll << 20) ? 8 : 0;
     set_fused(&p, fused);
+    finish_params(&p);
     return launch_gemm(bn, fused != nullptr, pair, ma, mb, mc, p, st);
 }
 
@@ -1637,6 +1668,7 @@ int umma_conv(const int8_t* x, const int8_t* w, void* out, unsigned* maxabs, int
     p.maxabs = maxabs; p.status = status;
     p.split_cols = (bn == 256 && p.m_tiles * p.n_tiles <= 2 * (pair ? sm_count() / 2 : sm_count())) ? 1 : 0;
     set_fused(&p, fused);
+    finish_params(&p);
     if (fused) p.out8 = static_cast<int8_t*>(out);
     if (fused && fused->pool_out != nullptr) {
         if (!parked || flip || !pool_box_ok(H, W, p.BW, p.BH)) return NITI_ERR_UNSUPPORTED;
