@@ -557,14 +557,24 @@ update_multi_kernel(const UpdateMultiParams p) {
     const long long tid = static_cast<long long>(static_cast<int>(blockIdx.x) - p.first_block[l]) * blockDim.x + threadIdx.x;
     const long long groups = it.n >> 2;
     const int4* g4 = reinterpret_cast<const int4*>(it.g32);
-    {   // ---- the layer's maximum: four independent 16-byte loads in flight per thread, one global atomic per block
+    uint32_t* w4 = reinterpret_cast<uint32_t*>(it.w);
+    // The first KEEP word groups of a thread (all of them, with the grid the host picks for VGG-sized layers) stay in
+    // registers from the maximum pass to the update, together with their weights, which do not depend on the maximum:
+    // after the barrier there is arithmetic and stores, no second round trip to memory.
+    constexpr int KEEP = 4;
+    int4 gv[KEEP];
+    uint32_t wv[KEEP];
+    {   // ---- the layer's maximum: the loads of all kept groups go out together, one global atomic per block
         unsigned m = 0;
-        long long g = tid;
-        for (; g + 3 * nthreads < groups; g += 4 * nthreads) {
-            const int4 v0 = g4[g], v1 = g4[g + nthreads], v2 = g4[g + 2 * nthreads], v3 = g4[g + 3 * nthreads];
-            m = max(max(m, absmax4(v0)), max(absmax4(v1), max(absmax4(v2), absmax4(v3))));
+#pragma unroll
+        for (int k = 0; k < KEEP; ++k) {
+            const long long g = tid + k * nthreads;
+            if (g < groups) { gv[k] = g4[g]; wv[k] = w4[g]; }
         }
-        for (; g < groups; g += nthreads) m = max(m, absmax4(g4[g]));
+#pragma unroll
+        for (int k = 0; k < KEEP; ++k)
+            if (tid + k * nthreads < groups) m = max(m, absmax4(gv[k]));
+        for (long long g = tid + KEEP * nthreads; g < groups; g += nthreads) m = max(m, absmax4(g4[g]));
         for (long long i = (groups << 2) + tid; i < it.n; i += nthreads) m = max(m, iabs_u(it.g32[i]));
         block_atomic_max(&umax[l], m);
     }
@@ -576,24 +586,17 @@ update_multi_kernel(const UpdateMultiParams p) {
     const int shift = shift_for(mx, CALC_GRAD, p.mu, &zero_out);
     const bool stochastic = (p.mode == ROUND_STOCHASTIC) && shift > 0;
     const unsigned long long seed = stochastic ? *p.seed : 0ull;
-    uint32_t* w4 = reinterpret_cast<uint32_t*>(it.w);
-    long long g = tid;
-    for (; g + nthreads < groups; g += 2 * nthreads) {  // two groups per iteration: their loads go out together
-        const int4 ga = __ldcs(g4 + g), gb = __ldcs(g4 + g + nthreads);
-        const uint32_t wa = w4[g], wb = w4[g + nthreads];
-        uint32_t ra[4] = {0, 0, 0, 0}, rb[4] = {0, 0, 0, 0};
-        if (stochastic) {
-            random_block(seed, it.rng_stream, static_cast<unsigned long long>(g), ra);
-            random_block(seed, it.rng_stream, static_cast<unsigned long long>(g + nthreads), rb);
-        }
-        w4[g] = update_word(ga, wa, ra, shift, p.mode, zero_out);
-        w4[g + nthreads] = update_word(gb, wb, rb, shift, p.mode, zero_out);
-        if (p.clear) {
-            reinterpret_cast<int4*>(it.g32)[g] = make_int4(0, 0, 0, 0);
-            reinterpret_cast<int4*>(it.g32)[g + nthreads] = make_int4(0, 0, 0, 0);
+#pragma unroll
+    for (int k = 0; k < KEEP; ++k) {
+        const long long g = tid + k * nthreads;
+        if (g < groups) {
+            uint32_t rnd[4] = {0, 0, 0, 0};
+            if (stochastic) random_block(seed, it.rng_stream, static_cast<unsigned long long>(g), rnd);
+            w4[g] = update_word(gv[k], wv[k], rnd, shift, p.mode, zero_out);
+            if (p.clear) reinterpret_cast<int4*>(it.g32)[g] = make_int4(0, 0, 0, 0);
         }
     }
-    for (; g < groups; g += nthreads) {
+    for (long long g = tid + KEEP * nthreads; g < groups; g += nthreads) {
         uint32_t rnd[4] = {0, 0, 0, 0};
         if (stochastic) random_block(seed, it.rng_stream, static_cast<unsigned long long>(g), rnd);
         w4[g] = update_word(__ldcs(g4 + g), w4[g], rnd, shift, p.mode, zero_out);
