@@ -242,11 +242,25 @@ __global__ void __launch_bounds__(HEAD_THREADS, 1) fc_head_kernel(const HeadPara
     }
     __syncthreads();
 
-    // ---- error-backward GEMM, first pass: only max|e32| (the values are recomputed once the shift is known)
+    // ---- error-backward GEMM, first pass: max|e32|.  The chunks of the block's FIRST sample (all there is when the
+    //      batch is not larger than the grid) stay in registers until the shift is known; the rest is recomputed then.
+    constexpr int KEEP_CHUNKS = 2;
+    int ekeep[KEEP_CHUNKS][16];
     {
         unsigned m = 0;
+        if (static_cast<int>(blockIdx.x) < B) {
+#pragma unroll
+            for (int k = 0; k < KEEP_CHUNKS; ++k) {
+                const int c = t + k * HEAD_THREADS;
+                if (c < F16) {
+                    dgrad_chunk(sW, sErr + blockIdx.x * J, J, F16, c, ekeep[k]);
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) m = max(m, iabs32(ekeep[k][i]));
+                }
+            }
+        }
         for (int b = blockIdx.x; b < B; b += G)
-            for (int c = t; c < F16; c += HEAD_THREADS) {
+            for (int c = t + (b == static_cast<int>(blockIdx.x) ? KEEP_CHUNKS * HEAD_THREADS : 0); c < F16; c += HEAD_THREADS) {
                 int e[16];
                 dgrad_chunk(sW, sErr + b * J, J, F16, c, e);
 #pragma unroll
@@ -317,27 +331,38 @@ __global__ void __launch_bounds__(HEAD_THREADS, 1) fc_head_kernel(const HeadPara
         const int shift = shift_for(__ldcg(&umax[1]), CALC_ERR, p.bits, &z);
         if (blockIdx.x == 0 && t == 0) *p.exp_err = shift + exp_w;  // the loss's error has exponent 0
         const bool stochastic = p.err_mode == ROUND_STOCHASTIC && shift > 0;
+        // one 16-feature chunk of sample b: narrow, apply the dropout bits, store
+        auto emit = [&](int b, int c, const int (&e)[16]) {
+            const unsigned long long e0 = (p.sample_offset + b) * static_cast<unsigned long long>(F) + c * 16;
+            uint32_t packed[4];
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                uint32_t rnd[4] = {0, 0, 0, 0};
+                if (stochastic) random_block(seed, p.layer_stream + 1, (e0 >> 2) + q, rnd);
+                uint32_t wd = 0;
+#pragma unroll
+                for (int r = 0; r < 4; ++r)
+                    wd |= static_cast<uint32_t>(static_cast<uint8_t>(narrow(e[q * 4 + r], shift, p.err_mode, rnd[r]))) << (8 * r);
+                packed[q] = wd;
+            }
+            const unsigned bits = sMask[c];
+            uint4 o;
+            o.x = packed[0] & expand4(bits); o.y = packed[1] & expand4(bits >> 4);
+            o.z = packed[2] & expand4(bits >> 8); o.w = packed[3] & expand4(bits >> 12);
+            reinterpret_cast<uint4*>(p.e8)[static_cast<size_t>(b) * F16 + c] = o;
+        };
+        if (static_cast<int>(blockIdx.x) < B) {
+#pragma unroll
+            for (int k = 0; k < KEEP_CHUNKS; ++k) {
+                const int c = t + k * HEAD_THREADS;
+                if (c < F16) emit(blockIdx.x, c, ekeep[k]);
+            }
+        }
         for (int b = blockIdx.x; b < B; b += G)
-            for (int c = t; c < F16; c += HEAD_THREADS) {
+            for (int c = t + (b == static_cast<int>(blockIdx.x) ? KEEP_CHUNKS * HEAD_THREADS : 0); c < F16; c += HEAD_THREADS) {
                 int e[16];
                 dgrad_chunk(sW, sErr + b * J, J, F16, c, e);
-                const unsigned long long e0 = (p.sample_offset + b) * static_cast<unsigned long long>(F) + c * 16;
-                uint32_t packed[4];
-#pragma unroll
-                for (int q = 0; q < 4; ++q) {
-                    uint32_t rnd[4] = {0, 0, 0, 0};
-                    if (stochastic) random_block(seed, p.layer_stream + 1, (e0 >> 2) + q, rnd);
-                    uint32_t wd = 0;
-#pragma unroll
-                    for (int r = 0; r < 4; ++r)
-                        wd |= static_cast<uint32_t>(static_cast<uint8_t>(narrow(e[q * 4 + r], shift, p.err_mode, rnd[r]))) << (8 * r);
-                    packed[q] = wd;
-                }
-                const unsigned bits = sMask[c];
-                uint4 o;
-                o.x = packed[0] & expand4(bits); o.y = packed[1] & expand4(bits >> 4);
-                o.z = packed[2] & expand4(bits >> 8); o.w = packed[3] & expand4(bits >> 12);
-                reinterpret_cast<uint4*>(p.e8)[static_cast<size_t>(b) * F16 + c] = o;
+                emit(b, c, e);
             }
     }
     HEAD_STAMP(9);
