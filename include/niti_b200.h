@@ -162,6 +162,19 @@ NITI_API int niti_conv_wgrad_accumulate_i8(const int8_t* x, const int8_t* err, i
                                   int N, int H, int W, int C, int K, int R, int S, int pad,
                                   int32_t* status, void* stream);
 
+/* niti_conv_wgrad_accumulate_i8 for up to niti_conv_wgrad_accumulate_multi_max() layers in ONE launch: every item's
+ * gradient is added into its g32.  The thread blocks of the launch are dealt to the layers so that each walks about the
+ * same number of pixels, which lets two layers of a step share one wave of the GPU (and one launch, one prologue and
+ * one flush of the accumulators) where each alone would leave its blocks short of work.  Every item must satisfy
+ * niti_conv_wgrad_accumulate_supported; results are those of `count` single calls in any order (integer sums).  No
+ * counterpart in the reference, which computes one layer's gradient at a time (ti_torch.py:429-432). */
+typedef struct niti_wgrad_item {
+    const int8_t* x; const int8_t* err; int32_t* g32;
+    int32_t N, H, W, C, K, R, S, pad;
+} niti_wgrad_item;
+NITI_API int niti_conv_wgrad_accumulate_multi_max(void);
+NITI_API int niti_conv_wgrad_accumulate_multi_i8(const niti_wgrad_item* items, int count, int32_t* status, void* stream);
+
 /* niti_conv_wgrad_i8 for callers that cannot hand over scratch memory.  This entry point has no
  * counterpart in the reference.  Some hosts of this library are not able to call cudaMalloc at all:
  * a plugin inside an application that owns every byte of device memory and offers no allocator, or a

@@ -39,6 +39,8 @@ SIGNATURES = {
     "niti_conv_dgrad_i8": (_i, [_p, _p, _p, _p] + [_i] * 8 + [_p, _p]),
     "niti_conv_wgrad_scratch_bytes": (_sz, [_i] * 7),
     "niti_conv_wgrad_i8": (_i, [_p, _p, _p, _p, _p, _sz] + [_i] * 8 + [_p, _p]),
+    "niti_conv_wgrad_accumulate_multi_max": (_i, []),
+    "niti_conv_wgrad_accumulate_multi_i8": (_i, [_p, _i, _p, _p]),
     "niti_conv_wgrad_patches_scratch_bytes": (_sz, [_i] * 7),
     "niti_conv_wgrad_patches_i8": (_i, [_p, _p, _p, _p, _p, _sz] + [_i] * 7 + [_p, _p]),
     "niti_conv_wgrad_builtin_scratch_i8": (_i, [_p, _p, _p, _p] + [_i] * 8 + [_p, _p]),
@@ -76,6 +78,11 @@ SIGNATURES = {
 class UpdateItem(C.Structure):
     """niti_update_item of include/niti_b200.h"""
     _fields_ = [("w", _p), ("g32", _p), ("maxabs", _p), ("n", _i64), ("rng_stream", _u32)]
+
+
+class WgradItem(C.Structure):
+    """niti_wgrad_item of include/niti_b200.h"""
+    _fields_ = [("x", _p), ("err", _p), ("g32", _p)] + [(n, C.c_int32) for n in ("N", "H", "W", "C", "K", "R", "S", "pad")]
 
 
 class DpItem(C.Structure):

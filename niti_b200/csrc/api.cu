@@ -263,6 +263,22 @@ extern "C" int niti_conv_wgrad_accumulate_i8(const int8_t* x, const int8_t* err,
     return umma_conv_wgrad_partials(x, err, g32, &splits, 0, N, H, W, C, K, R, S, pad, status, static_cast<cudaStream_t>(stream), 1);
 }
 
+extern "C" int niti_conv_wgrad_accumulate_multi_max(void) { return umma_wgrad_multi_max(); }
+
+extern "C" int niti_conv_wgrad_accumulate_multi_i8(const niti_wgrad_item* items, int count, int32_t* status, void* stream) {
+    NITI_REQUIRE(items && count >= 1 && count <= umma_wgrad_multi_max());
+    WgradJob jobs[8];
+    for (int i = 0; i < count; ++i) {
+        const niti_wgrad_item& it = items[i];
+        NITI_REQUIRE(it.x && it.err && it.g32 && it.N > 0 && it.H > 0 && it.W > 0 && it.C > 0 && it.K > 0 && it.R > 0 && it.S > 0 && it.pad >= 0);
+        NITI_REQUIRE(aligned16(it.g32) && aligned16(it.x) && aligned16(it.err));
+        if (it.H + 2 * it.pad - it.R + 1 <= 0 || it.W + 2 * it.pad - it.S + 1 <= 0) return NITI_ERR_BAD_ARG;
+        if (wgrad_path(it.C, it.K, it.R, it.S, it.pad) != CONV_TC) return NITI_ERR_UNSUPPORTED;
+        jobs[i] = WgradJob{it.x, it.err, it.g32, it.N, it.H, it.W, it.C, it.K, it.R, it.S, it.pad};
+    }
+    return umma_conv_wgrad_multi(jobs, count, status, static_cast<cudaStream_t>(stream));
+}
+
 extern "C" int niti_gemm_i8(const int8_t* A, const int8_t* B, int32_t* C32, uint32_t* maxabs, int M, int N, int K,
                             int trans_a, int trans_b, int32_t* status, void* stream) {
     NITI_REQUIRE(A && B && C32 && maxabs && M > 0 && N > 0 && K > 0);

@@ -45,6 +45,10 @@ size_t umma_wgrad_scratch_bytes(int Nimg, int H, int W, int C, int K, int R, int
 int umma_conv_wgrad_partials(const int8_t* x, const int8_t* err, int32_t* partial, int* splits_out, int max_splits,
                              int Nimg, int H, int W, int C, int K, int R, int S, int pad, int32_t* status, cudaStream_t st,
                              int direct = 0);
+// several layers' weight gradients, each ADDED into its g32, in one launch (umma_kernels.cu)
+struct WgradJob { const int8_t* x; const int8_t* err; int32_t* g32; int N, H, W, C, K, R, S, pad; };
+int umma_wgrad_multi_max();
+int umma_conv_wgrad_multi(const WgradJob* jobs, int count, int32_t* status, cudaStream_t st);
 int absmax_i32(const int32_t* acc, long long n, unsigned* maxabs, cudaStream_t st);  // reduces into *maxabs (not cleared)
 
 // CUDA-core paths, simt_kernels.cu

@@ -1246,10 +1246,11 @@ constexpr int WG_STAGES = 3;
 constexpr int WG_SMEM_BYTES = WG_STAGES * WG_STAGE_BYTES + 1024 + 256;
 constexpr int WG_TMEM_COLS = 512;
 
-__global__ void __launch_bounds__(UMMA_THREADS, 1)
-umma_wgrad_kernel(const __grid_constant__ CUtensorMap tmErr, const __grid_constant__ CUtensorMap tmX,
-                  const __grid_constant__ CUtensorMap tmP, const WgradParams p) {
-    if (threadIdx.x == 0 && blockIdx.y == 0) PARK_STAMP(10);
+// One CTA's share of one layer's weight gradient: work item `item` (filter row, k tile, c tile) over the pixel chunks of
+// split `split`.  The tensor maps live in kernel parameter space (grid constants of the calling kernel).
+__device__ __forceinline__ void wgrad_body(const CUtensorMap& tmErr, const CUtensorMap& tmX, const CUtensorMap& tmP,
+                                           const WgradParams& p, const int split, const int item, const bool probe_cta) {
+    if (threadIdx.x == 0 && probe_cta) PARK_STAMP(10);
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + WG_STAGES * WG_STAGE_BYTES);
@@ -1283,10 +1284,8 @@ umma_wgrad_kernel(const __grid_constant__ CUtensorMap tmErr, const __grid_consta
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
-    if (threadIdx.x == 0 && blockIdx.y == 0) PARK_STAMP(11);
+    if (threadIdx.x == 0 && probe_cta) PARK_STAMP(11);
 
-    const int split = blockIdx.x;
-    const int item = blockIdx.y;
     const int r = item % p.R;
     const int kt = (item / p.R) % p.k_tiles;
     const int ct = item / (p.R * p.k_tiles);
@@ -1332,7 +1331,7 @@ umma_wgrad_kernel(const __grid_constant__ CUtensorMap tmErr, const __grid_consta
             bool ready = false;  // the stage's "full" phase was seen complete by the previous chunk's probe
             for (int ch = chunk_lo; ch < chunk_hi; ++ch) {
                 if (!ready && !mbar_wait_uniform(full0 + 8u * s, ph, abort_addr)) { ok = false; *abort_flag = 1; report_abort(p.status, 13, 1); break; }
-                if (ch == chunk_lo && blockIdx.y == 0) PARK_STAMP(12);
+                if (ch == chunk_lo && probe_cta) PARK_STAMP(12);
                 const uint64_t a0 = d0 + ((static_cast<uint32_t>(s) * WG_STAGE_BYTES) >> 4);
                 const uint32_t first = static_cast<uint32_t>(ch != chunk_lo);
                 const int sn = (s + 1 == WG_STAGES) ? 0 : s + 1;
@@ -1364,7 +1363,7 @@ umma_wgrad_kernel(const __grid_constant__ CUtensorMap tmErr, const __grid_consta
                 s = sn; ph = phn;
             }
             if (ok && elect_one()) umma_commit(smem_u32(&tfull_bar[0]));
-            if (blockIdx.y == 0) PARK_STAMP(13);
+            if (probe_cta) PARK_STAMP(13);
         }
         __syncwarp();
     } else {
@@ -1380,7 +1379,7 @@ umma_wgrad_kernel(const __grid_constant__ CUtensorMap tmErr, const __grid_consta
             if (failed) report_abort(p.status, 14, 2);
         } else {
             tc_fence_after();
-            if (leader && blockIdx.y == 0) PARK_STAMP(14);
+            if (leader && probe_cta) PARK_STAMP(14);
             for (int sx = 0; sx < p.S; ++sx) {
                 const uint32_t buf = smem_u32(smem + sx * WG_STAGE_BYTES);
                 uint32_t v[4][32];
@@ -1401,9 +1400,9 @@ umma_wgrad_kernel(const __grid_constant__ CUtensorMap tmErr, const __grid_consta
                     bulk_commit();
                 }
             }
-            if (leader && blockIdx.y == 0) PARK_STAMP(15);
+            if (leader && probe_cta) PARK_STAMP(15);
             if (leader) bulk_wait_read<0>();
-            if (leader && blockIdx.y == 0) PARK_STAMP(16);
+            if (leader && probe_cta) PARK_STAMP(16);
         }
     }
 
@@ -1415,6 +1414,28 @@ umma_wgrad_kernel(const __grid_constant__ CUtensorMap tmErr, const __grid_consta
         __syncwarp();
         tmem_dealloc(tmem_base, WG_TMEM_COLS);
     }
+}
+
+__global__ void __launch_bounds__(UMMA_THREADS, 1)
+umma_wgrad_kernel(const __grid_constant__ CUtensorMap tmErr, const __grid_constant__ CUtensorMap tmX,
+                  const __grid_constant__ CUtensorMap tmP, const __grid_constant__ WgradParams p) {
+    wgrad_body(tmErr, tmX, tmP, p, blockIdx.x, blockIdx.y, blockIdx.y == 0);
+}
+
+// Several layers' weight gradients in ONE launch: CTAs [first_cta[l], first_cta[l + 1]) belong to layer l, split-major
+// inside.  The host picks the splits so that every CTA of the launch walks about the same number of pixel chunks: a
+// step's layers come in pairs of equal work (256->512 and 512->512 at 8x8, ...), which then fill one wave exactly and
+// pay the launch, the prologue and the accumulator flush once instead of twice.
+constexpr int WG_MULTI_MAX = 4;
+struct WgradMultiMaps { CUtensorMap err[WG_MULTI_MAX], x[WG_MULTI_MAX], g[WG_MULTI_MAX]; };
+struct WgradMultiParams { WgradParams layer[WG_MULTI_MAX]; int first_cta[WG_MULTI_MAX + 1]; int count; };
+__global__ void __launch_bounds__(UMMA_THREADS, 1)
+umma_wgrad_multi_kernel(const __grid_constant__ WgradMultiMaps maps, const __grid_constant__ WgradMultiParams mp) {
+    int l = 0;
+    while (l + 1 < mp.count && static_cast<int>(blockIdx.x) >= mp.first_cta[l + 1]) ++l;
+    const int local = static_cast<int>(blockIdx.x) - mp.first_cta[l];
+    const WgradParams& p = mp.layer[l];
+    wgrad_body(maps.err[l], maps.x[l], maps.g[l], p, local % p.splits, local / p.splits, blockIdx.x == 0);
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -1720,6 +1741,29 @@ size_t umma_wgrad_scratch_bytes(int Nimg, int H, int W, int C, int K, int R, int
     return static_cast<size_t>(p.splits) * K * R * S * C * sizeof(int32_t);
 }
 
+// Tensor maps and kernel parameters of one layer; p->splits (and the rest of the plan) must already be set.
+static int wgrad_setup(const int8_t* x, const int8_t* err, int32_t* out, int direct, int Nimg, int H, int W, int C, int K, int R,
+                       int S, int pad, int32_t* status, WgradParams* p, CUtensorMap* me, CUtensorMap* mx, CUtensorMap* mp) {
+    p->reduce_direct = direct;
+    uint32_t box[4] = {128, (uint32_t)p->BW, (uint32_t)p->BH, (uint32_t)p->BI};
+    uint64_t de[4] = {(uint64_t)K, (uint64_t)W, (uint64_t)H, (uint64_t)Nimg};
+    uint64_t se[3] = {(uint64_t)K, (uint64_t)W * K, (uint64_t)H * W * K};
+    if (int e = encode_map(me, err, false, 4, de, se, box)) return e;
+    uint64_t dx[4] = {(uint64_t)C, (uint64_t)W, (uint64_t)H, (uint64_t)Nimg};
+    uint64_t sx[3] = {(uint64_t)C, (uint64_t)W * C, (uint64_t)H * W * C};
+    if (int e = encode_map(mx, x, false, 4, dx, sx, box)) return e;
+    uint64_t dp[4] = {(uint64_t)C, (uint64_t)R * S, (uint64_t)K, (uint64_t)(direct ? 1 : p->splits)};
+    uint64_t sp[3] = {(uint64_t)C * 4, (uint64_t)R * S * C * 4, (uint64_t)K * R * S * C * 4};
+    uint32_t bp[4] = {32, 1, 128, 1};
+    if (int e = encode_map(mp, out, true, 4, dp, sp, bp)) return e;
+    p->H = H; p->W = W; p->C = C; p->K = K; p->R = R; p->S = S; p->pad = pad; p->Nimg = Nimg;
+    const int rows = p->BW * p->BH * p->BI;
+    p->box_bytes = rows * ROW_BYTES;
+    p->mma_per_chunk = (rows + 31) / 32;
+    p->partial = out; p->status = status;
+    return NITI_OK;
+}
+
 // partial != null, direct == 0: CTA (split, tile) stores its sums to partial[split] (the caller folds them);
 // direct == 1: `partial` is the gradient itself, zeroed by the caller, and every CTA adds into it.
 int umma_conv_wgrad_partials(const int8_t* x, const int8_t* err, int32_t* partial, int* splits_out, int max_splits,
@@ -1727,31 +1771,60 @@ int umma_conv_wgrad_partials(const int8_t* x, const int8_t* err, int32_t* partia
                              int direct) {
     WgradParams p{};
     wgrad_plan(Nimg, H, W, C, K, R, max_splits, &p);
-    p.reduce_direct = direct;
     CUtensorMap me, mx, mp;
-    {
-        uint32_t box[4] = {128, (uint32_t)p.BW, (uint32_t)p.BH, (uint32_t)p.BI};
-        uint64_t de[4] = {(uint64_t)K, (uint64_t)W, (uint64_t)H, (uint64_t)Nimg};
-        uint64_t se[3] = {(uint64_t)K, (uint64_t)W * K, (uint64_t)H * W * K};
-        if (int e = encode_map(&me, err, false, 4, de, se, box)) return e;
-        uint64_t dx[4] = {(uint64_t)C, (uint64_t)W, (uint64_t)H, (uint64_t)Nimg};
-        uint64_t sx[3] = {(uint64_t)C, (uint64_t)W * C, (uint64_t)H * W * C};
-        if (int e = encode_map(&mx, x, false, 4, dx, sx, box)) return e;
-        uint64_t dp[4] = {(uint64_t)C, (uint64_t)R * S, (uint64_t)K, (uint64_t)(direct ? 1 : p.splits)};
-        uint64_t sp[3] = {(uint64_t)C * 4, (uint64_t)R * S * C * 4, (uint64_t)K * R * S * C * 4};
-        uint32_t bp[4] = {32, 1, 128, 1};
-        if (int e = encode_map(&mp, partial, true, 4, dp, sp, bp)) return e;
-    }
-    p.H = H; p.W = W; p.C = C; p.K = K; p.R = R; p.S = S; p.pad = pad; p.Nimg = Nimg;
-    const int rows = p.BW * p.BH * p.BI;
-    p.box_bytes = rows * ROW_BYTES;
-    p.mma_per_chunk = (rows + 31) / 32;
-    p.partial = partial; p.status = status;
+    if (int e = wgrad_setup(x, err, partial, direct, Nimg, H, W, C, K, R, S, pad, status, &p, &me, &mx, &mp)) return e;
     *splits_out = p.splits;
     cudaError_t e = cudaFuncSetAttribute(umma_wgrad_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, WG_SMEM_BYTES);
     if (e != cudaSuccess) return set_cuda_error(e);
     dim3 grid(p.splits, R * p.k_tiles * p.c_tiles);
     umma_wgrad_kernel<<<grid, UMMA_THREADS, WG_SMEM_BYTES, st>>>(me, mx, mp, p);
+    return set_cuda_error(cudaGetLastError());
+}
+
+int umma_wgrad_multi_max() { return WG_MULTI_MAX; }
+
+// Up to WG_MULTI_MAX layers' gradients added into their (zeroed or accumulating) int32 buffers by one launch.
+int umma_conv_wgrad_multi(const WgradJob* jobs, int count, int32_t* status, cudaStream_t st) {
+    if (count < 1 || count > WG_MULTI_MAX) return NITI_ERR_BAD_ARG;
+    WgradMultiParams mp{};
+    WgradMultiMaps maps;
+    int items[WG_MULTI_MAX];
+    long long work = 0;  // item-chunks of the whole launch
+    for (int l = 0; l < count; ++l) {
+        const WgradJob& j = jobs[l];
+        wgrad_plan(j.N, j.H, j.W, j.C, j.K, j.R, 0, &mp.layer[l]);
+        items[l] = j.R * mp.layer[l].k_tiles * mp.layer[l].c_tiles;
+        work += static_cast<long long>(items[l]) * mp.layer[l].chunks;
+    }
+    // chunks per CTA: the smallest number for which the launch still fits in one wave
+    const int sms = sm_count();
+    long long per_cta = (work + sms - 1) / sms;
+    if (per_cta < 1) per_cta = 1;
+    for (;; ++per_cta) {
+        int ctas = 0;
+        for (int l = 0; l < count; ++l) {
+            int sp = static_cast<int>((mp.layer[l].chunks + per_cta - 1) / per_cta);
+            if (sp < 1) sp = 1;
+            mp.layer[l].splits = sp;
+            ctas += sp * items[l];
+        }
+        bool whole = true;  // nothing left to merge: every layer is down to one split
+        for (int l = 0; l < count; ++l) whole = whole && mp.layer[l].splits == 1;
+        if (ctas <= sms || whole) break;
+    }
+    int grid = 0;
+    for (int l = 0; l < count; ++l) {
+        const WgradJob& j = jobs[l];
+        if (int e = wgrad_setup(j.x, j.err, j.g32, 1, j.N, j.H, j.W, j.C, j.K, j.R, j.S, j.pad, status, &mp.layer[l], &maps.err[l],
+                                &maps.x[l], &maps.g[l])) return e;
+        mp.first_cta[l] = grid;
+        grid += mp.layer[l].splits * items[l];
+    }
+    mp.first_cta[count] = grid;
+    mp.count = count;
+    cudaError_t e = cudaFuncSetAttribute(umma_wgrad_multi_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, WG_SMEM_BYTES);
+    if (e != cudaSuccess) return set_cuda_error(e);
+    umma_wgrad_multi_kernel<<<grid, UMMA_THREADS, WG_SMEM_BYTES, st>>>(maps, mp);
     return set_cuda_error(cudaGetLastError());
 }
 

@@ -9,7 +9,7 @@ import torch
 
 import ctypes
 
-from ._lib import lib, check, FcHeadArgs, UpdateItem, DpItem, DpUpdateArgs
+from ._lib import lib, check, FcHeadArgs, UpdateItem, DpItem, DpUpdateArgs, WgradItem
 
 ROUND_NEAREST, ROUND_STOCHASTIC, ROUND_PSEUDO_STOCHASTIC = 0, 1, 2
 CALC_ACT, CALC_ERR, CALC_GRAD = 0, 1, 2
@@ -298,6 +298,28 @@ def conv_wgrad_accumulate(x, err, g32, R=3, S=3, pad=1):
           lib.niti_conv_wgrad_accumulate_i8, _p(x), _p(err), _p(g32), N, H, W, C, K, R, S, pad,
           _p(status_word(x.device)), _st())
     return g32
+
+
+def conv_wgrad_accumulate_multi_max():
+    return int(lib.niti_conv_wgrad_accumulate_multi_max())
+
+
+def conv_wgrad_accumulate_multi(jobs):
+    """[(x, err, g32, R, S, pad), ...] (at most conv_wgrad_accumulate_multi_max() layers): every g32 += its layer's weight
+    gradient, all in one launch whose thread blocks are shared out by work."""
+    items = (WgradItem * len(jobs))()
+    algo_ops = algo_bytes = 0
+    for i, (x, err, g32, R, S, pad) in enumerate(jobs):
+        _need_cuda(x, err, g32)
+        N, H, W, C = x.shape
+        K = err.shape[3]
+        assert g32.dtype == torch.int32 and g32.numel() == K * R * S * C
+        items[i] = WgradItem(_p(x), _p(err), _p(g32), N, H, W, C, K, R, S, pad)
+        algo_ops += 2 * N * H * W * K * R * S * C
+        algo_bytes += x.numel() + err.numel() + 4 * g32.numel()
+    dev = jobs[0][0].device
+    _call("niti_conv_wgrad_accumulate_i8", 1, algo_ops, algo_bytes, lib.niti_conv_wgrad_accumulate_multi_i8, items, len(jobs),
+          _p(status_word(dev)), _st())
 
 
 def gemm_acc(a, b, trans_a=False, trans_b=False, out=None):

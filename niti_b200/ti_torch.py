@@ -311,6 +311,26 @@ def RangeEstimate(input):
     return TensorBitwidth(ops.absmax(input.contiguous().to(torch.int32)).item())
 
 
+# weight gradients waiting for company: layers that run their gradient on a side stream hand it in here, and every
+# WGRAD_GROUP of them go out as ONE launch (ops.conv_wgrad_accumulate_multi), issued when the last one's inputs exist
+_WGRAD_PENDING = []
+
+
+def flush_wgrad():
+    """Launch the weight gradients collected so far (a layer without a successor in its group, the end of a step)."""
+    if not _WGRAD_PENDING:
+        return
+    stream, fork = _WGRAD_PENDING[-1][0], _WGRAD_PENDING[-1][1]  # the last layer's inputs are the last to be enqueued
+    jobs = [j for _, _, j in _WGRAD_PENDING]
+    del _WGRAD_PENDING[:]
+    stream.wait_event(fork)
+    with torch.cuda.stream(stream):
+        if len(jobs) == 1:
+            ops.conv_wgrad_accumulate(*jobs[0])
+        else:
+            ops.conv_wgrad_accumulate_multi(jobs)
+
+
 class TiConv2d(UpdateWeight):
     """3x3 (or RxR) convolution, stride 1, NHWC (:379-437).  ``fuse_relu`` applies the following
     TiReLU inside the requantisation kernel (pair it with ``TiReLU(fused=True)``)."""
@@ -405,15 +425,17 @@ class TiConv2d(UpdateWeight):
                 if self.relu_backward_fused:
                     err_out = ops.relu_bwd(self.act, err_out)
         K, R, S, C = self.weight.shape
+        if self.first_layer:
+            flush_wgrad()
         if (self.grad_accumulate and self.defer_update and self.grad_buffer is not None
                 and ops.conv_wgrad_accumulate_supported(C, K, R, S, self.padding)):
             if fork is not None:
                 # error-backward and weight gradient are independent: on two streams the SMs one kernel leaves idle
                 # (its last wave, its epilogue) are taken by the other
                 self._wgrad_inputs = (self.act, err_in)  # referenced until the owner of the side stream has joined it
-                self.wgrad_stream.wait_event(fork)
-                with torch.cuda.stream(self.wgrad_stream):
-                    ops.conv_wgrad_accumulate(self.act, err_in, self.grad_buffer, R, S, self.padding)
+                _WGRAD_PENDING.append((self.wgrad_stream, fork, (self.act, err_in, self.grad_buffer, R, S, self.padding)))
+                if len(_WGRAD_PENDING) >= min(WGRAD_GROUP, ops.conv_wgrad_accumulate_multi_max()):
+                    flush_wgrad()
                 self.grad_int32acc, self.grad_maxabs = self.grad_buffer, None
             else:
                 self.grad_int32acc, self.grad_maxabs = ops.conv_wgrad_accumulate(self.act, err_in, self.grad_buffer, R, S, self.padding), None
@@ -461,6 +483,7 @@ WEIGHT_INIT_METHOD = UniformWeights
 
 FUSE_REQUANT = True    # convolutions narrow to int8 inside their own kernel (predicted shift, verified, redone if wrong)
 STEP_DOWN_CODES = True  # error-backward layers that guess their shift keep two more bits per output (see ops.conv_dgrad_fused)
+WGRAD_GROUP = 4        # side-stream weight gradients leave in groups of this many layers, one launch per group
 KEEP_PATCHES = True    # the first layer's patch matrix is kept from the forward pass for its weight gradient
 FUSE_POOL = True       # conv -> ReLU -> 2x2 pool: the convolution's kernel also writes the pooled tensor where it can
 FUSE_HEAD = True       # TiNet.train_step runs [dropout,] FC, loss, FC backward and update as one kernel

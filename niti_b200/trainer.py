@@ -196,6 +196,7 @@ class Trainer:
     def _forward_backward(self):
         self.model.train_step(self.x, self.t)
         if self.side is not None:
+            ti_torch.flush_wgrad()  # a group of weight gradients that never filled up
             torch.cuda.current_stream(self.device).wait_stream(self.side)
 
     def _update(self):

@@ -548,6 +548,30 @@ def test_first_layer_weight_gradient_from_the_forward_patch_matrix(N, H, W, C, K
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("shapes", [
+    [(128, 8, 8, 512, 512), (128, 8, 8, 256, 512)],                       # a VGG-small-7 pair: one wave, equal shares
+    [(32, 16, 16, 256, 256), (32, 16, 16, 128, 256), (32, 32, 32, 128, 128)],
+    [(3, 8, 8, 16, 32), (2, 4, 4, 144, 16), (5, 16, 16, 48, 272), (1, 2, 2, 16, 16)],   # ragged, partial tiles
+    [(4, 8, 8, 64, 64)]])
+def test_weight_gradients_of_several_layers_in_one_launch(shapes):
+    """Every layer's gradient is ADDED into its own buffer by one launch; the sums equal the oracle's plus what the
+    buffers held."""
+    assert len(shapes) <= ops.conv_wgrad_accumulate_multi_max()
+    rng = np.random.default_rng(len(shapes) * 17 + shapes[0][0])
+    jobs, want = [], []
+    for (N, H, W, C, K) in shapes:
+        x, err = rnd8(rng, (N, H, W, C)), rnd8(rng, (N, H, W, K))
+        base = rng.integers(-1000, 1000, size=(K, 3, 3, C)).astype(np.int32)
+        g = cu(base)
+        jobs.append((cu(x), cu(err), g, 3, 3, 1))
+        want.append(base + O.conv_wgrad(x, err, 3, 3, 1))
+    ops.conv_wgrad_accumulate_multi(jobs)
+    ops.check_status(DEV)
+    for i, (job, w) in enumerate(zip(jobs, want)):
+        assert_same(job[2], w, f"layer {i} of {len(shapes)}")
+
+
+@pytest.mark.gpu
 def test_bounded_grid_barrier_gives_up_and_reports():
     """A grid barrier that cannot be met (one block, two expected) returns after its 0.5 s limit with a status code;
     nothing traps or hangs and the device keeps working afterwards."""
