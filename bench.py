@@ -685,6 +685,14 @@ def make_case(name, shape):
         trainer.x.copy_(torch.from_numpy(x))
         trainer.t.copy_(torch.from_numpy(t))
         return trainer.run_device_step, step_ops_per_image(cfg) * B, 0
+    if name == "conv_wgrad_multi":
+        # the four weight gradients of a VGG-small-7 step that leave as one launch: shape = (batch,)
+        B = shape[0]
+        layers = [(8, 512, 512), (8, 256, 512), (16, 256, 256), (16, 128, 256)]
+        jobs = [(r8(B, hw, hw, C), r8(B, hw, hw, K), torch.zeros((K, 3, 3, C), dtype=torch.int32, device=dev), 3, 3, 1) for hw, C, K in layers]
+        gop = sum(2 * B * hw * hw * K * 9 * C for hw, C, K in layers)
+        nbytes = sum(j[0].numel() + j[1].numel() + 4 * j[2].numel() for j in jobs)
+        return (lambda: ops.conv_wgrad_accumulate_multi(jobs)), gop, nbytes
     if name.startswith("gemm"):
         M, N, K = shape
         ta, tb = {"gemm_tn": (False, True), "gemm_nn": (False, False), "gemm_tn_a": (True, False)}[name]
