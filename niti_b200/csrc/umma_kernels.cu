@@ -591,6 +591,23 @@ __device__ __forceinline__ void apply_relu_mask(uint32_t (&packed)[WORDS], const
             packed[4 * q + 2] &= __vcmpgts4(x.z, 0); packed[4 * q + 3] &= __vcmpgts4(x.w, 0);
         }
 }
+// The same in two steps, so that the loads can be issued long before the bytes they gate exist: PIECES 16-byte pieces
+// of the mask row into registers, then the AND.  m null: nothing to do.
+template <int PIECES>
+__device__ __forceinline__ void mask_load(const int8_t* m, int cols, uint4 (&mk)[PIECES]) {
+#pragma unroll
+    for (int q = 0; q < PIECES; ++q)
+        if (m != nullptr && 16 * q + 16 <= cols) mk[q] = __ldg(reinterpret_cast<const uint4*>(m) + q);
+}
+template <int PIECES>
+__device__ __forceinline__ void mask_apply(uint32_t* packed, const int8_t* m, int cols, const uint4 (&mk)[PIECES]) {
+#pragma unroll
+    for (int q = 0; q < PIECES; ++q)
+        if (m != nullptr && 16 * q + 16 <= cols) {
+            packed[4 * q + 0] &= __vcmpgts4(mk[q].x, 0); packed[4 * q + 1] &= __vcmpgts4(mk[q].y, 0);
+            packed[4 * q + 2] &= __vcmpgts4(mk[q].z, 0); packed[4 * q + 3] &= __vcmpgts4(mk[q].w, 0);
+        }
+}
 // Byte-wise maximum over a 2x2 pixel window whose four pixels are the rows of lanes l, l^1, l^bw, l^bw^1 of this warp
 // (all 32 lanes call it): afterwards every lane of a window holds the window's maxima.
 __device__ __forceinline__ void pool_window(uint32_t (&w)[8], int bw) {
@@ -827,9 +844,8 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 #pragma unroll
                         for (int j = 0; j < 4; ++j)
 #pragma unroll
-                            for (int i = 0; i < 32; i += 16) {
+                            for (int i = 0; i < 32; i += 16)
                                 codes[j * 2 + (i >> 4)] = narrow16_nearest_codes(&v[j][i], shift - 2, half, &packed[j * 8 + (i >> 2)]);
-                            }
                         if (valid) {  // a row's codes are 32 consecutive bytes, the rows of a tile mostly consecutive: plain stores
                             uint32_t* srow = p.side + ((row_lin * p.N + col0 + g0) >> 4);
                             if (lim >= 128 && (p.N & 63) == 0) {  // rows of N / 4 bytes: 16-byte aligned when N is a multiple of 64
@@ -872,6 +888,8 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                                 packed[j * 8 + (i >> 2)] = narrow4(&v[j][i], shift, p.mode, p.relu, rnd);
                             }
                     }
+                    // (fetching the mask ahead of the narrowing, as the parked kernel does, costs this kernel registers it
+                    // does not have: 32.2 / 36.0 us per 128x32x32 call against 29.5 / 33.4 with the loads here)
                     if (p.mask != nullptr && valid) apply_relu_mask<32>(packed, p.mask + row_lin * p.N + col0 + g0, lim);
                     if (leader) bulk_wait_read<0>();  // the previous store has read the staging tile
                     named_barrier(bar_id, 128);
@@ -1079,6 +1097,8 @@ umma_parked_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
                 u_ri[k] = row_info(p, m_t, tile / mn_tiles, row_in_tile);
                 u_it[k] = it;
                 u_col[k] = n_t * BN + g0;
+                // the ReLU mask this row will be gated with after the main loop: start moving it towards the L2 now
+                if (p.mask != nullptr && u_ri[k].valid && u_col[k] < p.N) prefetch_l2(p.mask + u_ri[k].row_lin * p.N + u_col[k]);
                 u_taddr[k] = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + it * BN + g0;
             }
         }
@@ -1167,20 +1187,22 @@ umma_parked_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
                 const bool pooling = p.pool_out != nullptr;  // the same for the whole grid
                 int8_t* prow = (pooling && ri.valid && ri.pool_row >= 0) ? p.pool_out + ri.pool_row * p.N + col : nullptr;
                 uint32_t va[32], vb[32], packed[8];
+                uint4 ma[2], mb[2];  // the mask pieces of the chunk in va / vb, fetched one chunk ahead of their use
                 tmem_ld_32x32(taddr, va);
+                mask_load<2>(mrow, cols, ma);
 #pragma unroll 1
                 for (int j = 0; j < nch; j += 2) {
                     tmem_ld_wait();
-                    if (j + 1 < nch) tmem_ld_32x32(taddr + (j + 1) * 32, vb);
+                    if (j + 1 < nch) { tmem_ld_32x32(taddr + (j + 1) * 32, vb); mask_load<2>(mrow == nullptr ? nullptr : mrow + 32 * (j + 1), cols - 32 * (j + 1), mb); }
                     narrow32(va, packed, shift, p.mode, p.relu, seed, p.rng_stream, e0 + 32 * j);
-                    if (mrow != nullptr) apply_relu_mask<8>(packed, mrow + 32 * j, cols - 32 * j);
+                    mask_apply<2>(packed, mrow, cols - 32 * j, ma);
                     store_piece(orow, 32 * j, cols, packed);
                     if (pooling) { pool_window(packed, p.BW); store_piece(prow, 32 * j, cols, packed); }
                     tmem_ld_wait();
-                    if (j + 2 < nch) tmem_ld_32x32(taddr + (j + 2) * 32, va);
+                    if (j + 2 < nch) { tmem_ld_32x32(taddr + (j + 2) * 32, va); mask_load<2>(mrow == nullptr ? nullptr : mrow + 32 * (j + 2), cols - 32 * (j + 2), ma); }
                     if (j + 1 < nch) {
                         narrow32(vb, packed, shift, p.mode, p.relu, seed, p.rng_stream, e0 + 32 * (j + 1));
-                        if (mrow != nullptr) apply_relu_mask<8>(packed, mrow + 32 * (j + 1), cols - 32 * (j + 1));
+                        mask_apply<2>(packed, mrow, cols - 32 * (j + 1), mb);
                         store_piece(orow, 32 * (j + 1), cols, packed);
                         if (pooling) { pool_window(packed, p.BW); store_piece(prow, 32 * (j + 1), cols, packed); }
                     }
