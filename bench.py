@@ -356,6 +356,7 @@ def dp_parity_check(dev, rank, world, exchange, dist):
     wexps = [xavier_exp(s) for s in shapes]
     batches = [synth_batch(rng, glob) for _ in range(steps)]
     ti_torch.GRAD_BITWIDTH, ti_torch.TRAINING = 5, True
+    group_was, ti_torch.WGRAD_GROUP = ti_torch.WGRAD_GROUP, 2  # two layers fill a group here: their gradient slices are pushed, as in the timed net
     model = ti_vgg.TiVGG_cifar(list(PARITY_CFG), dropout=True, fuse_relu=True)
     for l, w, e in zip(model.weighted_layers(), weights, wexps):
         l.weight = torch.from_numpy(w).to(dev)
@@ -371,6 +372,7 @@ def dp_parity_check(dev, rank, world, exchange, dist):
         logits.append((out.numpy().copy(), int(exp)))
     got_w = [l.weight.cpu().numpy() for l in model.weighted_layers()]
     tr.close()
+    ti_torch.WGRAD_GROUP = group_was
     spans = [shard_range(glob, r, world) for r in range(world)]
     want, want_w = dp_oracle.expected(PARITY_CFG, weights, wexps, batches, spans, seed)
     ok = all(np.array_equal(logits[s][0], want[(s, lo)][0]) and logits[s][1] == want[(s, lo)][1] for s in range(steps))
@@ -434,7 +436,7 @@ def run_ours(args):
         l.weight = torch.from_numpy(w).to(dev)
         l.weight_exp = ti_torch.exp_tensor(xavier_exp(s), dev)
     trainer = Trainer(model, B, dev, rank=rank, world=world, use_graph=True, seed=1235,
-                      peer_update="auto" if args.exchange == "auto" else False)
+                      peer_update="auto" if args.exchange == "auto" else False, push_gradients=False if args.no_push else (True if args.push else "auto"))
     peer_exchange = trainer.peer is not None
     data_rng = np.random.default_rng(5000 + rank)
     batches = []
@@ -809,6 +811,9 @@ def main():
     ap.add_argument("--sustained-s", type=float, default=2.0, help="seconds of back-to-back steps after the timed regions (0: skip)")
     ap.add_argument("--no-parity-check", action="store_true", help="N > 1: skip the oracle check of the exchange route")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--push", action="store_true", help="N>2: push gradient slices as at N=2 (default there only)")
+    ap.add_argument("--no-push", action="store_true",
+                    help="ablation (N>1, peer-memory route): no gradient slices pushed under the backward pass; the update kernel reads every layer from the peers' buckets")
     ap.add_argument("--no-step-down-codes", action="store_true",
                     help="ablation: error-backward layers that guess their shift contract again on every wrong guess")
     ap.add_argument("--exchange", default="auto", choices=["auto", "nccl"],

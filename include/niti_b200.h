@@ -390,7 +390,13 @@ NITI_API int niti_peer_arena_create(size_t bytes, void** ptr, void* handle);
 NITI_API int niti_peer_arena_open(const void* handle, void** ptr);
 NITI_API int niti_peer_arena_close(void* ptr);
 NITI_API int niti_peer_arena_destroy(void* ptr);
-typedef struct niti_dp_item { int64_t w_offset; int64_t g_offset; int64_t n; uint32_t rng_stream; } niti_dp_item;
+/* staged (all null, or one pointer per rank < world; the own rank's entry is ignored): the gradients of this layer that
+ * rank r computed for THIS rank's slice already lie in this rank's memory, pushed there by r (niti_peer_copy, a copy
+ * engine transfer under r's backward pass, stream-ordered before r's call of niti_dp_update_i8); staged[r] is the address
+ * the layer's word group 0 would have if the whole layer had been pushed (slice start minus 16 * first group of the
+ * slice), 16-byte aligned.  The kernel then sums local memory for this layer instead of reading the peers' buckets over
+ * NVLink after the backward pass; the ranks' own buckets are still read, zeroed and must hold the layer as before. */
+typedef struct niti_dp_item { int64_t w_offset; int64_t g_offset; int64_t n; uint32_t rng_stream; const void* staged[8]; } niti_dp_item;
 typedef struct niti_dp_update_args {
     const niti_dp_item* items; int32_t count;
     int32_t rank, world;
@@ -401,6 +407,9 @@ typedef struct niti_dp_update_args {
     int32_t* status;
 } niti_dp_update_args;
 NITI_API size_t niti_dp_exchange_bytes(void);
+/* bytes device bytes from src to dst on `stream` (cudaMemcpyAsync, device to device): both may lie in any arena mapped
+ * into the calling process, so this is how a rank pushes a finished gradient slice into its owner's staging memory. */
+NITI_API int niti_peer_copy(void* dst, const void* src, size_t bytes, void* stream);
 NITI_API int niti_dp_update_i8(const niti_dp_update_args* args, void* stream);
 
 /* The classifier head of a training step in one (cooperative) kernel: TiDropout.forward

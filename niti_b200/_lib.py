@@ -67,6 +67,7 @@ SIGNATURES = {
     "niti_fc_head_scratch_bytes": (_sz, [_i, _i, _i]),
     "niti_fc_head_train_i8": (_i, [_p, _p]),
     "niti_dp_exchange_bytes": (_sz, []),
+    "niti_peer_copy": (_i, [_p, _p, _sz, _p]),
     "niti_peer_arena_create": (_i, [_sz, _p, _p]),
     "niti_peer_arena_open": (_i, [_p, _p]),
     "niti_peer_arena_close": (_i, [_p]),
@@ -87,7 +88,7 @@ class WgradItem(C.Structure):
 
 class DpItem(C.Structure):
     """niti_dp_item of include/niti_b200.h"""
-    _fields_ = [("w_offset", _i64), ("g_offset", _i64), ("n", _i64), ("rng_stream", _u32)]
+    _fields_ = [("w_offset", _i64), ("g_offset", _i64), ("n", _i64), ("rng_stream", _u32), ("staged", _p * 8)]
 
 
 class DpUpdateArgs(C.Structure):

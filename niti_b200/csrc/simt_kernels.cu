@@ -623,7 +623,10 @@ constexpr int DPX_EPOCH = 0, DPX_ARRIVALS = 1, DPX_GO = 2 /* and DPX_GO + 1 = fa
               DPX_OWN_MAX = 16 /* [UPDATE_MULTI_MAX] */, DPX_FLAGS = 32 /* [DP_MAX_RANKS], written by the peers */,
               DPX_MAXIMA = 64 /* [DP_MAX_RANKS][UPDATE_MULTI_MAX], written by the peers */,
               DPX_WORDS = DPX_MAXIMA + DP_MAX_RANKS * UPDATE_MULTI_MAX;
-struct DpItem { long long w_off, g_off, n; unsigned rng_stream; };
+// staged[r] (all null, or one pointer per rank; the own rank's is unused): where rank r's contribution to THIS rank's
+// slice of the layer already lies in THIS rank's memory (pushed there by r during its backward pass), as the address
+// word group 0 of the layer would have: the reduce phase then reads local memory instead of r's bucket.
+struct DpItem { long long w_off, g_off, n; unsigned rng_stream; const int32_t* staged[DP_MAX_RANKS]; };
 struct DpUpdateParams {
     DpItem item[UPDATE_MULTI_MAX];
     int first_block[UPDATE_MULTI_MAX + 1];
@@ -737,7 +740,8 @@ __device__ __forceinline__ unsigned reduce_slice(const DpUpdateParams& p, const 
                     if (r < p.world) {
                         int pr = p.rank + r;
                         if (pr >= p.world) pr -= p.world;
-                        v[u][r] = ld_relaxed_sys_v4(reinterpret_cast<const int4*>(p.grads[pr] + it.g_off) + g);
+                        const int32_t* src = it.staged[pr] != nullptr ? it.staged[pr] : p.grads[pr] + it.g_off;
+                        v[u][r] = ld_relaxed_sys_v4(reinterpret_cast<const int4*>(src) + g);
                     }
                 }
             }
@@ -1290,6 +1294,11 @@ extern "C" int niti_update_multi_i8(const niti_update_item* items, int count, in
 
 extern "C" size_t niti_dp_exchange_bytes(void) { return DPX_WORDS * sizeof(int32_t); }
 
+extern "C" int niti_peer_copy(void* dst, const void* src, size_t bytes, void* stream) {
+    NITI_REQUIRE(dst && src && bytes > 0);
+    return set_cuda_error(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToDevice, static_cast<cudaStream_t>(stream)));
+}
+
 extern "C" int niti_dp_update_i8(const niti_dp_update_args* a, void* stream) {
     NITI_REQUIRE(a && a->items && a->count > 0 && a->count <= UPDATE_MULTI_MAX);
     NITI_REQUIRE(a->world >= 1 && a->world <= DP_MAX_RANKS && a->rank >= 0 && a->rank < a->world);
@@ -1300,7 +1309,16 @@ extern "C" int niti_dp_update_i8(const niti_dp_update_args* a, void* stream) {
     for (int i = 0; i < a->count; ++i) {
         const niti_dp_item& it = a->items[i];
         NITI_REQUIRE(it.n > 0 && it.n % 4 == 0 && it.w_offset % 4 == 0 && it.g_offset % 4 == 0);
-        p.item[i] = DpItem{it.w_offset, it.g_offset, it.n, it.rng_stream};
+        p.item[i] = DpItem{it.w_offset, it.g_offset, it.n, it.rng_stream, {}};
+        for (int r = 0; r < DP_MAX_RANKS; ++r) {
+            p.item[i].staged[r] = (r < a->world && r != a->rank) ? static_cast<const int32_t*>(it.staged[r]) : nullptr;
+            NITI_REQUIRE(reinterpret_cast<uintptr_t>(p.item[i].staged[r]) % 16 == 0);
+        }
+        {   // all peers staged, or none
+            int have = 0;
+            for (int r = 0; r < a->world; ++r) have += (r != a->rank && p.item[i].staged[r] != nullptr) ? 1 : 0;
+            NITI_REQUIRE(have == 0 || have == a->world - 1);
+        }
         total += it.n;
     }
     for (int r = 0; r < DP_MAX_RANKS; ++r) {

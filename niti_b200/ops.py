@@ -487,7 +487,12 @@ def dp_update(items, rank, world, weight_ptrs, grad_ptrs, exchange_ptrs, mu, mod
     (w_offset bytes, g_offset elements, n, rng_stream); the three pointer lists hold one device address per rank."""
     _need_cuda(seed, maxabs)
     n = len(items)
-    arr = (DpItem * n)(*[DpItem(int(a), int(b), int(c), int(d)) for a, b, c, d in items])
+    arr = (DpItem * n)()
+    for i, it in enumerate(items):  # (w_offset, g_offset, n, rng_stream[, staged pointers per rank or None])
+        arr[i].w_offset, arr[i].g_offset, arr[i].n, arr[i].rng_stream = int(it[0]), int(it[1]), int(it[2]), int(it[3])
+        if len(it) > 4 and it[4] is not None:
+            for r, ptr in enumerate(it[4]):
+                arr[i].staged[r] = ptr
     vp = ctypes.c_void_p * world
     w, g, x = vp(*weight_ptrs), vp(*grad_ptrs), vp(*exchange_ptrs)
     args = DpUpdateArgs(ctypes.cast(arr, ctypes.c_void_p), n, rank, world, ctypes.cast(w, ctypes.c_void_p),
@@ -495,6 +500,11 @@ def dp_update(items, rank, world, weight_ptrs, grad_ptrs, exchange_ptrs, mu, mod
                         _p(status_word(device)))
     total = sum(it[2] for it in items)
     _call("niti_dp_update_i8", 1, 0, 9 * total, lib.niti_dp_update_i8, ctypes.byref(args), _st())
+
+
+def peer_copy(dst_ptr, src_ptr, nbytes):
+    """Device-to-device copy between raw addresses (own or peer-mapped arenas) on the current stream."""
+    check(lib.niti_peer_copy(ctypes.c_void_p(dst_ptr), ctypes.c_void_p(src_ptr), nbytes, _st()), "niti_peer_copy")
 
 
 def quantize_input(x, reduce_max=None):

@@ -314,14 +314,20 @@ def RangeEstimate(input):
 # weight gradients waiting for company: layers that run their gradient on a side stream hand it in here, and every
 # WGRAD_GROUP of them go out as ONE launch (ops.conv_wgrad_accumulate_multi), issued when the last one's inputs exist
 _WGRAD_PENDING = []
+# called after a FULL group has been launched, with (stream, layers of the group): behind that launch on `stream` the
+# gradients of these layers are complete while most of the backward pass is still to come.  A data-parallel trainer
+# starts moving them to their owners there.
+WGRAD_FLUSH_HOOK = None
 
 
-def flush_wgrad():
-    """Launch the weight gradients collected so far (a layer without a successor in its group, the end of a step)."""
+def flush_wgrad(full_group=False):
+    """Launch the weight gradients collected so far (a group that filled up, a layer without a successor in its group,
+    the end of a step)."""
     if not _WGRAD_PENDING:
         return
     stream, fork = _WGRAD_PENDING[-1][0], _WGRAD_PENDING[-1][1]  # the last layer's inputs are the last to be enqueued
-    jobs = [j for _, _, j in _WGRAD_PENDING]
+    jobs = [j for _, _, j, _ in _WGRAD_PENDING]
+    layers = [l for _, _, _, l in _WGRAD_PENDING]
     del _WGRAD_PENDING[:]
     stream.wait_event(fork)
     with torch.cuda.stream(stream):
@@ -329,6 +335,8 @@ def flush_wgrad():
             ops.conv_wgrad_accumulate(*jobs[0])
         else:
             ops.conv_wgrad_accumulate_multi(jobs)
+    if full_group and WGRAD_FLUSH_HOOK is not None:
+        WGRAD_FLUSH_HOOK(stream, layers)
 
 
 class TiConv2d(UpdateWeight):
@@ -433,9 +441,9 @@ class TiConv2d(UpdateWeight):
                 # error-backward and weight gradient are independent: on two streams the SMs one kernel leaves idle
                 # (its last wave, its epilogue) are taken by the other
                 self._wgrad_inputs = (self.act, err_in)  # referenced until the owner of the side stream has joined it
-                _WGRAD_PENDING.append((self.wgrad_stream, fork, (self.act, err_in, self.grad_buffer, R, S, self.padding)))
+                _WGRAD_PENDING.append((self.wgrad_stream, fork, (self.act, err_in, self.grad_buffer, R, S, self.padding), self))
                 if len(_WGRAD_PENDING) >= min(WGRAD_GROUP, ops.conv_wgrad_accumulate_multi_max()):
-                    flush_wgrad()
+                    flush_wgrad(full_group=True)
                 self.grad_int32acc, self.grad_maxabs = self.grad_buffer, None
             else:
                 self.grad_int32acc, self.grad_maxabs = ops.conv_wgrad_accumulate(self.act, err_in, self.grad_buffer, R, S, self.padding), None

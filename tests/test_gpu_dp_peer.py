@@ -28,19 +28,23 @@ def _worker(rank, world, port, q):
     try:
         shapes, weights, wexps, batches = _data()
         ti_torch.GRAD_BITWIDTH, ti_torch.TRAINING = 5, True
+        ti_torch.WGRAD_GROUP = 2  # this net has two layers with side-stream gradients: a full group, so their slices are PUSHED
         model = ti_vgg.TiVGG_cifar(list(CFG), dropout=True, fuse_relu=True)
         for l, w, e in zip(model.weighted_layers(), weights, wexps):
             l.weight = torch.from_numpy(w).to(dev)
             l.weight_exp = ti_torch.exp_tensor(e, dev)
         lo, hi = shard_range(GLOBAL_BATCH, rank, world)
         tr = Trainer(model, hi - lo, dev, rank=rank, world=world, use_graph=True, seed=SEED, warmup_steps=1, peer_update=True,
-                     sample_offset=lo)
+                     sample_offset=lo, push_gradients=True)
         assert tr.peer is not None
+        pushed_seen = []
         logits = []
         for x, t in batches:
             out, exp = tr.step(torch.from_numpy(x[lo:hi].copy()).pin_memory(), torch.from_numpy(t[lo:hi].copy()).pin_memory())
             tr.sync()
             logits.append((out.numpy().copy(), int(exp)))
+            pushed_seen.append(sorted(tr._pushed or []))
+        assert pushed_seen[0] == [1, 2, 3], pushed_seen  # both later conv layers and the classifier went by copy engine
         bucket_clear = int(tr.bucket.flat.abs().max().item()) == 0
         final_w = [l.weight.cpu().numpy().tobytes() for l in model.weighted_layers()]
         # a checkpoint loaded AFTER graph capture and after the weights moved into the peer-visible arena: the values
