@@ -766,8 +766,11 @@ __device__ __forceinline__ unsigned reduce_slice(const DpUpdateParams& p, const 
 // after each barrier and each phase; 6..8 = inside barrier 1..3, when the own grid had arrived
 #ifdef NITI_DP_TIMING
 #define DP_STAMP(i) do { if (blockIdx.x == 0 && threadIdx.x == 0) reinterpret_cast<unsigned long long*>(L + 40)[i] = grid_timer_ns(); } while (0)
+// a block in the middle of the largest layer's range, last thread: stamps 9..11 inside the update phase
+#define DP_PROBE(i) do { if (static_cast<int>(blockIdx.x) == (p.first_block[p.count - 2] + p.first_block[p.count - 1]) / 2 && threadIdx.x == blockDim.x - 1) reinterpret_cast<unsigned long long*>(L + 40)[i] = grid_timer_ns(); } while (0)
 #else
 #define DP_STAMP(i) do { } while (0)
+#define DP_PROBE(i) do { } while (0)
 #endif
 __global__ void __launch_bounds__(256)
 dp_update_kernel(const DpUpdateParams p) {
@@ -828,10 +831,13 @@ dp_update_kernel(const DpUpdateParams p) {
                 }
             }
         }
+        DP_PROBE(9);
         // the rest of the own bucket: the weight-gradient kernels of the next step add into a zeroed bucket
         for (long long g = tid; g < lo; g += nthreads) mine[g] = make_int4(0, 0, 0, 0);
         for (long long g = hi + tid; g < groups; g += nthreads) mine[g] = make_int4(0, 0, 0, 0);
+        DP_PROBE(10);
         __threadfence_system();
+        DP_PROBE(11);
     }
     DP_STAMP(4);
     // ---- 4: every rank's weight stores have landed
