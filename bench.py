@@ -591,6 +591,8 @@ def run_ours(args):
                        "l2": "256 MB buffer written between timed steps (L2 flush); per-step CUDA events",
                        "graph": "step replayed from CUDA graphs", "replicas_bit_identical": replicas_equal,
                        "exchange": ("none" if world == 1 else "reduce-scatter + update + weight broadcast in one kernel over peer memory"
+                                    + ("; gradient slices of the grouped layers pushed to their owners by copy engines under the backward pass"
+                                       if trainer.push_stream is not None else "")
                                     if peer_exchange else "NCCL all-reduce of the int32 gradients, then the update launch"),
                        "parity_vs_oracle": parity,
                        "parity_check": (None if parity is None else f"2 steps of a conv128-P-conv128-P-conv512-P-FC net, global batch {8 * world} "
