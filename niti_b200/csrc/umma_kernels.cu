@@ -902,7 +902,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 #pragma unroll
                     for (int half_i = 0; half_i < 2; ++half_i) {
                         if (col0 + g0 + half_i * 64 >= p.N) break;
-                        if (leader) bulk_wait_read<0>();  // the previous round's stores have read the staging tiles
+                        if (leader) bulk_wait_read<0>();  // the stores of the pass before have read the staging tiles
                         named_barrier(bar_id, 128);
                         stage_row(buf, row_in_tile, v[2 * half_i]);
                         stage_row(buf + EPI_CHUNK_BYTES, row_in_tile, v[2 * half_i + 1]);
