@@ -78,3 +78,22 @@ def test_exact_backends_agree():
 def test_int4_unpacking_order_and_sign():
     a = np.array([[0x10, 0x8F, 0x7A]], dtype=np.uint8)      # (lo, hi) = (0, 1), (-1, -8), (-6, 7)
     assert O.unpack_int4(a).tolist() == [[0, 1, -1, -8, -6, 7]]
+
+
+@settings(max_examples=200, deadline=None)
+@given(st.integers(2, 24), st.integers(0, 2 ** 31 - 1))
+def test_round_shift_one_lower_follows_from_the_upper_result_and_two_bits(S, seed):
+    """What the kernels' repair of a shift guessed one too high rests on (niti_conv_dgrad_requant_side_i8): with
+    u = x + 2^(S-1) - [x < 0], y = u >> S is RoundShift(x, S) before clamping and code = (u >> (S-2)) & 3; then
+    RoundShift(x, S-1) = clamp(2 y + [code == 3] - [code == 0]) for every x whose magnitude is below 2^(S+6), i.e.
+    whenever S - 1 is the shift the tensor really needs."""
+    rng = np.random.default_rng(seed)
+    lim = 1 << (S + 6)
+    x = rng.integers(-(lim - 1), lim, size=4096, dtype=np.int64)
+    x[:8] = [lim - 1, -(lim - 1), 0, 1, -1, (1 << (S - 2)), -(1 << (S - 2)), (1 << (S - 1)) - 1]
+    u = x + (1 << (S - 1)) - (x < 0)
+    y = u >> S
+    code = (u >> (S - 2)) & 3
+    assert np.array_equal(np.clip(y, -127, 127).astype(np.int8), O.round_shift(x, S))
+    lower = np.clip(2 * y + (code == 3) - (code == 0), -127, 127).astype(np.int8)
+    assert np.array_equal(lower, O.round_shift(x, S - 1))
